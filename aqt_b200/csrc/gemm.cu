@@ -1,0 +1,594 @@
+// Quantized batched GEMM with fused dequantizing epilogue for sm_100a.
+//
+//   acc[b,m,n] = sum_k A[b,m,k] * B[b,n,k]      (A, B: int8 or fp8, k contiguous)
+//   out        = cast(cast_D(acc) * scale_1 * scale_2)
+//
+// Persistent kernel, one CTA per SM, 192 threads:
+//   warp 0     : TMA producer  (cp.async.bulk.tensor, 128B-swizzled tiles)
+//   warp 1     : MMA issuer    (tcgen05.mma kind::i8 / kind::f8f6f4, cta_group::1)
+//   warps 2..5 : epilogue      (tcgen05.ld from TMEM -> scale -> global)
+// Tile 128 x 256 x 128(bytes of k), 4-stage shared-memory ring (192 KB), two
+// 256-column TMEM accumulators so the epilogue of tile i overlaps the
+// mainloop of tile i+1. Every mbarrier wait is bounded: when one runs out the
+// kernel records a code in `status`, lets in-flight copies land, frees its
+// TMEM and returns instead of hanging the device.
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace aqtb200 {
+
+int sm_count();
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 128;  // bytes (= elements) of k per stage: one 128B swizzle row
+constexpr int STAGES = 4;
+constexpr int A_STAGE = BM * BK;
+constexpr int B_STAGE = BN * BK;
+constexpr int GROUP_M = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr int TMEM_COLS = 512;
+constexpr size_t GEMM_SMEM = (size_t)STAGES * (A_STAGE + B_STAGE) + 1024;
+constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s
+
+struct GemmParams {
+  int64_t b0, b1, m, n, k;
+  const void* a_scale;
+  int64_t sa_b0, sa_b1, sa_m;
+  const void* b_scale;
+  int64_t sb_b0, sb_b1, sb_n;
+  int a_scale_dtype, b_scale_dtype;
+  int b_scale_first, d_dtype, out_dtype, is_int;
+  void* out;
+  int64_t o_b0, o_b1, o_m, o_n;
+  void* acc_out;
+  uint32_t idesc;
+  int64_t m_tiles, n_tiles, total_tiles, num_kb;
+  int32_t* status;
+  // SIMT reference kernel only:
+  const uint8_t* a; const uint8_t* b;
+  int64_t a_b0, a_b1, lda, b_b0, b_b1, ldb;
+  int a_dtype, b_dtype;
+};
+
+// ---------------------------------------------------------------------------
+// PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait. Returns false when the limit ran out or another role aborted.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
+                                          volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  for (;;) {
+#pragma unroll 1
+    for (int i = 0; i < 256; ++i)
+      if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > WAIT_LIMIT_CYCLES) return false;
+  }
+}
+
+__device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, uint64_t* bar,
+                                            int c0, int c1, int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   smem_u32(bar))
+               : "memory");
+}
+template <bool IS_INT>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                       uint32_t idesc, uint32_t accumulate) {
+  if (IS_INT) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
+        "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
+        "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// K-major, 128-byte swizzled operand tile: rows of 128 bytes, 8-row groups
+// 1024 bytes apart (SBO), descriptor version 1 (sm_100), layout type 2.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset
+  d |= (uint64_t)1 << 46;            // descriptor version
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+
+__device__ __forceinline__ void decode_tile(const GemmParams& P, int64_t t, int64_t& i0,
+                                            int64_t& i1, int64_t& mt, int64_t& nt) {
+  const int64_t per_batch = P.m_tiles * P.n_tiles;
+  int64_t b = t / per_batch, r = t % per_batch;
+  i1 = b % P.b1;
+  i0 = b / P.b1;
+  const int64_t group = GROUP_M * P.n_tiles;
+  int64_t g = r / group, in = r % group;
+  int64_t first = g * GROUP_M;
+  int64_t gm = min((int64_t)GROUP_M, P.m_tiles - first);
+  mt = first + in % gm;
+  nt = in / gm;
+}
+
+// One multiply of the dequantization chain: result dtype = promote(cur, sdt).
+__device__ __forceinline__ float scale_mul(float r, float s, int& cur, int sdt) {
+  if (sdt == AQTB200_F32) cur = AQTB200_F32;
+  return round_to(__fmul_rn(r, s), cur);
+}
+
+template <bool IS_INT>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
+                    const __grid_constant__ CUtensorMap tmB, GemmParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES * A_STAGE;
+  __shared__ __align__(8) uint64_t full_bar[STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  __shared__ __align__(8) uint64_t tfull_bar[2];
+  __shared__ __align__(8) uint64_t tempty_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull_bar[s], 1);
+      mbar_init(&tempty_bar[s], 4);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abortp = &abort_flag;
+  int fail = 0;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int64_t t = blockIdx.x; t < P.total_tiles && !fail; t += gridDim.x) {
+        int64_t i0, i1, mt, nt;
+        decode_tile(P, t, i0, i1, mt, nt);
+        for (int64_t kb = 0; kb < P.num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
+          mbar_expect_tx(&full_bar[stage], A_STAGE + B_STAGE);
+          tma_load_4d(smem_a + stage * A_STAGE, &tmA, &full_bar[stage], (int)(kb * BK),
+                      (int)(mt * BM), (int)i1, (int)i0);
+          tma_load_4d(smem_b + stage * B_STAGE, &tmB, &full_bar[stage], (int)(kb * BK),
+                      (int)(nt * BN), (int)i1, (int)i0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (fail) { *abortp = 1; if (P.status) atomicCAS(P.status, 0, 1); }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t aphase = 0;
+      for (int64_t t = blockIdx.x; t < P.total_tiles && !fail; t += gridDim.x) {
+        if (!mbar_wait(&tempty_bar[buf], aphase ^ 1, abortp)) { fail = 2; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int64_t kb = 0; kb < P.num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abortp)) { fail = 2; break; }
+          tc_fence_after();
+          const uint64_t ad = make_smem_desc(smem_u32(smem_a + stage * A_STAGE));
+          const uint64_t bd = make_smem_desc(smem_u32(smem_b + stage * B_STAGE));
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k) {
+            // advance 32 bytes of k inside the swizzle row: +2 in 16-byte units
+            tc_mma<IS_INT>(d_tmem, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), P.idesc,
+                           (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty_bar[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (fail) break;
+        tc_commit(&tfull_bar[buf]);
+        buf ^= 1;
+        if (buf == 0) aphase ^= 1;
+      }
+      if (fail) { *abortp = 1; if (P.status) atomicCAS(P.status, 0, 2); }
+    }
+  } else {
+    // ---------------- epilogue ----------------
+    const int quarter = warp & 3;  // TMEM lanes this warp may read
+    int buf = 0;
+    uint32_t aphase = 0;
+    const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
+    const int out_es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
+    for (int64_t t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
+      int64_t i0, i1, mt, nt;
+      decode_tile(P, t, i0, i1, mt, nt);
+      int ok = mbar_wait(&tfull_bar[buf], aphase, abortp) ? 1 : 0;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { fail = 3; break; }
+      tc_fence_after();
+      const int64_t row = mt * BM + quarter * 32 + lane;
+      const bool row_ok = row < P.m;
+      float sa = 1.f;
+      if (has_a && row_ok)
+        sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
+      const int64_t obase = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m;
+      const int64_t abase = ((i0 * P.b1 + i1) * P.m + row) * P.n;
+#pragma unroll 1
+      for (int chunk = 0; chunk < BN / 32; ++chunk) {
+        const int64_t col0 = nt * BN + chunk * 32;
+        if (col0 >= P.n) break;  // warp-uniform
+        uint32_t acc[32];
+        tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + chunk * 32),
+                acc);
+        tc_wait_ld();
+        float sbl = 1.f;
+        if (has_b && col0 + lane < P.n)
+          sbl = load1(P.b_scale, P.b_scale_dtype,
+                      i0 * P.sb_b0 + i1 * P.sb_b1 + (col0 + lane) * P.sb_n);
+        float res[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const float sb = __shfl_sync(0xffffffffu, sbl, j);
+          float r = IS_INT ? __int2float_rn((int)acc[j]) : __uint_as_float(acc[j]);
+          int cur = P.d_dtype;
+          r = round_to(r, cur);
+          if (P.b_scale_first) {
+            if (has_b) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+            if (has_a) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+          } else {
+            if (has_a) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+            if (has_b) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+          }
+          r = round_to(r, P.d_dtype);
+          res[j] = round_to(r, P.out_dtype);
+        }
+        if (row_ok) {
+          if (P.acc_out != nullptr) {
+            uint32_t* ao = (uint32_t*)P.acc_out + abase + col0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < P.n) ao[j] = acc[j];
+          }
+          const bool full = col0 + 32 <= P.n;
+          const bool vec_ok = full && P.o_n == 1 &&
+                              ((((uintptr_t)P.out) + (size_t)(obase + col0) * out_es) & 15) == 0;
+          if (vec_ok) {
+            if (out_es == 2) {
+              uint4* o = (uint4*)((__nv_bfloat16*)P.out + obase + col0);
+#pragma unroll
+              for (int v = 0; v < 4; ++v) {
+                __nv_bfloat162 p0 = __floats2bfloat162_rn(res[8 * v + 0], res[8 * v + 1]);
+                __nv_bfloat162 p1 = __floats2bfloat162_rn(res[8 * v + 2], res[8 * v + 3]);
+                __nv_bfloat162 p2 = __floats2bfloat162_rn(res[8 * v + 4], res[8 * v + 5]);
+                __nv_bfloat162 p3 = __floats2bfloat162_rn(res[8 * v + 6], res[8 * v + 7]);
+                uint4 u;
+                u.x = *(uint32_t*)&p0; u.y = *(uint32_t*)&p1;
+                u.z = *(uint32_t*)&p2; u.w = *(uint32_t*)&p3;
+                o[v] = u;
+              }
+            } else {
+              float4* o = (float4*)((float*)P.out + obase + col0);
+#pragma unroll
+              for (int v = 0; v < 8; ++v)
+                o[v] = make_float4(res[4 * v], res[4 * v + 1], res[4 * v + 2], res[4 * v + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < P.n) {
+                const int64_t oi = obase + (col0 + j) * P.o_n;
+                if (out_es == 2)
+                  ((__nv_bfloat16*)P.out)[oi] = __float2bfloat16_rn(res[j]);
+                else
+                  ((float*)P.out)[oi] = res[j];
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty_bar[buf]);
+      buf ^= 1;
+      if (buf == 0) aphase ^= 1;
+    }
+    if (fail && lane == 0) { *abortp = 1; if (P.status) atomicCAS(P.status, 0, 3); }
+  }
+
+  __syncwarp();
+  if (*abortp) {
+    // Give copies that are still in flight time to land before the shared
+    // memory they target is released.
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Plain CUDA-core kernel with the same epilogue; selected only through
+// aqtb200_set_gemm_impl(1) to cross-check the tensor-core kernel.
+__device__ __forceinline__ float qval(const uint8_t* p, int dt, int64_t i) {
+  return dt == AQTB200_S8 ? (float)(signed char)p[i] : fp8_to_float(p[i], dt);
+}
+
+__global__ void gemm_simt_kernel(GemmParams P) {
+  const int64_t total = P.b0 * P.b1 * P.m * P.n;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t col = i % P.n, t = i / P.n;
+    int64_t row = t % P.m;
+    t /= P.m;
+    int64_t i1 = t % P.b1, i0 = t / P.b1;
+    const uint8_t* ar = P.a + i0 * P.a_b0 + i1 * P.a_b1 + row * P.lda;
+    const uint8_t* br = P.b + i0 * P.b_b0 + i1 * P.b_b1 + col * P.ldb;
+    float r;
+    uint32_t raw;
+    if (P.is_int) {
+      int acc = 0;
+      for (int64_t k = 0; k < P.k; ++k) acc += (int)(signed char)ar[k] * (int)(signed char)br[k];
+      raw = (uint32_t)acc;
+      r = __int2float_rn(acc);
+    } else {
+      double acc = 0.0;
+      for (int64_t k = 0; k < P.k; ++k)
+        acc += (double)qval(ar, P.a_dtype, k) * (double)qval(br, P.b_dtype, k);
+      r = (float)acc;
+      raw = __float_as_uint(r);
+    }
+    if (P.acc_out) ((uint32_t*)P.acc_out)[i] = raw;
+    int cur = P.d_dtype;
+    r = round_to(r, cur);
+    float sa = P.a_scale ? load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m) : 1.f;
+    float sb = P.b_scale ? load1(P.b_scale, P.b_scale_dtype, i0 * P.sb_b0 + i1 * P.sb_b1 + col * P.sb_n) : 1.f;
+    if (P.b_scale_first) {
+      if (P.b_scale) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+      if (P.a_scale) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+    } else {
+      if (P.a_scale) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+      if (P.b_scale) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+    }
+    r = round_to(round_to(r, P.d_dtype), P.out_dtype);
+    const int64_t oi = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m + col * P.o_n;
+    if (P.out_dtype == AQTB200_BF16)
+      ((__nv_bfloat16*)P.out)[oi] = __float2bfloat16_rn(r);
+    else
+      ((float*)P.out)[oi] = r;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+
+static int g_gemm_impl = 0;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault,
+                                         &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 4-D map over a 1-byte tensor [b0][b1][rows][k] with k contiguous.
+static int make_operand_map(CUtensorMap* tm, const void* ptr, int64_t k, int64_t rows, int64_t b1,
+                            int64_t b0, int64_t ld, int64_t s_b1, int64_t s_b0, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  AQT_REQUIRE(enc != nullptr, AQTB200_EDRIVER, "cuTensorMapEncodeTiled entry point not found");
+  AQT_REQUIRE(((uintptr_t)ptr & 15) == 0, AQTB200_EINVAL, "operand not 16-byte aligned");
+  if (b1 <= 1 || s_b1 == 0) s_b1 = ld * rows;
+  if (b0 <= 1 || s_b0 == 0) s_b0 = s_b1 * std::max<int64_t>(b1, 1);
+  AQT_REQUIRE(ld % 16 == 0 && s_b1 % 16 == 0 && s_b0 % 16 == 0, AQTB200_EINVAL,
+              "operand strides must be multiples of 16 bytes (ld=%lld)", (long long)ld);
+  cuuint64_t dims[4] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)std::max<int64_t>(b1, 1),
+                        (cuuint64_t)std::max<int64_t>(b0, 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)ld, (cuuint64_t)s_b1, (cuuint64_t)s_b0};
+  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  AQT_REQUIRE(r == CUDA_SUCCESS, AQTB200_EDRIVER, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+static bool is_fp8(int dt) { return dt == AQTB200_E4M3 || dt == AQTB200_E5M2; }
+
+int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
+  AQT_REQUIRE(d != nullptr, AQTB200_EINVAL, "null gemm descriptor");
+  AQT_REQUIRE(d->b0 >= 0 && d->b1 >= 0 && d->m >= 0 && d->n >= 0 && d->k >= 0, AQTB200_EINVAL,
+              "negative extent");
+  const bool ints = d->a_dtype == AQTB200_S8 && d->b_dtype == AQTB200_S8;
+  const bool fps = is_fp8(d->a_dtype) && is_fp8(d->b_dtype);
+  AQT_REQUIRE(ints || fps, AQTB200_EUNSUPPORTED,
+              "operand dtypes %d x %d: need int8 x int8 or fp8 x fp8", d->a_dtype, d->b_dtype);
+  AQT_REQUIRE(d->dequant_dtype == AQTB200_F32 || d->dequant_dtype == AQTB200_BF16, AQTB200_EINVAL,
+              "dequant dtype must be f32 or bf16");
+  AQT_REQUIRE(d->out_dtype == AQTB200_F32 || d->out_dtype == AQTB200_BF16, AQTB200_EINVAL,
+              "out dtype must be f32 or bf16");
+  if (d->b0 * d->b1 * d->m * d->n == 0) return 0;
+  AQT_REQUIRE(d->out != nullptr, AQTB200_EINVAL, "null output");
+  AQT_REQUIRE(d->k == 0 || (d->a != nullptr && d->b != nullptr), AQTB200_EINVAL, "null operand");
+  AQT_REQUIRE(d->k < (int64_t)1 << 31 && d->m < (int64_t)1 << 31 && d->n < (int64_t)1 << 31,
+              AQTB200_EUNSUPPORTED, "extent too large for a tensor map");
+
+  GemmParams P{};
+  P.b0 = d->b0; P.b1 = d->b1; P.m = d->m; P.n = d->n; P.k = d->k;
+  P.a_scale = d->a_scale; P.sa_b0 = d->a_scale_b0_stride; P.sa_b1 = d->a_scale_b1_stride;
+  P.sa_m = d->a_scale_m_stride;
+  P.b_scale = d->b_scale; P.sb_b0 = d->b_scale_b0_stride; P.sb_b1 = d->b_scale_b1_stride;
+  P.sb_n = d->b_scale_n_stride;
+  P.a_scale_dtype = d->a_scale_dtype; P.b_scale_dtype = d->b_scale_dtype;
+  P.b_scale_first = d->b_scale_first; P.d_dtype = d->dequant_dtype; P.out_dtype = d->out_dtype;
+  P.is_int = ints ? 1 : 0;
+  P.out = d->out; P.o_b0 = d->out_b0_stride; P.o_b1 = d->out_b1_stride;
+  P.o_m = d->out_m_stride; P.o_n = d->out_n_stride;
+  P.acc_out = d->acc_out;
+  P.m_tiles = (d->m + BM - 1) / BM;
+  P.n_tiles = (d->n + BN - 1) / BN;
+  P.total_tiles = d->b0 * d->b1 * P.m_tiles * P.n_tiles;
+  P.num_kb = std::max<int64_t>(1, (d->k + BK - 1) / BK);
+  P.status = status;
+  P.a = (const uint8_t*)d->a; P.b = (const uint8_t*)d->b;
+  P.a_b0 = d->a_b0_stride; P.a_b1 = d->a_b1_stride; P.lda = d->lda;
+  P.b_b0 = d->b_b0_stride; P.b_b1 = d->b_b1_stride; P.ldb = d->ldb;
+  P.a_dtype = d->a_dtype; P.b_dtype = d->b_dtype;
+  const uint32_t cfmt = ints ? 2u : 1u;
+  const uint32_t afmt = ints ? 1u : (d->a_dtype == AQTB200_E5M2 ? 1u : 0u);
+  const uint32_t bfmt = ints ? 1u : (d->b_dtype == AQTB200_E5M2 ? 1u : 0u);
+  P.idesc = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
+            ((uint32_t)(BM >> 4) << 24);
+
+  if (g_gemm_impl == 1 || d->k == 0) {
+    int64_t total = d->b0 * d->b1 * d->m * d->n;
+    int grid = (int)std::min<int64_t>((total + 255) / 256, (int64_t)sm_count() * 16);
+    gemm_simt_kernel<<<grid, 256, 0, st>>>(P);
+    AQT_CUDA_OK(cudaGetLastError()); count_launch();
+    return 0;
+  }
+
+  CUtensorMap tmA, tmB;
+  int rc = make_operand_map(&tmA, d->a, d->k, d->m, d->b1, d->b0, d->lda, d->a_b1_stride,
+                            d->a_b0_stride, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tmB, d->b, d->k, d->n, d->b1, d->b0, d->ldb, d->b_b1_stride,
+                        d->b_b0_stride, BN);
+  if (rc) return rc;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[P.is_int]) {
+    if (P.is_int)
+      AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<true>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
+    else
+      AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false>,
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
+    attr_set[P.is_int] = true;
+  }
+  int grid = (int)std::min<int64_t>(P.total_tiles, sm_count());
+  if (P.is_int)
+    gemm_tcgen05_kernel<true><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmB, P);
+  else
+    gemm_tcgen05_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmB, P);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+}  // namespace aqtb200
+
+extern "C" {
+
+int aqtb200_gemm_dequant(const aqtb200_gemm_desc* desc, int32_t* status, void* stream) {
+  return aqtb200::gemm_dequant(desc, status, (cudaStream_t)stream);
+}
+
+int aqtb200_set_gemm_impl(int impl) {
+  if (impl != 0 && impl != 1) return AQTB200_EINVAL;
+  aqtb200::g_gemm_impl = impl;
+  return 0;
+}
+
+}  // extern "C"

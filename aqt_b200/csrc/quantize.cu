@@ -1,0 +1,691 @@
+// AbsMax calibration and quantization kernels (HBM-bound, CUDA cores).
+//
+// Three steps per operand, each a grid-stride kernel sized to the SM count:
+//   1. absmax_{row,col}_kernel : max |v| per kept row (or per tensor) into a
+//      zero-initialised uint32 cell per scale via atomicMax on float bits;
+//   2. finalize_scale_kernel   : amax -> scale (reference dtype semantics) and
+//      its rounded reciprocal;
+//   3. quant_{row,col}_kernel  : v * (1/scale) [+noise] -> clip -> round ->
+//      int8 / fp8, written with the contraction index contiguous.
+// "row" kernels read inputs whose contraction index is contiguous; "col"
+// kernels read inputs whose kept index is contiguous and transpose a 64x128
+// tile through shared memory so the output is contraction-contiguous as well.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace aqtb200 {
+
+struct DView {
+  const void* ptr;
+  int dtype;
+  int64_t b0, b1, rows, cols;
+  int64_t sb0, sb1, sr, sc;
+};
+
+struct QParams {
+  DView x, pre, noise;  // pre.ptr / noise.ptr null when absent
+  int t_dtype, s_dtype, y_dtype;
+  int kind, qdtype;
+  float clip_bound;
+  int per_tensor;
+  int pre_vec, noise_vec;  // vector loads allowed on prescale / noise
+  uint32_t* amax;
+  float* sinv;
+  uint8_t* q;
+  int64_t ldq;
+};
+
+static DView to_dview(const aqtb200_view* v) {
+  DView d{};
+  if (v == nullptr || v->ptr == nullptr) return d;
+  d.ptr = v->ptr; d.dtype = v->dtype;
+  d.b0 = v->b0; d.b1 = v->b1; d.rows = v->rows; d.cols = v->cols;
+  d.sb0 = v->b0_stride; d.sb1 = v->b1_stride;
+  d.sr = v->row_stride; d.sc = v->col_stride;
+  return d;
+}
+
+// v = round_T(x * round_T(pre))
+__device__ __forceinline__ float apply_pre(float x, float pre, int t_dtype) {
+  return round_to(__fmul_rn(x, round_to(pre, t_dtype)), t_dtype);
+}
+
+__device__ __forceinline__ uint8_t quant1(float v, float sinv, float noise,
+                                          bool has_noise, const QParams& P) {
+  float y = round_to(__fmul_rn(v, sinv), P.y_dtype);
+  if (has_noise) y = round_to(__fadd_rn(y, noise), P.y_dtype);
+  y = fminf(fmaxf(y, -P.clip_bound), P.clip_bound);
+  if (P.kind == AQTB200_NUM_INT) {
+    return (uint8_t)(signed char)__float2int_rn(y);  // rn = ties to even
+  }
+  return (uint8_t)__nv_cvt_float_to_fp8(
+      y, __NV_SATFINITE, P.qdtype == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2);
+}
+
+__device__ __forceinline__ void decode_brow(const DView& x, int64_t brow,
+                                            int64_t& i0, int64_t& i1,
+                                            int64_t& r) {
+  r = brow % x.rows;
+  int64_t b = brow / x.rows;
+  i1 = b % x.b1;
+  i0 = b / x.b1;
+}
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+  v = warp_max(v);
+  int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  int nw = (blockDim.x * blockDim.y + 31) >> 5;
+  v = (threadIdx.x < nw && threadIdx.y == 0) ? red[threadIdx.x] : 0.f;
+  if (warp == 0 && threadIdx.y == 0) v = warp_max(v);
+  return v;
+}
+
+// ---------------------------------------------------------------------------
+// absmax, contraction contiguous. One warp per (batch-row, 4096-column chunk).
+constexpr int kRowChunk = 4096;
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+absmax_row_kernel(QParams P, int64_t chunks_per_row, int64_t total_units) {
+  __shared__ float red[32];
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const DView& x = P.x;
+  const bool has_pre = P.pre.ptr != nullptr;
+  float tmax = 0.f;
+  for (int64_t u = warp_g; u < total_units; u += nwarps) {
+    int64_t brow = u / chunks_per_row, chunk = u % chunks_per_row;
+    int64_t i0, i1, r;
+    decode_brow(x, brow, i0, i1, r);
+    const int64_t base = i0 * x.sb0 + i1 * x.sb1 + r * x.sr;
+    const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+    const int64_t c0 = chunk * kRowChunk;
+    const int64_t c1 = min(x.cols, c0 + (int64_t)kRowChunk);
+    float m = 0.f;
+    if (VEC) {
+      for (int64_t c = c0 + lane * 16; c < c1; c += 32 * 16) {
+        float v[16];
+        loadN<16>(x.ptr, x.dtype, base + c, v);
+        if (has_pre) {
+          float p[16];
+          if (P.pre_vec) {
+            loadN<16>(P.pre.ptr, P.pre.dtype, pbase + c, p);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              p[j] = load1(P.pre.ptr, P.pre.dtype, pbase + (c + j) * P.pre.sc);
+          }
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = apply_pre(v[j], p[j], P.t_dtype);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) m = fmaxf(m, fabsf(v[j]));
+      }
+    } else {
+      for (int64_t c = c0 + lane; c < c1; c += 32) {
+        float v = load1(x.ptr, x.dtype, base + c * x.sc);
+        if (has_pre)
+          v = apply_pre(v, load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc),
+                        P.t_dtype);
+        m = fmaxf(m, fabsf(v));
+      }
+    }
+    if (P.per_tensor) {
+      tmax = fmaxf(tmax, m);
+    } else {
+      m = warp_max(m);
+      if (lane == 0 && m > 0.f) atomic_max_nonneg(P.amax + brow, m);
+    }
+  }
+  if (P.per_tensor) {
+    tmax = block_max(tmax, red);
+    if (threadIdx.x == 0 && tmax > 0.f) atomic_max_nonneg(P.amax, tmax);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// absmax, kept index contiguous. Block (32 x 8): x covers 32*V kept rows, y
+// strides over a 256-wide chunk of the contraction index.
+constexpr int kColChunk = 256;
+
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+absmax_col_kernel(QParams P, int64_t row_blocks, int64_t col_chunks,
+                  int64_t total_units) {
+  constexpr int V = VEC ? 4 : 1;
+  __shared__ float red[32];
+  const DView& x = P.x;
+  const bool has_pre = P.pre.ptr != nullptr;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  float tmax = 0.f;
+  for (int64_t u = blockIdx.x; u < total_units; u += gridDim.x) {
+    int64_t cc = u % col_chunks;
+    int64_t t = u / col_chunks;
+    int64_t rb = t % row_blocks;
+    int64_t b = t / row_blocks;
+    int64_t i1 = b % x.b1, i0 = b / x.b1;
+    const int64_t r0 = (rb * 32 + tx) * V;
+    const int64_t base = i0 * x.sb0 + i1 * x.sb1;
+    const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+    const int64_t cend = min(x.cols, (cc + 1) * (int64_t)kColChunk);
+    float m[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) m[j] = 0.f;
+    if (r0 < x.rows) {
+      for (int64_t c = cc * kColChunk + ty; c < cend; c += 8) {
+        float v[V];
+        if (VEC) {
+          loadN<4>(x.ptr, x.dtype, base + c * x.sc + r0, v);
+        } else {
+          v[0] = load1(x.ptr, x.dtype, base + c * x.sc + r0 * x.sr);
+        }
+        float p = has_pre ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
+#pragma unroll
+        for (int j = 0; j < V; ++j) {
+          float w = has_pre ? apply_pre(v[j], p, P.t_dtype) : v[j];
+          m[j] = fmaxf(m[j], fabsf(w));
+        }
+      }
+    }
+    if (P.per_tensor) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) tmax = fmaxf(tmax, m[j]);
+    } else if (r0 < x.rows) {
+      const int64_t sbase = (i0 * x.b1 + i1) * x.rows;
+#pragma unroll
+      for (int j = 0; j < V; ++j)
+        if (r0 + j < x.rows && m[j] > 0.f)
+          atomic_max_nonneg(P.amax + sbase + r0 + j, m[j]);
+    }
+  }
+  if (P.per_tensor) {
+    // fold the 8 y-lanes through warp ids: thread linear id = ty*32 + tx
+    float v = warp_max(tmax);
+    if (tx == 0) red[ty] = v;
+    __syncthreads();
+    if (ty == 0) {
+      v = tx < 8 ? red[tx] : 0.f;
+      v = warp_max(v);
+      if (tx == 0 && v > 0.f) atomic_max_nonneg(P.amax, v);
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// amax -> scale and rounded reciprocal (calibration.py:149-157,
+// aqt_tensor.py:151-153). All arithmetic in T, stored as S.
+struct FinalizeParams {
+  const uint32_t* amax;
+  const void* scale_in;  // when non-null: skip calibration, use this scale
+  void* scale_out;
+  float* sinv;
+  int64_t n;
+  int t_dtype, s_dtype;
+  float quant_bound, clipping_scale;
+  int po2;
+};
+
+__global__ void finalize_scale_kernel(FinalizeParams F) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= F.n) return;
+  float s;
+  if (F.scale_in != nullptr) {
+    s = load1(F.scale_in, F.s_dtype, i);
+  } else {
+    float a = __uint_as_float(F.amax[i]);
+    if (a == 0.f) a = 1.f;
+    float bound = F.clipping_scale != 0.f
+                      ? round_to(__fmul_rn(a, F.clipping_scale), F.t_dtype)
+                      : a;
+    s = round_to(__fdiv_rn(bound, F.quant_bound), F.t_dtype);
+    if (F.po2) {
+      // 1 / 2**floor(log2(1/s)); the exponent is read off the float directly.
+      float r = round_to(__fdiv_rn(1.f, s), F.t_dtype);
+      int e;
+      frexpf(r, &e);  // r = m * 2**e, m in [0.5, 1)
+      float p = round_to(ldexpf(1.f, e - 1), F.t_dtype);
+      s = round_to(__fdiv_rn(1.f, p), F.t_dtype);
+    }
+    s = round_to(s, F.s_dtype);
+  }
+  if (F.scale_out != nullptr && F.scale_out != F.scale_in) {
+    if (F.s_dtype == AQTB200_BF16)
+      ((__nv_bfloat16*)F.scale_out)[i] = __float2bfloat16_rn(s);
+    else
+      ((float*)F.scale_out)[i] = s;
+  }
+  float inv = round_to(__fdiv_rn(1.f, s), F.s_dtype);
+  if (isinf(inv)) inv = 1.f;
+  F.sinv[i] = inv;
+}
+
+// ---------------------------------------------------------------------------
+// quantize, contraction contiguous: one thread per 16 output bytes.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+quant_row_kernel(QParams P, int64_t units_per_row, int64_t total_units) {
+  const DView& x = P.x;
+  const bool has_pre = P.pre.ptr != nullptr;
+  const bool has_noise = P.noise.ptr != nullptr;
+  for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+       u < total_units; u += (int64_t)gridDim.x * blockDim.x) {
+    int64_t brow = u / units_per_row;
+    int64_t c = (u % units_per_row) * 16;
+    int64_t i0, i1, r;
+    decode_brow(x, brow, i0, i1, r);
+    const int64_t base = i0 * x.sb0 + i1 * x.sb1 + r * x.sr;
+    const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+    const int64_t nbase = i0 * P.noise.sb0 + i1 * P.noise.sb1 + r * P.noise.sr;
+    const float sinv = P.sinv[P.per_tensor ? 0 : brow];
+    float v[16], nz[16];
+    if (VEC) {
+      loadN<16>(x.ptr, x.dtype, base + c, v);
+      if (has_pre) {
+        float p[16];
+        if (P.pre_vec) {
+          loadN<16>(P.pre.ptr, P.pre.dtype, pbase + c, p);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            p[j] = load1(P.pre.ptr, P.pre.dtype, pbase + (c + j) * P.pre.sc);
+        }
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = apply_pre(v[j], p[j], P.t_dtype);
+      }
+      if (has_noise) {
+        if (P.noise_vec) {
+          loadN<16>(P.noise.ptr, AQTB200_F32, nbase + c, nz);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            nz[j] = load1(P.noise.ptr, AQTB200_F32, nbase + (c + j) * P.noise.sc);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        int64_t cj = c + j;
+        bool in = cj < x.cols;
+        v[j] = in ? load1(x.ptr, x.dtype, base + cj * x.sc) : 0.f;
+        if (has_pre && in)
+          v[j] = apply_pre(v[j], load1(P.pre.ptr, P.pre.dtype, pbase + cj * P.pre.sc),
+                           P.t_dtype);
+        nz[j] = (has_noise && in)
+                    ? load1(P.noise.ptr, AQTB200_F32, nbase + cj * P.noise.sc)
+                    : 0.f;
+      }
+    }
+    uint8_t q[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      q[j] = (c + j < x.cols) ? quant1(v[j], sinv, nz[j], has_noise, P) : 0;
+    }
+    *(uint4*)(P.q + brow * P.ldq + c) = *(uint4*)q;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// quantize + transpose, kept index contiguous in the input. Tile: 64 kept rows
+// x 128 contraction indices; 256 threads, thread (tx,ty) = (tid%16, tid/16)
+// owns rows 4*tx..4*tx+3 and contraction indices i*64 + 4*ty + e.
+template <bool VEC>
+__global__ void __launch_bounds__(256)
+quant_col_kernel(QParams P, int64_t row_tiles, int64_t col_tiles,
+                 int64_t total_units) {
+  __shared__ uint32_t tile[64][33];
+  const DView& x = P.x;
+  const bool has_pre = P.pre.ptr != nullptr;
+  const bool has_noise = P.noise.ptr != nullptr;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int64_t u = blockIdx.x; u < total_units; u += gridDim.x) {
+    int64_t ct = u % col_tiles;
+    int64_t t = u / col_tiles;
+    int64_t rt = t % row_tiles;
+    int64_t b = t / row_tiles;
+    int64_t i1 = b % x.b1, i0 = b / x.b1;
+    const int64_t base = i0 * x.sb0 + i1 * x.sb1;
+    const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+    const int64_t nbase = i0 * P.noise.sb0 + i1 * P.noise.sb1;
+    const int64_t sbase = (i0 * x.b1 + i1) * x.rows;
+    const int64_t r0 = rt * 64 + tx * 4;
+    float sinv[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      sinv[j] = P.per_tensor ? P.sinv[0]
+                             : (r0 + j < x.rows ? P.sinv[sbase + r0 + j] : 1.f);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t word[4] = {0u, 0u, 0u, 0u};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+        if (c < x.cols && r0 < x.rows) {
+          float v[4], nz[4] = {0.f, 0.f, 0.f, 0.f};
+          if (VEC) {
+            loadN<4>(x.ptr, x.dtype, base + c * x.sc + r0, v);
+            if (has_noise) {
+              if (P.noise_vec) {
+                loadN<4>(P.noise.ptr, AQTB200_F32, nbase + c * P.noise.sc + r0, nz);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  nz[j] = load1(P.noise.ptr, AQTB200_F32,
+                                nbase + c * P.noise.sc + (r0 + j) * P.noise.sr);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              bool in = r0 + j < x.rows;
+              v[j] = in ? load1(x.ptr, x.dtype, base + c * x.sc + (r0 + j) * x.sr) : 0.f;
+              nz[j] = (in && has_noise)
+                          ? load1(P.noise.ptr, AQTB200_F32,
+                                  nbase + c * P.noise.sc + (r0 + j) * P.noise.sr)
+                          : 0.f;
+            }
+          }
+          float p = has_pre ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            float w = has_pre ? apply_pre(v[j], p, P.t_dtype) : v[j];
+            uint32_t qb = (r0 + j < x.rows) ? quant1(w, sinv[j], nz[j], has_noise, P) : 0u;
+            word[j] |= qb << (8 * e);
+          }
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) tile[tx * 4 + j][i * 16 + ty] = word[j];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int s = 0; s < 2; ++s) {
+      const int id = tid + 256 * s;
+      const int row = id >> 3, seg = id & 7;
+      const int64_t gr = rt * 64 + row;
+      const int64_t gc = ct * 128 + seg * 16;
+      if (gr < x.rows && gc < P.ldq) {
+        uint4 o;
+        o.x = tile[row][seg * 4 + 0]; o.y = tile[row][seg * 4 + 1];
+        o.z = tile[row][seg * 4 + 2]; o.w = tile[row][seg * 4 + 3];
+        *(uint4*)(P.q + (sbase + gr) * P.ldq + gc) = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------------------
+// dequantize: out = cast_D(q) * scale (aqt_tensor.py:179-198, single scale).
+struct DeqParams {
+  DView q, s;
+  int d_dtype;
+  void* out;  // contiguous [b0][b1][rows][cols]
+};
+
+__global__ void dequant_kernel(DeqParams D, int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    int64_t c = i % D.q.cols;
+    int64_t t = i / D.q.cols;
+    int64_t r = t % D.q.rows;
+    t /= D.q.rows;
+    int64_t i1 = t % D.q.b1, i0 = t / D.q.b1;
+    float v = load1(D.q.ptr, D.q.dtype, i0 * D.q.sb0 + i1 * D.q.sb1 + r * D.q.sr + c * D.q.sc);
+    v = round_to(v, D.d_dtype);  // int32 -> f32 happened in load1 (RNE)
+    if (D.s.ptr != nullptr) {
+      float s = load1(D.s.ptr, D.s.dtype, i0 * D.s.sb0 + i1 * D.s.sb1 + r * D.s.sr + c * D.s.sc);
+      int wide = (D.d_dtype == AQTB200_F32 || D.s.dtype == AQTB200_F32) ? AQTB200_F32 : AQTB200_BF16;
+      v = round_to(round_to(__fmul_rn(v, s), wide), D.d_dtype);
+    }
+    if (D.d_dtype == AQTB200_BF16)
+      ((__nv_bfloat16*)D.out)[i] = __float2bfloat16_rn(v);
+    else
+      ((float*)D.out)[i] = v;
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host side
+
+static int g_sm_count = 0;
+int sm_count() {
+  if (g_sm_count == 0) {
+    int dev = 0, n = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess &&
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      g_sm_count = n;
+    else
+      g_sm_count = 148;
+  }
+  return g_sm_count;
+}
+
+static bool is_float_dt(int dt) { return dt == AQTB200_F32 || dt == AQTB200_BF16; }
+static bool is_q_dt(int dt) { return dt == AQTB200_S8 || dt == AQTB200_E4M3 || dt == AQTB200_E5M2; }
+
+static int64_t n_scales(const aqtb200_view* x, const aqtb200_quant_spec* s) {
+  return s->per_tensor ? 1 : x->b0 * x->b1 * x->rows;
+}
+
+static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+static int validate(const aqtb200_view* x, const aqtb200_view* pre,
+                    const aqtb200_view* noise, const aqtb200_quant_spec* spec,
+                    bool need_q) {
+  AQT_REQUIRE(x != nullptr && spec != nullptr, AQTB200_EINVAL, "null view or spec");
+  AQT_REQUIRE(x->b0 >= 0 && x->b1 >= 0 && x->rows >= 0 && x->cols >= 0,
+              AQTB200_EINVAL, "negative extent");
+  int64_t total = x->b0 * x->b1 * x->rows * x->cols;
+  AQT_REQUIRE(total == 0 || x->ptr != nullptr, AQTB200_EINVAL, "null input pointer");
+  AQT_REQUIRE(is_float_dt(x->dtype) || is_q_dt(x->dtype), AQTB200_EINVAL,
+              "input dtype %d is not f32/bf16/s8/e4m3/e5m2", x->dtype);
+  AQT_REQUIRE(is_float_dt(spec->compute_dtype) && is_float_dt(spec->scale_dtype),
+              AQTB200_EINVAL, "compute/scale dtype must be f32 or bf16");
+  AQT_REQUIRE(!(x->dtype == AQTB200_F32 && spec->compute_dtype == AQTB200_BF16),
+              AQTB200_EINVAL, "f32 input cannot have bf16 compute dtype");
+  AQT_REQUIRE(spec->kind == AQTB200_NUM_INT || spec->kind == AQTB200_NUM_FP8,
+              AQTB200_EUNSUPPORTED,
+              "numerics kind %d: only IntSymmetric and Fp8Numerics are quantized on the device",
+              spec->kind);
+  if (need_q) {
+    if (spec->kind == AQTB200_NUM_INT)
+      AQT_REQUIRE(spec->qdtype == AQTB200_S8, AQTB200_EUNSUPPORTED, "int numerics need an int8 container");
+    else
+      AQT_REQUIRE(spec->qdtype == AQTB200_E4M3 || spec->qdtype == AQTB200_E5M2,
+                  AQTB200_EUNSUPPORTED, "fp8 numerics need e4m3 or e5m2");
+    AQT_REQUIRE(spec->clip_bound > 0.f, AQTB200_EINVAL, "clip_bound must be positive");
+  }
+  AQT_REQUIRE(spec->quant_bound > 0.f, AQTB200_EINVAL, "quant_bound must be positive");
+  AQT_REQUIRE(x->col_stride == 1 || x->row_stride == 1 || x->rows <= 1 || x->cols <= 1,
+              AQTB200_EUNSUPPORTED,
+              "view must have the contraction index or the kept index contiguous");
+  if (pre && pre->ptr)
+    AQT_REQUIRE(is_float_dt(pre->dtype), AQTB200_EINVAL, "prescale must be f32 or bf16");
+  if (noise && noise->ptr) {
+    AQT_REQUIRE(noise->dtype == AQTB200_F32, AQTB200_EINVAL, "noise must be f32");
+    AQT_REQUIRE(spec->kind == AQTB200_NUM_INT, AQTB200_EUNSUPPORTED,
+                "noise-tensor stochastic rounding applies to int numerics only");
+  }
+  return 0;
+}
+
+static bool aligned(const void* p, size_t a) { return ((uintptr_t)p % a) == 0; }
+static bool mult(int64_t v, int64_t m) { return v % m == 0; }
+
+// Can every 16-element group along the contiguous contraction index be loaded
+// with 16-byte vector loads?
+static bool row_vec_ok(const DView& v, int64_t cols) {
+  int es = dtype_size(v.dtype);
+  int64_t g = 16 / es > 0 ? 16 / es : 1;  // elements per 16 bytes
+  return v.sc == 1 && mult(cols, 16) && aligned(v.ptr, 16) && mult(v.sr, g) &&
+         mult(v.sb0, g) && mult(v.sb1, g);
+}
+// Can 4 consecutive kept rows be loaded as one vector?
+static bool col_vec_ok(const DView& v, int64_t rows) {
+  int es = dtype_size(v.dtype);
+  int64_t g = 4;  // 4 elements: 16/8/4 bytes, natural alignment 4*es
+  (void)es;
+  return v.sr == 1 && mult(rows, 4) && aligned(v.ptr, 16) && mult(v.sc, g) &&
+         mult(v.sb0, g) && mult(v.sb1, g);
+}
+
+static int grid_for(int64_t units, int per_sm) {
+  int64_t cap = (int64_t)sm_count() * per_sm;
+  return (int)std::max<int64_t>(1, std::min<int64_t>(units, cap));
+}
+
+static int run(const aqtb200_view* xv, const aqtb200_view* prev,
+               const aqtb200_view* noisev, const aqtb200_quant_spec* spec,
+               const void* scale_in, void* q_out, void* scale_out,
+               void* workspace, size_t workspace_bytes, cudaStream_t st,
+               bool want_q) {
+  int rc = validate(xv, prev, noisev, spec, want_q);
+  if (rc) return rc;
+  const int64_t ns = n_scales(xv, spec);
+  const int64_t nbrow = xv->b0 * xv->b1 * xv->rows;
+  const int64_t total = nbrow * xv->cols;
+  if (ns == 0) return 0;
+  size_t need = aqtb200_quantize_workspace_bytes(xv, spec);
+  AQT_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned(workspace, 256),
+              AQTB200_EWORKSPACE, "workspace: need %zu bytes, 256-byte aligned (got %zu)",
+              need, workspace_bytes);
+  AQT_REQUIRE(scale_out != nullptr || scale_in != nullptr, AQTB200_EINVAL, "scale_out is null");
+  if (want_q) AQT_REQUIRE(q_out != nullptr && aligned(q_out, 16), AQTB200_EINVAL,
+                          "q_out null or not 16-byte aligned");
+
+  QParams P{};
+  P.x = to_dview(xv);
+  P.pre = to_dview(prev);
+  P.noise = to_dview(noisev);
+  P.t_dtype = spec->compute_dtype;
+  P.s_dtype = spec->scale_dtype;
+  P.y_dtype = (P.t_dtype == AQTB200_F32 || P.s_dtype == AQTB200_F32) ? AQTB200_F32 : AQTB200_BF16;
+  P.kind = spec->kind;
+  P.qdtype = spec->qdtype;
+  P.clip_bound = spec->clip_bound;
+  P.per_tensor = spec->per_tensor;
+  P.amax = (uint32_t*)workspace;
+  P.sinv = (float*)((char*)workspace + align256((size_t)ns * 4));
+  P.q = (uint8_t*)q_out;
+  P.ldq = aqtb200_round_up(xv->cols, 16);
+  // degenerate extents: pick the mode whose stride assumption holds
+  const bool row_mode = P.x.sc == 1 || P.x.cols <= 1 ? (P.x.sc == 1 || P.x.sr != 1) : false;
+  P.pre_vec = P.pre.ptr && row_vec_ok({P.pre.ptr, P.pre.dtype, 1, 1, 1, 1,
+                                       P.pre.sb0, P.pre.sb1, 16, P.pre.sc}, xv->cols);
+  if (P.noise.ptr)
+    P.noise_vec = row_mode ? row_vec_ok(P.noise, xv->cols) : col_vec_ok(P.noise, xv->rows);
+
+  if (scale_in == nullptr) {
+    AQT_CUDA_OK(cudaMemsetAsync(P.amax, 0, (size_t)ns * 4, st));
+    if (total > 0) {
+      if (row_mode) {
+        int64_t chunks = (xv->cols + kRowChunk - 1) / kRowChunk;
+        int64_t units = nbrow * chunks;
+        int grid = grid_for((units + 7) / 8, 8);
+        if (row_vec_ok(P.x, xv->cols))
+          absmax_row_kernel<true><<<grid, 256, 0, st>>>(P, chunks, units);
+        else
+          absmax_row_kernel<false><<<grid, 256, 0, st>>>(P, chunks, units);
+      } else {
+        bool vec = col_vec_ok(P.x, xv->rows);
+        int64_t rows_per_block = 32 * (vec ? 4 : 1);
+        int64_t rbs = (xv->rows + rows_per_block - 1) / rows_per_block;
+        int64_t ccs = (xv->cols + kColChunk - 1) / kColChunk;
+        int64_t units = xv->b0 * xv->b1 * rbs * ccs;
+        int grid = grid_for(units, 8);
+        dim3 block(32, 8);
+        if (vec)
+          absmax_col_kernel<true><<<grid, block, 0, st>>>(P, rbs, ccs, units);
+        else
+          absmax_col_kernel<false><<<grid, block, 0, st>>>(P, rbs, ccs, units);
+      }
+      AQT_CUDA_OK(cudaGetLastError()); count_launch();
+    }
+  }
+  FinalizeParams F{};
+  F.amax = P.amax; F.scale_in = scale_in; F.scale_out = scale_out; F.sinv = P.sinv;
+  F.n = ns; F.t_dtype = P.t_dtype; F.s_dtype = P.s_dtype;
+  F.quant_bound = spec->quant_bound; F.clipping_scale = spec->clipping_scale;
+  F.po2 = spec->po2_scale;
+  finalize_scale_kernel<<<(int)((ns + 255) / 256), 256, 0, st>>>(F);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  if (!want_q || nbrow == 0) return 0;
+
+  if (row_mode) {
+    int64_t upr = P.ldq / 16;
+    int64_t units = nbrow * upr;
+    int grid = grid_for((units + 255) / 256, 8);
+    if (row_vec_ok(P.x, xv->cols))
+      quant_row_kernel<true><<<grid, 256, 0, st>>>(P, upr, units);
+    else
+      quant_row_kernel<false><<<grid, 256, 0, st>>>(P, upr, units);
+  } else {
+    int64_t rts = (xv->rows + 63) / 64;
+    int64_t cts = (P.ldq + 127) / 128;
+    int64_t units = xv->b0 * xv->b1 * rts * cts;
+    int grid = grid_for(units, 8);
+    if (col_vec_ok(P.x, xv->rows))
+      quant_col_kernel<true><<<grid, 256, 0, st>>>(P, rts, cts, units);
+    else
+      quant_col_kernel<false><<<grid, 256, 0, st>>>(P, rts, cts, units);
+  }
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+}  // namespace aqtb200
+
+using namespace aqtb200;
+
+extern "C" {
+
+int64_t aqtb200_round_up(int64_t v, int64_t multiple) {
+  return multiple <= 0 ? v : ((v + multiple - 1) / multiple) * multiple;
+}
+
+size_t aqtb200_quantize_workspace_bytes(const aqtb200_view* x,
+                                        const aqtb200_quant_spec* spec) {
+  if (x == nullptr || spec == nullptr) return 0;
+  int64_t ns = std::max<int64_t>(1, n_scales(x, spec));
+  return 2 * align256((size_t)ns * 4);
+}
+
+int aqtb200_quantize(const aqtb200_view* x, const aqtb200_view* prescale,
+                     const aqtb200_view* noise, const aqtb200_quant_spec* spec,
+                     const void* scale_in, void* q_out, void* scale_out,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+  return run(x, prescale, noise, spec, scale_in, q_out, scale_out, workspace,
+             workspace_bytes, (cudaStream_t)stream, true);
+}
+
+int aqtb200_absmax_scale(const aqtb200_view* x, const aqtb200_view* prescale,
+                         const aqtb200_quant_spec* spec, void* scale_out,
+                         void* workspace, size_t workspace_bytes, void* stream) {
+  return run(x, prescale, nullptr, spec, nullptr, nullptr, scale_out, workspace,
+             workspace_bytes, (cudaStream_t)stream, false);
+}
+
+int aqtb200_dequantize(const aqtb200_view* q, const aqtb200_view* scale,
+                       int32_t dequant_dtype, void* out, void* stream) {
+  AQT_REQUIRE(q != nullptr && out != nullptr, AQTB200_EINVAL, "null argument");
+  AQT_REQUIRE(dequant_dtype == AQTB200_F32 || dequant_dtype == AQTB200_BF16,
+              AQTB200_EINVAL, "dequant dtype must be f32 or bf16");
+  DeqParams D{};
+  D.q = to_dview(q);
+  D.s = to_dview(scale);
+  D.d_dtype = dequant_dtype;
+  D.out = out;
+  int64_t total = q->b0 * q->b1 * q->rows * q->cols;
+  if (total == 0) return 0;
+  AQT_REQUIRE(q->ptr != nullptr, AQTB200_EINVAL, "null q pointer");
+  int grid = grid_for((total + 255) / 256, 8);
+  dequant_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(D, total);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+}  // extern "C"

@@ -1,0 +1,875 @@
+"""Host-side planner: turns AQT config objects + torch CUDA tensors into calls
+of the C ABI (include/aqt_b200.h).
+
+It owns no arithmetic. Its jobs are (1) to check that a configuration is one
+the sm_100a kernels implement and raise NotImplementedError otherwise, (2) to
+normalise arbitrary dimension_numbers into the strided [b0][b1][rows][cols]
+views the kernels take, without copying whenever the strides allow it, and
+(3) to allocate outputs / workspaces from torch's caching allocator and pass
+raw pointers and the current stream down.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import functools
+from typing import Any, Sequence
+
+import numpy as np
+import torch
+
+from aqt_b200 import _lib
+from aqt_b200.v2 import utils
+
+_TORCH_CODE = {
+    torch.float32: _lib.F32, torch.bfloat16: _lib.BF16, torch.int8: _lib.S8,
+    torch.float8_e4m3fn: _lib.E4M3, torch.float8_e5m2: _lib.E5M2,
+    torch.int32: _lib.S32,
+}
+_CODE_TORCH = {v: k for k, v in _TORCH_CODE.items()}
+_FLOAT_CODES = (_lib.F32, _lib.BF16)
+
+
+def _code(dtype) -> int:
+  if isinstance(dtype, torch.dtype):
+    if dtype not in _TORCH_CODE:
+      raise NotImplementedError(f'dtype {dtype} is not handled on the device')
+    return _TORCH_CODE[dtype]
+  d = utils.as_dtype(dtype)
+  if d.code < 0:
+    raise NotImplementedError(f'dtype {d} is not handled on the device')
+  return d.code
+
+
+# Set only by the CPU test-suite, together with a stand-in for the shared
+# library, to exercise the stride planner on host tensors.
+_HOST_TEST_MODE = False
+
+
+def _stream() -> int:
+  if _HOST_TEST_MODE:
+    return 0
+  return torch.cuda.current_stream().cuda_stream
+
+
+_status = {}
+
+
+def _status_buf(device):
+  key = str(device)
+  if key not in _status:
+    _status[key] = torch.zeros(4, dtype=torch.int32, device=device)
+  return _status[key]
+
+
+def check_status():
+  """Raises if a kernel reported a bounded wait that ran out (syncs)."""
+  for buf in _status.values():
+    code = int(buf[0].item())
+    if code:
+      buf.zero_()
+      raise _lib.AqtB200Error(
+          f'GEMM kernel gave up waiting on a barrier (role {code})')
+
+
+def set_gemm_impl(name: str):
+  """'tcgen05' (default) or 'simt' (debug cross-check kernel)."""
+  _lib.check(_lib.load().aqtb200_set_gemm_impl({'tcgen05': 0, 'simt': 1}[name]),
+             'set_gemm_impl')
+
+
+# ---------------------------------------------------------------------------
+# stride bookkeeping
+
+
+def _merge(extents: Sequence[int], strides: Sequence[Sequence[int]],
+           max_dims: int):
+  """Merges consecutive index positions into at most max_dims strided dims.
+
+  extents[p] is the extent of position p; strides[t][p] its stride in tensor t.
+  Two neighbours merge only if they do so in every tensor. Returns a list of
+  (extent, [stride per tensor]) or None when more than max_dims dims remain.
+  """
+  nt = len(strides)
+  dims = []
+  for p, e in enumerate(extents):
+    if e == 1:
+      continue
+    s = [strides[t][p] for t in range(nt)]
+    if dims and all(dims[-1][1][t] == s[t] * e for t in range(nt)):
+      dims[-1] = (dims[-1][0] * e, s)
+    else:
+      dims.append((e, s))
+  if len(dims) > max_dims:
+    return None
+  return dims
+
+
+class _Unmergeable(Exception):
+  pass
+
+
+def _view(ptr, code, b, rows, cols, bs, rs, cs) -> _lib.View:
+  v = _lib.View()
+  v.ptr = ptr
+  v.dtype = code
+  v.b0, v.b1 = b[0], b[1]
+  v.rows, v.cols = rows, cols
+  v.b0_stride, v.b1_stride = bs[0], bs[1]
+  v.row_stride, v.col_stride = rs, cs
+  return v
+
+
+# ---------------------------------------------------------------------------
+# config -> spec
+
+
+def _calibration_kwargs(quantizer):
+  cal = quantizer.calibration
+  kw = {}
+  if isinstance(cal, functools.partial):
+    kw = dict(cal.keywords)
+    cal = cal.func
+  if cal is None or cal.__name__ != 'AbsMaxCalibration':
+    raise NotImplementedError(
+        f'calibration {cal} is outside the sm_100a hot path '
+        '(AbsMaxCalibration only)')
+  extra = set(kw) - {'dtype', 'clipping_scale', 'po2_scale'}
+  if extra:
+    raise NotImplementedError(f'AbsMaxCalibration options {sorted(extra)}')
+  return kw
+
+
+def _round_to_dtype(value: float, code: int) -> float:
+  t = torch.tensor(value, dtype=torch.float64).to(_CODE_TORCH[code])
+  return float(t.to(torch.float32))
+
+
+def _numerics_fields(numerics):
+  """(kind, qdtype code, quant_bound, clip_bound) of a numerics object."""
+  name = type(numerics).__name__
+  if name == 'IntSymmetric':
+    if not (numerics.preserve_zero and numerics.clip and numerics.round):
+      raise NotImplementedError(
+          'IntSymmetric needs preserve_zero, clip and round on the sm_100a '
+          'path')
+    if not 2 <= numerics.bits <= 8:
+      raise NotImplementedError(f'IntSymmetric bits={numerics.bits}')
+    dt = numerics.get_dtype()
+    if dt is None or utils.as_dtype(dt) not in (utils.int8, utils.int4):
+      raise NotImplementedError(
+          f'IntSymmetric dtype={dt}: the kernels store int8 containers')
+    return (_lib.NUM_INT, _lib.S8, float(numerics.get_quant_bound()),
+            float(numerics._get_fwd_clip_bound()))  # pylint: disable=protected-access
+  if name == 'Fp8Numerics':
+    numerics.check()
+    bound = float(numerics.get_quant_bound())
+    return (_lib.NUM_FP8, _code(numerics.get_dtype()), bound, bound)
+  raise NotImplementedError(f'numerics {name} is outside the sm_100a hot path')
+
+
+def _make_spec(quantizer, compute_code: int, contraction_axes_ok: bool):
+  """aqtb200_quant_spec for one operand, or None for NoNumerics."""
+  numerics = quantizer.numerics
+  if type(numerics).__name__ == 'NoNumerics':
+    return None
+  kind, qcode, qb, cb = _numerics_fields(numerics)
+  kw = _calibration_kwargs(quantizer)
+  csa = quantizer.calib_shared_axes
+  if csa not in (None, 'per_tensor') and not contraction_axes_ok:
+    raise NotImplementedError(
+        f'calib_shared_axes={csa}: only the contraction axes or "per_tensor"')
+  scale_dtype = kw.get('dtype', quantizer.scale_dtype)
+  spec = _lib.QuantSpec()
+  spec.kind = kind
+  spec.qdtype = qcode
+  spec.quant_bound = qb
+  spec.clip_bound = cb
+  spec.per_tensor = 1 if csa == 'per_tensor' else 0
+  spec.compute_dtype = compute_code
+  spec.scale_dtype = compute_code if scale_dtype is None else _code(scale_dtype)
+  if spec.scale_dtype not in _FLOAT_CODES:
+    raise NotImplementedError(f'scale dtype {scale_dtype}')
+  spec.po2_scale = 1 if kw.get('po2_scale', False) else 0
+  cs = kw.get('clipping_scale')
+  spec.clipping_scale = _round_to_dtype(cs, compute_code) if cs else 0.0
+  return spec
+
+
+def _noise_for(quantizer, shape, device):
+  fn = getattr(quantizer.numerics, 'noise_fn', None)
+  if not fn:
+    return None
+  assert quantizer.context.key is not None, (
+      'noise_fn is set, requestic stochastic rounding, but RNG was not '
+      'passed in Context.key')
+  noise = fn(tuple(shape), quantizer.context.key)
+  if not isinstance(noise, torch.Tensor):
+    noise = torch.as_tensor(np.asarray(noise))
+  noise = noise.to(device=device, dtype=torch.float32)
+  return noise.expand(tuple(shape))
+
+
+# ---------------------------------------------------------------------------
+# one raw quantized dot
+
+
+def _prod(v):
+  return int(np.prod(list(v), dtype=np.int64)) if len(v) else 1
+
+
+def _check_raw_supported(raw):
+  from aqt_b200.v2 import aqt_dot_general as adg
+  q = raw.dg_quantizer
+  if not isinstance(q, adg.DefaultDotGeneralQuantizer):
+    raise NotImplementedError(
+        f'dg_quantizer {type(q).__name__}: DefaultDotGeneralQuantizer only')
+  if q.lhs_mid_alpha is not None or q.rhs_mid_alpha is not None:
+    raise NotImplementedError('mid-scale quantization')
+  if raw.local_aqt is not None:
+    raise NotImplementedError('local AQT (contraction-axis sharding)')
+  for side, t in (('lhs', raw.lhs), ('rhs', raw.rhs)):
+    if t.dequant_mode != adg.DequantMode.OUTPUT:
+      raise NotImplementedError(
+          f'{side}.dequant_mode={t.dequant_mode}: the fused epilogue '
+          'implements DequantMode.OUTPUT')
+    if t.calibration_mode != adg.CalibrationMode.CONTRACTING_AXIS:
+      raise NotImplementedError(
+          f'{side}.calibration_mode={t.calibration_mode}: CONTRACTING_AXIS '
+          'only')
+  if raw.dot_general is not adg.lax_dot_general:
+    raise NotImplementedError(
+        'a custom DotGeneralRaw.dot_general cannot be injected: the '
+        'contraction is fused with dequantization')
+  return q
+
+
+class _Operand:
+  """One operand of the raw dot with its axis groups."""
+
+  def __init__(self, t, ba, ra, ca):
+    self.t = t
+    self.ba, self.ra, self.ca = list(ba), list(ra), list(ca)
+
+  def strides_of(self, axes, tensor=None):
+    t = self.t if tensor is None else tensor
+    return [t.stride(a) for a in axes]
+
+  def extents_of(self, axes):
+    return [self.t.shape[a] for a in axes]
+
+
+def _as_scale_compact(scale, op: _Operand, per_tensor: bool, code: int):
+  """A caller-supplied scale (operand rank, shared axes 1) -> compact buffer."""
+  want = _CODE_TORCH[code]
+  if per_tensor:
+    return scale.reshape(1).to(want).contiguous()
+  s = scale.permute(*(op.ba + op.ra + op.ca))
+  return s.reshape(-1).to(want).contiguous()
+
+
+def _logical_scale(compact, op: _Operand, per_tensor: bool):
+  """Compact [batch..., rows...] scale -> operand-rank tensor, shared axes 1."""
+  nd = op.t.ndim
+  if per_tensor:
+    return compact.view([1] * nd)
+  shape = op.extents_of(op.ba) + op.extents_of(op.ra) + [1] * len(op.ca)
+  order = op.ba + op.ra + op.ca
+  inv = [order.index(i) for i in range(nd)]
+  return compact.view(shape).permute(*inv)
+
+
+def _strided_logical(buf, b_ext, r_ext, k_ext):
+  """Views a [B, rows, ld] buffer as a tensor of shape b_ext + r_ext + k_ext.
+
+  The contraction dims subdivide the first prod(k_ext) bytes of each row, the
+  kept dims subdivide `rows`, the batch dims subdivide B; no data moves.
+  """
+  def sub(extents, innermost):
+    strides, st = [], innermost
+    for e in reversed(list(extents)):
+      strides.append(st)
+      st *= e
+    return list(reversed(strides))
+
+  strides = (sub(b_ext, buf.stride(0)) + sub(r_ext, buf.stride(1))
+             + sub(k_ext, 1))
+  return buf.as_strided(list(b_ext) + list(r_ext) + list(k_ext), strides,
+                        buf.storage_offset())
+
+
+def _logical_q(buf, op: _Operand, k: int):
+  """[B, rows, ldk] byte buffer -> tensor with the operand's logical shape."""
+  del k
+  order = op.ba + op.ra + op.ca
+  inv = [order.index(i) for i in range(op.t.ndim)]
+  t = _strided_logical(buf, op.extents_of(op.ba), op.extents_of(op.ra),
+                       op.extents_of(op.ca))
+  return t.permute(*inv)
+
+
+def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
+           out_transpose_axes=None, want_acc=False):
+  """DotGeneralRaw.__call__ on the device (aqt_dot_general.py:757-840).
+
+  Returns (out, DotGeneralRes[, acc]). `out` is laid out as
+  transpose(out, out_transpose_axes) would be, written by the epilogue.
+  """
+  from aqt_b200.v2 import aqt_dot_general as adg
+  from aqt_b200.v2 import aqt_tensor
+  q = _check_raw_supported(raw)
+  (lca, rca), (lba, rba) = dimension_numbers
+  lca, rca, lba, rba = list(lca), list(rca), list(lba), list(rba)
+
+  # _maybe_use_fwd_quant (aqt_dot_general.py:675-729)
+  prescale = None  # fwd scale of the other operand, in the rhs operand's rank
+  rhs_float = rhs
+  rhs_compute_dtype = None
+  if isinstance(rhs, adg.MultiTensor):
+    if raw.rhs.use_fwd_quant:
+      n_scales = len(rhs.qx.scale) if rhs.qx.scale is not None else -1
+      assert n_scales == 1, (
+          f'Found use_fwd_quant is True in bwd. It is supported only if there '
+          f'is exactly one scale in a good shape.\nscale_count={n_scales}')
+      if rhs.qx.bias:
+        raise NotImplementedError(
+            'Quantization biases are not supported in forward quantization.')
+      prescale = rhs.qx.scale[0]
+      rhs_float = rhs.qx.qvalue
+      rhs_compute_dtype = rhs.qx.dequant_dtype
+    else:
+      rhs_float = rhs.x
+  assert isinstance(lhs, torch.Tensor) and isinstance(rhs_float, torch.Tensor)
+  if not (lhs.is_cuda and rhs_float.is_cuda) and not _HOST_TEST_MODE:
+    raise _lib.AqtB200Error('operands must be CUDA tensors (no CPU path)')
+
+  lra = utils.get_remaining_axes(lhs.ndim, lca, lba)
+  rra = utils.get_remaining_axes(rhs_float.ndim, rca, rba)
+  L = _Operand(lhs, lba, lra, lca)
+  R = _Operand(rhs_float, rba, rra, rca)
+  t_code_l = _code(lhs.dtype)
+  t_code_r = _code(rhs_compute_dtype) if rhs_compute_dtype is not None else (
+      _code(rhs_float.dtype))
+  if t_code_l not in _FLOAT_CODES or t_code_r not in _FLOAT_CODES:
+    raise NotImplementedError(
+        f'operand dtypes {lhs.dtype}, {rhs_float.dtype}: f32 / bf16 only')
+  d_code = _lib.F32 if _lib.F32 in (t_code_l, t_code_r) else _lib.BF16
+
+  lhs_spec = _make_spec(q.lhs, t_code_l,
+                        sorted(q.lhs.calib_shared_axes or []) == sorted(lca)
+                        if q.lhs.calib_shared_axes not in (None, 'per_tensor')
+                        else True)
+  rhs_spec = _make_spec(q.rhs, t_code_r,
+                        sorted(q.rhs.calib_shared_axes or []) == sorted(rca)
+                        if q.rhs.calib_shared_axes not in (None, 'per_tensor')
+                        else True)
+  if lhs_spec is None and rhs_spec is None:
+    return _dg_raw_unquantized(raw, lhs, rhs_float, lhs_qt, rhs_qt,
+                               dimension_numbers, out_transpose_axes)
+  if lhs_spec is None or rhs_spec is None:
+    raise NotImplementedError(
+        'one quantized and one unquantized operand: the tensor-core path '
+        'needs both operands in int8 or both in fp8')
+  ints = (lhs_spec.kind == _lib.NUM_INT, rhs_spec.kind == _lib.NUM_INT)
+  if ints[0] != ints[1]:
+    raise NotImplementedError('mixing int and fp8 operands in one dot')
+  want_accum = utils.int32 if ints[0] else utils.float32
+  if raw.dg_accumulator_dtype is not None and (
+      utils.as_dtype(raw.dg_accumulator_dtype) != want_accum):
+    raise NotImplementedError(
+        f'dg_accumulator_dtype={raw.dg_accumulator_dtype}: the tensor cores '
+        f'accumulate {want_accum} for these operands')
+
+  # caller-supplied QTensors (aqt_dot_general.py:623-653)
+  def split_qt(qt):
+    if qt is None:
+      return None, None
+    if qt.bias or qt.sparsity_mask is not None or qt.tiling_state is not None:
+      raise NotImplementedError('bias / sparsity / tiling in a QTensor')
+    assert len(qt.scale) == 1, 'exactly one scale per QTensor on this path'
+    return (qt.qvalue if qt.is_full() else None), qt.scale[0]
+
+  lhs_qv, lhs_sin = split_qt(lhs_qt)
+  rhs_qv, rhs_sin = split_qt(rhs_qt)
+
+  noise_l = None if lhs_qv is not None else _noise_for(q.lhs, lhs.shape, lhs.device)
+  noise_r = None if rhs_qv is not None else _noise_for(q.rhs, rhs_float.shape, lhs.device)
+  if noise_l is not None and lhs_spec.kind != _lib.NUM_INT:
+    raise NotImplementedError('noise_fn with fp8 numerics')
+
+  if lhs_qv is not None:
+    L = _Operand(lhs_qv, lba, lra, lca)
+  if rhs_qv is not None:
+    R = _Operand(rhs_qv, rba, rra, rca)
+
+  # ---- output tensor, laid out as the transposed result
+  nb, nm, nn = len(lba), len(lra), len(rra)
+  raw_shape = L.extents_of(lba) + L.extents_of(lra) + R.extents_of(rra)
+  perm = list(out_transpose_axes) if out_transpose_axes is not None else list(
+      range(len(raw_shape)))
+  out_dtype = _CODE_TORCH[d_code]
+  out_t = torch.empty([raw_shape[p] for p in perm], dtype=out_dtype,
+                      device=lhs.device)
+  raw_strides = [0] * len(raw_shape)
+  for i, p in enumerate(perm):
+    raw_strides[p] = out_t.stride(i)
+  out_b = raw_strides[:nb]
+  out_m = raw_strides[nb:nb + nm]
+  out_n = raw_strides[nb + nm:]
+
+  # prescale strides along the lhs operand's batch and contraction axes
+  pre_t = None
+  if prescale is not None:
+    # scale has the rhs operand's rank; its axes rba/rra map to lhs lba/lca.
+    if prescale.ndim < R.t.ndim:
+      prescale = prescale.reshape(list(prescale.shape) + [1] * (
+          R.t.ndim - prescale.ndim))
+    pre_t = prescale
+    # In the backward dimension numbers the operand's kept axes are the
+    # forward contraction axes, where a forward scale has extent 1; its
+    # contraction axes pair, in order, with the cotangent's.
+    for ax in rra:
+      assert pre_t.shape[ax] == 1, (
+          'forward scale varies along an axis the backward dot keeps; set '
+          'use_fwd_quant=False')
+
+  def pre_strides(axes):
+    return [0 if pre_t.shape[a] == 1 else pre_t.stride(a) for a in axes]
+
+  try:
+    # batch group: lhs, rhs, out (+ prescale, noises)
+    tensors_b = [L.strides_of(lba), R.strides_of(rba), out_b]
+    if pre_t is not None:
+      tensors_b.append(pre_strides(rba))
+    if noise_l is not None:
+      tensors_b.append([noise_l.stride(a) for a in lba])
+    if noise_r is not None:
+      tensors_b.append([noise_r.stride(a) for a in rba])
+    bdims = _merge(L.extents_of(lba), tensors_b, 2)
+    tensors_m = [L.strides_of(lra), out_m]
+    if noise_l is not None:
+      tensors_m.append([noise_l.stride(a) for a in lra])
+    mdims = _merge(L.extents_of(lra), tensors_m, 1)
+    tensors_n = [R.strides_of(rra), out_n]
+    if noise_r is not None:
+      tensors_n.append([noise_r.stride(a) for a in rra])
+    ndims = _merge(R.extents_of(rra), tensors_n, 1)
+    tensors_k = [L.strides_of(lca), R.strides_of(rca)]
+    if pre_t is not None:
+      tensors_k.append(pre_strides(rca))
+    if noise_l is not None:
+      tensors_k.append([noise_l.stride(a) for a in lca])
+    if noise_r is not None:
+      tensors_k.append([noise_r.stride(a) for a in rca])
+    kdims = _merge(L.extents_of(lca), tensors_k, 1)
+    if None in (bdims, mdims, ndims, kdims):
+      raise _Unmergeable()
+    if pre_t is not None:
+      for a, e in zip(rca, L.extents_of(lca)):
+        assert pre_t.shape[a] in (1, e), (
+            f'forward scale shape {tuple(pre_t.shape)} does not line up with '
+            'the cotangent; set use_fwd_quant=False')
+  except _Unmergeable:
+    return _dg_raw_via_copies(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
+                              out_transpose_axes, want_acc)
+
+  def pad(dims, n, nt):
+    dims = list(dims)
+    while len(dims) < n:
+      dims.insert(0, (1, [0] * nt))
+    return dims
+
+  bdims = pad(bdims, 2, len(tensors_b))
+  (M, ms), = pad(mdims, 1, len(tensors_m))
+  (N, ns), = pad(ndims, 1, len(tensors_n))
+  (K, ks), = pad(kdims, 1, len(tensors_k))
+  B = [bdims[0][0], bdims[1][0]]
+  bs = lambda t: [bdims[0][1][t], bdims[1][1][t]]
+
+  def dense(stride, extent):
+    # a dim of extent 1 gets stride 1 so either kernel mode is admissible
+    return 1 if extent == 1 else stride
+
+  desc = _lib.DgRawDesc()
+  desc.lhs = _view(L.t.data_ptr(), _code(L.t.dtype), B, M, K, bs(0),
+                   dense(ms[0], M), dense(ks[0], K))
+  desc.rhs = _view(R.t.data_ptr(), _code(R.t.dtype), B, N, K, bs(1),
+                   dense(ns[0], N), dense(ks[1], K))
+  ti_b, ti_m, ti_n, ti_k = 3, 2, 2, 2
+  if pre_t is not None:
+    desc.lhs_prescale = _view(pre_t.data_ptr(), _code(pre_t.dtype), B, 1, K,
+                              bs(ti_b), 0, ks[ti_k])
+    ti_b += 1
+    ti_k += 1
+  keep = [out_t]
+  if noise_l is not None:
+    desc.lhs_noise = _view(noise_l.data_ptr(), _lib.F32, B, M, K, bs(ti_b),
+                           ms[ti_m], ks[ti_k])
+    ti_b += 1
+    ti_m += 1
+    ti_k += 1
+    keep.append(noise_l)
+  if noise_r is not None:
+    desc.rhs_noise = _view(noise_r.data_ptr(), _lib.F32, B, N, K, bs(ti_b),
+                           ns[ti_n], ks[ti_k])
+    keep.append(noise_r)
+  desc.lhs_spec = lhs_spec
+  desc.rhs_spec = rhs_spec
+
+  dev = lhs.device
+  ldk = (K + 15) // 16 * 16
+  nB = B[0] * B[1]
+
+  def side_buffers(spec, rows, qv, sin, op):
+    n_sc = 1 if spec.per_tensor else nB * rows
+    s_dtype = _CODE_TORCH[spec.scale_dtype]
+    if qv is not None:
+      # pre-quantized operand: must already be contraction-contiguous
+      qbuf = None
+    else:
+      qbuf = torch.empty((nB, rows, ldk), dtype=_CODE_TORCH[spec.qdtype],
+                         device=dev)
+    sbuf = torch.empty(n_sc, dtype=s_dtype, device=dev)
+    sin_c = None
+    if sin is not None:
+      sin_c = _as_scale_compact(sin, op, bool(spec.per_tensor),
+                                spec.scale_dtype)
+      sbuf = sin_c
+    return qbuf, sbuf, sin_c
+
+  lq, ls, lsin = side_buffers(lhs_spec, M, lhs_qv, lhs_sin, L)
+  rq, rs_, rsin = side_buffers(rhs_spec, N, rhs_qv, rhs_sin, R)
+  keep += [lq, ls, rq, rs_, lsin, rsin]
+  desc.lhs_scale_in = lsin.data_ptr() if lsin is not None else None
+  desc.rhs_scale_in = rsin.data_ptr() if rsin is not None else None
+  desc.lhs_is_quantized = 1 if lhs_qv is not None else 0
+  desc.rhs_is_quantized = 1 if rhs_qv is not None else 0
+  if lhs_qv is not None and (desc.lhs.col_stride != 1 and K > 1):
+    raise _NeedsKMajor('lhs')
+  if rhs_qv is not None and (desc.rhs.col_stride != 1 and K > 1):
+    raise _NeedsKMajor('rhs')
+  desc.lhs_q = lq.data_ptr() if lq is not None else None
+  desc.lhs_scale = ls.data_ptr()
+  desc.rhs_q = rq.data_ptr() if rq is not None else None
+  desc.rhs_scale = rs_.data_ptr()
+  # Put the operand whose kept index is contiguous in the OUTPUT on the
+  # column side of the tile so the epilogue stores rows of the result.
+  swap = (ns[1] != 1 and ms[1] == 1 and N > 1)
+  desc.swap_ab = 1 if swap else 0
+  desc.dequant_dtype = d_code
+  desc.out = out_t.data_ptr()
+  desc.out_dtype = _code(out_dtype)
+  desc.out_b0_stride, desc.out_b1_stride = bs(2)
+  desc.out_m_stride = ms[1]
+  desc.out_n_stride = ns[1]
+  acc = None
+  if want_acc:
+    acc_shape = (nB, N, M) if swap else (nB, M, N)
+    acc = torch.empty(acc_shape, device=dev,
+                      dtype=torch.int32 if ints[0] else torch.float32)
+    desc.acc_out = acc.data_ptr()
+    if swap:
+      acc = acc.transpose(1, 2)
+
+  lib = _lib.load()
+  ws_bytes = lib.aqtb200_dot_general_raw_workspace_bytes(C.byref(desc))
+  ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+  status = _status_buf(dev)
+  rc = lib.aqtb200_dot_general_raw(C.byref(desc), ws.data_ptr(), ws.numel(),
+                                   status.data_ptr(), _stream())
+  _lib.check(rc, f'aqtb200_dot_general_raw[{raw.jax_scope_name}]')
+  del keep  # buffers stay alive until here; frees are stream-ordered
+
+  # residuals: QTensors with the reference's logical shapes
+  dd_l = utils.as_dtype(lhs.dtype)
+  dd_r = utils.as_dtype(rhs_compute_dtype) if rhs_compute_dtype is not None else (
+      utils.as_dtype(rhs_float.dtype))
+  if lhs_qv is not None:
+    lhs_q_out = lhs_qt
+  else:
+    lhs_q_out = aqt_tensor.QTensor(
+        qvalue=_logical_q(lq.view(nB, M, ldk), L, K),
+        scale=[_logical_scale(ls, L, bool(lhs_spec.per_tensor))], scale_t=None,
+        bias=[], dequant_dtype=dd_l)
+  if rhs_qv is not None:
+    rhs_q_out = rhs_qt
+  else:
+    rhs_q_out = aqt_tensor.QTensor(
+        qvalue=_logical_q(rq.view(nB, N, ldk), R, K),
+        scale=[_logical_scale(rs_, R, bool(rhs_spec.per_tensor))],
+        scale_t=None, bias=[], dequant_dtype=dd_r)
+
+  def grad_fn(quantizer, x, given):
+    if given is not None and not raw.allow_dummy_gradient_into_qtensor:
+      return adg._POISON  # pylint: disable=protected-access
+    n = quantizer.numerics
+    if getattr(n, 'clip_gradient', False):
+      raise NotImplementedError('clip_gradient on the fused path')
+    return functools.partial(n.vjp_bwd, (None,))
+
+  res = adg.DotGeneralRes(
+      lhs=adg.TensorRes(mt=adg.MultiTensor(x=lhs, qx=lhs_q_out),
+                        quant_grad=grad_fn(q.lhs, lhs, lhs_qv)),
+      rhs=adg.TensorRes(mt=adg.MultiTensor(x=rhs_float, qx=rhs_q_out),
+                        quant_grad=grad_fn(q.rhs, rhs_float, rhs_qv)))
+  if want_acc:
+    return out_t, res, acc
+  return out_t, res
+
+
+class _NeedsKMajor(NotImplementedError):
+
+  def __init__(self, side):
+    super().__init__(
+        f'the pre-quantized {side} QTensor must store its contraction axis '
+        'contiguously; convert it once with engine.to_k_major()')
+
+
+def to_k_major(qt, contraction_axes: Sequence[int]):
+  """Re-lays a QTensor's qvalue so the given contraction axes are innermost.
+
+  A one-off conversion for frozen serving weights (flax/freezer.py keeps them
+  in the weight's own layout, contraction axis first for a [K, N] kernel).
+  The logical shape is unchanged; only strides differ.
+  """
+  q = qt.qvalue
+  ca = list(contraction_axes)
+  rest = [a for a in range(q.ndim) if a not in ca]
+  order = rest + ca
+  inv = [order.index(i) for i in range(q.ndim)]
+  k = _prod([q.shape[a] for a in ca])
+  ldk = (k + 15) // 16 * 16
+  rows = _prod([q.shape[a] for a in rest])
+  buf = torch.zeros((1, rows, ldk), dtype=torch.uint8, device=q.device)
+  buf[0, :, :k] = q.permute(*order).reshape(rows, k).contiguous().view(
+      torch.uint8)
+  buf = buf.view(q.dtype)
+  t = _strided_logical(buf, [], [q.shape[a] for a in rest],
+                       [q.shape[a] for a in ca])
+  return qt.replace(qvalue=t.permute(*inv))
+
+
+def _dg_raw_unquantized(raw, lhs, rhs, lhs_qt, rhs_qt, dims,
+                        out_transpose_axes):
+  """Both operands NoNumerics: a plain library GEMM (not the hot path)."""
+  from aqt_b200.v2 import aqt_dot_general as adg
+  from aqt_b200.v2 import aqt_tensor
+  out = adg.lax_dot_general(lhs, rhs, dims)
+  if out_transpose_axes is not None:
+    out = out.permute(*out_transpose_axes)
+
+  def qt(x):
+    return aqt_tensor.QTensor(qvalue=x, scale=[], scale_t=None, bias=[],
+                              dequant_dtype=utils.as_dtype(x.dtype))
+
+  res = adg.DotGeneralRes(
+      lhs=adg.TensorRes(mt=adg.MultiTensor(x=lhs, qx=qt(lhs)), quant_grad=None),
+      rhs=adg.TensorRes(mt=adg.MultiTensor(x=rhs, qx=qt(rhs)), quant_grad=None))
+  return out, res
+
+
+def _dg_raw_via_copies(raw, lhs, rhs, lhs_qt, rhs_qt, dims,
+                       out_transpose_axes, want_acc):
+  """Strides the kernels cannot express: regroup axes with copies, then retry.
+
+  Operands are permuted to (batch, kept, contraction) order and made
+  contiguous, the dot runs on the regrouped tensors, and the result is
+  returned as a permuted view.
+  """
+  from aqt_b200.v2 import aqt_dot_general as adg
+  if lhs_qt is not None or rhs_qt is not None:
+    raise NotImplementedError(
+        'caller-supplied QTensors with dimension_numbers that need a '
+        'regrouping copy')
+  (lca, rca), (lba, rba) = dims
+  if isinstance(rhs, adg.MultiTensor) and raw.rhs.use_fwd_quant:
+    raise NotImplementedError(
+        'use_fwd_quant with dimension_numbers that need a regrouping copy')
+  rhs_x = rhs.x if isinstance(rhs, adg.MultiTensor) else rhs
+  lra = utils.get_remaining_axes(lhs.ndim, lca, lba)
+  rra = utils.get_remaining_axes(rhs_x.ndim, rca, rba)
+  l2 = lhs.permute(*lba, *lra, *lca).contiguous()
+  r2 = rhs_x.permute(*rba, *rra, *rca).contiguous()
+  nb, nm, nn, nk = len(lba), len(lra), len(rra), len(lca)
+  if l2.data_ptr() == lhs.data_ptr() and r2.data_ptr() == rhs_x.data_ptr() and (
+      l2.stride() == lhs.stride() and r2.stride() == rhs_x.stride()):
+    raise NotImplementedError(
+        f'dimension_numbers {dims} with these strides cannot be expressed as '
+        'one strided batched GEMM')
+  dims2 = ((tuple(range(nb + nm, nb + nm + nk)),
+            tuple(range(nb + nn, nb + nn + nk))),
+           (tuple(range(nb)), tuple(range(nb))))
+  got = dg_raw(raw, l2, r2, None, None, dims2, None, want_acc)
+  out = got[0]
+  if out_transpose_axes is not None:
+    out = out.permute(*out_transpose_axes)
+  return (out,) + tuple(got[1:])
+
+
+# ---------------------------------------------------------------------------
+# piecewise API (Quantizer.calibrate / calculate_qvalue, QTensor.dequant)
+
+
+def _single_operand(x, shared_axes):
+  nd = x.ndim
+  ca = sorted(int(a) % nd for a in shared_axes)
+  ra = [a for a in range(nd) if a not in ca]
+  op = _Operand(x, [], ra, ca)
+  rdims = _merge(op.extents_of(ra), [op.strides_of(ra)], 1)
+  kdims = _merge(op.extents_of(ca), [op.strides_of(ca)], 1)
+  if rdims is None or kdims is None:
+    xc = x.permute(*ra, *ca).contiguous()
+    order = ra + ca
+    inv = [order.index(i) for i in range(nd)]
+    return _single_operand(xc.permute(*inv), shared_axes)
+  (rows, rs), = rdims or [(1, [1])]
+  (cols, cs), = kdims or [(1, [1])]
+  rs = 1 if rows == 1 else rs[0]
+  cs = 1 if cols == 1 else cs[0]
+  if rs != 1 and cs != 1:
+    xc = x.permute(*ra, *ca).contiguous()
+    order = ra + ca
+    inv = [order.index(i) for i in range(nd)]
+    return _single_operand(xc.permute(*inv), shared_axes)
+  view = _view(x.data_ptr(), _code(x.dtype), [1, 1], rows, cols, [0, 0], rs, cs)
+  return op, view, rows, cols
+
+
+def _spec_for(numerics, x_code, scale_dtype, per_tensor, clipping_scale=None,
+              po2_scale=False):
+  kind, qcode, qb, cb = _numerics_fields(numerics)
+  spec = _lib.QuantSpec()
+  spec.kind, spec.qdtype, spec.quant_bound, spec.clip_bound = kind, qcode, qb, cb
+  spec.per_tensor = 1 if per_tensor else 0
+  spec.compute_dtype = x_code
+  spec.scale_dtype = x_code if scale_dtype is None else _code(scale_dtype)
+  spec.po2_scale = 1 if po2_scale else 0
+  spec.clipping_scale = (
+      _round_to_dtype(clipping_scale, x_code) if clipping_scale else 0.0)
+  return spec
+
+
+def absmax_scale(x, shared_axes, numerics, scale_dtype=None,
+                 clipping_scale=None, po2_scale=False):
+  """AbsMaxCalibration on the device: the scale, x's rank, shared axes 1."""
+  per_tensor = len(shared_axes) == x.ndim
+  op, view, rows, cols = _single_operand(x, shared_axes)
+  spec = _spec_for(numerics, _code(x.dtype), scale_dtype, per_tensor,
+                   clipping_scale, po2_scale)
+  lib = _lib.load()
+  n = 1 if per_tensor else rows
+  sbuf = torch.empty(n, dtype=_CODE_TORCH[spec.scale_dtype], device=x.device)
+  ws_bytes = lib.aqtb200_quantize_workspace_bytes(C.byref(view), C.byref(spec))
+  ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=x.device)
+  rc = lib.aqtb200_absmax_scale(C.byref(view), None, C.byref(spec),
+                                sbuf.data_ptr(), ws.data_ptr(), ws.numel(),
+                                _stream())
+  _lib.check(rc, 'aqtb200_absmax_scale')
+  return _logical_scale(sbuf, op, per_tensor)
+
+
+def quantize_with_scale(x, scale, numerics, noise=None):
+  """Quantizer.calculate_qvalue with a given scale: returns qvalue."""
+  shared = [a for a in range(x.ndim) if scale.shape[a] == 1 and x.shape[a] != 1]
+  per_tensor = scale.numel() == 1
+  if per_tensor:
+    shared = list(range(x.ndim))
+  op, view, rows, cols = _single_operand(x, shared)
+  x_code = _code(x.dtype)
+  spec = _spec_for(numerics, x_code, utils.as_dtype(scale.dtype), per_tensor)
+  sin = _as_scale_compact(scale, op, per_tensor, spec.scale_dtype)
+  ldk = (cols + 15) // 16 * 16
+  qbuf = torch.empty((1, rows, ldk), dtype=_CODE_TORCH[spec.qdtype],
+                     device=x.device)
+  nview = None
+  if noise is not None:
+    if not isinstance(noise, torch.Tensor):
+      noise = torch.as_tensor(np.asarray(noise), device=x.device)
+    noise = noise.to(device=x.device, dtype=torch.float32).expand(
+        tuple(x.shape)).contiguous()
+    nop, nview, _, _ = _single_operand(noise.as_strided(
+        x.shape, x.stride()) if noise.stride() == x.stride() else noise, shared)
+    if (nview.row_stride, nview.col_stride) != (view.row_stride,
+                                                view.col_stride):
+      noise = torch.empty_strided(x.shape, x.stride(), dtype=torch.float32,
+                                  device=x.device).copy_(noise)
+      nop, nview, _, _ = _single_operand(noise, shared)
+  lib = _lib.load()
+  ws_bytes = lib.aqtb200_quantize_workspace_bytes(C.byref(view), C.byref(spec))
+  ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=x.device)
+  rc = lib.aqtb200_quantize(C.byref(view), None,
+                            C.byref(nview) if nview is not None else None,
+                            C.byref(spec), sin.data_ptr(), qbuf.data_ptr(),
+                            sin.data_ptr(), ws.data_ptr(), ws.numel(),
+                            _stream())
+  _lib.check(rc, 'aqtb200_quantize')
+  return _logical_q(qbuf, op, cols)
+
+
+def apply_numerics(x, numerics, noise=None):
+  """numerics.vjp_fwd on an already scaled tensor (unit scale)."""
+  one = torch.ones([1] * x.ndim, dtype=x.dtype, device=x.device)
+  return quantize_with_scale(x, one, numerics, noise)
+
+
+def apply_inv_scales(x, scales):
+  raise NotImplementedError(
+      'QTensor.quant() as a stand-alone float op is not part of the sm_100a '
+      'path; the multiply by 1/scale is fused into the quantize kernel '
+      '(use Quantizer.quant / calculate_qvalue)')
+
+
+def dequant(qvalue, scales, dequant_dtype):
+  """QTensor.dequant on the device (zero or one scale)."""
+  if len(scales) > 1:
+    raise NotImplementedError('dequant with more than one scale')
+  d_code = _code(dequant_dtype)
+  out = torch.empty(qvalue.shape, dtype=_CODE_TORCH[d_code],
+                    device=qvalue.device)
+  if not scales:
+    return out.copy_(qvalue)
+  scale = scales[0].expand(qvalue.shape)
+  nd = qvalue.ndim
+  if nd > 4:
+    raise NotImplementedError('dequant of tensors with more than 4 axes')
+  pad = [1] * (4 - nd)
+  ext = pad + list(qvalue.shape)
+  qs = [0] * (4 - nd) + list(qvalue.stride())
+  ss = [0] * (4 - nd) + list(scale.stride())
+  qv = _view(qvalue.data_ptr(), _code(qvalue.dtype), ext[:2], ext[2], ext[3],
+             qs[:2], qs[2], qs[3])
+  sv = _view(scale.data_ptr(), _code(scale.dtype), ext[:2], ext[2], ext[3],
+             ss[:2], ss[2], ss[3])
+  rc = _lib.load().aqtb200_dequantize(C.byref(qv), C.byref(sv), d_code,
+                                      out.data_ptr(), _stream())
+  _lib.check(rc, 'aqtb200_dequantize')
+  return out
+
+
+# ---------------------------------------------------------------------------
+# autograd bridge (the custom_vjp of aqt_dot_general.py:993-997)
+
+
+def dg_core_autograd(cfg, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers):
+  from aqt_b200.v2 import aqt_dot_general as adg
+
+  holder = []
+
+  class _Fn(torch.autograd.Function):
+
+    @staticmethod
+    def forward(ctx, lhs_, rhs_):
+      (out, qret), res = adg.dg_core_vjp_fwd(
+          lhs_.detach(), rhs_.detach(), lhs_qt, rhs_qt, dimension_numbers, cfg)
+      ctx.res = res
+      holder.append(qret)
+      return out
+
+    @staticmethod
+    def backward(ctx, g):
+      dlhs, drhs, *_ = adg.dg_core_vjp_bwd(dimension_numbers, ctx.res,
+                                           (g.contiguous(), None))
+      return dlhs, drhs
+
+  out = _Fn.apply(lhs, rhs)
+  return out, holder[0]

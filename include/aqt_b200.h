@@ -1,0 +1,242 @@
+/*
+ * aqt_b200.h -- C ABI of libaqt_b200.so: the quantized dot_general hot path of
+ * google/aqt's aqt.jax.v2 as sm_100a CUDA kernels.
+ *
+ * The reference is pure Python on JAX and has no native boundary; the calls
+ * below are what an XLA FFI custom-call handler (or any other host) binds in
+ * place of the jnp/lax ops the reference traces. Each entry point names the
+ * reference code it replaces (paths relative to aqt/jax/v2/).
+ *
+ * Conventions
+ *  - every function returns 0 on success, a negative AQTB200_E* code for a bad
+ *    argument / unsupported configuration, or a positive cudaError_t value;
+ *    aqtb200_last_error() gives a human-readable message for the calling thread;
+ *  - compute calls only ENQUEUE work on the caller's stream: no allocation, no
+ *    synchronisation, no host readback. Scratch memory comes from the caller
+ *    (size it with the matching *_workspace_bytes call);
+ *  - all pointers in views/descriptors are device pointers unless stated;
+ *  - strides are in ELEMENTS of the tensor they describe.
+ */
+#ifndef AQT_B200_H_
+#define AQT_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AQTB200_VERSION 1
+
+/* error codes (negative); positive return values are cudaError_t */
+#define AQTB200_OK 0
+#define AQTB200_EINVAL (-1)      /* malformed argument (null pointer, bad extent, bad stride) */
+#define AQTB200_EUNSUPPORTED (-2) /* valid request outside what the kernels cover */
+#define AQTB200_EWORKSPACE (-3)  /* workspace too small or misaligned */
+#define AQTB200_EDRIVER (-4)     /* CUDA driver entry point / tensor-map encode failed */
+#define AQTB200_EDEVICE (-5)     /* a kernel reported a bounded wait that ran out */
+
+typedef enum aqtb200_dtype {
+  AQTB200_F32 = 0,
+  AQTB200_BF16 = 1,
+  AQTB200_S8 = 2,   /* also the container of int4 / intN values, N < 8 */
+  AQTB200_E4M3 = 3, /* float8_e4m3fn */
+  AQTB200_E5M2 = 4, /* float8_e5m2 */
+  AQTB200_S32 = 5
+} aqtb200_dtype;
+
+typedef enum aqtb200_numerics_kind {
+  AQTB200_NUM_NONE = 0, /* no_numerics.NoNumerics: value passes through as float */
+  AQTB200_NUM_INT = 1,  /* int_numerics.IntSymmetric, preserve_zero, clip, round */
+  AQTB200_NUM_FP8 = 2   /* fp8_numerics.Fp8Numerics, round-to-nearest-even */
+} aqtb200_numerics_kind;
+
+/*
+ * A strided 4-D view [b0][b1][rows][cols] of one tensor.
+ *   cols = the contraction index of the dot (the axis AbsMax shares a scale
+ *          over, calibration.py:149), rows = the kept ("remaining") index,
+ *   b0,b1 = up to two batch indices (extent 1 when unused).
+ * Either col_stride == 1 (contraction contiguous) or row_stride == 1; the
+ * latter makes the quantize kernel transpose through shared memory, because
+ * its OUTPUT always has the contraction index contiguous.
+ */
+typedef struct aqtb200_view {
+  const void* ptr;
+  int32_t dtype; /* aqtb200_dtype */
+  int32_t reserved;
+  int64_t b0, b1, rows, cols;
+  int64_t b0_stride, b1_stride, row_stride, col_stride;
+} aqtb200_view;
+
+/*
+ * How one operand is calibrated and quantized. Mirrors aqt_quantizer.Quantizer
+ * + calibration.AbsMaxCalibration + the numerics object
+ * (aqt_quantizer.py:37-176, calibration.py:106-157, numerics/int_numerics.py:
+ * 24-111, numerics/fp8_numerics.py:67-123).
+ */
+typedef struct aqtb200_quant_spec {
+  int32_t kind;          /* aqtb200_numerics_kind */
+  int32_t qdtype;        /* container: AQTB200_S8, _E4M3, _E5M2 (NONE: = compute_dtype) */
+  float quant_bound;     /* numerics.get_quant_bound(): 127.5, 7.5, 448, 57344, ... */
+  float clip_bound;      /* forward clip: 127, 7, 448, 57344, ... */
+  int32_t per_tensor;    /* calib_shared_axes == "per_tensor": one scale for everything */
+  int32_t compute_dtype; /* T: dtype the operand has when arithmetic starts (F32|BF16);
+                            int8/fp8 inputs are widened to it exactly first */
+  int32_t scale_dtype;   /* dtype of the scale array (F32|BF16); T unless scale_dtype set */
+  int32_t po2_scale;     /* calibration.ceil_to_po2 */
+  float clipping_scale;  /* AbsMaxCalibration.clipping_scale ALREADY ROUNDED to T; 0 = unset */
+  int32_t reserved;
+} aqtb200_quant_spec;
+
+/*
+ * aqtb200_quantize: AbsMax calibrate + quantize one operand.
+ * Replaces: AbsMaxCalibration.get_scale_and_bias_and_sparsity (calibration.py:
+ * 117-157), QTensor.quant (aqt_tensor.py:125-159), IntSymmetric.vjp_fwd
+ * (numerics/int_numerics.py:81-111) / Fp8Numerics.vjp_fwd (numerics/
+ * fp8_numerics.py:88-123) and, when `prescale` is given, the cotangent
+ * pre-scaling of _maybe_use_fwd_quant (aqt_dot_general.py:714-720).
+ *
+ *   v      = widen(x) [* cast_T(prescale[b0,b1,col])]            (rounded to T)
+ *   scale  = where(max|v|==0, 1, max|v|) [* clipping_scale] / quant_bound   (in T, stored as scale_dtype)
+ *   q      = cast(round_half_even(clip(v * (1/scale) [+ noise])))           (int)
+ *          = cast_fp8(clip(v * (1/scale)))                                  (fp8)
+ *
+ * x        : input view (dtype F32/BF16, or S8/E4M3/E5M2 when re-quantizing a
+ *            stored QTensor as the backward pass does with use_fwd_quant).
+ * prescale : optional (ptr may be NULL). Indexed [b0][b1][col] through its
+ *            b0/b1/col strides (rows, row_stride ignored); dtype F32/BF16.
+ * noise    : optional f32 view with x's extents (stochastic rounding input,
+ *            U[-0.5,0.5)); int numerics only.
+ * scale_in : optional. When non-NULL calibration is skipped and this scale
+ *            (layout of scale_out) is used: Quantizer.calculate_qvalue on a
+ *            caller-supplied incomplete QTensor (aqt_dot_general.py:645-653).
+ * q_out    : [b0][b1][rows][ldq] bytes, contraction contiguous, ldq =
+ *            aqtb200_round_up(cols,16); batch strides rows*ldq and b1*rows*ldq;
+ *            bytes past `cols` in each row are written as zero.
+ * scale_out: [b0][b1][rows] of scale_dtype, or a single element when
+ *            spec->per_tensor.
+ * workspace: aqtb200_quantize_workspace_bytes() bytes, 256-byte aligned.
+ */
+int aqtb200_quantize(const aqtb200_view* x, const aqtb200_view* prescale,
+                     const aqtb200_view* noise, const aqtb200_quant_spec* spec,
+                     const void* scale_in, void* q_out, void* scale_out,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+size_t aqtb200_quantize_workspace_bytes(const aqtb200_view* x,
+                                        const aqtb200_quant_spec* spec);
+
+/* aqtb200_absmax_scale: the calibration half alone (scale_out only).
+ * Replaces Quantizer.calibrate (aqt_quantizer.py:79-157). */
+int aqtb200_absmax_scale(const aqtb200_view* x, const aqtb200_view* prescale,
+                         const aqtb200_quant_spec* spec, void* scale_out,
+                         void* workspace, size_t workspace_bytes, void* stream);
+
+int64_t aqtb200_round_up(int64_t v, int64_t multiple);
+
+/*
+ * One batched GEMM  acc[b,m,n] = sum_k A[b,m,k] * B[b,n,k]  on tcgen05 tensor
+ * cores (kind::i8 -> int32, kind::f8f6f4 -> f32) with the dequantizing
+ * epilogue fused. Replaces lax.dot_general at aqt_dot_general.py:921-927
+ * together with QTensor.dequant (aqt_tensor.py:161-200) and the output
+ * transpose of the backward pass (aqt_dot_general.py:1201).
+ *
+ *   r = cast_D(acc); r *= first scale; r *= second scale; out = cast_out(r)
+ * where each multiply rounds to promote(current dtype, scale dtype), exactly
+ * as the chain of jnp multiplies does; "first" is A's scale unless
+ * b_scale_first.
+ */
+typedef struct aqtb200_gemm_desc {
+  int64_t b0, b1, m, n, k;
+  /* operands: 1-byte elements, k contiguous, row strides multiples of 16 */
+  const void* a;
+  int64_t a_b0_stride, a_b1_stride, lda;
+  const void* b;
+  int64_t b_b0_stride, b_b1_stride, ldb;
+  int32_t a_dtype, b_dtype; /* S8/S8, or any mix of E4M3/E5M2 */
+  /* scales: NULL = operand not quantized (factor 1). A stride of 0 on every
+     index = per-tensor scalar. */
+  const void* a_scale;
+  int64_t a_scale_b0_stride, a_scale_b1_stride, a_scale_m_stride;
+  const void* b_scale;
+  int64_t b_scale_b0_stride, b_scale_b1_stride, b_scale_n_stride;
+  int32_t a_scale_dtype, b_scale_dtype; /* F32|BF16 */
+  int32_t b_scale_first;                /* multiply by B's scale before A's */
+  int32_t dequant_dtype;                /* D: F32|BF16 (promote(lhs.dtype, rhs.dtype)) */
+  void* out;
+  int32_t out_dtype; /* F32|BF16 */
+  int32_t reserved;
+  int64_t out_b0_stride, out_b1_stride, out_m_stride, out_n_stride;
+  /* optional raw accumulator dump, contiguous [b0][b1][m][n], int32 or f32;
+     for parity checks of the tensor-core result. NULL in production. */
+  void* acc_out;
+} aqtb200_gemm_desc;
+
+/* status: device int32[4], zeroed by the caller before first use; a kernel
+ * whose bounded wait ran out writes a non-zero code there instead of hanging.
+ * May be NULL. */
+int aqtb200_gemm_dequant(const aqtb200_gemm_desc* desc, int32_t* status,
+                         void* stream);
+
+/*
+ * aqtb200_dot_general_raw: one whole DotGeneralRaw.__call__
+ * (aqt_dot_general.py:757-840) = quantize lhs, quantize rhs, contraction,
+ * dequantize, for operands already normalised to views. The forward pass, the
+ * dlhs pass and the drhs pass of dg_core_vjp_fwd / dg_core_vjp_bwd
+ * (aqt_dot_general.py:1098-1221) are three calls of it with different views,
+ * specs and prescales.
+ *
+ * lhs_q_in / rhs_q_in: when non-NULL the operand arrives already quantized
+ * (serving, aqt_dot_general.py:623-635): the view's dtype is the container
+ * type with contraction contiguous and its scale is passed in *_scale_in.
+ */
+typedef struct aqtb200_dg_raw_desc {
+  aqtb200_view lhs, rhs;                    /* rows = M resp. N, cols = K */
+  aqtb200_view lhs_prescale, rhs_prescale;  /* ptr NULL when absent */
+  aqtb200_view lhs_noise, rhs_noise;        /* ptr NULL when absent */
+  aqtb200_quant_spec lhs_spec, rhs_spec;
+  const void* lhs_scale_in;                 /* optional caller-supplied scales */
+  const void* rhs_scale_in;
+  int32_t lhs_is_quantized, rhs_is_quantized;
+  /* outputs of the quantization step (residuals of the forward pass) */
+  void* lhs_q;      /* [b0][b1][M][ldk] */
+  void* lhs_scale;  /* [b0][b1][M] or [1] */
+  void* rhs_q;      /* [b0][b1][N][ldk] */
+  void* rhs_scale;  /* [b0][b1][N] or [1] */
+  /* output of the dot */
+  int32_t swap_ab;  /* run the GEMM as (rhs rows) x (lhs rows): out tile rows = N */
+  int32_t dequant_dtype;
+  void* out;
+  int32_t out_dtype;
+  int32_t reserved;
+  int64_t out_b0_stride, out_b1_stride, out_m_stride, out_n_stride;
+  void* acc_out;
+} aqtb200_dg_raw_desc;
+
+size_t aqtb200_dot_general_raw_workspace_bytes(const aqtb200_dg_raw_desc* desc);
+
+int aqtb200_dot_general_raw(const aqtb200_dg_raw_desc* desc, void* workspace,
+                            size_t workspace_bytes, int32_t* status,
+                            void* stream);
+
+/* Elementwise helpers for the piecewise API (QTensor.quant / QTensor.dequant
+ * used outside the fused path, aqt_tensor.py:125-200):
+ *   dequantize: out = cast_D(q) * scale   (one scale, broadcast by strides) */
+int aqtb200_dequantize(const aqtb200_view* q, const aqtb200_view* scale,
+                       int32_t dequant_dtype, void* out, void* stream);
+
+/* library / device queries */
+int aqtb200_version(void);
+const char* aqtb200_last_error(void);
+int aqtb200_device_sm_count(int* out);
+/* number of kernels this library has launched in this process (all threads);
+ * lets a harness report how much of its timed region ran in these kernels. */
+int64_t aqtb200_kernel_launch_count(void);
+/* selects the contraction kernel: 0 = tcgen05 (default), 1 = plain CUDA-core
+ * reference kernel kept for debugging the tensor-core path. */
+int aqtb200_set_gemm_impl(int impl);
+
+#ifdef __cplusplus
+} /* extern "C" */
+#endif
+#endif /* AQT_B200_H_ */

@@ -1,0 +1,153 @@
+"""Host-logic tests: the planner in aqt_b200/engine.py against the oracle.
+
+The shared library is replaced by tests/fake_lib.py (numpy on host memory), so
+what is under test is everything ABOVE the C ABI: stride normalisation for
+arbitrary dimension_numbers, operand swapping, output-transpose folding,
+residual QTensor layouts, use_fwd_quant plumbing, noise plumbing.
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from aqt_b200.v2 import config
+from aqt_b200.v2 import aqt_dot_general as aqt
+from oracle import aqt_oracle as orc
+from tests import fake_lib
+from tests import util
+
+
+def _run_both(cfg, lhs, rhs, g, dims):
+  tl, tr, tg = util.to_torch(lhs), util.to_torch(rhs), util.to_torch(g)
+  out, backprop = cfg.vjp(tl, tr, dims)
+  dl, dr = backprop(tg)
+  want = orc.dg_fwd_bwd(cfg, lhs, rhs, g, dims)
+  return (out, dl, dr), want
+
+
+def _assert_same(got, want, what):
+  g = util.to_numpy(got)
+  assert g.shape == want.shape, (what, g.shape, want.shape)
+  assert g.dtype == want.dtype, (what, g.dtype, want.dtype)
+  np.testing.assert_array_equal(g.astype(np.float32), want.astype(np.float32),
+                                err_msg=what)
+
+
+CASES = [
+    # dims, lhs shape, rhs shape
+    ((((1,), (0,)), ((), ())), (12, 40), (40, 24)),
+    ((((3,), (3,)), ((0, 2), (0, 2))), (2, 9, 3, 16), (2, 7, 3, 16)),
+    ((((2,), (1,)), ((0,), (0,))), (3, 5, 32), (3, 32, 6)),
+    ((((1,), (1,)), ((), ())), (8, 20), (10, 20)),
+    ((((0,), (0,)), ((), ())), (20, 8), (20, 10)),
+    ((((2,), (0,)), ((), ())), (4, 6, 32), (32, 12)),
+]
+
+
+@pytest.mark.parametrize('dims,ls,rs', CASES)
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+@pytest.mark.parametrize('use_fwd_quant', [True, False])
+def test_int8_fwd_bwd_matches_oracle(monkeypatch, dims, ls, rs, np_dtype,
+                                     use_fwd_quant):
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(0)
+  lhs = util.rand_normal(rng, ls, 1.0, np_dtype)
+  rhs = util.rand_normal(rng, rs, 0.2, np_dtype)
+  cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                               use_fwd_quant=use_fwd_quant,
+                               use_stochastic_rounding=False)
+  out_shape = orc.dg_fwd(cfg, lhs, rhs, dims)[0].shape
+  g = util.rand_normal(rng, out_shape, 1.0, np_dtype)
+  (out, dl, dr), (wo, wl, wr, res) = _run_both(cfg, lhs, rhs, g, dims)
+  _assert_same(out, wo, 'out')
+  _assert_same(dl, wl, 'dlhs')
+  _assert_same(dr, wr, 'drhs')
+
+
+@pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e4m3', 'e4m3')])
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+def test_fp8_per_tensor_matches_oracle(monkeypatch, fwd, bwd, np_dtype):
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(1)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = util.rand_normal(rng, (24, 48), 1.0, np_dtype)
+  rhs = util.rand_normal(rng, (48, 40), 0.1, np_dtype)
+  g = util.rand_normal(rng, (24, 40), 1.0, np_dtype)
+  cfg = config.fully_quantized(fwd_bits=fwd, bwd_bits=bwd,
+                               use_stochastic_rounding=False)
+  for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
+    raw.dg_quantizer.lhs.calib_shared_axes = 'per_tensor'
+    raw.dg_quantizer.rhs.calib_shared_axes = 'per_tensor'
+  (out, dl, dr), (wo, wl, wr, _) = _run_both(cfg, lhs, rhs, g, dims)
+  _assert_same(out, wo, 'out')
+  _assert_same(dl, wl, 'dlhs')
+  _assert_same(dr, wr, 'drhs')
+
+
+def test_residual_qtensors_have_reference_layout(monkeypatch):
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(2)
+  dims = (((3,), (3,)), ((0, 2), (0, 2)))
+  lhs = util.rand_normal(rng, (2, 9, 3, 16), 1.0, orc.bfloat16)
+  rhs = util.rand_normal(rng, (2, 7, 3, 16), 1.0, orc.bfloat16)
+  cfg = config.fully_quantized(use_stochastic_rounding=False)
+  (out, (lq, rq)), _ = aqt.dg_core_vjp_fwd(
+      util.to_torch(lhs), util.to_torch(rhs), None, None, dims, cfg)
+  _, res = orc.dg_fwd(cfg, lhs, rhs, dims)
+  for got, want in ((lq, res.lhs.qx), (rq, res.rhs.qx)):
+    assert tuple(got.qvalue.shape) == want.qvalue.shape
+    np.testing.assert_array_equal(util.to_numpy(got.qvalue), want.qvalue)
+    assert tuple(got.scale[0].shape) == want.scale[0].shape
+    _assert_same(got.scale[0], want.scale[0], 'scale')
+
+
+def test_stochastic_rounding_noise_is_plumbed(monkeypatch):
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(3)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = util.rand_normal(rng, (16, 32), 1.0, np.float32)
+  rhs = util.rand_normal(rng, (32, 48), 0.2, np.float32)
+  g = util.rand_normal(rng, (16, 48), 1.0, np.float32)
+  cfg = config.fully_quantized(use_stochastic_rounding=True)
+  noise_rng = np.random.default_rng(7)
+  table = {}
+
+  def noise_fn(shape, key):
+    k = (tuple(shape), int(key[0]), int(key[1]))
+    if k not in table:
+      table[k] = torch.from_numpy(
+          (noise_rng.random(shape, np.float32) - 0.5).astype(np.float32))
+    return table[k]
+
+  for raw in (cfg.dlhs, cfg.drhs):
+    raw.dg_quantizer.lhs.numerics.noise_fn = noise_fn
+    raw.dg_quantizer.rhs.numerics.noise_fn = noise_fn
+  from aqt_b200.v2 import stochastic_rounding as sr
+  cfg = config.set_context(cfg, key=sr.PRNGKey(5), train_step=None)
+  (out, dl, dr), (wo, wl, wr, _) = _run_both(cfg, lhs, rhs, g, dims)
+  assert len(table) == 4  # four distinct (shape, key) draws
+  _assert_same(out, wo, 'out')
+  _assert_same(dl, wl, 'dlhs')
+  _assert_same(dr, wr, 'drhs')
+
+
+def test_unsupported_configs_raise(monkeypatch):
+  fake_lib.install(monkeypatch)
+  x = torch.zeros(4, 16)
+  y = torch.zeros(16, 8)
+  dims = (((1,), (0,)), ((), ()))
+  cfg = config.fully_quantized(use_stochastic_rounding=False)
+  cfg.fwd.lhs.dequant_mode = aqt.DequantMode.THIS_INPUT
+  with pytest.raises(NotImplementedError):
+    cfg(x, y, dims)
+  cfg = config.fully_quantized(use_stochastic_rounding=False,
+                               drhs_local_aqt=aqt.LocalAqt(
+                                   contraction_axis_shard_count=2))
+  out, bp = cfg.vjp(x, y, dims)
+  with pytest.raises(NotImplementedError):
+    bp(torch.zeros(4, 8))
+  cfg = config.fully_quantized(use_stochastic_rounding=False)
+  with pytest.raises(AssertionError):
+    cfg(x, y, dims, precision='highest')
+  with pytest.raises(AssertionError):
+    cfg(x, y.to(torch.bfloat16), dims)

@@ -1,0 +1,77 @@
+"""AqtDotGeneral / AqtEinsum wrappers and the autograd bridge (host logic)."""
+
+import numpy as np
+import torch
+
+from aqt_b200.v2 import aqt_dot_general as aqt
+from aqt_b200.v2 import config
+from aqt_b200.v2 import utils
+from aqt_b200.v2.flax import aqt_flax
+from oracle import aqt_oracle as orc
+from tests import fake_lib
+from tests import util
+
+
+def test_einsum_lowering():
+  dims, perm, swap = aqt.einsum_to_dot_general('bthd,bshd->bhts', 4, 4)
+  assert dims == (((3,), (3,)), ((0, 2), (0, 2)))
+  assert perm is None and not swap
+  dims, perm, swap = aqt.einsum_to_dot_general('ab,bc->ac', 2, 2)
+  assert dims == (((1,), (0,)), ((), ())) and perm is None and not swap
+  # output wants rhs-free before lhs-free: operands are swapped instead of
+  # transposing the result
+  dims, perm, swap = aqt.einsum_to_dot_general('ab,bc->ca', 2, 2)
+  assert swap and perm is None and dims == (((0,), (1,)), ((), ()))
+
+
+def test_aqt_einsum_matches_oracle(monkeypatch):
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(0)
+  q = util.rand_normal(rng, (2, 8, 3, 16), 1.0, orc.bfloat16)
+  k = util.rand_normal(rng, (2, 6, 3, 16), 1.0, orc.bfloat16)
+  cfg = config.fully_quantized(use_stochastic_rounding=False)
+  got = aqt_flax.AqtEinsum(cfg)('bthd,bshd->bhts', util.to_torch(q),
+                                util.to_torch(k))
+  want, _ = orc.dg_fwd(cfg, q, k, (((3,), (3,)), ((0, 2), (0, 2))))
+  np.testing.assert_array_equal(util.to_numpy(got).astype(np.float32),
+                                want.astype(np.float32))
+
+
+def test_autograd_bridge(monkeypatch):
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(1)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = util.rand_normal(rng, (8, 32), 1.0, np.float32)
+  rhs = util.rand_normal(rng, (32, 16), 0.2, np.float32)
+  g = util.rand_normal(rng, (8, 16), 1.0, np.float32)
+  cfg = config.fully_quantized(use_stochastic_rounding=False)
+  tl = util.to_torch(lhs).requires_grad_()
+  tr = util.to_torch(rhs).requires_grad_()
+  out = aqt_flax.AqtDotGeneral(cfg)(tl, tr, dims)
+  out.backward(util.to_torch(g))
+  wo, wl, wr, _ = orc.dg_fwd_bwd(cfg, lhs, rhs, g, dims)
+  np.testing.assert_array_equal(util.to_numpy(out), wo)
+  np.testing.assert_array_equal(util.to_numpy(tl.grad), wl)
+  np.testing.assert_array_equal(util.to_numpy(tr.grad), wr)
+
+
+def test_convert_then_serve_is_bit_identical(monkeypatch):
+  # examples/flax_e2e_model_test.py:255-257: logits served from the frozen
+  # weights equal the training-mode logits exactly.
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(2)
+  dims = (((1,), (0,)), ((), ()))
+  x = util.to_torch(util.rand_normal(rng, (8, 32), 1.0, np.float32))
+  w = util.to_torch(util.rand_normal(rng, (32, 16), 0.2, np.float32))
+  cfg = config.fully_quantized(use_stochastic_rounding=False)
+  train = aqt_flax.AqtDotGeneral(cfg)(x, w, dims)
+  conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
+  conv(x, w, dims)
+  frozen = conv.rhs_qtensor
+  assert frozen is not None and frozen.qvalue.dtype == torch.int8
+  assert tuple(frozen.qvalue.shape) == (32, 16)
+  assert tuple(frozen.scale[0].shape) == (1, 16)
+  serve = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE)
+  serve.rhs_qtensor = frozen
+  got = serve(x, torch.zeros_like(w), dims)  # the float weights are unused
+  np.testing.assert_array_equal(util.to_numpy(got), util.to_numpy(train))

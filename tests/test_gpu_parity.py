@@ -1,0 +1,318 @@
+"""Parity of the sm_100a path against the CPU oracle, through the C ABI.
+
+int8: quantized values, scales, int32 accumulators and dequantized outputs are
+compared bit for bit. fp8: quantized values and scales bit for bit; outputs
+within max(1 bf16 ulp of the oracle value, 1e-5 * sum_k |a_k b_k| * scales)
+for bf16 outputs and 1e-5 * sum_k |a_k b_k| * scales for f32 outputs, because
+the tensor core's f32 accumulation order is not the oracle's (exact sum,
+rounded once).
+"""
+
+import numpy as np
+import pytest
+import torch
+
+from aqt_b200 import engine
+from aqt_b200.v2 import aqt_dot_general as aqt
+from aqt_b200.v2 import config
+from aqt_b200.v2 import stochastic_rounding as sr
+from aqt_b200.v2 import utils
+from aqt_b200.v2.flax import aqt_flax
+from oracle import aqt_oracle as orc
+from tests import util
+
+pytestmark = pytest.mark.gpu
+
+DEV = 'cuda'
+
+
+def _cuda(a):
+  return util.to_torch(a, DEV)
+
+
+def _sync():
+  torch.cuda.synchronize()
+  engine.check_status()
+
+
+def _exact(got, want, what):
+  g = util.to_numpy(got)
+  assert g.shape == want.shape, (what, g.shape, want.shape)
+  assert g.dtype == want.dtype, (what, g.dtype, want.dtype)
+  a, b = g.astype(np.float32), want.astype(np.float32)
+  bad = a != b
+  assert not bad.any(), (
+      f'{what}: {int(bad.sum())} of {bad.size} differ; first at '
+      f'{np.argwhere(bad)[0].tolist()}: got {a[bad][0]!r} want {b[bad][0]!r}')
+
+
+def _per_tensor(cfg):
+  for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
+    raw.dg_quantizer.lhs.calib_shared_axes = 'per_tensor'
+    raw.dg_quantizer.rhs.calib_shared_axes = 'per_tensor'
+  return cfg
+
+
+def _fp8_close(got, want, bound, what):
+  """|got-want| <= max(1 bf16 ulp of want [bf16 outputs], 1e-5*bound)."""
+  g = util.to_numpy(got)
+  assert g.shape == want.shape and g.dtype == want.dtype, what
+  a, b = g.astype(np.float64), want.astype(np.float64)
+  tol = 1e-5 * bound
+  if want.dtype == orc.bfloat16:
+    ulp = 2.0 ** (np.floor(np.log2(np.maximum(np.abs(b), 1e-38))) - 7)
+    tol = np.maximum(tol, ulp)
+  bad = np.abs(a - b) > tol
+  assert not bad.any(), (
+      f'{what}: {int(bad.sum())} of {bad.size} outside tolerance; worst '
+      f'{np.max(np.abs(a - b) / tol):.3g}x')
+
+
+CASES = [
+    ((((1,), (0,)), ((), ())), (12, 40), (40, 24)),
+    ((((1,), (0,)), ((), ())), (130, 200), (200, 270)),
+    ((((1,), (0,)), ((), ())), (256, 512), (512, 384)),
+    ((((3,), (3,)), ((0, 2), (0, 2))), (2, 9, 3, 16), (2, 7, 3, 16)),
+    ((((3,), (3,)), ((0, 2), (0, 2))), (2, 160, 3, 128), (2, 272, 3, 128)),
+    ((((2,), (1,)), ((0,), (0,))), (3, 5, 32), (3, 32, 6)),
+    ((((1,), (1,)), ((), ())), (8, 20), (10, 20)),
+    ((((0,), (0,)), ((), ())), (20, 8), (20, 10)),
+    ((((2,), (0,)), ((), ())), (4, 6, 32), (32, 12)),
+    ((((1,), (0,)), ((), ())), (1, 17), (17, 1)),
+]
+
+
+@pytest.mark.parametrize('dims,ls,rs', CASES)
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+@pytest.mark.parametrize('use_fwd_quant', [True, False])
+def test_int8_fwd_bwd_bit_exact(dims, ls, rs, np_dtype, use_fwd_quant):
+  rng = np.random.default_rng(0)
+  lhs = util.rand_normal(rng, ls, 1.0, np_dtype)
+  rhs = util.rand_normal(rng, rs, 0.2, np_dtype)
+  cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                               use_fwd_quant=use_fwd_quant,
+                               use_stochastic_rounding=False)
+  wo, res = orc.dg_fwd(cfg, lhs, rhs, dims)
+  g = util.rand_normal(rng, wo.shape, 1.0, np_dtype)
+  wl, wr = orc.dg_bwd(cfg, dims, res, g)
+  (out, (lq, rq)), vres = aqt.dg_core_vjp_fwd(_cuda(lhs), _cuda(rhs), None,
+                                              None, dims, cfg)
+  dl, dr, *_ = aqt.dg_core_vjp_bwd(dims, vres, (_cuda(g), None))
+  _sync()
+  _exact(lq.qvalue, res.lhs.qx.qvalue, 'q_lhs')
+  _exact(rq.qvalue, res.rhs.qx.qvalue, 'q_rhs')
+  _exact(lq.scale[0], res.lhs.qx.scale[0], 's_lhs')
+  _exact(rq.scale[0], res.rhs.qx.scale[0], 's_rhs')
+  _exact(out, wo, 'out')
+  _exact(dl, wl, 'dlhs')
+  _exact(dr, wr, 'drhs')
+
+
+@pytest.mark.parametrize('bits', [2, 4, 8])
+@pytest.mark.parametrize('shape', [(64, 256, 96), (130, 200, 270), (5, 33, 7)])
+def test_int_accumulators_bit_exact(bits, shape):
+  m, k, n = shape
+  rng = np.random.default_rng(bits)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = util.rand_normal(rng, (m, k), 1.0, np.float32)
+  rhs = util.rand_normal(rng, (k, n), 1.0, np.float32)
+  raw = aqt.dot_general_raw_make(bits, bits)
+  raw.dg_quantizer.lhs.numerics.dtype = utils.int8
+  raw.dg_quantizer.rhs.numerics.dtype = utils.int8
+  wo, _, wacc = orc.dg_raw(raw, lhs, rhs, None, None, dims, return_acc=True)
+  out, _, acc = engine.dg_raw(raw, _cuda(lhs), _cuda(rhs), None, None, dims,
+                              want_acc=True)
+  _sync()
+  _exact(acc.reshape(m, n), wacc, 'acc')
+  _exact(out, wo, 'out')
+
+
+def test_tensor_core_kernel_agrees_with_cuda_core_kernel():
+  rng = np.random.default_rng(5)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = _cuda(util.rand_normal(rng, (300, 1000), 1.0, np.float32))
+  rhs = _cuda(util.rand_normal(rng, (1000, 520), 1.0, np.float32))
+  raw = aqt.dot_general_raw_make(8, 8)
+  a = engine.dg_raw(raw, lhs, rhs, None, None, dims, want_acc=True)
+  engine.set_gemm_impl('simt')
+  try:
+    b = engine.dg_raw(raw, lhs, rhs, None, None, dims, want_acc=True)
+  finally:
+    engine.set_gemm_impl('tcgen05')
+  _sync()
+  assert torch.equal(a[2], b[2]) and torch.equal(a[0], b[0])
+
+
+@pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e4m3', 'e4m3'),
+                                     ('e5m2', 'e5m2')])
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+@pytest.mark.parametrize('per_tensor', [True, False])
+def test_fp8_fwd_bwd(fwd, bwd, np_dtype, per_tensor):
+  rng = np.random.default_rng(1)
+  dims = (((1,), (0,)), ((), ()))
+  m, k, n = 200, 520, 300
+  lhs = util.rand_normal(rng, (m, k), 1.0, np_dtype)
+  rhs = util.rand_normal(rng, (k, n), 0.05, np_dtype)
+  g = util.rand_normal(rng, (m, n), 1.0, np_dtype)
+  cfg = config.fully_quantized(fwd_bits=fwd, bwd_bits=bwd,
+                               use_stochastic_rounding=False)
+  if per_tensor:
+    _per_tensor(cfg)
+  wo, wl, wr, res = orc.dg_fwd_bwd(cfg, lhs, rhs, g, dims)
+  (out, (lq, rq)), vres = aqt.dg_core_vjp_fwd(_cuda(lhs), _cuda(rhs), None,
+                                              None, dims, cfg)
+  dl, dr, *_ = aqt.dg_core_vjp_bwd(dims, vres, (_cuda(g), None))
+  _sync()
+  _exact(lq.qvalue, res.lhs.qx.qvalue, 'q_lhs')
+  _exact(rq.qvalue, res.rhs.qx.qvalue, 'q_rhs')
+  _exact(lq.scale[0], res.lhs.qx.scale[0], 's_lhs')
+  _exact(rq.scale[0], res.rhs.qx.scale[0], 's_rhs')
+  f = lambda a: np.abs(np.asarray(a).astype(np.float64))
+  ql, qr = f(res.lhs.qx.qvalue), f(res.rhs.qx.qvalue)
+  sl, sr_ = f(res.lhs.qx.scale[0]), f(res.rhs.qx.scale[0])
+  _fp8_close(out, wo, (ql @ qr) * sl * sr_, 'out')
+  # gradients: bound from the magnitudes of the operands of each dot
+  gl = f(g) * sr_  # |g * s_rhs|
+  _fp8_close(dl, wl, 2.0 * (gl @ f(rhs / np.maximum(sr_, 1e-30)).T) + 1e-30,
+             'dlhs')
+  gr = f(g) * sl
+  _fp8_close(dr, wr, 2.0 * (f(lhs / np.maximum(sl, 1e-30)).T @ gr) + 1e-30,
+             'drhs')
+
+
+def test_stochastic_rounding_with_given_noise_bit_exact():
+  rng = np.random.default_rng(3)
+  dims = (((3,), (3,)), ((0, 2), (0, 2)))
+  q = util.rand_normal(rng, (2, 48, 3, 64), 1.0, orc.bfloat16)
+  k = util.rand_normal(rng, (2, 40, 3, 64), 1.0, orc.bfloat16)
+  g = util.rand_normal(rng, (2, 3, 48, 40), 1.0, orc.bfloat16)
+  cfg = config.fully_quantized(use_stochastic_rounding=True)
+  noise_rng = np.random.default_rng(1)
+  table = {}
+
+  def noise_fn(shape, key):
+    kk = (tuple(shape), int(key[0]), int(key[1]))
+    if kk not in table:
+      table[kk] = torch.from_numpy(
+          (noise_rng.random(shape, np.float32) - 0.5).astype(np.float32)).to(DEV)
+    return table[kk]
+
+  for raw in (cfg.dlhs, cfg.drhs):
+    raw.dg_quantizer.lhs.numerics.noise_fn = noise_fn
+    raw.dg_quantizer.rhs.numerics.noise_fn = noise_fn
+  cfg = config.set_context(cfg, key=sr.PRNGKey(1), train_step=None)
+  out, bp = cfg.vjp(_cuda(q), _cuda(k), dims)
+  dq, dk = bp(_cuda(g))
+  _sync()
+  wo, wq, wk, _ = orc.dg_fwd_bwd(cfg, q, k, g, dims)
+  assert len(table) == 4
+  _exact(out, wo, 'scores')
+  _exact(dq, wq, 'dq')
+  _exact(dk, wk, 'dk')
+
+
+def test_einsum_attention_scores():
+  rng = np.random.default_rng(4)
+  q = util.rand_normal(rng, (2, 256, 4, 128), 1.0, orc.bfloat16)
+  k = util.rand_normal(rng, (2, 320, 4, 128), 1.0, orc.bfloat16)
+  cfg = config.fully_quantized(use_stochastic_rounding=False)
+  got = aqt_flax.AqtEinsum(cfg)('bthd,bshd->bhts', _cuda(q), _cuda(k))
+  _sync()
+  want, _ = orc.dg_fwd(cfg, q, k, (((3,), (3,)), ((0, 2), (0, 2))))
+  _exact(got, want, 'scores')
+
+
+@pytest.mark.parametrize('m', [16, 64, 256])
+def test_serving_int4_weights_in_int8_container(m):
+  # activations int8 per token, weights 4-bit values stored as int8 with a
+  # per-output-channel scale, fed back as a frozen QTensor.
+  rng = np.random.default_rng(6)
+  k, n = 1024, 768
+  dims = (((1,), (0,)), ((), ()))
+  x = util.rand_normal(rng, (m, k), 1.0, orc.bfloat16)
+  w = util.rand_normal(rng, (k, n), 1.0 / 32, orc.bfloat16)
+  cfg = aqt.dot_general_make(lhs_bits=8, rhs_bits=4)
+  cfg.fwd.dg_quantizer.rhs.numerics.dtype = utils.int8
+  conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
+  train_out = conv(_cuda(x), _cuda(w), dims)
+  frozen = conv.rhs_qtensor
+  _sync()
+  want, res = orc.dg_fwd(cfg, x, w, dims)
+  _exact(frozen.qvalue, res.rhs.qx.qvalue, 'frozen weights')
+  assert int(frozen.qvalue.abs().max()) <= 7
+  _exact(train_out, want, 'train-mode out')
+  serve = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE)
+  serve.rhs_qtensor = frozen
+  got = serve(_cuda(x), torch.zeros_like(_cuda(w)), dims)
+  _sync()
+  _exact(got, want, 'served out')
+
+
+def test_piecewise_quantizer_api():
+  rng = np.random.default_rng(7)
+  x = util.rand_normal(rng, (96, 200), 3.0, np.float32)
+  from aqt_b200.v2 import aqt_quantizer
+  for axes in ([1], [0], [0, 1]):
+    qz = aqt_quantizer.quantizer_make(8)
+    if len(axes) == 2:
+      qz.calib_shared_axes = 'per_tensor'
+    qt, _ = qz.quant(_cuda(x), calibration_axes=axes)
+    _sync()
+    oq = orc.quantizer_calculate_qvalue(
+        qz, x, orc.quantizer_calibrate(qz, x, axes))
+    _exact(qt.scale[0], oq.scale[0], f'scale axes={axes}')
+    _exact(qt.qvalue, oq.qvalue, f'qvalue axes={axes}')
+    _exact(qt.dequant(), oq.dequant(), f'dequant axes={axes}')
+
+
+def test_config1_full_size_bit_exact():
+  # BASELINE config 1: f32 [1024,4096] x [4096,4096], int8 per-channel, RNE.
+  rng = np.random.default_rng(0)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = util.rand_normal(rng, (1024, 4096), 1.0, np.float32)
+  rhs = util.rand_normal(rng, (4096, 4096), 1.0 / 64, np.float32)
+  g = util.rand_normal(rng, (1024, 4096), 1.0, np.float32)
+  cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                               use_stochastic_rounding=False)
+  out, bp = cfg.vjp(_cuda(lhs), _cuda(rhs), dims)
+  dl, dr = bp(_cuda(g))
+  _sync()
+  wo, wl, wr, _ = orc.dg_fwd_bwd(cfg, lhs, rhs, g, dims)
+  _exact(out, wo, 'out')
+  _exact(dl, wl, 'dlhs')
+  _exact(dr, wr, 'drhs')
+
+
+@pytest.mark.parametrize('kind', ['int8', 'fp8'])
+def test_full_size_checksum_8192(kind):
+  # Size-independent property at BASELINE config 2's size: the sum of all
+  # accumulators equals dot(column sums of A, column sums of B).
+  torch.manual_seed(0)
+  n = 8192
+  dims = (((1,), (0,)), ((), ()))
+  lhs = torch.randn(n, n, device=DEV, dtype=torch.bfloat16)
+  rhs = torch.randn(n, n, device=DEV, dtype=torch.bfloat16) * (n ** -0.5)
+  raw = aqt.dot_general_raw_make(8, 8) if kind == 'int8' else (
+      aqt.dot_general_raw_make('e4m3', 'e4m3'))
+  raw.dg_quantizer.lhs.calib_shared_axes = 'per_tensor'
+  raw.dg_quantizer.rhs.calib_shared_axes = 'per_tensor'
+  out, res, acc = engine.dg_raw(raw, lhs, rhs, None, None, dims, want_acc=True)
+  _sync()
+  qa = res.lhs.mt.qx.qvalue.to(torch.float64)
+  qb = res.rhs.mt.qx.qvalue.to(torch.float64)
+  want = torch.dot(qa.sum(0), qb.sum(1))
+  got = acc.to(torch.float64).sum()
+  if kind == 'int8':
+    assert got.item() == want.item()
+  else:
+    ref = torch.dot(qa.abs().sum(0), qb.abs().sum(1)).item()
+    assert abs(got.item() - want.item()) <= 1e-6 * ref
+  # and a band of rows against an exact product of the same quantized operands
+  rows = slice(4000, 4032)
+  exact = qa[rows] @ qb
+  if kind == 'int8':
+    assert torch.equal(acc.reshape(n, n)[rows].to(torch.float64), exact)
+  else:
+    bound = qa[rows].abs() @ qb.abs()
+    assert ((acc.reshape(n, n)[rows].to(torch.float64) - exact).abs()
+            <= 1e-5 * bound).all()
