@@ -215,6 +215,440 @@ absmax_col_kernel(QParams P, int64_t row_blocks, int64_t col_chunks,
   }
 }
 
+
+// ===========================================================================
+// Fast paths: 16-byte vector loads, several independent loads in flight per
+// thread, branch-free inner loops. EPV = elements per 16-byte vector of the
+// INPUT: 4 (f32), 8 (bf16), 16 (int8 / fp8).
+
+__device__ __forceinline__ uint4 ldg16(const void* base, int64_t byte_off) {
+  return __ldg((const uint4*)((const char*)base + byte_off));
+}
+
+template <int EPV>
+__device__ __forceinline__ void unpack(const uint4& raw, int dt, float* v) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  if constexpr (EPV == 4) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] = __uint_as_float(w[i]);
+  } else if constexpr (EPV == 8) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { v[2 * i] = bf16lo(w[i]); v[2 * i + 1] = bf16hi(w[i]); }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t b = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+      v[i] = dt == AQTB200_S8 ? (float)(signed char)b : fp8_to_float((uint8_t)b, dt);
+    }
+  }
+}
+
+// Running |x| maximum kept in the input's own packed format: magnitudes of
+// non-negative floats (any width) order like unsigned integers.
+template <int EPV>
+__device__ __forceinline__ void packed_absmax(uint4& run, const uint4& raw, int dt) {
+  if constexpr (EPV == 4) {
+    run.x = max(run.x, raw.x & 0x7fffffffu); run.y = max(run.y, raw.y & 0x7fffffffu);
+    run.z = max(run.z, raw.z & 0x7fffffffu); run.w = max(run.w, raw.w & 0x7fffffffu);
+  } else if constexpr (EPV == 8) {
+    run.x = __vmaxu2(run.x, raw.x & 0x7fff7fffu); run.y = __vmaxu2(run.y, raw.y & 0x7fff7fffu);
+    run.z = __vmaxu2(run.z, raw.z & 0x7fff7fffu); run.w = __vmaxu2(run.w, raw.w & 0x7fff7fffu);
+  } else if (dt == AQTB200_S8) {
+    run.x = __vmaxu4(run.x, __vabsss4(raw.x)); run.y = __vmaxu4(run.y, __vabsss4(raw.y));
+    run.z = __vmaxu4(run.z, __vabsss4(raw.z)); run.w = __vmaxu4(run.w, __vabsss4(raw.w));
+  } else {
+    run.x = __vmaxu4(run.x, raw.x & 0x7f7f7f7fu); run.y = __vmaxu4(run.y, raw.y & 0x7f7f7f7fu);
+    run.z = __vmaxu4(run.z, raw.z & 0x7f7f7f7fu); run.w = __vmaxu4(run.w, raw.w & 0x7f7f7f7fu);
+  }
+}
+
+// The packed running maximum as EPV non-negative floats (one per lane slot).
+template <int EPV>
+__device__ __forceinline__ void packed_to_floats(const uint4& run, int dt, float* v) {
+  if constexpr (EPV == 16) {
+    const uint32_t w[4] = {run.x, run.y, run.z, run.w};
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t b = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+      v[i] = dt == AQTB200_S8 ? (float)b : fp8_to_float((uint8_t)b, dt);
+    }
+  } else {
+    unpack<EPV>(run, dt, v);
+  }
+}
+
+template <int EPV>
+__device__ __forceinline__ float packed_hmax(const uint4& run, int dt) {
+  float v[EPV];
+  packed_to_floats<EPV>(run, dt, v);
+  float m = 0.f;
+#pragma unroll
+  for (int i = 0; i < EPV; ++i) m = fmaxf(m, v[i]);
+  return m;
+}
+
+// |round_T(x * round_T(p))| for x >= 0 is monotone in x, so a prescale that is
+// constant over the reduced range can be applied to the maximum afterwards.
+__device__ __forceinline__ float apply_pre_abs(float amax, float pre, int t_dtype) {
+  return fabsf(apply_pre(amax, pre, t_dtype));
+}
+
+// 4 quantized values -> one little-endian word.
+__device__ __forceinline__ uint32_t quant4(const float* v, const float* sinv, const float* nz,
+                                           bool has_noise, const QParams& P) {
+  float y[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    y[j] = round_to(__fmul_rn(v[j], sinv[j]), P.y_dtype);
+    if (has_noise) y[j] = round_to(__fadd_rn(y[j], nz[j]), P.y_dtype);
+  }
+  if (P.kind == AQTB200_NUM_INT) {
+    uint32_t w = 0;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float c = fminf(fmaxf(y[j], -P.clip_bound), P.clip_bound);
+      w |= ((uint32_t)__float2int_rn(c) & 0xffu) << (8 * j);
+    }
+    return w;
+  }
+  // fp8: the saturating convert clamps to +-max finite, which is the clip bound.
+  const __nv_fp8_interpretation_t k = P.qdtype == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(y[0], y[1]), __NV_SATFINITE, k);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(y[2], y[3]), __NV_SATFINITE, k);
+  return lo | (hi << 16);
+}
+
+constexpr int kFastRowChunk = 8192;  // elements of one (row, chunk) work unit
+
+// absmax, contraction contiguous, one warp per (batch-row, chunk).
+// PRE: 0 none, 1 constant over the row (applied to the maximum), 2 per column.
+template <int EPV, int PRE>
+__global__ void __launch_bounds__(256)
+absmax_row_fast(QParams P, int64_t chunks_per_row, int64_t total_units) {
+  constexpr int ES = 16 / EPV;
+  constexpr int U = 4;
+  __shared__ float red[32];
+  const int lane = threadIdx.x & 31;
+  const int64_t warp_g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const DView& x = P.x;
+  float tmax = 0.f;
+  for (int64_t u = warp_g; u < total_units; u += nwarps) {
+    const int64_t brow = u / chunks_per_row, chunk = u % chunks_per_row;
+    int64_t i0, i1, r;
+    decode_brow(x, brow, i0, i1, r);
+    const int64_t c0 = chunk * kFastRowChunk;
+    const int64_t nvec = (min(x.cols, c0 + (int64_t)kFastRowChunk) - c0) / EPV;
+    const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + r * x.sr + c0) * ES;
+    const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+    uint4 run = make_uint4(0u, 0u, 0u, 0u);
+    float fm = 0.f;
+    for (int64_t i = lane; i < nvec; i += 32 * U) {
+      uint4 raw[U];
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const int64_t idx = i + 32 * k;
+        raw[k] = idx < nvec ? ldg16(xp, idx * 16) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        if constexpr (PRE == 2) {
+          const int64_t idx = i + 32 * k;
+          if (idx < nvec) {
+            float v[EPV], p[EPV];
+            unpack<EPV>(raw[k], x.dtype, v);
+            loadN<EPV>(P.pre.ptr, P.pre.dtype, pbase + c0 + idx * EPV, p);
+#pragma unroll
+            for (int j = 0; j < EPV; ++j) fm = fmaxf(fm, fabsf(apply_pre(v[j], p[j], P.t_dtype)));
+          }
+        } else {
+          packed_absmax<EPV>(run, raw[k], x.dtype);
+        }
+      }
+    }
+    float m = PRE == 2 ? fm : packed_hmax<EPV>(run, x.dtype);
+    if constexpr (PRE == 1)
+      m = apply_pre_abs(m, load1(P.pre.ptr, P.pre.dtype, pbase), P.t_dtype);
+    if (P.per_tensor) {
+      tmax = fmaxf(tmax, m);
+    } else {
+      m = warp_max(m);
+      if (lane == 0 && m > 0.f) atomic_max_nonneg(P.amax + brow, m);
+    }
+  }
+  if (P.per_tensor) {
+    tmax = block_max(tmax, red);
+    if (threadIdx.x == 0 && tmax > 0.f) atomic_max_nonneg(P.amax, tmax);
+  }
+}
+
+// absmax, kept index contiguous. Block (32 x 8): thread (tx, ty) owns the EPV
+// kept rows of one 16-byte vector and strides over a chunk of the contraction
+// index. PRE: 0 none, 1 constant over the contraction index, 2 varying with it.
+constexpr int kFastColChunk = 256;
+
+template <int EPV, int PRE>
+__global__ void __launch_bounds__(256)
+absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total_units) {
+  constexpr int ES = 16 / EPV;
+  constexpr int U = 4;
+  __shared__ float red[32];
+  const DView& x = P.x;
+  const int tx = threadIdx.x, ty = threadIdx.y;
+  float tmax = 0.f;
+  for (int64_t u = blockIdx.x; u < total_units; u += gridDim.x) {
+    const int64_t cc = u % col_chunks;
+    int64_t t = u / col_chunks;
+    const int64_t rb = t % row_blocks;
+    const int64_t b = t / row_blocks;
+    const int64_t i1 = b % x.b1, i0 = b / x.b1;
+    const int64_t r0 = (rb * 32 + tx) * EPV;
+    const int64_t cbeg = cc * kFastColChunk;
+    const int64_t cend = min(x.cols, cbeg + (int64_t)kFastColChunk);
+    const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + r0) * ES;
+    const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+    uint4 run = make_uint4(0u, 0u, 0u, 0u);
+    float fm[PRE == 2 ? EPV : 1];
+#pragma unroll
+    for (int j = 0; j < (PRE == 2 ? EPV : 1); ++j) fm[j] = 0.f;
+    if (r0 < x.rows) {
+      for (int64_t c = cbeg + ty; c < cend; c += 8 * U) {
+        uint4 raw[U];
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+          const int64_t ck = c + 8 * k;
+          raw[k] = ck < cend ? ldg16(xp, ck * x.sc * ES) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+        for (int k = 0; k < U; ++k) {
+          if constexpr (PRE == 2) {
+            const int64_t ck = c + 8 * k;
+            if (ck < cend) {
+              float v[EPV];
+              unpack<EPV>(raw[k], x.dtype, v);
+              const float p = load1(P.pre.ptr, P.pre.dtype, pbase + ck * P.pre.sc);
+#pragma unroll
+              for (int j = 0; j < EPV; ++j) fm[j] = fmaxf(fm[j], fabsf(apply_pre(v[j], p, P.t_dtype)));
+            }
+          } else {
+            packed_absmax<EPV>(run, raw[k], x.dtype);
+          }
+        }
+      }
+    }
+    float m[EPV];
+    if constexpr (PRE == 2) {
+#pragma unroll
+      for (int j = 0; j < EPV; ++j) m[j] = fm[j];
+    } else {
+      packed_to_floats<EPV>(run, x.dtype, m);
+      if constexpr (PRE == 1) {
+        const float p = load1(P.pre.ptr, P.pre.dtype, pbase);
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) m[j] = apply_pre_abs(m[j], p, P.t_dtype);
+      }
+    }
+    if (P.per_tensor) {
+#pragma unroll
+      for (int j = 0; j < EPV; ++j) tmax = fmaxf(tmax, m[j]);
+    } else if (r0 < x.rows) {
+      const int64_t sbase = (i0 * x.b1 + i1) * x.rows;
+#pragma unroll
+      for (int j = 0; j < EPV; ++j)
+        if (m[j] > 0.f) atomic_max_nonneg(P.amax + sbase + r0 + j, m[j]);
+    }
+  }
+  if (P.per_tensor) {
+    float v = warp_max(tmax);
+    if (tx == 0) red[ty] = v;
+    __syncthreads();
+    if (ty == 0) {
+      v = tx < 8 ? red[tx] : 0.f;
+      v = warp_max(v);
+      if (tx == 0 && v > 0.f) atomic_max_nonneg(P.amax, v);
+    }
+  }
+}
+
+// quantize, contraction contiguous: one thread per 16 output bytes, two units
+// per loop trip so 32-64 bytes of input are in flight per thread. Units are
+// walked from the END of the tensor: the calibration pass that just ran read
+// it front to back, so its tail is what the L2 still holds.
+template <int EPV, int PRE>
+__global__ void __launch_bounds__(256)
+quant_row_fast(QParams P, int64_t units_per_row, int64_t total_units) {
+  constexpr int ES = 16 / EPV;
+  constexpr int NV = 16 / EPV;  // input vectors per 16 outputs
+  constexpr int UU = 2;
+  const DView& x = P.x;
+  const bool has_noise = P.noise.ptr != nullptr;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t u0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u0 < total_units;
+       u0 += nthreads * UU) {
+    uint4 raw[UU][NV];
+    int64_t brow[UU], col[UU];
+    bool ok[UU];
+#pragma unroll
+    for (int k = 0; k < UU; ++k) {
+      const int64_t uf = u0 + k * nthreads;
+      ok[k] = uf < total_units;
+      const int64_t u = total_units - 1 - (ok[k] ? uf : u0);
+      brow[k] = u / units_per_row;
+      col[k] = (u % units_per_row) * 16;
+      int64_t i0, i1, r;
+      decode_brow(x, brow[k], i0, i1, r);
+      const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + r * x.sr + col[k]) * ES;
+#pragma unroll
+      for (int n = 0; n < NV; ++n) raw[k][n] = ldg16(xp, n * 16);
+    }
+#pragma unroll
+    for (int k = 0; k < UU; ++k) {
+      if (!ok[k]) continue;
+      int64_t i0, i1, r;
+      decode_brow(x, brow[k], i0, i1, r);
+      const float s = P.sinv[P.per_tensor ? 0 : brow[k]];
+      const float sinv4[4] = {s, s, s, s};
+      const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+      const int64_t nbase = i0 * P.noise.sb0 + i1 * P.noise.sb1 + r * P.noise.sr;
+      float pconst = 0.f;
+      if constexpr (PRE == 1) pconst = load1(P.pre.ptr, P.pre.dtype, pbase);
+      uint32_t outw[4];
+#pragma unroll
+      for (int n = 0; n < NV; ++n) {
+        float v[EPV];
+        unpack<EPV>(raw[k][n], x.dtype, v);
+        const int64_t c = col[k] + n * EPV;
+        if constexpr (PRE == 1) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) v[j] = apply_pre(v[j], pconst, P.t_dtype);
+        } else if constexpr (PRE == 2) {
+          float p[EPV];
+          if (P.pre_vec) {
+            loadN<EPV>(P.pre.ptr, P.pre.dtype, pbase + c, p);
+          } else {
+#pragma unroll
+            for (int j = 0; j < EPV; ++j) p[j] = load1(P.pre.ptr, P.pre.dtype, pbase + (c + j) * P.pre.sc);
+          }
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) v[j] = apply_pre(v[j], p[j], P.t_dtype);
+        }
+#pragma unroll
+        for (int g = 0; g < EPV / 4; ++g) {
+          float nz[4] = {0.f, 0.f, 0.f, 0.f};
+          if (has_noise) {
+            if (P.noise_vec) {
+              loadN<4>(P.noise.ptr, AQTB200_F32, nbase + c + 4 * g, nz);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                nz[j] = load1(P.noise.ptr, AQTB200_F32, nbase + (c + 4 * g + j) * P.noise.sc);
+            }
+          }
+          outw[(n * EPV) / 4 + g] = quant4(v + 4 * g, sinv4, nz, has_noise, P);
+        }
+      }
+      *(uint4*)(P.q + brow[k] * P.ldq + col[k]) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+    }
+  }
+}
+
+// quantize + transpose, kept index contiguous in the input.
+// Tile: (16 * EPV) kept rows x 128 contraction indices, 256 threads. Thread
+// (tx, ty) = (tid % 16, tid / 16) loads, for i in {0,1} and e in 0..3, the
+// 16-byte vector of rows tx*EPV.. at contraction index i*64 + 4*ty + e, packs
+// the four e's of each row into one word and parks it in shared memory with a
+// per-row-group rotation (kills bank conflicts); the tile then leaves as
+// 128-byte row segments.
+template <int EPV, int PRE>
+__global__ void __launch_bounds__(256)
+quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_units) {
+  constexpr int ES = 16 / EPV;
+  constexpr int TR = 16 * EPV;
+  __shared__ __align__(16) uint32_t tile[TR][32];
+  const DView& x = P.x;
+  const bool has_noise = P.noise.ptr != nullptr;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int64_t uf = blockIdx.x; uf < total_units; uf += gridDim.x) {
+    const int64_t u = total_units - 1 - uf;  // back to front, see quant_row_fast
+    const int64_t ct = u % col_tiles;
+    int64_t t = u / col_tiles;
+    const int64_t rt = t % row_tiles;
+    const int64_t b = t / row_tiles;
+    const int64_t i1 = b % x.b1, i0 = b / x.b1;
+    const int64_t sbase = (i0 * x.b1 + i1) * x.rows;
+    const int64_t r0 = rt * TR + tx * EPV;
+    const bool row_ok = r0 < x.rows;  // rows % EPV == 0: a vector is all in or all out
+    const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + (row_ok ? r0 : 0)) * ES;
+    const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+    const int64_t nbase = i0 * P.noise.sb0 + i1 * P.noise.sb1;
+    uint4 raw[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+        raw[i][e] = (row_ok && c < x.cols) ? ldg16(xp, c * x.sc * ES)
+                                           : make_uint4(0u, 0u, 0u, 0u);
+      }
+    float sinv[EPV];
+#pragma unroll
+    for (int j = 0; j < EPV; ++j)
+      sinv[j] = P.per_tensor ? P.sinv[0] : (row_ok ? P.sinv[sbase + r0 + j] : 1.f);
+    float pconst = 0.f;
+    if constexpr (PRE == 1) pconst = load1(P.pre.ptr, P.pre.dtype, pbase);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t word[EPV];
+#pragma unroll
+      for (int j = 0; j < EPV; ++j) word[j] = 0u;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+        const bool in = row_ok && c < x.cols;
+        float v[EPV];
+        unpack<EPV>(raw[i][e], x.dtype, v);
+        float p = pconst;
+        if constexpr (PRE == 2) p = in ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
+#pragma unroll
+        for (int g = 0; g < EPV / 4; ++g) {
+          float w4[4], nz[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            w4[j] = PRE ? apply_pre(v[4 * g + j], p, P.t_dtype) : v[4 * g + j];
+          if (has_noise && in) {
+            if (P.noise_vec) {
+              loadN<4>(P.noise.ptr, AQTB200_F32, nbase + c * P.noise.sc + r0 + 4 * g, nz);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                nz[j] = load1(P.noise.ptr, AQTB200_F32,
+                              nbase + c * P.noise.sc + (r0 + 4 * g + j) * P.noise.sr);
+            }
+          }
+          const uint32_t q4 = in ? quant4(w4, sinv + 4 * g, nz, has_noise, P) : 0u;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) word[4 * g + j] |= ((q4 >> (8 * j)) & 0xffu) << (8 * e);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < EPV; ++j) tile[tx * EPV + j][(i * 16 + ty + 4 * tx) & 31] = word[j];
+    }
+    __syncthreads();
+#pragma unroll
+    for (int s = 0; s < TR / 32; ++s) {
+      const int id = tid + 256 * s;
+      const int row = id >> 3, seg = id & 7;
+      const int64_t gr = rt * TR + row;
+      const int64_t gc = ct * 128 + seg * 16;
+      if (gr < x.rows && gc < P.ldq) {
+        const uint4 o = *(const uint4*)&tile[row][(seg * 4 + 4 * (row / EPV)) & 31];
+        *(uint4*)(P.q + (sbase + gr) * P.ldq + gc) = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // ---------------------------------------------------------------------------
 // amax -> scale and rounded reciprocal (calibration.py:149-157,
 // aqt_tensor.py:151-153). All arithmetic in T, stored as S.
@@ -500,9 +934,6 @@ static int validate(const aqtb200_view* x, const aqtb200_view* pre,
     AQT_REQUIRE(spec->clip_bound > 0.f, AQTB200_EINVAL, "clip_bound must be positive");
   }
   AQT_REQUIRE(spec->quant_bound > 0.f, AQTB200_EINVAL, "quant_bound must be positive");
-  AQT_REQUIRE(x->col_stride == 1 || x->row_stride == 1 || x->rows <= 1 || x->cols <= 1,
-              AQTB200_EUNSUPPORTED,
-              "view must have the contraction index or the kept index contiguous");
   if (pre && pre->ptr)
     AQT_REQUIRE(is_float_dt(pre->dtype), AQTB200_EINVAL, "prescale must be f32 or bf16");
   if (noise && noise->ptr) {
@@ -531,6 +962,12 @@ static bool col_vec_ok(const DView& v, int64_t rows) {
   (void)es;
   return v.sr == 1 && mult(rows, 4) && aligned(v.ptr, 16) && mult(v.sc, g) &&
          mult(v.sb0, g) && mult(v.sb1, g);
+}
+
+// 16-byte vectors of `epv` consecutive kept rows at every contraction index?
+static bool col_fast_ok(const DView& v, int64_t rows, int epv) {
+  return v.sr == 1 && mult(rows, epv) && aligned(v.ptr, 16) && mult(v.sc, epv) &&
+         mult(v.sb0, epv) && mult(v.sb1, epv);
 }
 
 static int grid_for(int64_t units, int per_sm) {
@@ -572,24 +1009,56 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
   P.sinv = (float*)((char*)workspace + align256((size_t)ns * 4));
   P.q = (uint8_t*)q_out;
   P.ldq = aqtb200_round_up(xv->cols, 16);
-  // degenerate extents: pick the mode whose stride assumption holds
-  const bool row_mode = P.x.sc == 1 || P.x.cols <= 1 ? (P.x.sc == 1 || P.x.sr != 1) : false;
+  // Row mode reads along the contraction index; its scalar kernel takes any
+  // strides, so it also serves degenerate and doubly-strided views.
+  const bool row_mode = !(P.x.sr == 1 && P.x.sc != 1);
   P.pre_vec = P.pre.ptr && row_vec_ok({P.pre.ptr, P.pre.dtype, 1, 1, 1, 1,
                                        P.pre.sb0, P.pre.sb1, 16, P.pre.sc}, xv->cols);
   if (P.noise.ptr)
     P.noise_vec = row_mode ? row_vec_ok(P.noise, xv->cols) : col_vec_ok(P.noise, xv->rows);
+  const int epv = 16 / dtype_size(P.x.dtype);
+  // prescale class: 0 none, 1 constant along the contraction index, 2 varying
+  const int pre_kind = P.pre.ptr == nullptr ? 0 : (P.pre.sc == 0 || xv->cols <= 1 ? 1 : 2);
+  const bool fast_row = row_mode && row_vec_ok(P.x, xv->cols);
+  const bool fast_col = !row_mode && col_fast_ok(P.x, xv->rows, epv);
+
+#define AQT_DISPATCH_EPV_PRE(KERNEL, GRID, BLOCK, ...)                                   \
+  do {                                                                                   \
+    if (epv == 4) {                                                                      \
+      if (pre_kind == 0) KERNEL<4, 0><<<GRID, BLOCK, 0, st>>>(__VA_ARGS__);              \
+      else if (pre_kind == 1) KERNEL<4, 1><<<GRID, BLOCK, 0, st>>>(__VA_ARGS__);         \
+      else KERNEL<4, 2><<<GRID, BLOCK, 0, st>>>(__VA_ARGS__);                            \
+    } else if (epv == 8) {                                                               \
+      if (pre_kind == 0) KERNEL<8, 0><<<GRID, BLOCK, 0, st>>>(__VA_ARGS__);              \
+      else if (pre_kind == 1) KERNEL<8, 1><<<GRID, BLOCK, 0, st>>>(__VA_ARGS__);         \
+      else KERNEL<8, 2><<<GRID, BLOCK, 0, st>>>(__VA_ARGS__);                            \
+    } else {                                                                             \
+      if (pre_kind == 0) KERNEL<16, 0><<<GRID, BLOCK, 0, st>>>(__VA_ARGS__);             \
+      else if (pre_kind == 1) KERNEL<16, 1><<<GRID, BLOCK, 0, st>>>(__VA_ARGS__);        \
+      else KERNEL<16, 2><<<GRID, BLOCK, 0, st>>>(__VA_ARGS__);                           \
+    }                                                                                    \
+  } while (0)
 
   if (scale_in == nullptr) {
     AQT_CUDA_OK(cudaMemsetAsync(P.amax, 0, (size_t)ns * 4, st));
     if (total > 0) {
-      if (row_mode) {
+      if (fast_row && (pre_kind != 2 || P.pre_vec)) {
+        int64_t chunks = (xv->cols + kFastRowChunk - 1) / kFastRowChunk;
+        int64_t units = nbrow * chunks;
+        int grid = grid_for((units + 7) / 8, 8);
+        AQT_DISPATCH_EPV_PRE(absmax_row_fast, grid, 256, P, chunks, units);
+      } else if (row_mode) {
         int64_t chunks = (xv->cols + kRowChunk - 1) / kRowChunk;
         int64_t units = nbrow * chunks;
         int grid = grid_for((units + 7) / 8, 8);
-        if (row_vec_ok(P.x, xv->cols))
-          absmax_row_kernel<true><<<grid, 256, 0, st>>>(P, chunks, units);
-        else
-          absmax_row_kernel<false><<<grid, 256, 0, st>>>(P, chunks, units);
+        absmax_row_kernel<false><<<grid, 256, 0, st>>>(P, chunks, units);
+      } else if (fast_col) {
+        int64_t rbs = (xv->rows + 32 * epv - 1) / (32 * epv);
+        int64_t ccs = (xv->cols + kFastColChunk - 1) / kFastColChunk;
+        int64_t units = xv->b0 * xv->b1 * rbs * ccs;
+        int grid = grid_for(units, 8);
+        dim3 block(32, 8);
+        AQT_DISPATCH_EPV_PRE(absmax_col_fast, grid, block, P, rbs, ccs, units);
       } else {
         bool vec = col_vec_ok(P.x, xv->rows);
         int64_t rows_per_block = 32 * (vec ? 4 : 1);
@@ -615,14 +1084,22 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   if (!want_q || nbrow == 0) return 0;
 
-  if (row_mode) {
+  if (fast_row) {
+    int64_t upr = P.ldq / 16;
+    int64_t units = nbrow * upr;
+    int grid = grid_for((units + 511) / 512, 8);
+    AQT_DISPATCH_EPV_PRE(quant_row_fast, grid, 256, P, upr, units);
+  } else if (row_mode) {
     int64_t upr = P.ldq / 16;
     int64_t units = nbrow * upr;
     int grid = grid_for((units + 255) / 256, 8);
-    if (row_vec_ok(P.x, xv->cols))
-      quant_row_kernel<true><<<grid, 256, 0, st>>>(P, upr, units);
-    else
-      quant_row_kernel<false><<<grid, 256, 0, st>>>(P, upr, units);
+    quant_row_kernel<false><<<grid, 256, 0, st>>>(P, upr, units);
+  } else if (fast_col) {
+    int64_t rts = (xv->rows + 16 * epv - 1) / (16 * epv);
+    int64_t cts = (P.ldq + 127) / 128;
+    int64_t units = xv->b0 * xv->b1 * rts * cts;
+    int grid = grid_for(units, 4);
+    AQT_DISPATCH_EPV_PRE(quant_col_fast, grid, 256, P, rts, cts, units);
   } else {
     int64_t rts = (xv->rows + 63) / 64;
     int64_t cts = (P.ldq + 127) / 128;
@@ -633,6 +1110,7 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
     else
       quant_col_kernel<false><<<grid, 256, 0, st>>>(P, rts, cts, units);
   }
+#undef AQT_DISPATCH_EPV_PRE
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   return 0;
 }

@@ -1,0 +1,408 @@
+"""Benchmark of the quantized dot_general hot path (forward + dlhs + drhs).
+
+Workload (BASELINE.json configs[1]): fp8 dot_general, 8192 x 8192 x 8192, bf16
+inputs lhs ~ N(0,1), rhs ~ N(0,1/8192), cotangent ~ N(0,1); forward operands
+e4m3, backward operands e5m2, per-tensor AbsMax scales, f32 accumulation, bf16
+outputs. One "step" = forward + both gradient dot_generals, calibration and
+quantization kernels included.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+                  [--scaling weak|strong] [--size S] [--kind fp8|int8]
+
+Prints ONE JSON line (rank 0). `value` is whole-job TOPS with inputs resident
+in HBM; `e2e` is the same metric through the public API with pinned host
+buffers, host->device and device->host copies inside the timed region.
+`--impl reference` times the CPU restatement of the reference (the reference
+itself needs jax, which is not installed here) on a bounded sample.
+"""
+
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+  sys.path.insert(0, ROOT)
+
+METRIC = 'quantized_dot_general_fwd_bwd_tops'
+UNIT = 'TOPS'
+
+
+def parse_args():
+  p = argparse.ArgumentParser()
+  p.add_argument('--gpus', type=int, default=1)
+  p.add_argument('--steps', type=int, default=20)
+  p.add_argument('--warmup', type=int, default=5)
+  p.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+  p.add_argument('--scaling', default='weak', choices=['weak', 'strong'])
+  p.add_argument('--size', type=int, default=8192)
+  p.add_argument('--kind', default='fp8', choices=['fp8', 'int8'])
+  p.add_argument('--cpu-sample-rows', type=int, default=256)
+  p.add_argument('--no-cpu-baseline', action='store_true')
+  p.add_argument('--no-e2e', action='store_true')
+  return p.parse_args()
+
+
+def make_cfg(kind):
+  from aqt_b200.v2 import config
+  if kind == 'fp8':
+    cfg = config.fully_quantized(fwd_bits='e4m3', bwd_bits='e5m2',
+                                 use_stochastic_rounding=False)
+  else:
+    cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                                 use_stochastic_rounding=False)
+  for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
+    raw.dg_quantizer.lhs.calib_shared_axes = 'per_tensor'
+    raw.dg_quantizer.rhs.calib_shared_axes = 'per_tensor'
+  return cfg
+
+
+DIMS = (((1,), (0,)), ((), ()))
+
+
+def workload_name(args):
+  return (f'{args.kind} dot_general {args.size}x{args.size}x{args.size} '
+          'fwd+dlhs+drhs, bf16 in/out, per-tensor absmax scales')
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle on a bounded sample
+
+
+def cpu_sample(args, rows):
+  """Times the numpy restatement on `rows` rows of lhs/cotangent (rhs full)."""
+  import numpy as np
+  from oracle import aqt_oracle as orc
+  n = args.size
+  rng = np.random.default_rng(0)
+  f = lambda shape, std: (rng.standard_normal(shape, np.float32) * std).astype(
+      orc.bfloat16)
+  lhs, rhs, g = f((rows, n), 1.0), f((n, n), n ** -0.5), f((rows, n), 1.0)
+  cfg = make_cfg(args.kind)
+  t0 = time.perf_counter()
+  orc.dg_fwd_bwd(cfg, lhs, rhs, g, DIMS, fast_float=True)
+  dt = time.perf_counter() - t0
+  ops = 3 * 2 * rows * n * n
+  return ops / dt / 1e12, dt
+
+
+def blas_threads():
+  try:
+    import threadpoolctl
+    infos = threadpoolctl.threadpool_info()
+    return max([i.get('num_threads', 1) for i in infos] + [1])
+  except Exception:  # pylint: disable=broad-except
+    return os.cpu_count() or 1
+
+
+def run_reference_arm(args):
+  rank = int(os.environ.get('RANK', '0'))
+  if rank != 0:
+    return
+  rows = args.cpu_sample_rows
+  for _ in range(min(args.warmup, 1)):
+    cpu_sample(args, rows)
+  steps = max(1, min(args.steps, 3))
+  vals, times = [], []
+  for _ in range(steps):
+    v, dt = cpu_sample(args, rows)
+    vals.append(v)
+    times.append(dt)
+  value = sum(vals) / len(vals)
+  sample = (f'{rows} of {args.size} lhs/cotangent rows against the full '
+            f'{args.size}x{args.size} rhs, numpy+ml_dtypes restatement '
+            '(jax is not installed, so the reference itself cannot run)')
+  line = {
+      'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': UNIT,
+      'n_gpus': args.gpus, 'steps': steps, 'warmup': min(args.warmup, 1),
+      'ms_per_step': 1e3 * sum(times) / len(times), 'higher_is_better': True,
+      'scaling': args.scaling, 'vs_baseline': None, 'dtype': args.kind,
+      'data': 'synthetic',
+      'config': {'workload': workload_name(args), 'sample': sample},
+      'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': blas_threads(),
+                       'kind': 'port', 'sample': sample},
+      'e2e': {'value': value, 'unit': UNIT, 'h2d_bytes_per_step': 0,
+              'd2h_bytes_per_step': 0},
+      'gpu_launches': 0,
+  }
+  print(json.dumps(line), flush=True)
+
+
+# ---------------------------------------------------------------------------
+# clocks
+
+
+class ClockSampler:
+  """Samples SM clock and throttle reasons DURING the timed region.
+
+  A separate `nvidia-smi -lms` process does the polling (read-only queries):
+  polling NVML from a thread of this process stalls kernel launches for
+  milliseconds per query and would distort the number being measured.
+  """
+
+  QUERY = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,'
+           'clocks_event_reasons.hw_thermal_slowdown,'
+           'clocks_event_reasons.sw_thermal_slowdown,'
+           'clocks_event_reasons.sw_power_cap')
+  NAMES = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown',
+           'sw_power_cap')
+
+  def __init__(self, index, period_ms=50):
+    self.index, self.period_ms = index, period_ms
+    self.proc = None
+
+  def start(self):
+    import subprocess
+    try:
+      self.proc = subprocess.Popen(
+          ['nvidia-smi', '-i', str(self.index), f'--query-gpu={self.QUERY}',
+           '--format=csv,noheader,nounits', '-lms', str(self.period_ms)],
+          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+      # wait for the first line so that polling is under way before timing
+      self.first = self.proc.stdout.readline()
+    except Exception:  # pylint: disable=broad-except
+      self.proc = None
+
+  def stop(self):
+    if self.proc is None:
+      return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
+    time.sleep(self.period_ms / 1e3)
+    self.proc.terminate()
+    try:
+      rest, _ = self.proc.communicate(timeout=5)
+    except Exception:  # pylint: disable=broad-except
+      self.proc.kill()
+      rest = ''
+    # the line read before the timed region started is not a sample under load
+    clocks, reasons, mx = [], set(), None
+    for line in rest.splitlines():
+      parts = [x.strip() for x in line.split(',')]
+      if len(parts) < 6:
+        continue
+      try:
+        clocks.append(int(parts[0]))
+        mx = int(parts[1])
+      except ValueError:
+        continue
+      for name, flag in zip(self.NAMES, parts[2:6]):
+        if flag.lower().startswith('active'):
+          reasons.add(name)
+    clocks.sort()
+    return {'sm_mhz': clocks[len(clocks) // 2] if clocks else None,
+            'sm_max_mhz': mx, 'reasons': sorted(reasons),
+            'samples': len(clocks)}
+
+
+# ---------------------------------------------------------------------------
+# our arm
+
+
+def run_ours(args):
+  import torch
+  import torch.distributed as dist
+  from aqt_b200 import _lib
+  from aqt_b200 import engine
+
+  world = int(os.environ.get('WORLD_SIZE', '1'))
+  rank = int(os.environ.get('RANK', '0'))
+  local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+  assert world == args.gpus or world == 1 and args.gpus == 1, (
+      f'--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun')
+  torch.cuda.set_device(local_rank)
+  dev = torch.device('cuda', local_rank)
+  if world > 1:
+    dist.init_process_group('nccl', device_id=dev)
+  lib = _lib.load()
+
+  n = args.size
+  m_local = n if args.scaling == 'weak' else n // world
+  m_global = m_local * world
+  gen = torch.Generator(device=dev)
+  gen.manual_seed(1234 + rank)
+  lhs = torch.randn(m_local, n, device=dev, dtype=torch.float32,
+                    generator=gen).to(torch.bfloat16)
+  g = torch.randn(m_local, n, device=dev, dtype=torch.float32,
+                  generator=gen).to(torch.bfloat16)
+  gen.manual_seed(99)  # the weights are replicated
+  rhs = (torch.randn(n, n, device=dev, dtype=torch.float32, generator=gen)
+         * n ** -0.5).to(torch.bfloat16)
+  cfg = make_cfg(args.kind)
+  op = None
+  if world > 1:
+    from aqt_b200 import distributed as aqt_dist
+    op = aqt_dist.ShardedDotGeneral(cfg)
+
+  def step(a, b, c):
+    if op is not None:
+      out, bp = op.vjp(a, b, DIMS)
+    else:
+      out, bp = cfg.vjp(a, b, DIMS)
+    dl, dr = bp(c)
+    return out, dl, dr
+
+  def barrier():
+    if world > 1:
+      dist.barrier()
+    torch.cuda.synchronize()
+
+  for _ in range(args.warmup):
+    step(lhs, rhs, g)
+  barrier()
+  engine.check_status()
+
+  sampler = ClockSampler(local_rank)
+  launches0 = lib.aqtb200_kernel_launch_count()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  sampler.start()
+  barrier()
+  e0.record()
+  for _ in range(args.steps):
+    outs = step(lhs, rhs, g)
+  e1.record()
+  barrier()
+  clocks = sampler.stop()
+  launches = lib.aqtb200_kernel_launch_count() - launches0
+  engine.check_status()
+  ms = e0.elapsed_time(e1) / args.steps
+  if world > 1:
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+  ops_step = 3 * 2 * m_global * n * n
+  value = ops_step / (ms * 1e-3) / 1e12
+
+  # ---- end to end through the public API with pinned host buffers
+  e2e = None
+  if not args.no_e2e:
+    h = [t.cpu().pin_memory() for t in (lhs, rhs, g)]
+    ho = [torch.empty_like(t, device='cpu').pin_memory() for t in outs]
+
+    def e2e_step():
+      d = [t.to(dev, non_blocking=True) for t in h]
+      res = step(*d)
+      for dst, src in zip(ho, res):
+        dst.copy_(src, non_blocking=True)
+
+    for _ in range(3):
+      e2e_step()
+    barrier()
+    k = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(k):
+      e2e_step()
+    e1.record()
+    barrier()
+    ems = e0.elapsed_time(e1) / k
+    if world > 1:
+      t = torch.tensor([ems], device=dev, dtype=torch.float64)
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+      ems = float(t.item())
+    e2e = {'value': ops_step / (ems * 1e-3) / 1e12, 'unit': UNIT,
+           'h2d_bytes_per_step': sum(t.numel() * t.element_size() for t in h),
+           'd2h_bytes_per_step': sum(t.numel() * t.element_size() for t in ho),
+           'ms_per_step': ems}
+
+  # ---- roofline of the dominant kernel: the tcgen05 GEMM, timed alone
+  roof = None
+  if rank == 0:
+    roof = gemm_roofline(args, cfg, lhs, rhs, torch, engine)
+
+  if rank != 0:
+    if world > 1:
+      dist.destroy_process_group()
+    return
+
+  cpu = None
+  if not args.no_cpu_baseline and world == 1:
+    v, dt = cpu_sample(args, args.cpu_sample_rows)
+    cpu = {'value': v, 'unit': UNIT, 'cores': blas_threads(), 'kind': 'port',
+           'sample': (f'{args.cpu_sample_rows} of {n} lhs/cotangent rows against '
+                      f'the full rhs, one pass, {dt:.1f} s; numpy+ml_dtypes '
+                      'restatement (jax not installed)')}
+  line = {
+      'metric': METRIC, 'value': value, 'unit': UNIT, 'n_gpus': world,
+      'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': ms,
+      'higher_is_better': True, 'scaling': args.scaling, 'vs_baseline': None,
+      'dtype': 'f8e4m3/f8e5m2->f32' if args.kind == 'fp8' else 's8->s32',
+      'data': 'synthetic',
+      'config': {
+          'workload': workload_name(args),
+          'rows_per_gpu': m_local, 'global_rows': m_global,
+          'parallelism': f'rows sharded over {world} GPU(s)',
+          'l2': 'inputs (3 x 134 MB bf16 + quantized copies) exceed the 126 MB L2',
+      },
+      'clocks': clocks,
+      'e2e': e2e,
+      'gpu_launches': int(launches),
+      'roofline': roof,
+      'cpu_baseline': cpu,
+  }
+  print(json.dumps(line), flush=True)
+  if world > 1:
+    dist.destroy_process_group()
+
+
+def gemm_roofline(args, cfg, lhs, rhs, torch, engine):
+  """Average duration of the forward GEMM launch alone (CUDA events on the
+  launching stream) against the measured tensor peak."""
+  import ctypes as C
+  from aqt_b200 import _lib
+  lib = _lib.load()
+  out, res = engine.dg_raw(cfg.fwd, lhs, rhs, None, None, DIMS)
+  ql, qr = res.lhs.mt.qx, res.rhs.mt.qx
+  m, k = lhs.shape
+  n = rhs.shape[1]
+  # the quantized buffers are contraction-contiguous: [m, k] and [n, k]
+  a = ql.qvalue
+  b = qr.qvalue.t()
+  assert a.stride(1) == 1 and b.stride(1) == 1
+  d = _lib.GemmDesc()
+  d.b0 = d.b1 = 1
+  d.m, d.n, d.k = m, n, k
+  d.a, d.lda, d.a_dtype = a.data_ptr(), a.stride(0), engine._code(a.dtype)
+  d.b, d.ldb, d.b_dtype = b.data_ptr(), b.stride(0), engine._code(b.dtype)
+  d.a_scale, d.a_scale_dtype = ql.scale[0].data_ptr(), _lib.BF16
+  d.b_scale, d.b_scale_dtype = qr.scale[0].data_ptr(), _lib.BF16
+  d.dequant_dtype = d.out_dtype = _lib.BF16
+  d.out = out.data_ptr()
+  d.out_m_stride, d.out_n_stride = n, 1
+  stream = torch.cuda.current_stream().cuda_stream
+  for _ in range(3):
+    _lib.check(lib.aqtb200_gemm_dequant(C.byref(d), None, stream), 'gemm')
+  torch.cuda.synchronize()
+  reps = 10
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(reps):
+    lib.aqtb200_gemm_dequant(C.byref(d), None, stream)
+  e1.record()
+  torch.cuda.synchronize()
+  ms = e0.elapsed_time(e1) / reps
+  achieved = 2.0 * m * n * k / (ms * 1e-3) / 1e12
+  peaks_path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+  if os.path.exists(peaks_path):
+    with open(peaks_path) as f:
+      bf16 = json.load(f)['bf16_tflops']
+    src = 'of measured: 2 x bf16_tflops (burst) from MEASURED_PEAKS.json'
+  else:
+    bf16 = 1590.0
+    src = 'of fallback: 2 x 1.59 PFLOP/s bf16'
+  peak = 2.0 * bf16
+  return {'bound': 'tensor', 'kernel': 'gemm_tcgen05_kernel (forward GEMM)',
+          'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s',
+          'frac': achieved / peak, 'traffic': None, 'ms_per_launch': ms,
+          'peak_source': src + '; 8-bit operands run at twice the bf16 rate'}
+
+
+def main():
+  args = parse_args()
+  if args.impl == 'reference':
+    run_reference_arm(args)
+  else:
+    run_ours(args)
+
+
+if __name__ == '__main__':
+  main()
