@@ -91,6 +91,8 @@ SYMBOLS = {
         C.POINTER(DgRawDesc)]),
     'aqtb200_dot_general_raw': (C.c_int, [
         C.POINTER(DgRawDesc), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
+    'aqtb200_dot_general_raw_dequant': (C.c_int, [
+        C.POINTER(DgRawDesc), C.c_void_p]),
     'aqtb200_dequantize': (C.c_int, [
         C.POINTER(View), C.POINTER(View), C.c_int32, C.c_void_p, C.c_void_p]),
     'aqtb200_version': (C.c_int, []),

@@ -22,6 +22,7 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int sm_count();
 int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st);
+int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st);
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -68,6 +69,50 @@ static int prepare_side(const aqtb200_view& v, const aqtb200_view& pre, const aq
     out->sc_b0 = v.b1 * v.rows;
   }
   return 0;
+}
+
+// Scale side of an operand as aqtb200_dot_general_raw left it (no kernels run).
+static void side_after_quantize(const aqtb200_view& v, const aqtb200_quant_spec& spec,
+                                const void* scale_in, int is_quantized, void* q_out,
+                                void* scale_out, Side* out) {
+  if (is_quantized) {
+    out->q = v.ptr; out->q_dtype = v.dtype; out->ld = v.row_stride;
+    out->s_b1 = v.b1_stride; out->s_b0 = v.b0_stride; out->scale = scale_in;
+  } else {
+    out->q = q_out; out->q_dtype = spec.qdtype; out->ld = aqtb200_round_up(v.cols, 16);
+    out->s_b1 = v.rows * out->ld; out->s_b0 = v.b1 * out->s_b1;
+    out->scale = scale_out != nullptr ? scale_out : scale_in;
+  }
+  out->scale_dtype = spec.scale_dtype;
+  if (spec.per_tensor) {
+    out->sc_b0 = out->sc_b1 = out->sc_row = 0;
+  } else {
+    out->sc_row = 1; out->sc_b1 = v.rows; out->sc_b0 = v.b1 * v.rows;
+  }
+}
+
+static void fill_gemm_desc(const aqtb200_dg_raw_desc* d, const Side& L, const Side& R,
+                           aqtb200_gemm_desc* gp) {
+  aqtb200_gemm_desc& g = *gp;
+  g.b0 = d->lhs.b0; g.b1 = d->lhs.b1; g.k = d->lhs.cols;
+  const Side& A = d->swap_ab ? R : L;
+  const Side& B = d->swap_ab ? L : R;
+  g.m = d->swap_ab ? d->rhs.rows : d->lhs.rows;
+  g.n = d->swap_ab ? d->lhs.rows : d->rhs.rows;
+  g.a = A.q; g.a_b0_stride = A.s_b0; g.a_b1_stride = A.s_b1; g.lda = A.ld; g.a_dtype = A.q_dtype;
+  g.b = B.q; g.b_b0_stride = B.s_b0; g.b_b1_stride = B.s_b1; g.ldb = B.ld; g.b_dtype = B.q_dtype;
+  g.a_scale = A.scale; g.a_scale_dtype = A.scale_dtype;
+  g.a_scale_b0_stride = A.sc_b0; g.a_scale_b1_stride = A.sc_b1; g.a_scale_m_stride = A.sc_row;
+  g.b_scale = B.scale; g.b_scale_dtype = B.scale_dtype;
+  g.b_scale_b0_stride = B.sc_b0; g.b_scale_b1_stride = B.sc_b1; g.b_scale_n_stride = B.sc_row;
+  // The reference multiplies by the lhs scale first (aqt_dot_general.py:939-957).
+  g.b_scale_first = d->swap_ab ? 1 : 0;
+  g.dequant_dtype = d->dequant_dtype;
+  g.out = d->out; g.out_dtype = d->out_dtype;
+  g.out_b0_stride = d->out_b0_stride; g.out_b1_stride = d->out_b1_stride;
+  g.out_m_stride = d->swap_ab ? d->out_n_stride : d->out_m_stride;
+  g.out_n_stride = d->swap_ab ? d->out_m_stride : d->out_n_stride;
+  g.acc_out = d->acc_out;
 }
 
 }  // namespace aqtb200
@@ -118,26 +163,22 @@ int aqtb200_dot_general_raw(const aqtb200_dg_raw_desc* d, void* workspace, size_
   if (rc) return rc;
 
   aqtb200_gemm_desc g{};
-  g.b0 = d->lhs.b0; g.b1 = d->lhs.b1; g.k = d->lhs.cols;
-  const Side& A = d->swap_ab ? R : L;
-  const Side& B = d->swap_ab ? L : R;
-  g.m = d->swap_ab ? d->rhs.rows : d->lhs.rows;
-  g.n = d->swap_ab ? d->lhs.rows : d->rhs.rows;
-  g.a = A.q; g.a_b0_stride = A.s_b0; g.a_b1_stride = A.s_b1; g.lda = A.ld; g.a_dtype = A.q_dtype;
-  g.b = B.q; g.b_b0_stride = B.s_b0; g.b_b1_stride = B.s_b1; g.ldb = B.ld; g.b_dtype = B.q_dtype;
-  g.a_scale = A.scale; g.a_scale_dtype = A.scale_dtype;
-  g.a_scale_b0_stride = A.sc_b0; g.a_scale_b1_stride = A.sc_b1; g.a_scale_m_stride = A.sc_row;
-  g.b_scale = B.scale; g.b_scale_dtype = B.scale_dtype;
-  g.b_scale_b0_stride = B.sc_b0; g.b_scale_b1_stride = B.sc_b1; g.b_scale_n_stride = B.sc_row;
-  // The reference multiplies by the lhs scale first (aqt_dot_general.py:939-957).
-  g.b_scale_first = d->swap_ab ? 1 : 0;
-  g.dequant_dtype = d->dequant_dtype;
-  g.out = d->out; g.out_dtype = d->out_dtype;
-  g.out_b0_stride = d->out_b0_stride; g.out_b1_stride = d->out_b1_stride;
-  g.out_m_stride = d->swap_ab ? d->out_n_stride : d->out_m_stride;
-  g.out_n_stride = d->swap_ab ? d->out_m_stride : d->out_n_stride;
-  g.acc_out = d->acc_out;
+  fill_gemm_desc(d, L, R, &g);
   return gemm_dequant(&g, status, st);
+}
+
+int aqtb200_dot_general_raw_dequant(const aqtb200_dg_raw_desc* d, void* stream) {
+  AQT_REQUIRE(d != nullptr, AQTB200_EINVAL, "null descriptor");
+  AQT_REQUIRE(d->acc_out != nullptr && d->out != nullptr, AQTB200_EINVAL,
+              "deferred dequantization needs both acc_out and out");
+  Side L{}, R{};
+  side_after_quantize(d->lhs, d->lhs_spec, d->lhs_scale_in, d->lhs_is_quantized, d->lhs_q,
+                      d->lhs_scale, &L);
+  side_after_quantize(d->rhs, d->rhs_spec, d->rhs_scale_in, d->rhs_is_quantized, d->rhs_q,
+                      d->rhs_scale, &R);
+  aqtb200_gemm_desc g{};
+  fill_gemm_desc(d, L, R, &g);
+  return dequant_acc(&g, d->acc_out, (cudaStream_t)stream);
 }
 
 }  // extern "C"

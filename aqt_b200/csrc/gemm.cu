@@ -329,13 +329,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           r = round_to(r, P.d_dtype);
           res[j] = round_to(r, P.out_dtype);
         }
-        if (row_ok) {
-          if (P.acc_out != nullptr) {
-            uint32_t* ao = (uint32_t*)P.acc_out + abase + col0;
+        if (row_ok && P.acc_out != nullptr) {
+          uint32_t* ao = (uint32_t*)P.acc_out + abase + col0;
+          if (col0 + 32 <= P.n && (((uintptr_t)ao) & 15) == 0) {
+#pragma unroll
+            for (int v = 0; v < 8; ++v)
+              ((uint4*)ao)[v] = make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+          } else {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (col0 + j < P.n) ao[j] = acc[j];
           }
+        }
+        if (row_ok && P.out != nullptr) {
           const bool full = col0 + 32 <= P.n;
           const bool vec_ok = full && P.o_n == 1 &&
                               ((((uintptr_t)P.out) + (size_t)(obase + col0) * out_es) & 15) == 0;
@@ -444,10 +450,76 @@ __global__ void gemm_simt_kernel(GemmParams P) {
     }
     r = round_to(round_to(r, P.d_dtype), P.out_dtype);
     const int64_t oi = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m + col * P.o_n;
+    if (P.out == nullptr) continue;
     if (P.out_dtype == AQTB200_BF16)
       ((__nv_bfloat16*)P.out)[oi] = __float2bfloat16_rn(r);
     else
       ((float*)P.out)[oi] = r;
+  }
+}
+
+// Dequantizing epilogue alone, on accumulators that already sit in memory
+// (contiguous [b0][b1][m][n]); same arithmetic as the GEMM's epilogue.
+__device__ __forceinline__ float dequant_one(const GemmParams& P, uint32_t raw, float sa, float sb) {
+  float r = P.is_int ? __int2float_rn((int)raw) : __uint_as_float(raw);
+  int cur = P.d_dtype;
+  r = round_to(r, cur);
+  if (P.b_scale_first) {
+    if (P.b_scale) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+    if (P.a_scale) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+  } else {
+    if (P.a_scale) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+    if (P.b_scale) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+  }
+  return round_to(round_to(r, P.d_dtype), P.out_dtype);
+}
+
+// VEC: n % 4 == 0, acc 16-byte aligned; four consecutive columns per thread.
+template <bool VEC>
+__global__ void __launch_bounds__(256) dequant_acc_kernel(GemmParams P, const uint32_t* acc) {
+  constexpr int W = VEC ? 4 : 1;
+  const int64_t total = P.b0 * P.b1 * P.m * P.n / W;
+  const int64_t nq = P.n / W;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t col = (i % nq) * W;
+    int64_t t = i / nq;
+    const int64_t row = t % P.m;
+    t /= P.m;
+    const int64_t i1 = t % P.b1, i0 = t / P.b1;
+    uint32_t raw[W];
+    if (VEC) {
+      const uint4 u = __ldg((const uint4*)acc + i);
+      raw[0] = u.x; raw[W > 1 ? 1 : 0] = u.y; raw[W > 1 ? 2 : 0] = u.z; raw[W > 1 ? 3 : 0] = u.w;
+    } else {
+      raw[0] = acc[i];
+    }
+    const float sa = P.a_scale ? load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m) : 1.f;
+    float res[W];
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      const float sb = P.b_scale ? load1(P.b_scale, P.b_scale_dtype, i0 * P.sb_b0 + i1 * P.sb_b1 + (col + j) * P.sb_n) : 1.f;
+      res[j] = dequant_one(P, raw[j], sa, sb);
+    }
+    const int64_t oi = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m + col * P.o_n;
+    const int es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
+    if (VEC && P.o_n == 1 && ((((uintptr_t)P.out) + (size_t)oi * es) & (4 * es - 1)) == 0) {
+      if (es == 2) {
+        __nv_bfloat162 p0 = __floats2bfloat162_rn(res[0], res[W > 1 ? 1 : 0]);
+        __nv_bfloat162 p1 = __floats2bfloat162_rn(res[W > 1 ? 2 : 0], res[W > 1 ? 3 : 0]);
+        *(uint2*)((__nv_bfloat16*)P.out + oi) = make_uint2(*(uint32_t*)&p0, *(uint32_t*)&p1);
+      } else {
+        *(float4*)((float*)P.out + oi) = make_float4(res[0], res[W > 1 ? 1 : 0], res[W > 1 ? 2 : 0], res[W > 1 ? 3 : 0]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < W; ++j) {
+        if (es == 2)
+          ((__nv_bfloat16*)P.out)[oi + j * P.o_n] = __float2bfloat16_rn(res[j]);
+        else
+          ((float*)P.out)[oi + j * P.o_n] = res[j];
+      }
+    }
   }
 }
 
@@ -498,7 +570,7 @@ static int make_operand_map(CUtensorMap* tm, const void* ptr, int64_t k, int64_t
 
 static bool is_fp8(int dt) { return dt == AQTB200_E4M3 || dt == AQTB200_E5M2; }
 
-int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
+static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& P, bool* empty) {
   AQT_REQUIRE(d != nullptr, AQTB200_EINVAL, "null gemm descriptor");
   AQT_REQUIRE(d->b0 >= 0 && d->b1 >= 0 && d->m >= 0 && d->n >= 0 && d->k >= 0, AQTB200_EINVAL,
               "negative extent");
@@ -510,13 +582,14 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
               "dequant dtype must be f32 or bf16");
   AQT_REQUIRE(d->out_dtype == AQTB200_F32 || d->out_dtype == AQTB200_BF16, AQTB200_EINVAL,
               "out dtype must be f32 or bf16");
-  if (d->b0 * d->b1 * d->m * d->n == 0) return 0;
-  AQT_REQUIRE(d->out != nullptr, AQTB200_EINVAL, "null output");
+  *empty = d->b0 * d->b1 * d->m * d->n == 0;
+  if (*empty) return 0;
+  AQT_REQUIRE(d->out != nullptr || d->acc_out != nullptr, AQTB200_EINVAL, "null output");
   AQT_REQUIRE(d->k == 0 || (d->a != nullptr && d->b != nullptr), AQTB200_EINVAL, "null operand");
   AQT_REQUIRE(d->k < (int64_t)1 << 31 && d->m < (int64_t)1 << 31 && d->n < (int64_t)1 << 31,
               AQTB200_EUNSUPPORTED, "extent too large for a tensor map");
 
-  GemmParams P{};
+  P = GemmParams{};
   P.b0 = d->b0; P.b1 = d->b1; P.m = d->m; P.n = d->n; P.k = d->k;
   P.a_scale = d->a_scale; P.sa_b0 = d->a_scale_b0_stride; P.sa_b1 = d->a_scale_b1_stride;
   P.sa_m = d->a_scale_m_stride;
@@ -543,6 +616,14 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   P.idesc = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
             ((uint32_t)(BM >> 4) << 24);
 
+  return 0;
+}
+
+int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
+  GemmParams P;
+  bool empty = false;
+  int rc0 = fill_params(d, status, P, &empty);
+  if (rc0 || empty) return rc0;
   if (g_gemm_impl == 1 || d->k == 0) {
     int64_t total = d->b0 * d->b1 * d->m * d->n;
     int grid = (int)std::min<int64_t>((total + 255) / 256, (int64_t)sm_count() * 16);
@@ -573,6 +654,24 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
     gemm_tcgen05_kernel<true><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmB, P);
   else
     gemm_tcgen05_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmB, P);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st) {
+  GemmParams P;
+  bool empty = false;
+  int rc0 = fill_params(d, nullptr, P, &empty);
+  if (rc0 || empty) return rc0;
+  AQT_REQUIRE(acc != nullptr && d->out != nullptr, AQTB200_EINVAL, "null accumulator or output");
+  const int64_t total = d->b0 * d->b1 * d->m * d->n;
+  const bool vec = d->n % 4 == 0 && (((uintptr_t)acc) & 15) == 0;
+  int grid = (int)std::min<int64_t>((total / (vec ? 4 : 1) + 255) / 256, (int64_t)sm_count() * 8);
+  grid = std::max(grid, 1);
+  if (vec)
+    dequant_acc_kernel<true><<<grid, 256, 0, st>>>(P, (const uint32_t*)acc);
+  else
+    dequant_acc_kernel<false><<<grid, 256, 0, st>>>(P, (const uint32_t*)acc);
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   return 0;
 }

@@ -1,0 +1,161 @@
+"""Row-sharded execution of one quantized dot_general as ONE logical op.
+
+The rows of lhs (and of the cotangent) are split over the ranks of a
+torch.distributed group; rhs (the weights) is replicated. The result equals,
+rank by rank, the rows a single device would have produced for the
+concatenated lhs -- bit for bit for int8, to f32 summation order for fp8:
+
+  * scales that do not span the sharded axis (per-row) stay local;
+  * scales that do (per-tensor; every scale of drhs, whose contraction runs
+    over the sharded rows) are computed locally, max-all-reduced, and handed
+    to the dot through the reference's own "incomplete QTensor" input
+    (aqt_dot_general.py:645-653). The scale is a monotone function of the
+    absolute maximum, so max(scale_r) == scale(max_r amax);
+  * drhs sums raw int32 / f32 accumulators across ranks before the single
+    dequantizing epilogue (engine.DeferredDequant).
+
+Only a 2-D contraction lhs[M,K] . rhs[K,N] is handled; that is the projection
+layer the reference's data-parallel users shard. The reference itself has no
+collective on this path (cross-replica statistics raise NotImplementedError,
+flax/aqt_flax_calibration.py:161-164).
+"""
+
+from __future__ import annotations
+
+import functools
+
+import torch
+import torch.distributed as dist
+
+from aqt_b200 import engine
+from aqt_b200.v2 import aqt_dot_general as adg
+from aqt_b200.v2 import aqt_tensor
+from aqt_b200.v2 import utils
+
+_DIMS_2D = (((1,), (0,)), ((), ()))
+
+
+def _calib_kwargs(quantizer):
+  cal = quantizer.calibration
+  kw = dict(cal.keywords) if isinstance(cal, functools.partial) else {}
+  return kw
+
+
+class ShardedDotGeneral:
+  """cfg.vjp for row-sharded operands (see module docstring)."""
+
+  def __init__(self, cfg: adg.DotGeneral, group=None):
+    self.cfg = cfg
+    self.group = group
+
+  # -- collectives -----------------------------------------------------------
+  def _max(self, t):
+    if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+      dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+    return t
+
+  def _sum(self, t):
+    if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+      dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+    return t
+
+  def _sum_async(self, t):
+    """Starts a sum-all-reduce of t in place; returns a handle or None."""
+    if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+      return dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group,
+                             async_op=True)
+    return None
+
+  # -- scales ------------------------------------------------------------------
+  def _global_scale(self, quantizer, x, contraction_axes, sharded_axis,
+                    prescale=None, compute_dtype=None):
+    """Incomplete QTensor with a cross-rank scale, or None if scales are local."""
+    if type(quantizer.numerics).__name__ == 'NoNumerics':
+      return None
+    per_tensor = quantizer.calib_shared_axes == 'per_tensor'
+    shared = list(range(x.ndim)) if per_tensor else list(contraction_axes)
+    if sharded_axis not in shared:
+      return None
+    kw = _calib_kwargs(quantizer)
+    scale = engine.absmax_scale(
+        x, shared, quantizer.numerics,
+        scale_dtype=kw.get('dtype', quantizer.scale_dtype),
+        clipping_scale=kw.get('clipping_scale'),
+        po2_scale=kw.get('po2_scale', False), prescale=prescale,
+        compute_dtype=compute_dtype)
+    scale = self._max(scale.contiguous())
+    dd = compute_dtype if compute_dtype is not None else utils.as_dtype(x.dtype)
+    return aqt_tensor.QTensor(qvalue=None, scale=[scale], scale_t=None,
+                              bias=[], dequant_dtype=dd)
+
+  # -- forward / backward ------------------------------------------------------
+  def vjp(self, lhs, rhs, dimension_numbers=_DIMS_2D):
+    dims = adg._canon_dims(dimension_numbers)  # pylint: disable=protected-access
+    if dims != _DIMS_2D or lhs.ndim != 2 or rhs.ndim != 2:
+      raise NotImplementedError(
+          'ShardedDotGeneral handles lhs[M,K] . rhs[K,N] with M sharded')
+    cfg = self.cfg
+    cfg.assert_config_validity()
+    for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
+      adg._init_calibration_once(raw.dg_quantizer)  # pylint: disable=protected-access
+    lhs_qt = self._global_scale(cfg.fwd.dg_quantizer.lhs, lhs, [1], 0)
+    out, res = engine.dg_raw(cfg.fwd, lhs, rhs, lhs_qt, None, dims)
+    out = out.to(lhs.dtype)
+
+    def backprop(g):
+      return self._bwd(dims, res, g)
+
+    return out, backprop
+
+  def _other_operand(self, raw, mt):
+    """(tensor the raw dot quantizes, forward scale to fold into g, dtype)."""
+    if raw.rhs.use_fwd_quant:
+      return mt.qx.qvalue, mt.qx.scale[0], mt.qx.dequant_dtype
+    return mt.x, None, None
+
+  def _bwd(self, dims, res, g):
+    cfg = self.cfg
+    upd = adg._update_dimension_numbers_for_backward  # pylint: disable=protected-access
+
+    # drhs = g[M,N]^T . lhs'[M,K] : contraction over the sharded rows. It runs
+    # first so that the all-reduce of its accumulators overlaps with dlhs.
+    r_dims, r_perm = upd(dims, True, g.ndim, res.lhs.mt.x.ndim)
+    other, fwd_scale, other_dt = self._other_operand(cfg.drhs, res.lhs.mt)
+    pre = None
+    if fwd_scale is not None:
+      # lhs scale [M,1] (or a scalar) varies along g's contraction axis M
+      pre = fwd_scale.reshape(-1, 1) if fwd_scale.numel() > 1 else (
+          fwd_scale.reshape(1, 1))
+    g_qt = self._global_scale(cfg.drhs.dg_quantizer.lhs, g, [0], 0,
+                              prescale=pre)
+    x_qt = self._global_scale(cfg.drhs.dg_quantizer.rhs, other, [0], 0,
+                              compute_dtype=other_dt)
+    deferred, work, drhs = None, None, None
+    if g_qt is None and x_qt is None:  # unquantized gradient dot
+      drhs = engine.dg_raw(cfg.drhs, g, res.lhs.mt, None, None, r_dims,
+                           out_transpose_axes=r_perm)[0].contiguous()
+      work = self._sum_async(drhs)
+    else:
+      deferred, _ = engine.dg_raw(cfg.drhs, g, res.lhs.mt, g_qt, x_qt, r_dims,
+                                  out_transpose_axes=r_perm,
+                                  defer_dequant=True)
+      work = self._sum_async(deferred.acc)
+
+    # dlhs = g[M,N] . rhs'[K,N]^T : rows of g sharded, contraction over N local
+    d_dims, d_perm = upd(dims, False, g.ndim, res.rhs.mt.x.ndim)
+    _, fwd_scale, _ = self._other_operand(cfg.dlhs, res.rhs.mt)
+    pre = None
+    if fwd_scale is not None:
+      # rhs scale [1,N] laid along g's [M,N]: constant along the kept axis M
+      pre = fwd_scale.reshape(1, -1) if fwd_scale.numel() > 1 else (
+          fwd_scale.reshape(1, 1))
+    g_qt = self._global_scale(cfg.dlhs.dg_quantizer.lhs, g, [1], 0,
+                              prescale=pre)
+    dlhs = engine.dg_raw(cfg.dlhs, g, res.rhs.mt, g_qt, None, d_dims,
+                         out_transpose_axes=d_perm)[0]
+
+    if work is not None:
+      work.wait()
+    if deferred is not None:
+      drhs = deferred.finish()
+    return dlhs, drhs

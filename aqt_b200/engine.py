@@ -308,8 +308,27 @@ def _logical_q(buf, op: _Operand, k: int):
   return t.permute(*inv)
 
 
+class DeferredDequant:
+  """Accumulators of a raw dot whose dequantization has been postponed.
+
+  `acc` is the raw int32 / f32 accumulator tensor (sum it across ranks when
+  the contraction index is sharded); finish() applies the dequantizing
+  epilogue once and returns the output.
+  """
+
+  def __init__(self, desc, acc, out, keep):
+    self._desc, self.acc, self._out, self._keep = desc, acc, out, keep
+
+  def finish(self):
+    self._desc.out = self._out.data_ptr()
+    rc = _lib.load().aqtb200_dot_general_raw_dequant(C.byref(self._desc),
+                                                     _stream())
+    _lib.check(rc, 'aqtb200_dot_general_raw_dequant')
+    return self._out
+
+
 def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
-           out_transpose_axes=None, want_acc=False):
+           out_transpose_axes=None, want_acc=False, defer_dequant=False):
   """DotGeneralRaw.__call__ on the device (aqt_dot_general.py:757-840).
 
   Returns (out, DotGeneralRes[, acc]). `out` is laid out as
@@ -563,13 +582,18 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
   desc.out_m_stride = ms[1]
   desc.out_n_stride = ns[1]
   acc = None
+  if defer_dequant:
+    want_acc = True
   if want_acc:
     acc_shape = (nB, N, M) if swap else (nB, M, N)
     acc = torch.empty(acc_shape, device=dev,
                       dtype=torch.int32 if ints[0] else torch.float32)
     desc.acc_out = acc.data_ptr()
+    acc_storage = acc
     if swap:
       acc = acc.transpose(1, 2)
+  if defer_dequant:
+    desc.out = None
 
   lib = _lib.load()
   ws_bytes = lib.aqtb200_dot_general_raw_workspace_bytes(C.byref(desc))
@@ -612,6 +636,9 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
                         quant_grad=grad_fn(q.lhs, lhs, lhs_qv)),
       rhs=adg.TensorRes(mt=adg.MultiTensor(x=rhs_float, qx=rhs_q_out),
                         quant_grad=grad_fn(q.rhs, rhs_float, rhs_qv)))
+  if defer_dequant:
+    return DeferredDequant(desc, acc_storage, out_t,
+                           [lq, ls, rq, rs_, lsin, rsin]), res
   if want_acc:
     return out_t, res, acc
   return out_t, res
@@ -750,20 +777,46 @@ def _spec_for(numerics, x_code, scale_dtype, per_tensor, clipping_scale=None,
 
 
 def absmax_scale(x, shared_axes, numerics, scale_dtype=None,
-                 clipping_scale=None, po2_scale=False):
-  """AbsMaxCalibration on the device: the scale, x's rank, shared axes 1."""
+                 clipping_scale=None, po2_scale=False, prescale=None,
+                 compute_dtype=None):
+  """AbsMaxCalibration on the device: the scale, x's rank, shared axes 1.
+
+  prescale: optional tensor broadcastable against x that is constant along
+  the kept (non-shared) axes; x is multiplied by it (rounded to the compute
+  dtype) before the maximum is taken, as the backward pass does with the
+  other operand's forward scale. compute_dtype: the float dtype x counts as
+  when it is a stored int8/fp8 tensor.
+  """
   per_tensor = len(shared_axes) == x.ndim
   op, view, rows, cols = _single_operand(x, shared_axes)
-  spec = _spec_for(numerics, _code(x.dtype), scale_dtype, per_tensor,
+  x_code = _code(compute_dtype) if compute_dtype is not None else _code(x.dtype)
+  spec = _spec_for(numerics, x_code, scale_dtype, per_tensor,
                    clipping_scale, po2_scale)
+  pre_view = None
+  if prescale is not None:
+    pre = prescale.expand(x.shape) if prescale.ndim == x.ndim else prescale
+    pop = _Operand(pre, [], op.ra, op.ca)
+    for a in op.ra:
+      assert prescale.ndim != x.ndim or prescale.shape[a] == 1 or per_tensor, (
+          'prescale must be constant along the kept axes')
+    kd = _merge(op.extents_of(op.ca), [pop.strides_of(op.ca)], 1)
+    if kd is None or (view.col_stride != 1 and view.row_stride != 1):
+      raise NotImplementedError('prescale layout for absmax_scale')
+    pcs = kd[0][1][0] if kd else 0
+    if per_tensor and any(pre.stride(a) != 0 for a in range(x.ndim)):
+      # every axis is reduced: rows/cols came from an arbitrary split, so
+      # only a scalar prescale can be expressed
+      raise NotImplementedError('non-scalar prescale with a per-tensor scale')
+    pre_view = _view(prescale.data_ptr(), _code(prescale.dtype), [1, 1], 1,
+                     cols, [0, 0], 0, pcs)
   lib = _lib.load()
   n = 1 if per_tensor else rows
   sbuf = torch.empty(n, dtype=_CODE_TORCH[spec.scale_dtype], device=x.device)
   ws_bytes = lib.aqtb200_quantize_workspace_bytes(C.byref(view), C.byref(spec))
   ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=x.device)
-  rc = lib.aqtb200_absmax_scale(C.byref(view), None, C.byref(spec),
-                                sbuf.data_ptr(), ws.data_ptr(), ws.numel(),
-                                _stream())
+  rc = lib.aqtb200_absmax_scale(
+      C.byref(view), C.byref(pre_view) if pre_view is not None else None,
+      C.byref(spec), sbuf.data_ptr(), ws.data_ptr(), ws.numel(), _stream())
   _lib.check(rc, 'aqtb200_absmax_scale')
   return _logical_scale(sbuf, op, per_tensor)
 

@@ -215,9 +215,19 @@ typedef struct aqtb200_dg_raw_desc {
 
 size_t aqtb200_dot_general_raw_workspace_bytes(const aqtb200_dg_raw_desc* desc);
 
+/* When desc->out is NULL and desc->acc_out is set, aqtb200_dot_general_raw
+ * stops after the contraction and leaves the raw accumulators in acc_out
+ * ([b0][b1][M][N], or [b0][b1][N][M] with swap_ab). A caller that shards the
+ * contraction index over several GPUs sums those accumulators across ranks
+ * and then calls aqtb200_dot_general_raw_dequant with the SAME descriptor
+ * (out now set) to apply the dequantizing epilogue once, to the total. */
+
 int aqtb200_dot_general_raw(const aqtb200_dg_raw_desc* desc, void* workspace,
                             size_t workspace_bytes, int32_t* status,
                             void* stream);
+
+int aqtb200_dot_general_raw_dequant(const aqtb200_dg_raw_desc* desc,
+                                    void* stream);
 
 /* Elementwise helpers for the piecewise API (QTensor.quant / QTensor.dequant
  * used outside the fused path, aqt_tensor.py:125-200):

@@ -148,18 +148,23 @@ class FakeLib:
                           _deref(spec, _lib.QuantSpec), None, None, scale_out)
 
   # -- gemm
-  def _gemm(self, g):
+  def _gemm(self, g, acc_in=None):
     ext = [g.b0, g.b1]
-    a = _strided(g.a, g.a_dtype, ext + [g.m, g.k],
-                 [g.a_b0_stride, g.a_b1_stride, g.lda, 1])
-    b = _strided(g.b, g.b_dtype, ext + [g.n, g.k],
-                 [g.b_b0_stride, g.b_b1_stride, g.ldb, 1])
-    dims = (((3,), (3,)), ((0, 1), (0, 1)))
     ints = g.a_dtype == _lib.S8
-    acc = orc.dot_general(np.array(a), np.array(b), dims,
-                          preferred_element_type=orc.int32 if ints else
-                          orc.float32)
-    if g.acc_out:
+    if acc_in is not None:
+      acc = np.array(_strided(acc_in, _lib.S32 if ints else _lib.F32,
+                              ext + [g.m, g.n],
+                              [g.b1 * g.m * g.n, g.m * g.n, g.n, 1]))
+    else:
+      a = _strided(g.a, g.a_dtype, ext + [g.m, g.k],
+                   [g.a_b0_stride, g.a_b1_stride, g.lda, 1])
+      b = _strided(g.b, g.b_dtype, ext + [g.n, g.k],
+                   [g.b_b0_stride, g.b_b1_stride, g.ldb, 1])
+      dims = (((3,), (3,)), ((0, 1), (0, 1)))
+      acc = orc.dot_general(np.array(a), np.array(b), dims,
+                            preferred_element_type=orc.int32 if ints else
+                            orc.float32)
+    if g.acc_out and acc_in is None:
       _strided(g.acc_out, _lib.S32 if ints else _lib.F32, ext + [g.m, g.n],
                [g.b1 * g.m * g.n, g.m * g.n, g.n, 1], True)[...] = acc
     D = _NP[g.dequant_dtype]
@@ -177,6 +182,8 @@ class FakeLib:
       if s is not None:
         r = orc.mul(r, s)
     r = r.astype(D).astype(_NP[g.out_dtype])
+    if not g.out:
+      return 0
     _strided(g.out, g.out_dtype, ext + [g.m, g.n],
              [g.out_b0_stride, g.out_b1_stride, g.out_m_stride,
               g.out_n_stride], True)[...] = r
@@ -189,9 +196,14 @@ class FakeLib:
   def aqtb200_dot_general_raw_workspace_bytes(self, desc):
     return 1024
 
-  def aqtb200_dot_general_raw(self, desc, ws, ws_bytes, status, stream):
+  def aqtb200_dot_general_raw_dequant(self, desc, stream):
+    return self.aqtb200_dot_general_raw(desc, None, 0, None, stream,
+                                        dequant_only=True)
+
+  def aqtb200_dot_general_raw(self, desc, ws, ws_bytes, status, stream,
+                              dequant_only=False):
     d = _deref(desc, _lib.DgRawDesc)
-    self.calls.append('dg_raw')
+    self.calls.append('dg_raw_dequant' if dequant_only else 'dg_raw')
     sides = []
     for (v, pre, noise, spec, sin, isq, qo, so) in (
         (d.lhs, d.lhs_prescale, d.lhs_noise, d.lhs_spec, d.lhs_scale_in,
@@ -204,7 +216,8 @@ class FakeLib:
         side = dict(q=v.ptr, dt=v.dtype, ld=v.row_stride, b1=v.b1_stride,
                     b0=v.b0_stride, scale=sin)
       else:
-        rc = self._quantize(v, pre, noise, spec, sin, qo, so)
+        rc = 0 if dequant_only else self._quantize(v, pre, noise, spec, sin,
+                                                   qo, so)
         if rc:
           return rc
         ld = (v.cols + 15) // 16 * 16
@@ -233,7 +246,7 @@ class FakeLib:
     g.out_m_stride = d.out_n_stride if d.swap_ab else d.out_m_stride
     g.out_n_stride = d.out_m_stride if d.swap_ab else d.out_n_stride
     g.acc_out = d.acc_out
-    return self._gemm(g)
+    return self._gemm(g, acc_in=d.acc_out if dequant_only else None)
 
   # -- dequantize
   def aqtb200_dequantize(self, q, scale, d_dtype, out, stream):
