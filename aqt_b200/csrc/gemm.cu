@@ -46,8 +46,9 @@ struct GemmParams {
   void* out;
   int64_t o_b0, o_b1, o_m, o_n;
   void* acc_out;
-  uint32_t idesc;
+  uint32_t idesc, idesc2;
   int64_t m_tiles, n_tiles, total_tiles, num_kb;
+  int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
   int32_t* status;
   // SIMT reference kernel only:
   const uint8_t* a; const uint8_t* b;
@@ -183,7 +184,161 @@ __device__ __forceinline__ float scale_mul(float r, float s, int& cur, int sdt) 
   return round_to(__fmul_rn(r, s), cur);
 }
 
-template <bool IS_INT>
+// Drains one 128 x BN accumulator tile: TMEM -> registers -> dequantizing chain
+// -> global. `taddr` addresses this warp's 32 lanes and the tile's first column.
+// EPI selects the arithmetic: 0 generic (any mix of f32 / bf16 dtypes),
+// 1 dequant, output and scales all bf16, 2 all f32.
+template <bool IS_INT, int EPI>
+__device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t taddr, int lane,
+                                              int64_t i0, int64_t i1, int64_t row, int64_t ncol0) {
+  const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
+  const int out_es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
+  const bool row_ok = row < P.m;
+  float sa = 1.f;
+  if (has_a && row_ok)
+    sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
+  const int64_t obase = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m;
+  const int64_t abase = ((i0 * P.b1 + i1) * P.m + row) * P.n;
+#pragma unroll 1
+  for (int chunk = 0; chunk < BN / 32; ++chunk) {
+    const int64_t col0 = ncol0 + chunk * 32;
+    if (col0 >= P.n) break;  // warp-uniform
+    uint32_t acc[32];
+    tc_ld32(taddr + (uint32_t)(chunk * 32), acc);
+    tc_wait_ld();
+    float res[32];
+    uint32_t pk[16];  // EPI == 1: the 32 results as packed bf16 pairs
+    if constexpr (EPI == 1) {
+      // Everything bf16: cast_bf16(acc) then two bf16 multiplies. A bf16 x bf16
+      // product is exact in f32, so the hardware's packed bf16 multiply (one
+      // rounding) equals "multiply in f32, round to bf16".
+      const __nv_bfloat162 sa2 = __float2bfloat162_rn(sa);
+      uint32_t sbw = 0x3f803f80u;  // (1.0, 1.0)
+      if (has_b) {
+        if (P.sb_n == 0) {
+          const float sb = load1(P.b_scale, AQTB200_BF16, i0 * P.sb_b0 + i1 * P.sb_b1);
+          const __nv_bfloat162 t = __float2bfloat162_rn(sb);
+          sbw = *(const uint32_t*)&t;
+        } else if (lane < 16) {
+          const int64_t c = col0 + 2 * lane;
+          const unsigned short* sp = (const unsigned short*)P.b_scale + i0 * P.sb_b0 + i1 * P.sb_b1;
+          const uint32_t lo = c < P.n ? __ldg(sp + c * P.sb_n) : 0x3f80u;
+          const uint32_t hi = c + 1 < P.n ? __ldg(sp + (c + 1) * P.sb_n) : 0x3f80u;
+          sbw = lo | (hi << 16);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 16; ++j) {
+        uint32_t w = (has_b && P.sb_n != 0) ? __shfl_sync(0xffffffffu, sbw, j) : sbw;
+        const __nv_bfloat162 sb2 = *(const __nv_bfloat162*)&w;
+        const float f0 = IS_INT ? __int2float_rn((int)acc[2 * j]) : __uint_as_float(acc[2 * j]);
+        const float f1 = IS_INT ? __int2float_rn((int)acc[2 * j + 1]) : __uint_as_float(acc[2 * j + 1]);
+        __nv_bfloat162 v = __floats2bfloat162_rn(f0, f1);
+        if (P.b_scale_first) {
+          if (has_b) v = __hmul2(v, sb2);
+          if (has_a) v = __hmul2(v, sa2);
+        } else {
+          if (has_a) v = __hmul2(v, sa2);
+          if (has_b) v = __hmul2(v, sb2);
+        }
+        pk[j] = *(const uint32_t*)&v;
+      }
+    } else {
+      float sbl = 1.f;
+      if (has_b && col0 + lane < P.n)
+        sbl = load1(P.b_scale, P.b_scale_dtype,
+                    i0 * P.sb_b0 + i1 * P.sb_b1 + (col0 + lane) * P.sb_n);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) {
+        const float sb = __shfl_sync(0xffffffffu, sbl, j);
+        float r = IS_INT ? __int2float_rn((int)acc[j]) : __uint_as_float(acc[j]);
+        if constexpr (EPI == 2) {
+          // everything f32: two rounded f32 multiplies
+          if (P.b_scale_first) {
+            if (has_b) r = __fmul_rn(r, sb);
+            if (has_a) r = __fmul_rn(r, sa);
+          } else {
+            if (has_a) r = __fmul_rn(r, sa);
+            if (has_b) r = __fmul_rn(r, sb);
+          }
+          res[j] = r;
+        } else {
+          int cur = P.d_dtype;
+          r = round_to(r, cur);
+          if (P.b_scale_first) {
+            if (has_b) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+            if (has_a) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+          } else {
+            if (has_a) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+            if (has_b) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+          }
+          r = round_to(r, P.d_dtype);
+          res[j] = round_to(r, P.out_dtype);
+        }
+      }
+    }
+    if (row_ok && P.acc_out != nullptr) {
+      uint32_t* ao = (uint32_t*)P.acc_out + abase + col0;
+      if (col0 + 32 <= P.n && (((uintptr_t)ao) & 15) == 0) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v)
+          ((uint4*)ao)[v] = make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < P.n) ao[j] = acc[j];
+      }
+    }
+    if (row_ok && P.out != nullptr) {
+      const bool full = col0 + 32 <= P.n;
+      const bool vec_ok = full && P.o_n == 1 &&
+                          ((((uintptr_t)P.out) + (size_t)(obase + col0) * out_es) & 15) == 0;
+      if (vec_ok) {
+        if (EPI == 1) {
+          uint4* o = (uint4*)((__nv_bfloat16*)P.out + obase + col0);
+#pragma unroll
+          for (int v = 0; v < 4; ++v)
+            o[v] = make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+        } else if (out_es == 2) {
+          uint4* o = (uint4*)((__nv_bfloat16*)P.out + obase + col0);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            __nv_bfloat162 p0 = __floats2bfloat162_rn(res[8 * v + 0], res[8 * v + 1]);
+            __nv_bfloat162 p1 = __floats2bfloat162_rn(res[8 * v + 2], res[8 * v + 3]);
+            __nv_bfloat162 p2 = __floats2bfloat162_rn(res[8 * v + 4], res[8 * v + 5]);
+            __nv_bfloat162 p3 = __floats2bfloat162_rn(res[8 * v + 6], res[8 * v + 7]);
+            uint4 u;
+            u.x = *(uint32_t*)&p0; u.y = *(uint32_t*)&p1;
+            u.z = *(uint32_t*)&p2; u.w = *(uint32_t*)&p3;
+            o[v] = u;
+          }
+        } else {
+          float4* o = (float4*)((float*)P.out + obase + col0);
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            o[v] = make_float4(res[4 * v], res[4 * v + 1], res[4 * v + 2], res[4 * v + 3]);
+        }
+      } else {
+        if constexpr (EPI == 1) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) { res[2 * j] = bf16lo(pk[j]); res[2 * j + 1] = bf16hi(pk[j]); }
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (col0 + j < P.n) {
+            const int64_t oi = obase + (col0 + j) * P.o_n;
+            if (out_es == 2)
+              ((__nv_bfloat16*)P.out)[oi] = __float2bfloat16_rn(res[j]);
+            else
+              ((float*)P.out)[oi] = res[j];
+          }
+        }
+      }
+    }
+  }
+}
+
+template <bool IS_INT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                     const __grid_constant__ CUtensorMap tmB, GemmParams P) {
@@ -284,8 +439,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const int quarter = warp & 3;  // TMEM lanes this warp may read
     int buf = 0;
     uint32_t aphase = 0;
-    const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
-    const int out_es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
     for (int64_t t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
       int64_t i0, i1, mt, nt;
       decode_tile(P, t, i0, i1, mt, nt);
@@ -294,91 +447,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       if (!ok) { fail = 3; break; }
       tc_fence_after();
       const int64_t row = mt * BM + quarter * 32 + lane;
-      const bool row_ok = row < P.m;
-      float sa = 1.f;
-      if (has_a && row_ok)
-        sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
-      const int64_t obase = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m;
-      const int64_t abase = ((i0 * P.b1 + i1) * P.m + row) * P.n;
-#pragma unroll 1
-      for (int chunk = 0; chunk < BN / 32; ++chunk) {
-        const int64_t col0 = nt * BN + chunk * 32;
-        if (col0 >= P.n) break;  // warp-uniform
-        uint32_t acc[32];
-        tc_ld32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + chunk * 32),
-                acc);
-        tc_wait_ld();
-        float sbl = 1.f;
-        if (has_b && col0 + lane < P.n)
-          sbl = load1(P.b_scale, P.b_scale_dtype,
-                      i0 * P.sb_b0 + i1 * P.sb_b1 + (col0 + lane) * P.sb_n);
-        float res[32];
-#pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const float sb = __shfl_sync(0xffffffffu, sbl, j);
-          float r = IS_INT ? __int2float_rn((int)acc[j]) : __uint_as_float(acc[j]);
-          int cur = P.d_dtype;
-          r = round_to(r, cur);
-          if (P.b_scale_first) {
-            if (has_b) r = scale_mul(r, sb, cur, P.b_scale_dtype);
-            if (has_a) r = scale_mul(r, sa, cur, P.a_scale_dtype);
-          } else {
-            if (has_a) r = scale_mul(r, sa, cur, P.a_scale_dtype);
-            if (has_b) r = scale_mul(r, sb, cur, P.b_scale_dtype);
-          }
-          r = round_to(r, P.d_dtype);
-          res[j] = round_to(r, P.out_dtype);
-        }
-        if (row_ok && P.acc_out != nullptr) {
-          uint32_t* ao = (uint32_t*)P.acc_out + abase + col0;
-          if (col0 + 32 <= P.n && (((uintptr_t)ao) & 15) == 0) {
-#pragma unroll
-            for (int v = 0; v < 8; ++v)
-              ((uint4*)ao)[v] = make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < P.n) ao[j] = acc[j];
-          }
-        }
-        if (row_ok && P.out != nullptr) {
-          const bool full = col0 + 32 <= P.n;
-          const bool vec_ok = full && P.o_n == 1 &&
-                              ((((uintptr_t)P.out) + (size_t)(obase + col0) * out_es) & 15) == 0;
-          if (vec_ok) {
-            if (out_es == 2) {
-              uint4* o = (uint4*)((__nv_bfloat16*)P.out + obase + col0);
-#pragma unroll
-              for (int v = 0; v < 4; ++v) {
-                __nv_bfloat162 p0 = __floats2bfloat162_rn(res[8 * v + 0], res[8 * v + 1]);
-                __nv_bfloat162 p1 = __floats2bfloat162_rn(res[8 * v + 2], res[8 * v + 3]);
-                __nv_bfloat162 p2 = __floats2bfloat162_rn(res[8 * v + 4], res[8 * v + 5]);
-                __nv_bfloat162 p3 = __floats2bfloat162_rn(res[8 * v + 6], res[8 * v + 7]);
-                uint4 u;
-                u.x = *(uint32_t*)&p0; u.y = *(uint32_t*)&p1;
-                u.z = *(uint32_t*)&p2; u.w = *(uint32_t*)&p3;
-                o[v] = u;
-              }
-            } else {
-              float4* o = (float4*)((float*)P.out + obase + col0);
-#pragma unroll
-              for (int v = 0; v < 8; ++v)
-                o[v] = make_float4(res[4 * v], res[4 * v + 1], res[4 * v + 2], res[4 * v + 3]);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < P.n) {
-                const int64_t oi = obase + (col0 + j) * P.o_n;
-                if (out_es == 2)
-                  ((__nv_bfloat16*)P.out)[oi] = __float2bfloat16_rn(res[j]);
-                else
-                  ((float*)P.out)[oi] = res[j];
-              }
-            }
-          }
-        }
-      }
+      epilogue_tile<IS_INT, EPI>(P, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN),
+                            lane, i0, i1, row, nt * BN);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
@@ -400,6 +470,246 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   if (warp == 1) {
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// CTA-pair variant: a cluster of two CTAs (one SM pair) computes a 256 x 256
+// tile with tcgen05.mma.cta_group::2. CTA r of the pair loads rows
+// [r*128, r*128+128) of the A tile and rows [r*128, ...) of the B tile (32 KB
+// per stage instead of 48 KB), holds the accumulator rows of its own half in
+// its own TMEM, and runs its own epilogue. Only the even CTA issues MMAs; its
+// commits are delivered to the barriers of both CTAs. Per flop this pulls one
+// third fewer bytes through the L2 -> SM fabric than the 128 x 256 kernel.
+constexpr int BM2 = 256;           // tile rows per CTA pair
+constexpr int B_HALF = 128 * BK;   // bytes of B one CTA stages per k-block
+constexpr int STAGES2 = 6;
+constexpr size_t GEMM2_SMEM = (size_t)STAGES2 * (A_STAGE + B_HALF) + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// shared::cluster address of the same shared variable in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tma_load_4d_pair(void* dst, const CUtensorMap* tm,
+                                                 uint32_t leader_bar, int c0, int c1, int c2,
+                                                 int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(tm), "r"(leader_bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile(
+      "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64"
+      " [%0], %1;" ::"r"(smem_u32(bar)),
+      "h"((uint16_t)3)
+      : "memory");
+}
+template <bool IS_INT>
+__device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                            uint32_t idesc, uint32_t accumulate) {
+  if (IS_INT) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+
+__device__ __forceinline__ void decode_tile2(const GemmParams& P, int64_t t, int64_t& i0,
+                                             int64_t& i1, int64_t& mt, int64_t& nt) {
+  const int64_t per_batch = P.m_tiles2 * P.n_tiles;
+  int64_t b = t / per_batch, r = t % per_batch;
+  i1 = b % P.b1;
+  i0 = b / P.b1;
+  constexpr int64_t G = GROUP_M / 2;
+  const int64_t group = G * P.n_tiles;
+  int64_t g = r / group, in = r % group;
+  int64_t first = g * G;
+  int64_t gm = min(G, P.m_tiles2 - first);
+  mt = first + in % gm;
+  nt = in / gm;
+}
+
+template <bool IS_INT, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB, GemmParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint8_t* smem_a = smem;
+  uint8_t* smem_b = smem + STAGES2 * A_STAGE;
+  __shared__ __align__(8) uint64_t full_bar[STAGES2];   // used in the even CTA only
+  __shared__ __align__(8) uint64_t empty_bar[STAGES2];  // one per CTA
+  __shared__ __align__(8) uint64_t tfull_bar[2];        // one per CTA
+  __shared__ __align__(8) uint64_t tempty_bar[2];       // used in the even CTA only
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int64_t cluster_id = blockIdx.x >> 1;
+  const int64_t num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES2; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&tfull_bar[s], 1);
+      mbar_init(&tempty_bar[s], 8);  // 4 epilogue warps in each of the two CTAs
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers exist before anyone signals them
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abortp = &abort_flag;
+  const uint32_t peer_abort = map_to_cta(smem_u32(&abort_flag), rank ^ 1u);
+  int fail = 0;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int64_t t = cluster_id; t < P.total_tiles2 && !fail; t += num_clusters) {
+        int64_t i0, i1, mt, nt;
+        decode_tile2(P, t, i0, i1, mt, nt);
+        for (int64_t kb = 0; kb < P.num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
+          const uint32_t lbar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          if (leader) mbar_expect_tx(&full_bar[stage], 2 * (A_STAGE + B_HALF));
+          tma_load_4d_pair(smem_a + stage * A_STAGE, &tmA, lbar, (int)(kb * BK),
+                           (int)(mt * BM2 + rank * 128), (int)i1, (int)i0);
+          tma_load_4d_pair(smem_b + stage * B_HALF, &tmB, lbar, (int)(kb * BK),
+                           (int)(nt * BN + rank * 128), (int)i1, (int)i0);
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (fail) {
+        *abortp = 1;
+        st_cluster_u32(peer_abort, 1u);
+        if (P.status) atomicCAS(P.status, 0, 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (lane == 0 && leader) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int buf = 0;
+      uint32_t aphase = 0;
+      for (int64_t t = cluster_id; t < P.total_tiles2 && !fail; t += num_clusters) {
+        if (!mbar_wait(&tempty_bar[buf], aphase ^ 1, abortp)) { fail = 2; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
+        for (int64_t kb = 0; kb < P.num_kb; ++kb) {
+          if (!mbar_wait(&full_bar[stage], phase, abortp)) { fail = 2; break; }
+          tc_fence_after();
+          const uint64_t ad = make_smem_desc(smem_u32(smem_a + stage * A_STAGE));
+          const uint64_t bd = make_smem_desc(smem_u32(smem_b + stage * B_HALF));
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k) {
+            tc_mma_pair<IS_INT>(d_tmem, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), P.idesc2,
+                                (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit_pair(&empty_bar[stage]);
+          if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+        }
+        if (fail) break;
+        tc_commit_pair(&tfull_bar[buf]);
+        buf ^= 1;
+        if (buf == 0) aphase ^= 1;
+      }
+      if (fail) {
+        *abortp = 1;
+        st_cluster_u32(peer_abort, 1u);
+        if (P.status) atomicCAS(P.status, 0, 2);
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, own half of the rows) ----------------
+    const int quarter = warp & 3;
+    int buf = 0;
+    uint32_t aphase = 0;
+    for (int64_t t = cluster_id; t < P.total_tiles2; t += num_clusters) {
+      int64_t i0, i1, mt, nt;
+      decode_tile2(P, t, i0, i1, mt, nt);
+      int ok = mbar_wait(&tfull_bar[buf], aphase, abortp) ? 1 : 0;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { fail = 3; break; }
+      tc_fence_after();
+      const int64_t row = mt * BM2 + rank * 128 + quarter * 32 + lane;
+      epilogue_tile<IS_INT, EPI>(P, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN),
+                            lane, i0, i1, row, nt * BN);
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
+      buf ^= 1;
+      if (buf == 0) aphase ^= 1;
+    }
+    if (fail && lane == 0) {
+      *abortp = 1;
+      st_cluster_u32(peer_abort, 1u);
+      if (P.status) atomicCAS(P.status, 0, 3);
+    }
+  }
+
+  __syncwarp();
+  if (*abortp) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { }
+  }
+  tc_fence_before();
+  __syncthreads();
+  // Neither CTA may release its TMEM or leave while the other can still read
+  // its shared memory or write its accumulators.
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"(TMEM_COLS)
                  : "memory");
   }
@@ -615,6 +925,10 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   const uint32_t bfmt = ints ? 1u : (d->b_dtype == AQTB200_E5M2 ? 1u : 0u);
   P.idesc = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
             ((uint32_t)(BM >> 4) << 24);
+  P.idesc2 = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
+             ((uint32_t)(256 >> 4) << 24);
+  P.m_tiles2 = (d->m + 255) / 256;
+  P.total_tiles2 = d->b0 * d->b1 * P.m_tiles2 * P.n_tiles;
 
   return 0;
 }
@@ -632,28 +946,51 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
     return 0;
   }
 
+  // CTA pairs pay off once a 256-row tile is mostly full; skinny problems keep
+  // the single-CTA 128-row tiles. g_gemm_impl 2 / 3 force one or the other.
+  const bool pair = g_gemm_impl == 3 ? true : (g_gemm_impl == 2 ? false : d->m > 128);
   CUtensorMap tmA, tmB;
   int rc = make_operand_map(&tmA, d->a, d->k, d->m, d->b1, d->b0, d->lda, d->a_b1_stride,
                             d->a_b0_stride, BM);
   if (rc) return rc;
   rc = make_operand_map(&tmB, d->b, d->k, d->n, d->b1, d->b0, d->ldb, d->b_b1_stride,
-                        d->b_b0_stride, BN);
+                        d->b_b0_stride, pair ? 128 : BN);
   if (rc) return rc;
-  static bool attr_set[2] = {false, false};
-  if (!attr_set[P.is_int]) {
-    if (P.is_int)
-      AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<true>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
-    else
-      AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<false>,
-                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GEMM_SMEM));
-    attr_set[P.is_int] = true;
+  const bool sa_bf = d->a_scale == nullptr || d->a_scale_dtype == AQTB200_BF16;
+  const bool sb_bf = d->b_scale == nullptr || d->b_scale_dtype == AQTB200_BF16;
+  const bool sa_f = d->a_scale == nullptr || d->a_scale_dtype == AQTB200_F32;
+  const bool sb_f = d->b_scale == nullptr || d->b_scale_dtype == AQTB200_F32;
+  int epi = 0;
+  if (d->dequant_dtype == AQTB200_BF16 && d->out_dtype == AQTB200_BF16 && sa_bf && sb_bf) epi = 1;
+  if (d->dequant_dtype == AQTB200_F32 && d->out_dtype == AQTB200_F32 && sa_f && sb_f) epi = 2;
+  const int grid = pair ? 2 * std::max((int)std::min<int64_t>(P.total_tiles2, sm_count() / 2), 1)
+                        : (int)std::min<int64_t>(P.total_tiles, sm_count());
+  const size_t smem = pair ? GEMM2_SMEM : GEMM_SMEM;
+#define AQT_LAUNCH_GEMM(KERNEL, I, E)                                                         \
+  do {                                                                                        \
+    static bool attr_done = false;                                                            \
+    if (!attr_done) {                                                                         \
+      AQT_CUDA_OK(cudaFuncSetAttribute(KERNEL<I, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                       (int)smem));                                           \
+      attr_done = true;                                                                       \
+    }                                                                                         \
+    KERNEL<I, E><<<grid, GEMM_THREADS, smem, st>>>(tmA, tmB, P);                              \
+  } while (0)
+#define AQT_LAUNCH_GEMM_E(KERNEL, I)                    \
+  do {                                                  \
+    if (epi == 1) AQT_LAUNCH_GEMM(KERNEL, I, 1);        \
+    else if (epi == 2) AQT_LAUNCH_GEMM(KERNEL, I, 2);   \
+    else AQT_LAUNCH_GEMM(KERNEL, I, 0);                 \
+  } while (0)
+  if (pair) {
+    if (P.is_int) AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, true);
+    else AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, false);
+  } else {
+    if (P.is_int) AQT_LAUNCH_GEMM_E(gemm_tcgen05_kernel, true);
+    else AQT_LAUNCH_GEMM_E(gemm_tcgen05_kernel, false);
   }
-  int grid = (int)std::min<int64_t>(P.total_tiles, sm_count());
-  if (P.is_int)
-    gemm_tcgen05_kernel<true><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmB, P);
-  else
-    gemm_tcgen05_kernel<false><<<grid, GEMM_THREADS, GEMM_SMEM, st>>>(tmA, tmB, P);
+#undef AQT_LAUNCH_GEMM_E
+#undef AQT_LAUNCH_GEMM
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   return 0;
 }
@@ -685,7 +1022,7 @@ int aqtb200_gemm_dequant(const aqtb200_gemm_desc* desc, int32_t* status, void* s
 }
 
 int aqtb200_set_gemm_impl(int impl) {
-  if (impl != 0 && impl != 1) return AQTB200_EINVAL;
+  if (impl < 0 || impl > 3) return AQTB200_EINVAL;
   aqtb200::g_gemm_impl = impl;
   return 0;
 }

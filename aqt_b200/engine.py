@@ -73,9 +73,9 @@ def check_status():
 
 
 def set_gemm_impl(name: str):
-  """'tcgen05' (default) or 'simt' (debug cross-check kernel)."""
-  _lib.check(_lib.load().aqtb200_set_gemm_impl({'tcgen05': 0, 'simt': 1}[name]),
-             'set_gemm_impl')
+  """'tcgen05' (default), 'simt' (cross-check kernel), 'cta1' or 'cta2'."""
+  code = {'tcgen05': 0, 'simt': 1, 'cta1': 2, 'cta2': 3}[name]
+  _lib.check(_lib.load().aqtb200_set_gemm_impl(code), 'set_gemm_impl')
 
 
 # ---------------------------------------------------------------------------

@@ -242,8 +242,10 @@ int aqtb200_device_sm_count(int* out);
 /* number of kernels this library has launched in this process (all threads);
  * lets a harness report how much of its timed region ran in these kernels. */
 int64_t aqtb200_kernel_launch_count(void);
-/* selects the contraction kernel: 0 = tcgen05 (default), 1 = plain CUDA-core
- * reference kernel kept for debugging the tensor-core path. */
+/* selects the contraction kernel: 0 = tcgen05, CTA pairs (cta_group::2,
+ * 256 x 256 tiles) when M > 128 and single CTAs (128 x 256) otherwise
+ * (default); 1 = plain CUDA-core reference kernel kept for cross-checking the
+ * tensor-core path; 2 = always single CTAs; 3 = always CTA pairs. */
 int aqtb200_set_gemm_impl(int impl);
 
 #ifdef __cplusplus
