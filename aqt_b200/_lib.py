@@ -100,6 +100,7 @@ SYMBOLS = {
     'aqtb200_device_sm_count': (C.c_int, [C.POINTER(C.c_int)]),
     'aqtb200_kernel_launch_count': (C.c_int64, []),
     'aqtb200_set_gemm_impl': (C.c_int, [C.c_int]),
+    'aqtb200_set_gemm_sm_budget': (C.c_int, [C.c_int]),
 }
 
 _lib = None

@@ -837,6 +837,11 @@ __global__ void __launch_bounds__(256) dequant_acc_kernel(GemmParams P, const ui
 // host side
 
 static int g_gemm_impl = 0;
+static int g_sm_budget = 0;
+static int gemm_sms() {
+  int n = sm_count();
+  return (g_sm_budget > 0 && g_sm_budget < n) ? g_sm_budget : n;
+}
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -963,8 +968,8 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   int epi = 0;
   if (d->dequant_dtype == AQTB200_BF16 && d->out_dtype == AQTB200_BF16 && sa_bf && sb_bf) epi = 1;
   if (d->dequant_dtype == AQTB200_F32 && d->out_dtype == AQTB200_F32 && sa_f && sb_f) epi = 2;
-  const int grid = pair ? 2 * std::max((int)std::min<int64_t>(P.total_tiles2, sm_count() / 2), 1)
-                        : (int)std::min<int64_t>(P.total_tiles, sm_count());
+  const int grid = pair ? 2 * std::max((int)std::min<int64_t>(P.total_tiles2, gemm_sms() / 2), 1)
+                        : (int)std::min<int64_t>(P.total_tiles, gemm_sms());
   const size_t smem = pair ? GEMM2_SMEM : GEMM_SMEM;
 #define AQT_LAUNCH_GEMM(KERNEL, I, E)                                                         \
   do {                                                                                        \
@@ -1019,6 +1024,12 @@ extern "C" {
 
 int aqtb200_gemm_dequant(const aqtb200_gemm_desc* desc, int32_t* status, void* stream) {
   return aqtb200::gemm_dequant(desc, status, (cudaStream_t)stream);
+}
+
+int aqtb200_set_gemm_sm_budget(int max_sms) {
+  if (max_sms < 0) return AQTB200_EINVAL;
+  aqtb200::g_sm_budget = max_sms;
+  return 0;
 }
 
 int aqtb200_set_gemm_impl(int impl) {

@@ -44,9 +44,11 @@ def _calib_kwargs(quantizer):
 class ShardedDotGeneral:
   """cfg.vjp for row-sharded operands (see module docstring)."""
 
-  def __init__(self, cfg: adg.DotGeneral, group=None):
+  def __init__(self, cfg: adg.DotGeneral, group=None, overlap_sms: int = 32):
     self.cfg = cfg
     self.group = group
+    # SMs left to the all-reduce kernel while the dlhs GEMM runs beside it.
+    self.overlap_sms = overlap_sms
 
   # -- collectives -----------------------------------------------------------
   def _max(self, t):
@@ -151,8 +153,14 @@ class ShardedDotGeneral:
           fwd_scale.reshape(1, 1))
     g_qt = self._global_scale(cfg.dlhs.dg_quantizer.lhs, g, [1], 0,
                               prescale=pre)
-    dlhs = engine.dg_raw(cfg.dlhs, g, res.rhs.mt, g_qt, None, d_dims,
-                         out_transpose_axes=d_perm)[0]
+    if work is not None and self.overlap_sms and not engine._HOST_TEST_MODE:  # pylint: disable=protected-access
+      engine.set_gemm_sm_budget(max(engine.sm_count() - self.overlap_sms, 2))
+    try:
+      dlhs = engine.dg_raw(cfg.dlhs, g, res.rhs.mt, g_qt, None, d_dims,
+                           out_transpose_axes=d_perm)[0]
+    finally:
+      if work is not None and self.overlap_sms and not engine._HOST_TEST_MODE:  # pylint: disable=protected-access
+        engine.set_gemm_sm_budget(0)
 
     if work is not None:
       work.wait()

@@ -78,6 +78,18 @@ def set_gemm_impl(name: str):
   _lib.check(_lib.load().aqtb200_set_gemm_impl(code), 'set_gemm_impl')
 
 
+def set_gemm_sm_budget(max_sms: int):
+  """Caps the SMs the persistent GEMM grids take (0 = all)."""
+  _lib.check(_lib.load().aqtb200_set_gemm_sm_budget(int(max_sms)),
+             'set_gemm_sm_budget')
+
+
+def sm_count() -> int:
+  n = C.c_int(0)
+  _lib.check(_lib.load().aqtb200_device_sm_count(C.byref(n)), 'sm_count')
+  return n.value
+
+
 # ---------------------------------------------------------------------------
 # stride bookkeeping
 

@@ -39,9 +39,15 @@ def parse_args():
   p.add_argument('--scaling', default='weak', choices=['weak', 'strong'])
   p.add_argument('--size', type=int, default=8192)
   p.add_argument('--kind', default='fp8', choices=['fp8', 'int8'])
-  p.add_argument('--cpu-sample-rows', type=int, default=256)
+  p.add_argument('--cpu-sample-rows', type=int, default=0,
+                 help='rows of lhs/cotangent the CPU arm processes (0 = all: '
+                 'the whole workload, which keeps the ratio of contraction to '
+                 'quantization work of the real problem)')
   p.add_argument('--no-cpu-baseline', action='store_true')
   p.add_argument('--no-e2e', action='store_true')
+  p.add_argument('--gemm', default='tcgen05',
+                 choices=['tcgen05', 'cta1', 'cta2'],
+                 help='tile shape of the tensor-core kernel (default: automatic)')
   return p.parse_args()
 
 
@@ -97,11 +103,11 @@ def blas_threads():
     return os.cpu_count() or 1
 
 
-def run_reference_arm(args):
+def run_reference_arm(args, lines):
   rank = int(os.environ.get('RANK', '0'))
   if rank != 0:
     return
-  rows = args.cpu_sample_rows
+  rows = args.cpu_sample_rows or args.size
   for _ in range(min(args.warmup, 1)):
     cpu_sample(args, rows)
   steps = max(1, min(args.steps, 3))
@@ -127,7 +133,7 @@ def run_reference_arm(args):
               'd2h_bytes_per_step': 0},
       'gpu_launches': 0,
   }
-  print(json.dumps(line), flush=True)
+  lines.append(json.dumps(line))
 
 
 # ---------------------------------------------------------------------------
@@ -199,7 +205,7 @@ class ClockSampler:
 # our arm
 
 
-def run_ours(args):
+def run_ours(args, lines):
   import torch
   import torch.distributed as dist
   from aqt_b200 import _lib
@@ -215,6 +221,7 @@ def run_ours(args):
   if world > 1:
     dist.init_process_group('nccl', device_id=dev)
   lib = _lib.load()
+  engine.set_gemm_impl(args.gemm)
 
   n = args.size
   m_local = n if args.scaling == 'weak' else n // world
@@ -316,9 +323,10 @@ def run_ours(args):
 
   cpu = None
   if not args.no_cpu_baseline and world == 1:
-    v, dt = cpu_sample(args, args.cpu_sample_rows)
+    cpu_rows = args.cpu_sample_rows or n
+    v, dt = cpu_sample(args, cpu_rows)
     cpu = {'value': v, 'unit': UNIT, 'cores': blas_threads(), 'kind': 'port',
-           'sample': (f'{args.cpu_sample_rows} of {n} lhs/cotangent rows against '
+           'sample': (f'{cpu_rows} of {n} lhs/cotangent rows against '
                       f'the full rhs, one pass, {dt:.1f} s; numpy+ml_dtypes '
                       'restatement (jax not installed)')}
   line = {
@@ -339,7 +347,7 @@ def run_ours(args):
       'roofline': roof,
       'cpu_baseline': cpu,
   }
-  print(json.dumps(line), flush=True)
+  lines.append(json.dumps(line))
   if world > 1:
     dist.destroy_process_group()
 
@@ -398,10 +406,22 @@ def gemm_roofline(args, cfg, lhs, rhs, torch, engine):
 
 def main():
   args = parse_args()
-  if args.impl == 'reference':
-    run_reference_arm(args)
-  else:
-    run_ours(args)
+  # Libraries (NCCL's version banner, torchrun notices) write to stdout; the
+  # contract is ONE JSON line there, so everything else is sent to stderr.
+  real_stdout = os.dup(1)
+  os.dup2(2, 1)
+  lines = []
+  try:
+    if args.impl == 'reference':
+      run_reference_arm(args, lines)
+    else:
+      run_ours(args, lines)
+  finally:
+    sys.stdout.flush()
+    os.dup2(real_stdout, 1)
+    os.close(real_stdout)
+  for line in lines:
+    print(line, flush=True)
 
 
 if __name__ == '__main__':

@@ -247,6 +247,11 @@ int64_t aqtb200_kernel_launch_count(void);
  * (default); 1 = plain CUDA-core reference kernel kept for cross-checking the
  * tensor-core path; 2 = always single CTAs; 3 = always CTA pairs. */
 int aqtb200_set_gemm_impl(int impl);
+/* Caps the number of SMs the persistent GEMM kernels occupy (0 = all of them).
+ * A caller that runs a collective concurrently with a GEMM leaves it room
+ * this way: a persistent grid that fills every SM would otherwise make the
+ * collective's kernel (or the GEMM's last CTAs) wait for a free SM. */
+int aqtb200_set_gemm_sm_budget(int max_sms);
 
 #ifdef __cplusplus
 } /* extern "C" */

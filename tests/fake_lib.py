@@ -71,6 +71,9 @@ class FakeLib:
   def aqtb200_set_gemm_impl(self, impl):
     return 0
 
+  def aqtb200_set_gemm_sm_budget(self, n):
+    return 0
+
   def aqtb200_round_up(self, v, m):
     return (v + m - 1) // m * m
 
