@@ -79,6 +79,9 @@ SYMBOLS = {
         C.POINTER(View), C.POINTER(View), C.POINTER(View),
         C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p,
         C.c_size_t, C.c_void_p]),
+    'aqtb200_quantize_static': (C.c_int, [
+        C.POINTER(View), C.POINTER(View), C.POINTER(View),
+        C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]),
     'aqtb200_quantize_workspace_bytes': (C.c_size_t, [
         C.POINTER(View), C.POINTER(QuantSpec)]),
     'aqtb200_absmax_scale': (C.c_int, [

@@ -11,6 +11,7 @@
 // kernels read inputs whose kept index is contiguous and transpose a 64x128
 // tile through shared memory so the output is contraction-contiguous as well.
 #include <algorithm>
+#include <mutex>
 
 #include "common.cuh"
 
@@ -1138,6 +1139,50 @@ int aqtb200_quantize(const aqtb200_view* x, const aqtb200_view* prescale,
                      void* workspace, size_t workspace_bytes, void* stream) {
   return run(x, prescale, noise, spec, scale_in, q_out, scale_out, workspace,
              workspace_bytes, (cudaStream_t)stream, true);
+}
+
+// ---------------------------------------------------------------------------
+// Allocation-free variant of aqtb200_quantize. Its scratch (the amax cells and
+// the reciprocal scales) lives in the library image instead of a caller
+// buffer: a file-scope device array, present on every GPU that loads the
+// library until the process exits.
+static __device__ __align__(256) unsigned char
+    g_static_scratch[2 * ((AQTB200_STATIC_MAX_SCALES * 4 + 255) / 256 * 256)];
+
+// In host code the array's name is only a handle for the runtime, not a device
+// address; the address is looked up once per device, with that device current.
+static void* g_static_scratch_ptr[64] = {nullptr};
+static std::mutex g_static_scratch_mu;
+
+static int static_scratch_for_current_device(void** out) {
+  int dev = 0;
+  AQT_CUDA_OK(cudaGetDevice(&dev));
+  AQT_REQUIRE(dev >= 0 && dev < 64, AQTB200_EUNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    AQT_CUDA_OK(cudaGetSymbolAddress(&p, g_static_scratch));
+    AQT_REQUIRE(p != nullptr, AQTB200_EDRIVER, "cudaGetSymbolAddress returned a null address");
+    g_static_scratch_ptr[dev] = p;
+  }
+  *out = g_static_scratch_ptr[dev];
+  return 0;
+}
+
+int aqtb200_quantize_static(const aqtb200_view* x, const aqtb200_view* prescale,
+                            const aqtb200_view* noise, const aqtb200_quant_spec* spec,
+                            const void* scale_in, void* q_out, void* scale_out, void* stream) {
+  AQT_REQUIRE(x != nullptr && spec != nullptr, AQTB200_EINVAL, "null view or spec");
+  const int64_t ns = n_scales(x, spec);
+  AQT_REQUIRE(ns <= AQTB200_STATIC_MAX_SCALES, AQTB200_EUNSUPPORTED,
+              "aqtb200_quantize_static handles at most %d scales (b0*b1*rows, or 1 per tensor); "
+              "this call needs %lld -- use aqtb200_quantize with a caller workspace",
+              AQTB200_STATIC_MAX_SCALES, (long long)ns);
+  void* scratch = nullptr;
+  int rc = static_scratch_for_current_device(&scratch);
+  if (rc) return rc;
+  return run(x, prescale, noise, spec, scale_in, q_out, scale_out, scratch,
+             sizeof(g_static_scratch), (cudaStream_t)stream, true);
 }
 
 int aqtb200_absmax_scale(const aqtb200_view* x, const aqtb200_view* prescale,

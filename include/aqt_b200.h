@@ -126,6 +126,40 @@ int aqtb200_quantize(const aqtb200_view* x, const aqtb200_view* prescale,
 size_t aqtb200_quantize_workspace_bytes(const aqtb200_view* x,
                                         const aqtb200_quant_spec* spec);
 
+/*
+ * aqtb200_quantize_static: aqtb200_quantize for callers that cannot hand over
+ * scratch memory. (No counterpart in the reference: it exists for the hosts
+ * this library gets embedded in, not for AQT's semantics.)
+ *
+ * Who needs it: a host that owns every byte of device memory through its own
+ * allocator and passes a custom call only its operands and results -- an XLA
+ * custom call registered without a scratch result is the typical case -- or a
+ * serving loop that forbids calls into the CUDA allocator once it is warm.
+ * Such a caller has nowhere to get the amax cells and reciprocal scales that
+ * aqtb200_quantize wants in `workspace`, and must not cudaMalloc them.
+ *
+ * The scratch therefore lives inside the library: one fixed device array per
+ * GPU (2 x 256 KiB, resident from library load to process exit). Consequences:
+ *  - at most AQTB200_STATIC_MAX_SCALES scales per call (b0*b1*rows, or 1 with
+ *    a per-tensor scale); larger requests return AQTB200_EUNSUPPORTED with a
+ *    message and launch nothing;
+ *  - the first call on each device looks the array's address up
+ *    (cudaGetSymbolAddress, with that device current) and caches it; make that
+ *    first call before starting any stream capture on the device;
+ *  - every call on a device shares the one array, which still holds the
+ *    previous call's values when the next one starts (the kernel sequence
+ *    zeroes the cells it accumulates into). Two calls whose kernels can run at
+ *    the same time -- different streams, no ordering between them -- race on
+ *    it; order them, or use aqtb200_quantize with separate workspaces;
+ *  - it calls no cudaMalloc / cudaFree and no allocating library routine.
+ * Arguments and results are those of aqtb200_quantize minus the workspace.
+ */
+#define AQTB200_STATIC_MAX_SCALES 65536
+int aqtb200_quantize_static(const aqtb200_view* x, const aqtb200_view* prescale,
+                            const aqtb200_view* noise,
+                            const aqtb200_quant_spec* spec, const void* scale_in,
+                            void* q_out, void* scale_out, void* stream);
+
 /* aqtb200_absmax_scale: the calibration half alone (scale_out only).
  * Replaces Quantizer.calibrate (aqt_quantizer.py:79-157). */
 int aqtb200_absmax_scale(const aqtb200_view* x, const aqtb200_view* prescale,
