@@ -30,10 +30,12 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE = BM * BK;
 constexpr int B_STAGE = BN * BK;
 constexpr int GROUP_M = 16;
-constexpr int GEMM_THREADS = 192;
+constexpr int EPI_WARPS = 8;     // two per TMEM lane quarter, each draining half the columns
+constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr size_t GEMM_SMEM = (size_t)STAGES * (A_STAGE + B_STAGE) + 1024;
 constexpr long long WAIT_LIMIT_CYCLES = 4000000000LL;  // ~2 s
+constexpr int kStagePitch = 128;  // bytes per staged epilogue row (16-byte pieces XOR-swizzled)
 
 struct GemmParams {
   int64_t b0, b1, m, n, k;
@@ -49,6 +51,7 @@ struct GemmParams {
   uint32_t idesc, idesc2;
   int64_t m_tiles, n_tiles, total_tiles, num_kb;
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
+  int stage_ok;  // output rows can be written as aligned 16-byte pieces
   int32_t* status;
   // SIMT reference kernel only:
   const uint8_t* a; const uint8_t* b;
@@ -186,21 +189,65 @@ __device__ __forceinline__ float scale_mul(float r, float s, int& cur, int sdt) 
 
 // Drains one 128 x BN accumulator tile: TMEM -> registers -> dequantizing chain
 // -> global. `taddr` addresses this warp's 32 lanes and the tile's first column.
+// Scales of one output tile, fetched BEFORE the warp waits for the
+// accumulator: they do not depend on it, and a load issued per 32-column chunk
+// after the wait would put a memory round trip on every chunk's critical path.
+struct EpiScales {
+  float sa;          // this thread's row scale (1 when absent)
+  uint32_t sbw[4];   // EPI == 1: lanes 0..15 hold bf16 pairs (col 2l, 2l+1) of chunk c
+  float sbl[4];      // otherwise: lane l holds the scale of column 32c + l
+};
+
+template <int EPI>
+__device__ __forceinline__ void load_epi_scales(const GemmParams& P, int lane, int64_t i0,
+                                                int64_t i1, int64_t row, int64_t ncol0,
+                                                EpiScales& sc) {
+  const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
+  sc.sa = 1.f;
+  if (has_a && row < P.m)
+    sc.sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const int64_t col0 = ncol0 + c * 32;
+    if constexpr (EPI == 1) {
+      uint32_t w = 0x3f803f80u;  // (1.0, 1.0)
+      if (has_b) {
+        const unsigned short* sp = (const unsigned short*)P.b_scale + i0 * P.sb_b0 + i1 * P.sb_b1;
+        if (P.sb_n == 0) {
+          const uint32_t v = __ldg(sp);
+          w = v | (v << 16);
+        } else if (lane < 16) {
+          const int64_t cc = col0 + 2 * lane;
+          const uint32_t lo = cc < P.n ? __ldg(sp + cc * P.sb_n) : 0x3f80u;
+          const uint32_t hi = cc + 1 < P.n ? __ldg(sp + (cc + 1) * P.sb_n) : 0x3f80u;
+          w = lo | (hi << 16);
+        }
+      }
+      sc.sbw[c] = w;
+    } else {
+      float v = 1.f;
+      if (has_b && col0 + lane < P.n)
+        v = load1(P.b_scale, P.b_scale_dtype,
+                  i0 * P.sb_b0 + i1 * P.sb_b1 + (col0 + lane) * P.sb_n);
+      sc.sbl[c] = v;
+    }
+  }
+}
+
 // EPI selects the arithmetic: 0 generic (any mix of f32 / bf16 dtypes),
 // 1 dequant, output and scales all bf16, 2 all f32.
 template <bool IS_INT, int EPI>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t taddr, int lane,
-                                              int64_t i0, int64_t i1, int64_t row, int64_t ncol0) {
+                                              int64_t i0, int64_t i1, int64_t row, int64_t ncol0,
+                                              uint8_t* stage, const EpiScales& sc) {
   const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
   const int out_es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
   const bool row_ok = row < P.m;
-  float sa = 1.f;
-  if (has_a && row_ok)
-    sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
+  const float sa = sc.sa;
   const int64_t obase = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m;
   const int64_t abase = ((i0 * P.b1 + i1) * P.m + row) * P.n;
-#pragma unroll 1
-  for (int chunk = 0; chunk < BN / 32; ++chunk) {
+#pragma unroll
+  for (int chunk = 0; chunk < 4; ++chunk) {
     const int64_t col0 = ncol0 + chunk * 32;
     if (col0 >= P.n) break;  // warp-uniform
     uint32_t acc[32];
@@ -213,20 +260,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tadd
       // product is exact in f32, so the hardware's packed bf16 multiply (one
       // rounding) equals "multiply in f32, round to bf16".
       const __nv_bfloat162 sa2 = __float2bfloat162_rn(sa);
-      uint32_t sbw = 0x3f803f80u;  // (1.0, 1.0)
-      if (has_b) {
-        if (P.sb_n == 0) {
-          const float sb = load1(P.b_scale, AQTB200_BF16, i0 * P.sb_b0 + i1 * P.sb_b1);
-          const __nv_bfloat162 t = __float2bfloat162_rn(sb);
-          sbw = *(const uint32_t*)&t;
-        } else if (lane < 16) {
-          const int64_t c = col0 + 2 * lane;
-          const unsigned short* sp = (const unsigned short*)P.b_scale + i0 * P.sb_b0 + i1 * P.sb_b1;
-          const uint32_t lo = c < P.n ? __ldg(sp + c * P.sb_n) : 0x3f80u;
-          const uint32_t hi = c + 1 < P.n ? __ldg(sp + (c + 1) * P.sb_n) : 0x3f80u;
-          sbw = lo | (hi << 16);
-        }
-      }
+      const uint32_t sbw = sc.sbw[chunk];
 #pragma unroll
       for (int j = 0; j < 16; ++j) {
         uint32_t w = (has_b && P.sb_n != 0) ? __shfl_sync(0xffffffffu, sbw, j) : sbw;
@@ -244,10 +278,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tadd
         pk[j] = *(const uint32_t*)&v;
       }
     } else {
-      float sbl = 1.f;
-      if (has_b && col0 + lane < P.n)
-        sbl = load1(P.b_scale, P.b_scale_dtype,
-                    i0 * P.sb_b0 + i1 * P.sb_b1 + (col0 + lane) * P.sb_n);
+      const float sbl = sc.sbl[chunk];
 #pragma unroll
       for (int j = 0; j < 32; ++j) {
         const float sb = __shfl_sync(0xffffffffu, sbl, j);
@@ -289,7 +320,39 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tadd
           if (col0 + j < P.n) ao[j] = acc[j];
       }
     }
-    if (row_ok && P.out != nullptr) {
+    // bf16 fast path: two 32-column chunks are parked in this warp's staging
+    // rows and leave together, so that one warp store covers four whole
+    // 128-byte lines instead of 32 scattered 16-byte pieces.
+    bool staged = false;
+    if constexpr (EPI == 1) {
+      staged = stage != nullptr && P.stage_ok && P.out != nullptr &&
+               ncol0 + (chunk & ~1) * 32 + 64 <= P.n;
+      if (staged) {
+        uint8_t* srow = stage + lane * kStagePitch;
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+          const int piece = ((chunk & 1) * 4 + v) ^ (lane & 7);
+          *(uint4*)(srow + piece * 16) =
+              make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+        }
+        if (chunk & 1) {
+          __syncwarp();
+          const int64_t colp = ncol0 + (chunk - 1) * 32;
+          const int64_t row0 = row - lane;
+          __nv_bfloat16* ob = (__nv_bfloat16*)P.out + i0 * P.o_b0 + i1 * P.o_b1 + colp;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int r = i * 4 + (lane >> 3), seg = lane & 7;
+            if (row0 + r < P.m) {
+              const uint4 v = *(const uint4*)(stage + r * kStagePitch + ((seg ^ (r & 7)) * 16));
+              *(uint4*)(ob + (row0 + r) * P.o_m + seg * 8) = v;
+            }
+          }
+          __syncwarp();
+        }
+      }
+    }
+    if (row_ok && P.out != nullptr && !staged) {
       const bool full = col0 + 32 <= P.n;
       const bool vec_ok = full && P.o_n == 1 &&
                           ((((uintptr_t)P.out) + (size_t)(obase + col0) * out_es) & 15) == 0;
@@ -352,6 +415,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) uint8_t epi_stage[EPI_WARPS][32 * kStagePitch];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -362,7 +426,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tfull_bar[s], 1);
-      mbar_init(&tempty_bar[s], 4);
+      mbar_init(&tempty_bar[s], EPI_WARPS);
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -436,19 +500,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else {
     // ---------------- epilogue ----------------
-    const int quarter = warp & 3;  // TMEM lanes this warp may read
+    const int quarter = warp & 3;          // TMEM lanes this warp may read
+    const int half = (warp - 2) >> 2;      // which 128 columns of the tile it drains
     int buf = 0;
     uint32_t aphase = 0;
     for (int64_t t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
       int64_t i0, i1, mt, nt;
       decode_tile(P, t, i0, i1, mt, nt);
+      const int64_t row = mt * BM + quarter * 32 + lane;
+      EpiScales sc;
+      load_epi_scales<EPI>(P, lane, i0, i1, row, nt * BN + half * 128, sc);
       int ok = mbar_wait(&tfull_bar[buf], aphase, abortp) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
       tc_fence_after();
-      const int64_t row = mt * BM + quarter * 32 + lane;
-      epilogue_tile<IS_INT, EPI>(P, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN),
-                            lane, i0, i1, row, nt * BN);
+      epilogue_tile<IS_INT, EPI>(
+          P, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128), lane,
+          i0, i1, row, nt * BN + half * 128, epi_stage[warp - 2], sc);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
@@ -499,8 +567,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
   asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
   return r;
 }
+// Relaxed on purpose: the only thing the waiting MMA thread must observe is
+// that this warp's tcgen05.ld reads are done, which tcgen05.wait::ld plus
+// tcgen05.fence::before_thread_sync already order. A release at cluster scope
+// would also wait for every global store of the tile to drain, and stall the
+// accumulator hand-back by microseconds per tile.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
                : "memory");
 }
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
@@ -573,6 +646,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   __shared__ __align__(8) uint64_t tempty_bar[2];       // used in the even CTA only
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ __align__(16) uint8_t epi_stage[EPI_WARPS][32 * kStagePitch];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -587,7 +661,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(&tfull_bar[s], 1);
-      mbar_init(&tempty_bar[s], 8);  // 4 epilogue warps in each of the two CTAs
+      mbar_init(&tempty_bar[s], 2 * EPI_WARPS);  // the epilogue warps of both CTAs
     }
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -672,18 +746,22 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   } else {
     // ---------------- epilogue (both CTAs, own half of the rows) ----------------
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     int buf = 0;
     uint32_t aphase = 0;
     for (int64_t t = cluster_id; t < P.total_tiles2; t += num_clusters) {
       int64_t i0, i1, mt, nt;
       decode_tile2(P, t, i0, i1, mt, nt);
+      const int64_t row = mt * BM2 + rank * 128 + quarter * 32 + lane;
+      EpiScales sc;
+      load_epi_scales<EPI>(P, lane, i0, i1, row, nt * BN + half * 128, sc);
       int ok = mbar_wait(&tfull_bar[buf], aphase, abortp) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
       tc_fence_after();
-      const int64_t row = mt * BM2 + rank * 128 + quarter * 32 + lane;
-      epilogue_tile<IS_INT, EPI>(P, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN),
-                            lane, i0, i1, row, nt * BN);
+      epilogue_tile<IS_INT, EPI>(
+          P, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128), lane,
+          i0, i1, row, nt * BN + half * 128, epi_stage[warp - 2], sc);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
@@ -916,6 +994,9 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   P.out = d->out; P.o_b0 = d->out_b0_stride; P.o_b1 = d->out_b1_stride;
   P.o_m = d->out_m_stride; P.o_n = d->out_n_stride;
   P.acc_out = d->acc_out;
+  P.stage_ok = d->out != nullptr && d->out_dtype == AQTB200_BF16 && d->out_n_stride == 1 &&
+               (((uintptr_t)d->out) & 15) == 0 && d->out_m_stride % 8 == 0 &&
+               d->out_b0_stride % 8 == 0 && d->out_b1_stride % 8 == 0;
   P.m_tiles = (d->m + BM - 1) / BM;
   P.n_tiles = (d->n + BN - 1) / BN;
   P.total_tiles = d->b0 * d->b1 * P.m_tiles * P.n_tiles;

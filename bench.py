@@ -45,6 +45,14 @@ def parse_args():
                  'quantization work of the real problem)')
   p.add_argument('--no-cpu-baseline', action='store_true')
   p.add_argument('--no-e2e', action='store_true')
+  p.add_argument('--workload', default='c2', choices=['c1', 'c2', 'c3', 'c4'],
+                 help='BASELINE.json config to time; c2 is the headline '
+                 'workload, the others are extra single-GPU measurements')
+  p.add_argument('--m', type=int, default=16,
+                 help='rows of the activation for --workload c4')
+  p.add_argument('--graph', action='store_true',
+                 help='extra workloads only: replay the step from a CUDA graph '
+                 '(removes host launch overhead from small problems)')
   p.add_argument('--gemm', default='tcgen05',
                  choices=['tcgen05', 'cta1', 'cta2'],
                  help='tile shape of the tensor-core kernel (default: automatic)')
@@ -404,6 +412,132 @@ def gemm_roofline(args, cfg, lhs, rhs, torch, engine):
           'peak_source': src + '; 8-bit operands run at twice the bf16 rate'}
 
 
+def run_extra_workload(args, lines):
+  """Single-GPU timing of BASELINE configs 1, 3 and 4 (device-resident)."""
+  import numpy as np
+  import torch
+  from aqt_b200 import _lib
+  from aqt_b200 import engine
+  from aqt_b200.v2 import aqt_dot_general as adg
+  from aqt_b200.v2 import config
+  from aqt_b200.v2 import stochastic_rounding as sr
+  from aqt_b200.v2 import utils
+  from aqt_b200.v2.flax import aqt_flax
+  torch.cuda.set_device(0)
+  dev = torch.device('cuda', 0)
+  lib = _lib.load()
+  engine.set_gemm_impl(args.gemm)
+  gen = torch.Generator(device=dev)
+  gen.manual_seed(0)
+  rn = lambda shape, std, dt: (torch.randn(shape, device=dev, generator=gen)
+                               * std).to(dt)
+  extra = {}
+  if args.workload == 'c1':
+    lhs = rn((1024, 4096), 1.0, torch.float32)
+    rhs = rn((4096, 4096), 1.0 / 64, torch.float32)
+    g = rn((1024, 4096), 1.0, torch.float32)
+    cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                                 use_stochastic_rounding=False)
+    ops = 3 * 2 * 1024 * 4096 * 4096
+    min_bytes = 201e6
+    name = ('config 1: int8 [1024,4096]x[4096,4096] f32 in/out, per-channel '
+            'absmax, RNE, fwd+dlhs+drhs')
+
+    def step():
+      out, bp = cfg.vjp(lhs, rhs, DIMS)
+      return out, bp(g)
+  elif args.workload == 'c3':
+    b, t, h, d = 8, 2048, 32, 128
+    q = rn((b, t, h, d), 1.0, torch.bfloat16)
+    k = rn((b, t, h, d), 1.0, torch.bfloat16)
+    g = rn((b, h, t, t), 1.0, torch.bfloat16)
+    cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                                 use_stochastic_rounding=True)
+    noise = {}
+
+    def noise_fn(shape, key):
+      kk = (tuple(shape), int(key[0]), int(key[1]))
+      if kk not in noise:
+        noise[kk] = torch.rand(shape, device=dev, generator=gen) - 0.5
+      return noise[kk]
+
+    for raw in (cfg.dlhs, cfg.drhs):
+      raw.dg_quantizer.lhs.numerics.noise_fn = noise_fn
+      raw.dg_quantizer.rhs.numerics.noise_fn = noise_fn
+    cfg = config.set_context(cfg, key=sr.PRNGKey(1), train_step=None)
+    dims = (((3,), (3,)), ((0, 2), (0, 2)))
+    ops = 3 * 2 * b * h * t * t * d
+    min_bytes = 5.1e9
+    name = ("config 3: int8 einsum 'bthd,bshd->bhts' B8 H32 T=S=2048 D128, "
+            'bf16, per-token scales, fwd + both gradients, stochastic '
+            'rounding from 4 given f32 noise tensors (2 x 4.29 GB + 2 x 0.27 GB '
+            'read on top of the minimum bytes)')
+
+    def step():
+      out, bp = cfg.vjp(q, k, dims)
+      return out, bp(g)
+  else:
+    m, kk, n = args.m, 8192, 28672
+    x = rn((m, kk), 1.0, torch.bfloat16)
+    w = rn((kk, n), kk ** -0.5, torch.bfloat16)
+    cfg = adg.dot_general_make(lhs_bits=8, rhs_bits=4)
+    cfg.fwd.dg_quantizer.rhs.numerics.dtype = utils.int8
+    conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
+    conv(x, w, DIMS)
+    serve = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE)
+    serve.rhs_qtensor = conv.rhs_qtensor
+    del conv
+    wz = torch.empty(0, device=dev)
+    dummy_w = w  # the float weights are not read in SERVE mode
+    ops = 2 * m * kk * n
+    min_bytes = kk * n + m * kk * 2 + m * n * 2 + 2 * n + 2 * m
+    name = (f'config 4: serving GEMM M={m} K=8192 N=28672, int8 activations '
+            'per token x int4-in-int8 frozen weights per channel, bf16 out')
+    del wz
+
+    rhs_qt = serve.rhs_qtensor
+
+    def step():
+      # dg_core is what AqtDotGeneral calls after copying its config; calling
+      # it directly keeps the per-call deepcopy out of a serving loop.
+      return cfg.dg_core(x, dummy_w, None, rhs_qt, DIMS)[0]
+  for _ in range(max(args.warmup, 3)):
+    step()
+  torch.cuda.synchronize()
+  engine.check_status()
+  if args.graph:
+    eager_step = step
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+      keep = eager_step()
+    step = graph.replay
+    for _ in range(3):
+      step()
+    torch.cuda.synchronize()
+  l0 = lib.aqtb200_kernel_launch_count()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  sampler = ClockSampler(0)
+  sampler.start()
+  e0.record()
+  for _ in range(args.steps):
+    step()
+  e1.record()
+  torch.cuda.synchronize()
+  clocks = sampler.stop()
+  engine.check_status()
+  ms = e0.elapsed_time(e1) / args.steps
+  lines.append(json.dumps({
+      'metric': METRIC, 'value': ops / (ms * 1e-3) / 1e12, 'unit': UNIT,
+      'n_gpus': 1, 'steps': args.steps, 'warmup': max(args.warmup, 3),
+      'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
+      'vs_baseline': None, 'dtype': 's8->s32', 'data': 'synthetic',
+      'config': {'workload': name, 'cuda_graph': bool(args.graph)},
+      'min_bytes_gbs': min_bytes / (ms * 1e-3) / 1e9,
+      'clocks': clocks,
+      'gpu_launches': int(lib.aqtb200_kernel_launch_count() - l0),
+  }))
+
+
 def main():
   args = parse_args()
   # Libraries (NCCL's version banner, torchrun notices) write to stdout; the
@@ -414,6 +548,8 @@ def main():
   try:
     if args.impl == 'reference':
       run_reference_arm(args, lines)
+    elif args.workload != 'c2':
+      run_extra_workload(args, lines)
     else:
       run_ours(args, lines)
   finally:
