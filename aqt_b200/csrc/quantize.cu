@@ -31,6 +31,8 @@ struct QParams {
   float clip_bound;
   int per_tensor;
   int pre_vec, noise_vec;  // vector loads allowed on prescale / noise
+  int use_lut;    // 1-byte input, one scale and one prescale for the whole call: byte -> byte table
+  int fast_bf16;  // bf16 in, bf16 scale, fp8 out, no noise: packed bf16 arithmetic
   uint32_t* amax;
   float* sinv;
   uint8_t* q;
@@ -319,6 +321,52 @@ __device__ __forceinline__ uint32_t quant4(const float* v, const float* sinv, co
   return lo | (hi << 16);
 }
 
+// 4 x 4 byte transpose: in[e] holds rows 0..3 of column e, out[j] holds
+// columns 0..3 of row j.
+__device__ __forceinline__ void transpose4x4(const uint32_t* in, uint32_t* out) {
+  const uint32_t t0 = __byte_perm(in[0], in[1], 0x5140);  // a0 b0 a1 b1
+  const uint32_t t1 = __byte_perm(in[0], in[1], 0x7362);  // a2 b2 a3 b3
+  const uint32_t t2 = __byte_perm(in[2], in[3], 0x5140);  // c0 d0 c1 d1
+  const uint32_t t3 = __byte_perm(in[2], in[3], 0x7362);  // c2 d2 c3 d3
+  out[0] = __byte_perm(t0, t2, 0x5410);
+  out[1] = __byte_perm(t0, t2, 0x7632);
+  out[2] = __byte_perm(t1, t3, 0x5410);
+  out[3] = __byte_perm(t1, t3, 0x7632);
+}
+
+// Requantizing a 1-byte tensor with ONE scale (and at most one prescale) is a
+// fixed function of the input byte; each block tabulates it once.
+__device__ __forceinline__ void build_lut(uint8_t* lut, const QParams& P, bool has_pre) {
+  const int t = threadIdx.y * blockDim.x + threadIdx.x;
+  if (t < 256) {
+    float v = P.x.dtype == AQTB200_S8 ? (float)(signed char)t : fp8_to_float((uint8_t)t, P.x.dtype);
+    if (has_pre) v = apply_pre(v, load1(P.pre.ptr, P.pre.dtype, 0), P.t_dtype);
+    lut[t] = quant1(v, P.sinv[0], 0.f, false, P);
+  }
+  __syncthreads();
+}
+__device__ __forceinline__ uint32_t lut4(uint32_t w, const uint8_t* lut) {
+  return (uint32_t)lut[w & 0xffu] | ((uint32_t)lut[(w >> 8) & 0xffu] << 8) |
+         ((uint32_t)lut[(w >> 16) & 0xffu] << 16) | ((uint32_t)lut[w >> 24] << 24);
+}
+
+// Two bf16 values (one raw word) -> two fp8 bytes, all arithmetic in packed
+// bf16: round_bf16(x * pre) then round_bf16(. * sinv), then the saturating
+// RNE convert. A bf16 product is exact in f32, so the packed multiply's single
+// rounding equals "multiply in f32, round to bf16".
+__device__ __forceinline__ uint32_t bf16x2_to_fp8x2(uint32_t w, uint32_t pre2, bool has_pre,
+                                                    uint32_t sinv2, __nv_fp8_interpretation_t k) {
+  __nv_bfloat162 v = *(const __nv_bfloat162*)&w;
+  if (has_pre) v = __hmul2(v, *(const __nv_bfloat162*)&pre2);
+  v = __hmul2(v, *(const __nv_bfloat162*)&sinv2);
+  const uint32_t r = *(const uint32_t*)&v;
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(bf16lo(r), bf16hi(r)), __NV_SATFINITE, k);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  const __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
+  return *(const uint32_t*)&t;
+}
+
 constexpr int kFastRowChunk = 8192;  // elements of one (row, chunk) work unit
 
 // absmax, contraction contiguous, one warp per (batch-row, chunk).
@@ -481,8 +529,10 @@ quant_row_fast(QParams P, int64_t units_per_row, int64_t total_units) {
   constexpr int ES = 16 / EPV;
   constexpr int NV = 16 / EPV;  // input vectors per 16 outputs
   constexpr int UU = 2;
+  __shared__ uint8_t lut[256];
   const DView& x = P.x;
   const bool has_noise = P.noise.ptr != nullptr;
+  if (EPV == 16 && P.use_lut) build_lut(lut, P, PRE != 0);
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   for (int64_t u0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u0 < total_units;
        u0 += nthreads * UU) {
@@ -514,6 +564,39 @@ quant_row_fast(QParams P, int64_t units_per_row, int64_t total_units) {
       float pconst = 0.f;
       if constexpr (PRE == 1) pconst = load1(P.pre.ptr, P.pre.dtype, pbase);
       uint32_t outw[4];
+      if (EPV == 16 && P.use_lut) {
+        const uint32_t rw[4] = {raw[k][0].x, raw[k][0].y, raw[k][0].z, raw[k][0].w};
+#pragma unroll
+        for (int g = 0; g < 4; ++g) outw[g] = lut4(rw[g], lut);
+      } else if (EPV == 8 && P.fast_bf16) {
+        const __nv_fp8_interpretation_t f8k = P.qdtype == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
+        const uint32_t sinv2 = pack_bf16x2(s, s);
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+          const uint32_t rw[4] = {raw[k][n].x, raw[k][n].y, raw[k][n].z, raw[k][n].w};
+          uint32_t pw[4] = {0u, 0u, 0u, 0u};
+          if constexpr (PRE == 1) {
+            pw[0] = pw[1] = pw[2] = pw[3] = pack_bf16x2(pconst, pconst);
+          } else if constexpr (PRE == 2) {
+            float p[8];
+            const int64_t c = col[k] + n * EPV;
+            if (P.pre_vec) {
+              loadN<8>(P.pre.ptr, P.pre.dtype, pbase + c, p);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) p[j] = load1(P.pre.ptr, P.pre.dtype, pbase + (c + j) * P.pre.sc);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) pw[j] = pack_bf16x2(p[2 * j], p[2 * j + 1]);
+          }
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            const uint32_t lo = bf16x2_to_fp8x2(rw[2 * g], pw[2 * g], PRE != 0, sinv2, f8k);
+            const uint32_t hi = bf16x2_to_fp8x2(rw[2 * g + 1], pw[2 * g + 1], PRE != 0, sinv2, f8k);
+            outw[(n * 2 + g) & 3] = lo | (hi << 16);
+          }
+        }
+      } else {
 #pragma unroll
       for (int n = 0; n < NV; ++n) {
         float v[EPV];
@@ -548,6 +631,7 @@ quant_row_fast(QParams P, int64_t units_per_row, int64_t total_units) {
           outw[(n * EPV) / 4 + g] = quant4(v + 4 * g, sinv4, nz, has_noise, P);
         }
       }
+      }
       *(uint4*)(P.q + brow[k] * P.ldq + col[k]) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
     }
   }
@@ -566,9 +650,11 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
   constexpr int ES = 16 / EPV;
   constexpr int TR = 16 * EPV;
   __shared__ __align__(16) uint32_t tile[TR][32];
+  __shared__ uint8_t lut[256];
   const DView& x = P.x;
   const bool has_noise = P.noise.ptr != nullptr;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  if (EPV == 16 && P.use_lut) build_lut(lut, P, PRE != 0);
   for (int64_t uf = blockIdx.x; uf < total_units; uf += gridDim.x) {
     const int64_t u = total_units - 1 - uf;  // back to front, see quant_row_fast
     const int64_t ct = u % col_tiles;
@@ -597,42 +683,64 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
       sinv[j] = P.per_tensor ? P.sinv[0] : (row_ok ? P.sinv[sbase + r0 + j] : 1.f);
     float pconst = 0.f;
     if constexpr (PRE == 1) pconst = load1(P.pre.ptr, P.pre.dtype, pbase);
+    const __nv_fp8_interpretation_t f8k = P.qdtype == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
-      uint32_t word[EPV];
-#pragma unroll
-      for (int j = 0; j < EPV; ++j) word[j] = 0u;
+      uint32_t q4[4][EPV / 4];  // [column e][row group g]: bytes of rows 4g..4g+3
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
         const bool in = row_ok && c < x.cols;
-        float v[EPV];
-        unpack<EPV>(raw[i][e], x.dtype, v);
-        float p = pconst;
-        if constexpr (PRE == 2) p = in ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
+        const uint32_t rw[4] = {raw[i][e].x, raw[i][e].y, raw[i][e].z, raw[i][e].w};
+        if (EPV == 16 && P.use_lut) {
 #pragma unroll
-        for (int g = 0; g < EPV / 4; ++g) {
-          float w4[4], nz[4] = {0.f, 0.f, 0.f, 0.f};
+          for (int g = 0; g < EPV / 4; ++g) q4[e][g] = in ? lut4(rw[g & 3], lut) : 0u;
+        } else if (EPV == 8 && P.fast_bf16) {
+          float p = pconst;
+          if constexpr (PRE == 2) p = in ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
+          const uint32_t pre2 = pack_bf16x2(p, p);
 #pragma unroll
-          for (int j = 0; j < 4; ++j)
-            w4[j] = PRE ? apply_pre(v[4 * g + j], p, P.t_dtype) : v[4 * g + j];
-          if (has_noise && in) {
-            if (P.noise_vec) {
-              loadN<4>(P.noise.ptr, AQTB200_F32, nbase + c * P.noise.sc + r0 + 4 * g, nz);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-                nz[j] = load1(P.noise.ptr, AQTB200_F32,
-                              nbase + c * P.noise.sc + (r0 + 4 * g + j) * P.noise.sr);
-            }
+          for (int g = 0; g < EPV / 4; ++g) {
+            const uint32_t lo = bf16x2_to_fp8x2(rw[(2 * g) & 3], pre2, PRE != 0,
+                                                pack_bf16x2(sinv[(4 * g) % EPV], sinv[(4 * g + 1) % EPV]), f8k);
+            const uint32_t hi = bf16x2_to_fp8x2(rw[(2 * g + 1) & 3], pre2, PRE != 0,
+                                                pack_bf16x2(sinv[(4 * g + 2) % EPV], sinv[(4 * g + 3) % EPV]), f8k);
+            q4[e][g] = in ? (lo | (hi << 16)) : 0u;
           }
-          const uint32_t q4 = in ? quant4(w4, sinv + 4 * g, nz, has_noise, P) : 0u;
+        } else {
+          float v[EPV];
+          unpack<EPV>(raw[i][e], x.dtype, v);
+          float p = pconst;
+          if constexpr (PRE == 2) p = in ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) word[4 * g + j] |= ((q4 >> (8 * j)) & 0xffu) << (8 * e);
+          for (int g = 0; g < EPV / 4; ++g) {
+            float w4[4], nz[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              w4[j] = PRE ? apply_pre(v[4 * g + j], p, P.t_dtype) : v[4 * g + j];
+            if (has_noise && in) {
+              if (P.noise_vec) {
+                loadN<4>(P.noise.ptr, AQTB200_F32, nbase + c * P.noise.sc + r0 + 4 * g, nz);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  nz[j] = load1(P.noise.ptr, AQTB200_F32,
+                                nbase + c * P.noise.sc + (r0 + 4 * g + j) * P.noise.sr);
+              }
+            }
+            q4[e][g] = in ? quant4(w4, sinv + 4 * g, nz, has_noise, P) : 0u;
+          }
         }
       }
 #pragma unroll
-      for (int j = 0; j < EPV; ++j) tile[tx * EPV + j][(i * 16 + ty + 4 * tx) & 31] = word[j];
+      for (int g = 0; g < EPV / 4; ++g) {
+        const uint32_t cols4[4] = {q4[0][g], q4[1][g], q4[2][g], q4[3][g]};
+        uint32_t rows4[4];
+        transpose4x4(cols4, rows4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          tile[tx * EPV + 4 * g + j][(i * 16 + ty + 4 * tx) & 31] = rows4[j];
+      }
     }
     __syncthreads();
 #pragma unroll
@@ -1018,6 +1126,12 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
   if (P.noise.ptr)
     P.noise_vec = row_mode ? row_vec_ok(P.noise, xv->cols) : col_vec_ok(P.noise, xv->rows);
   const int epv = 16 / dtype_size(P.x.dtype);
+  const bool pre_is_scalar = P.pre.ptr == nullptr ||
+                             (P.pre.sb0 == 0 && P.pre.sb1 == 0 && (P.pre.sc == 0 || xv->cols <= 1));
+  P.use_lut = dtype_size(P.x.dtype) == 1 && P.per_tensor && P.noise.ptr == nullptr && pre_is_scalar;
+  P.fast_bf16 = P.x.dtype == AQTB200_BF16 && P.t_dtype == AQTB200_BF16 &&
+                P.s_dtype == AQTB200_BF16 && P.kind == AQTB200_NUM_FP8 && P.noise.ptr == nullptr &&
+                (P.pre.ptr == nullptr || P.pre.dtype == AQTB200_BF16 || true);
   // prescale class: 0 none, 1 constant along the contraction index, 2 varying
   const int pre_kind = P.pre.ptr == nullptr ? 0 : (P.pre.sc == 0 || xv->cols <= 1 ? 1 : 2);
   const bool fast_row = row_mode && row_vec_ok(P.x, xv->cols);

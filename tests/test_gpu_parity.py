@@ -108,6 +108,28 @@ def test_int8_fwd_bwd_bit_exact(dims, ls, rs, np_dtype, use_fwd_quant):
   _exact(dr, wr, 'drhs')
 
 
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+@pytest.mark.parametrize('shape', [(256, 512, 384), (130, 200, 270)])
+def test_int8_per_tensor_fwd_bwd_bit_exact(np_dtype, shape):
+  # per-tensor scales: the stored int8 operands are re-quantized in the
+  # backward pass by a byte -> byte table (one scale, one prescale)
+  m, k, n = shape
+  rng = np.random.default_rng(11)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = util.rand_normal(rng, (m, k), 1.0, np_dtype)
+  rhs = util.rand_normal(rng, (k, n), 0.2, np_dtype)
+  g = util.rand_normal(rng, (m, n), 1.0, np_dtype)
+  cfg = _per_tensor(config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                                           use_stochastic_rounding=False))
+  wo, wl, wr, _ = orc.dg_fwd_bwd(cfg, lhs, rhs, g, dims)
+  out, bp = cfg.vjp(_cuda(lhs), _cuda(rhs), dims)
+  dl, dr = bp(_cuda(g))
+  _sync()
+  _exact(out, wo, 'out')
+  _exact(dl, wl, 'dlhs')
+  _exact(dr, wr, 'drhs')
+
+
 @pytest.mark.parametrize('bits', [2, 4, 8])
 @pytest.mark.parametrize('shape', [(64, 256, 96), (130, 200, 270), (5, 33, 7)])
 def test_int_accumulators_bit_exact(bits, shape):
