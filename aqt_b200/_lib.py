@@ -87,6 +87,11 @@ SYMBOLS = {
     'aqtb200_absmax_scale': (C.c_int, [
         C.POINTER(View), C.POINTER(View), C.POINTER(QuantSpec), C.c_void_p,
         C.c_void_p, C.c_size_t, C.c_void_p]),
+    'aqtb200_absmax_raw': (C.c_int, [
+        C.POINTER(View), C.c_int32, C.c_void_p, C.c_void_p]),
+    'aqtb200_scale_from_amax': (C.c_int, [
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.POINTER(QuantSpec),
+        C.c_void_p, C.c_void_p]),
     'aqtb200_round_up': (C.c_int64, [C.c_int64, C.c_int64]),
     'aqtb200_gemm_dequant': (C.c_int, [
         C.POINTER(GemmDesc), C.c_void_p, C.c_void_p]),

@@ -862,50 +862,70 @@ __device__ __forceinline__ float dequant_one(const GemmParams& P, uint32_t raw, 
   return round_to(round_to(r, P.d_dtype), P.out_dtype);
 }
 
-// VEC: n % 4 == 0, acc 16-byte aligned; four consecutive columns per thread.
+// VEC: n % 4 == 0, acc 16-byte aligned; four consecutive columns per unit and
+// two units in flight per thread.
 template <bool VEC>
 __global__ void __launch_bounds__(256) dequant_acc_kernel(GemmParams P, const uint32_t* acc) {
   constexpr int W = VEC ? 4 : 1;
+  constexpr int UU = 2;
   const int64_t total = P.b0 * P.b1 * P.m * P.n / W;
   const int64_t nq = P.n / W;
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total;
-       i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t col = (i % nq) * W;
-    int64_t t = i / nq;
-    const int64_t row = t % P.m;
-    t /= P.m;
-    const int64_t i1 = t % P.b1, i0 = t / P.b1;
-    uint32_t raw[W];
-    if (VEC) {
-      const uint4 u = __ldg((const uint4*)acc + i);
-      raw[0] = u.x; raw[W > 1 ? 1 : 0] = u.y; raw[W > 1 ? 2 : 0] = u.z; raw[W > 1 ? 3 : 0] = u.w;
-    } else {
-      raw[0] = acc[i];
-    }
-    const float sa = P.a_scale ? load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m) : 1.f;
-    float res[W];
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
+  for (int64_t i0u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0u < total;
+       i0u += nthreads * UU) {
+    uint32_t raw[UU][W];
 #pragma unroll
-    for (int j = 0; j < W; ++j) {
-      const float sb = P.b_scale ? load1(P.b_scale, P.b_scale_dtype, i0 * P.sb_b0 + i1 * P.sb_b1 + (col + j) * P.sb_n) : 1.f;
-      res[j] = dequant_one(P, raw[j], sa, sb);
-    }
-    const int64_t oi = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m + col * P.o_n;
-    const int es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
-    if (VEC && P.o_n == 1 && ((((uintptr_t)P.out) + (size_t)oi * es) & (4 * es - 1)) == 0) {
-      if (es == 2) {
-        __nv_bfloat162 p0 = __floats2bfloat162_rn(res[0], res[W > 1 ? 1 : 0]);
-        __nv_bfloat162 p1 = __floats2bfloat162_rn(res[W > 1 ? 2 : 0], res[W > 1 ? 3 : 0]);
-        *(uint2*)((__nv_bfloat16*)P.out + oi) = make_uint2(*(uint32_t*)&p0, *(uint32_t*)&p1);
-      } else {
-        *(float4*)((float*)P.out + oi) = make_float4(res[0], res[W > 1 ? 1 : 0], res[W > 1 ? 2 : 0], res[W > 1 ? 3 : 0]);
+    for (int k = 0; k < UU; ++k) {
+      const int64_t i = i0u + k * nthreads;
+      if (i < total) {
+        if (VEC) {
+          const uint4 u = __ldg((const uint4*)acc + i);
+          raw[k][0] = u.x; raw[k][W > 1 ? 1 : 0] = u.y; raw[k][W > 1 ? 2 : 0] = u.z;
+          raw[k][W > 1 ? 3 : 0] = u.w;
+        } else {
+          raw[k][0] = acc[i];
+        }
       }
-    } else {
+    }
+#pragma unroll
+    for (int k = 0; k < UU; ++k) {
+      const int64_t i = i0u + k * nthreads;
+      if (i >= total) continue;
+      const int64_t col = (i % nq) * W;
+      int64_t t = i / nq;
+      const int64_t row = t % P.m;
+      t /= P.m;
+      const int64_t i1 = t % P.b1, i0 = t / P.b1;
+      const float sa = P.a_scale ? load1(P.a_scale, P.a_scale_dtype,
+                                         i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m)
+                                 : 1.f;
+      float res[W];
 #pragma unroll
       for (int j = 0; j < W; ++j) {
-        if (es == 2)
-          ((__nv_bfloat16*)P.out)[oi + j * P.o_n] = __float2bfloat16_rn(res[j]);
-        else
-          ((float*)P.out)[oi + j * P.o_n] = res[j];
+        const float sb = P.b_scale ? load1(P.b_scale, P.b_scale_dtype,
+                                           i0 * P.sb_b0 + i1 * P.sb_b1 + (col + j) * P.sb_n)
+                                   : 1.f;
+        res[j] = dequant_one(P, raw[k][j], sa, sb);
+      }
+      const int64_t oi = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m + col * P.o_n;
+      if (VEC && P.o_n == 1 && ((((uintptr_t)P.out) + (size_t)oi * es) & (4 * es - 1)) == 0) {
+        if (es == 2) {
+          __nv_bfloat162 p0 = __floats2bfloat162_rn(res[0], res[W > 1 ? 1 : 0]);
+          __nv_bfloat162 p1 = __floats2bfloat162_rn(res[W > 1 ? 2 : 0], res[W > 1 ? 3 : 0]);
+          *(uint2*)((__nv_bfloat16*)P.out + oi) = make_uint2(*(uint32_t*)&p0, *(uint32_t*)&p1);
+        } else {
+          *(float4*)((float*)P.out + oi) =
+              make_float4(res[0], res[W > 1 ? 1 : 0], res[W > 1 ? 2 : 0], res[W > 1 ? 3 : 0]);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < W; ++j) {
+          if (es == 2)
+            ((__nv_bfloat16*)P.out)[oi + j * P.o_n] = __float2bfloat16_rn(res[j]);
+          else
+            ((float*)P.out)[oi + j * P.o_n] = res[j];
+        }
       }
     }
   }
@@ -1089,7 +1109,7 @@ int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st) {
   AQT_REQUIRE(acc != nullptr && d->out != nullptr, AQTB200_EINVAL, "null accumulator or output");
   const int64_t total = d->b0 * d->b1 * d->m * d->n;
   const bool vec = d->n % 4 == 0 && (((uintptr_t)acc) & 15) == 0;
-  int grid = (int)std::min<int64_t>((total / (vec ? 4 : 1) + 255) / 256, (int64_t)sm_count() * 8);
+  int grid = (int)std::min<int64_t>((total / (vec ? 4 : 1) + 511) / 512, (int64_t)sm_count() * 8);
   grid = std::max(grid, 1);
   if (vec)
     dequant_acc_kernel<true><<<grid, 256, 0, st>>>(P, (const uint32_t*)acc);

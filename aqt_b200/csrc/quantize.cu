@@ -770,6 +770,8 @@ struct FinalizeParams {
   int t_dtype, s_dtype;
   float quant_bound, clipping_scale;
   int po2;
+  const void* pre;  // optional single prescale applied to the maximum
+  int pre_dtype;
 };
 
 __global__ void finalize_scale_kernel(FinalizeParams F) {
@@ -780,6 +782,7 @@ __global__ void finalize_scale_kernel(FinalizeParams F) {
     s = load1(F.scale_in, F.s_dtype, i);
   } else {
     float a = __uint_as_float(F.amax[i]);
+    if (F.pre != nullptr) a = apply_pre_abs(a, load1(F.pre, F.pre_dtype, 0), F.t_dtype);
     if (a == 0.f) a = 1.f;
     float bound = F.clipping_scale != 0.f
                       ? round_to(__fmul_rn(a, F.clipping_scale), F.t_dtype)
@@ -801,6 +804,7 @@ __global__ void finalize_scale_kernel(FinalizeParams F) {
     else
       ((float*)F.scale_out)[i] = s;
   }
+  if (F.sinv == nullptr) return;
   float inv = round_to(__fdiv_rn(1.f, s), F.s_dtype);
   if (isinf(inv)) inv = 1.f;
   F.sinv[i] = inv;
@@ -1088,18 +1092,23 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
                const aqtb200_view* noisev, const aqtb200_quant_spec* spec,
                const void* scale_in, void* q_out, void* scale_out,
                void* workspace, size_t workspace_bytes, cudaStream_t st,
-               bool want_q) {
+               bool want_q, float* amax_only_out = nullptr) {
   int rc = validate(xv, prev, noisev, spec, want_q);
   if (rc) return rc;
   const int64_t ns = n_scales(xv, spec);
   const int64_t nbrow = xv->b0 * xv->b1 * xv->rows;
   const int64_t total = nbrow * xv->cols;
   if (ns == 0) return 0;
-  size_t need = aqtb200_quantize_workspace_bytes(xv, spec);
-  AQT_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned(workspace, 256),
-              AQTB200_EWORKSPACE, "workspace: need %zu bytes, 256-byte aligned (got %zu)",
-              need, workspace_bytes);
-  AQT_REQUIRE(scale_out != nullptr || scale_in != nullptr, AQTB200_EINVAL, "scale_out is null");
+  if (amax_only_out != nullptr) {
+    workspace = amax_only_out;  // the maxima land in the caller's buffer
+  } else {
+    size_t need = aqtb200_quantize_workspace_bytes(xv, spec);
+    AQT_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned(workspace, 256),
+                AQTB200_EWORKSPACE, "workspace: need %zu bytes, 256-byte aligned (got %zu)",
+                need, workspace_bytes);
+    AQT_REQUIRE(scale_out != nullptr || scale_in != nullptr, AQTB200_EINVAL,
+                "scale_out is null");
+  }
   if (want_q) AQT_REQUIRE(q_out != nullptr && aligned(q_out, 16), AQTB200_EINVAL,
                           "q_out null or not 16-byte aligned");
 
@@ -1190,6 +1199,7 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
       AQT_CUDA_OK(cudaGetLastError()); count_launch();
     }
   }
+  if (amax_only_out != nullptr) return 0;
   FinalizeParams F{};
   F.amax = P.amax; F.scale_in = scale_in; F.scale_out = scale_out; F.sinv = P.sinv;
   F.n = ns; F.t_dtype = P.t_dtype; F.s_dtype = P.s_dtype;
@@ -1297,6 +1307,39 @@ int aqtb200_quantize_static(const aqtb200_view* x, const aqtb200_view* prescale,
   if (rc) return rc;
   return run(x, prescale, noise, spec, scale_in, q_out, scale_out, scratch,
              sizeof(g_static_scratch), (cudaStream_t)stream, true);
+}
+
+int aqtb200_absmax_raw(const aqtb200_view* x, int32_t per_tensor, float* amax_out, void* stream) {
+  AQT_REQUIRE(x != nullptr && amax_out != nullptr, AQTB200_EINVAL, "null argument");
+  aqtb200_quant_spec spec{};
+  spec.kind = AQTB200_NUM_INT;  // only the reduction runs; numerics are irrelevant
+  spec.qdtype = AQTB200_S8;
+  spec.quant_bound = spec.clip_bound = 1.f;
+  spec.per_tensor = per_tensor;
+  spec.compute_dtype = spec.scale_dtype = x->dtype == AQTB200_BF16 ? AQTB200_BF16 : AQTB200_F32;
+  return run(x, nullptr, nullptr, &spec, nullptr, nullptr, nullptr, nullptr, 0,
+             (cudaStream_t)stream, false, amax_out);
+}
+
+int aqtb200_scale_from_amax(const float* amax, int64_t n, const void* prescale,
+                            int32_t prescale_dtype, const aqtb200_quant_spec* spec,
+                            void* scale_out, void* stream) {
+  AQT_REQUIRE(amax != nullptr && spec != nullptr && scale_out != nullptr && n >= 0, AQTB200_EINVAL,
+              "null argument");
+  AQT_REQUIRE(is_float_dt(spec->compute_dtype) && is_float_dt(spec->scale_dtype), AQTB200_EINVAL,
+              "compute/scale dtype must be f32 or bf16");
+  AQT_REQUIRE(spec->quant_bound > 0.f, AQTB200_EINVAL, "quant_bound must be positive");
+  if (prescale != nullptr)
+    AQT_REQUIRE(is_float_dt(prescale_dtype), AQTB200_EINVAL, "prescale must be f32 or bf16");
+  if (n == 0) return 0;
+  FinalizeParams F{};
+  F.amax = (const uint32_t*)amax; F.scale_out = scale_out; F.sinv = nullptr; F.n = n;
+  F.t_dtype = spec->compute_dtype; F.s_dtype = spec->scale_dtype;
+  F.quant_bound = spec->quant_bound; F.clipping_scale = spec->clipping_scale;
+  F.po2 = spec->po2_scale; F.pre = prescale; F.pre_dtype = prescale_dtype;
+  finalize_scale_kernel<<<(int)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(F);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
 }
 
 int aqtb200_absmax_scale(const aqtb200_view* x, const aqtb200_view* prescale,

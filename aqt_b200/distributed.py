@@ -128,10 +128,34 @@ class ShardedDotGeneral:
       # lhs scale [M,1] (or a scalar) varies along g's contraction axis M
       pre = fwd_scale.reshape(-1, 1) if fwd_scale.numel() > 1 else (
           fwd_scale.reshape(1, 1))
-    g_qt = self._global_scale(cfg.drhs.dg_quantizer.lhs, g, [0], 0,
-                              prescale=pre)
+    # Per-tensor scales everywhere: one pass over g and one max-all-reduce give
+    # the cotangent's scale for both gradient dots.
+    shared = None
+    try:
+      shared = engine.shared_cotangent_scales(cfg, res, g,
+                                              reduce_max=self._max)
+    except NotImplementedError:
+      shared = None
+    d_dims, d_perm = upd(dims, False, g.ndim, res.rhs.mt.x.ndim)
+    if shared is not None:
+      g_qt_dlhs, g_qt = shared
+    else:
+      g_qt = self._global_scale(cfg.drhs.dg_quantizer.lhs, g, [0], 0,
+                                prescale=pre)
+      # Every cross-rank scale is agreed on BEFORE the big all-reduce starts:
+      # a small collective queued behind it on the same communicator would
+      # wait for it and serialise the dlhs pass after it.
+      _, fwd_scale_r, _ = self._other_operand(cfg.dlhs, res.rhs.mt)
+      pre_r = None
+      if fwd_scale_r is not None:
+        # rhs scale [1,N] laid along g's [M,N]: constant along the kept axis M
+        pre_r = fwd_scale_r.reshape(1, -1) if fwd_scale_r.numel() > 1 else (
+            fwd_scale_r.reshape(1, 1))
+      g_qt_dlhs = self._global_scale(cfg.dlhs.dg_quantizer.lhs, g, [1], 0,
+                                     prescale=pre_r)
     x_qt = self._global_scale(cfg.drhs.dg_quantizer.rhs, other, [0], 0,
                               compute_dtype=other_dt)
+
     deferred, work, drhs = None, None, None
     if g_qt is None and x_qt is None:  # unquantized gradient dot
       drhs = engine.dg_raw(cfg.drhs, g, res.lhs.mt, None, None, r_dims,
@@ -144,15 +168,7 @@ class ShardedDotGeneral:
       work = self._sum_async(deferred.acc)
 
     # dlhs = g[M,N] . rhs'[K,N]^T : rows of g sharded, contraction over N local
-    d_dims, d_perm = upd(dims, False, g.ndim, res.rhs.mt.x.ndim)
-    _, fwd_scale, _ = self._other_operand(cfg.dlhs, res.rhs.mt)
-    pre = None
-    if fwd_scale is not None:
-      # rhs scale [1,N] laid along g's [M,N]: constant along the kept axis M
-      pre = fwd_scale.reshape(1, -1) if fwd_scale.numel() > 1 else (
-          fwd_scale.reshape(1, 1))
-    g_qt = self._global_scale(cfg.dlhs.dg_quantizer.lhs, g, [1], 0,
-                              prescale=pre)
+    g_qt = g_qt_dlhs
     if work is not None and self.overlap_sms and not engine._HOST_TEST_MODE:  # pylint: disable=protected-access
       engine.set_gemm_sm_budget(max(engine.sm_count() - self.overlap_sms, 2))
     try:

@@ -521,11 +521,18 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
     # a dim of extent 1 gets stride 1 so either kernel mode is admissible
     return 1 if extent == 1 else stride
 
+  def row_stride(stride, extent, k_stride):
+    # a single row takes the dense stride when the contraction index is
+    # contiguous, so that the 16-byte-vector kernels still apply
+    if extent == 1:
+      return K if dense(k_stride, K) == 1 else 1
+    return stride
+
   desc = _lib.DgRawDesc()
   desc.lhs = _view(L.t.data_ptr(), _code(L.t.dtype), B, M, K, bs(0),
-                   dense(ms[0], M), dense(ks[0], K))
+                   row_stride(ms[0], M, ks[0]), dense(ks[0], K))
   desc.rhs = _view(R.t.data_ptr(), _code(R.t.dtype), B, N, K, bs(1),
-                   dense(ns[0], N), dense(ks[1], K))
+                   row_stride(ns[0], N, ks[1]), dense(ks[1], K))
   ti_b, ti_m, ti_n, ti_k = 3, 2, 2, 2
   if pre_t is not None:
     desc.lhs_prescale = _view(pre_t.data_ptr(), _code(pre_t.dtype), B, 1, K,
@@ -763,8 +770,10 @@ def _single_operand(x, shared_axes):
     return _single_operand(xc.permute(*inv), shared_axes)
   (rows, rs), = rdims or [(1, [1])]
   (cols, cs), = kdims or [(1, [1])]
-  rs = 1 if rows == 1 else rs[0]
   cs = 1 if cols == 1 else cs[0]
+  # a single row: give it the dense stride, so the 16-byte-vector kernels
+  # (which want row starts aligned) still apply
+  rs = (cols * cs if cs == 1 else 1) if rows == 1 else rs[0]
   if rs != 1 and cs != 1:
     xc = x.permute(*ra, *ca).contiguous()
     order = ra + ca
@@ -831,6 +840,87 @@ def absmax_scale(x, shared_axes, numerics, scale_dtype=None,
       C.byref(spec), sbuf.data_ptr(), ws.data_ptr(), ws.numel(), _stream())
   _lib.check(rc, 'aqtb200_absmax_scale')
   return _logical_scale(sbuf, op, per_tensor)
+
+
+def absmax_raw(x):
+  """max |x| over the whole tensor as a 1-element f32 device tensor."""
+  op, view, rows, cols = _single_operand(x, list(range(x.ndim)))
+  out = torch.empty(1, dtype=torch.float32, device=x.device)
+  rc = _lib.load().aqtb200_absmax_raw(C.byref(view), 1, out.data_ptr(),
+                                      _stream())
+  _lib.check(rc, 'aqtb200_absmax_raw')
+  return out
+
+
+def scale_from_amax(amax, numerics, compute_dtype, scale_dtype=None,
+                    clipping_scale=None, po2_scale=False, prescale=None,
+                    ndim=2):
+  """Per-tensor scale from a precomputed maximum (and one prescale value).
+
+  Returns the scale with `ndim` axes of extent 1, like the reference's
+  per-tensor scale.
+  """
+  code = _code(compute_dtype)
+  spec = _spec_for(numerics, code, scale_dtype, True, clipping_scale, po2_scale)
+  out = torch.empty(1, dtype=_CODE_TORCH[spec.scale_dtype], device=amax.device)
+  pre_ptr, pre_code = None, 0
+  if prescale is not None:
+    assert prescale.numel() == 1
+    pre_ptr, pre_code = prescale.data_ptr(), _code(prescale.dtype)
+  rc = _lib.load().aqtb200_scale_from_amax(
+      amax.data_ptr(), 1, pre_ptr, pre_code, C.byref(spec), out.data_ptr(),
+      _stream())
+  _lib.check(rc, 'aqtb200_scale_from_amax')
+  return out.view([1] * ndim)
+
+
+def _per_tensor_absmax(quantizer):
+  """Calibration keywords if the quantizer is per-tensor AbsMax, else None."""
+  if type(quantizer.numerics).__name__ == 'NoNumerics':
+    return None
+  if quantizer.calib_shared_axes != 'per_tensor':
+    return None
+  kw = _calibration_kwargs(quantizer)
+  if getattr(quantizer.numerics, 'noise_fn', None):
+    pass  # noise does not change the scale
+  return kw
+
+
+def shared_cotangent_scales(cfg, res, g, reduce_max=None):
+  """Scales of the cotangent for dlhs and drhs from ONE pass over it.
+
+  Applies when both gradient dots quantize g with a per-tensor scale and the
+  forward scales folded into g (use_fwd_quant) are per-tensor too: then
+  max|g * s| = |round(max|g| * s)| and a single raw maximum serves both.
+  `reduce_max`, if given, is applied to the raw maximum (cross-rank max).
+  Returns (g_qt_dlhs, g_qt_drhs) as incomplete QTensors, or None.
+  """
+  from aqt_b200.v2 import aqt_tensor
+  ql, qr = cfg.dlhs.dg_quantizer.lhs, cfg.drhs.dg_quantizer.lhs
+  kwl, kwr = _per_tensor_absmax(ql), _per_tensor_absmax(qr)
+  if kwl is None or kwr is None:
+    return None
+  pres = []
+  for raw, mt in ((cfg.dlhs, res.rhs.mt), (cfg.drhs, res.lhs.mt)):
+    if raw.rhs.use_fwd_quant:
+      if mt.qx.scale is None or len(mt.qx.scale) != 1 or (
+          mt.qx.scale[0].numel() != 1):
+        return None
+      pres.append(mt.qx.scale[0])
+    else:
+      pres.append(None)
+  amax = absmax_raw(g)
+  if reduce_max is not None:
+    amax = reduce_max(amax)
+  out = []
+  dd = utils.as_dtype(g.dtype)
+  for q, kw, pre in ((ql, kwl, pres[0]), (qr, kwr, pres[1])):
+    scale = scale_from_amax(
+        amax, q.numerics, g.dtype, kw.get('dtype', q.scale_dtype),
+        kw.get('clipping_scale'), kw.get('po2_scale', False), pre, g.ndim)
+    out.append(aqt_tensor.QTensor(qvalue=None, scale=[scale], scale_t=None,
+                                  bias=[], dequant_dtype=dd))
+  return tuple(out)
 
 
 def quantize_with_scale(x, scale, numerics, noise=None):

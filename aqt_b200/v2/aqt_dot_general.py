@@ -520,11 +520,21 @@ def dg_core_vjp_bwd(fwd_dimension_numbers, res, g):
       'dg_res can only be None in 2nd derivative. It is not yet supported.')
   g = g[0]  # g[1] would be the gradient w.r.t. the returned QTensors.
 
+  from aqt_b200 import engine
+  # One pass over the cotangent can serve both of its quantizations when all
+  # the scales involved are per-tensor; otherwise each raw dot calibrates it.
+  shared = None
+  if cfg.dlhs.local_aqt is None and cfg.drhs.local_aqt is None:
+    try:
+      shared = engine.shared_cotangent_scales(cfg, dg_res, g)
+    except NotImplementedError:
+      shared = None
+
   def grad_dot_general(y_res: TensorRes, quant_grad, dg_raw, y_is_lhs):
     dims, out_transpose_axes = _update_dimension_numbers_for_backward(
         fwd_dimension_numbers, y_is_lhs, g.ndim, y_res.mt.x.ndim)
-    from aqt_b200 import engine
-    out = engine.dg_raw(dg_raw, g, y_res.mt, None, None, dims,
+    g_qt = None if shared is None else shared[1 if y_is_lhs else 0]
+    out = engine.dg_raw(dg_raw, g, y_res.mt, g_qt, None, dims,
                         out_transpose_axes=out_transpose_axes)[0]
     if isinstance(quant_grad, str):
       raise AssertionError(quant_grad)

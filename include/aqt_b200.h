@@ -166,6 +166,26 @@ int aqtb200_absmax_scale(const aqtb200_view* x, const aqtb200_view* prescale,
                          const aqtb200_quant_spec* spec, void* scale_out,
                          void* workspace, size_t workspace_bytes, void* stream);
 
+/*
+ * The two halves of aqtb200_absmax_scale, for callers that combine maxima
+ * before turning them into scales -- several ranks holding shards of one
+ * tensor (max-all-reduce in between), or one tensor that is quantized more
+ * than once with different prescales, as the cotangent is in the backward
+ * pass (aqt_dot_general.py:1206-1217).
+ *   aqtb200_absmax_raw     : amax_out[i] = max |x| over the contraction index
+ *                            (or the whole tensor), f32, 0 for an all-zero unit;
+ *   aqtb200_scale_from_amax: scale = where(a==0,1,a)[*clipping]/quant_bound with
+ *                            a = |round_T(amax * round_T(prescale[0]))|. Because
+ *                            rounding is monotone this equals the maximum of the
+ *                            prescaled elements whenever ONE prescale value
+ *                            covers the reduced range (per-tensor forward scale).
+ */
+int aqtb200_absmax_raw(const aqtb200_view* x, int32_t per_tensor, float* amax_out,
+                       void* stream);
+int aqtb200_scale_from_amax(const float* amax, int64_t n, const void* prescale,
+                            int32_t prescale_dtype, const aqtb200_quant_spec* spec,
+                            void* scale_out, void* stream);
+
 int64_t aqtb200_round_up(int64_t v, int64_t multiple);
 
 /*

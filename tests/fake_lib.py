@@ -150,6 +150,32 @@ class FakeLib:
     return self._quantize(_deref(x, _lib.View), _deref(pre, _lib.View), None,
                           _deref(spec, _lib.QuantSpec), None, None, scale_out)
 
+  def aqtb200_absmax_raw(self, x, per_tensor, amax_out, stream):
+    x = _deref(x, _lib.View)
+    xv = np.abs(_view_array(x).astype(np.float32))
+    n = 1 if per_tensor else x.b0 * x.b1 * x.rows
+    a = xv.max(initial=0) if per_tensor else xv.max(axis=3, initial=0).reshape(-1)
+    _strided(amax_out, _lib.F32, [n], [1], True)[...] = a
+    return 0
+
+  def aqtb200_scale_from_amax(self, amax, n, pre, pre_dtype, spec, scale_out,
+                              stream):
+    spec = _deref(spec, _lib.QuantSpec)
+    T = _NP[spec.compute_dtype]
+    S = _NP[spec.scale_dtype]
+    a = np.array(_strided(amax, _lib.F32, [n], [1])).astype(T)
+    if pre:
+      p = np.array(_strided(pre, pre_dtype, [1], [1])).astype(np.float32).astype(T)
+      a = np.abs(orc.mul(a, p))
+    a = np.where(a == 0, np.ones_like(a), a).astype(T)
+    bound = orc.mul(a, np.asarray(spec.clipping_scale, T)) if (
+        spec.clipping_scale) else a
+    scale = orc.div(bound, np.asarray(spec.quant_bound, T))
+    if spec.po2_scale:
+      scale = orc.ceil_to_po2(scale)
+    _strided(scale_out, spec.scale_dtype, [n], [1], True)[...] = scale.astype(S)
+    return 0
+
   # -- gemm
   def _gemm(self, g, acc_in=None):
     ext = [g.b0, g.b1]
