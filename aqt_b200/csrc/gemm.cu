@@ -101,6 +101,32 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   }
 }
 
+// Wait used where a whole warp idles for most of a tile (the epilogue warps
+// while the mainloop runs): lane 0 polls with a sleep between polls, so 8 warps
+// do not occupy issue slots the MMA and TMA warps could use; once it has seen
+// the phase every lane observes the barrier itself (one poll that succeeds).
+__device__ __forceinline__ bool mbar_wait_warp_idle(uint64_t* bar, uint32_t parity,
+                                                    volatile int* abort_flag, int lane) {
+#ifdef AQT_EPI_SPIN
+  return mbar_wait(bar, parity, abort_flag);
+#endif
+  int ok = 1;
+  if (lane == 0 && !mbar_try_wait(bar, parity)) {
+    const long long t0 = clock64();
+    int it = 0;
+    for (;;) {
+      __nanosleep(96);
+      if (mbar_try_wait(bar, parity)) break;
+      if ((++it & 63) == 0) {
+        if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { ok = 0; break; }
+      }
+    }
+  }
+  ok = __shfl_sync(0xffffffffu, ok, 0);
+  if (!ok) return false;
+  return mbar_wait(bar, parity, abort_flag);
+}
+
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, uint64_t* bar,
                                             int c0, int c1, int c2, int c3) {
   asm volatile(
@@ -510,7 +536,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const int64_t row = mt * BM + quarter * 32 + lane;
       EpiScales sc;
       load_epi_scales<EPI>(P, lane, i0, i1, row, nt * BN + half * 128, sc);
-      int ok = mbar_wait(&tfull_bar[buf], aphase, abortp) ? 1 : 0;
+      int ok = mbar_wait_warp_idle(&tfull_bar[buf], aphase, abortp, lane) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
       tc_fence_after();
@@ -755,7 +781,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       const int64_t row = mt * BM2 + rank * 128 + quarter * 32 + lane;
       EpiScales sc;
       load_epi_scales<EPI>(P, lane, i0, i1, row, nt * BN + half * 128, sc);
-      int ok = mbar_wait(&tfull_bar[buf], aphase, abortp) ? 1 : 0;
+      int ok = mbar_wait_warp_idle(&tfull_bar[buf], aphase, abortp, lane) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
       tc_fence_after();
