@@ -16,6 +16,8 @@
 #include <cudaTypedefs.h>
 
 #include <algorithm>
+#include <cstdlib>
+#include <cstring>
 
 #include "common.cuh"
 
@@ -51,7 +53,9 @@ struct GemmParams {
   uint32_t idesc, idesc2;
   int64_t m_tiles, n_tiles, total_tiles, num_kb;
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
+  int64_t n_tiles3, total_tiles3;  // 512-column tiles of the wide CTA-pair kernel
   int stage_ok;  // output rows can be written as aligned 16-byte pieces
+  int tma_store;  // a tensor map of the bf16 output exists: staged rows leave through the TMA unit
   int32_t* status;
   // SIMT reference kernel only:
   const uint8_t* a; const uint8_t* b;
@@ -101,32 +105,6 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
   }
 }
 
-// Wait used where a whole warp idles for most of a tile (the epilogue warps
-// while the mainloop runs): lane 0 polls with a sleep between polls, so 8 warps
-// do not occupy issue slots the MMA and TMA warps could use; once it has seen
-// the phase every lane observes the barrier itself (one poll that succeeds).
-__device__ __forceinline__ bool mbar_wait_warp_idle(uint64_t* bar, uint32_t parity,
-                                                    volatile int* abort_flag, int lane) {
-#ifdef AQT_EPI_SPIN
-  return mbar_wait(bar, parity, abort_flag);
-#endif
-  int ok = 1;
-  if (lane == 0 && !mbar_try_wait(bar, parity)) {
-    const long long t0 = clock64();
-    int it = 0;
-    for (;;) {
-      __nanosleep(96);
-      if (mbar_try_wait(bar, parity)) break;
-      if ((++it & 63) == 0) {
-        if (*abort_flag || clock64() - t0 > WAIT_LIMIT_CYCLES) { ok = 0; break; }
-      }
-    }
-  }
-  ok = __shfl_sync(0xffffffffu, ok, 0);
-  if (!ok) return false;
-  return mbar_wait(bar, parity, abort_flag);
-}
-
 __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, uint64_t* bar,
                                             int c0, int c1, int c2, int c3) {
   asm volatile(
@@ -134,6 +112,21 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, ui
       " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
       "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+
+// Shared memory -> global tile store through the TMA unit (bulk async group).
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap* tm, const void* src, int c0, int c1,
+                                             int c2, int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tm),
+      "r"(smem_u32(src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+// Blocks until the TMA unit has finished READING the shared memory of every
+// store this thread has issued (the global writes may still be in flight).
+__device__ __forceinline__ void tma_store_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -174,6 +167,16 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t* r) {
         "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]),
         "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]),
         "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
       : "r"(taddr)
       : "memory");
 }
@@ -266,6 +269,11 @@ template <bool IS_INT, int EPI>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t taddr, int lane,
                                               int64_t i0, int64_t i1, int64_t row, int64_t ncol0,
                                               uint8_t* stage, const EpiScales& sc) {
+  if (P.tma_store && stage != nullptr) {
+    // an earlier tile of this warp may have left through the TMA unit
+    if (lane == 0) tma_store_wait_read();
+    __syncwarp();
+  }
   const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
   const int out_es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
   const bool row_ok = row < P.m;
@@ -427,10 +435,97 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tadd
   }
 }
 
+// bf16 epilogue for a full 128-column slice of an accumulator (dequant, output
+// and scales all bf16; no raw-accumulator output): TMEM is read 16 columns at a
+// time with the next read in flight while the current one is converted, rows
+// are staged in the 128-byte swizzle of the output tensor map, and each
+// 32 x 64 block leaves with one TMA store (rows past M are clipped by the unit).
+// Without an output map the same staged rows are stored by the warp.
+template <bool IS_INT>
+__device__ __forceinline__ void epilogue_tile_bf16(const GemmParams& P, const CUtensorMap* tmO,
+                                                   uint32_t taddr, int lane, int64_t i0,
+                                                   int64_t i1, int64_t row, int64_t ncol0,
+                                                   uint8_t* stage, const EpiScales& sc) {
+  const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
+  const bool vary_b = has_b && P.sb_n != 0;
+  const __nv_bfloat162 sa2 = __float2bfloat162_rn(sc.sa);
+  const int64_t row0 = row - lane;
+  uint8_t* srow = stage + lane * kStagePitch;
+  uint32_t buf[2][16];
+  tc_ld16(taddr, buf[0]);
+#pragma unroll 1
+  for (int g = 0; g < 2; ++g) {  // 64-column groups
+    // the staging rows are free once the store of the previous group has read them
+    if (P.tma_store && lane == 0) tma_store_wait_read();
+    __syncwarp();
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {  // 16-column pieces
+      tc_wait_ld();
+      if (h < 3 || g == 0) tc_ld16(taddr + (uint32_t)((g * 4 + h + 1) * 16), buf[(h + 1) & 1]);
+      const uint32_t* acc = buf[h & 1];
+      const uint32_t sbw = g ? (h < 2 ? sc.sbw[2] : sc.sbw[3]) : (h < 2 ? sc.sbw[0] : sc.sbw[1]);
+      uint32_t pk[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        uint32_t w = vary_b ? __shfl_sync(0xffffffffu, sbw, (h & 1) * 8 + j) : sbw;
+        const __nv_bfloat162 sb2 = *(const __nv_bfloat162*)&w;
+        const float f0 = IS_INT ? __int2float_rn((int)acc[2 * j]) : __uint_as_float(acc[2 * j]);
+        const float f1 = IS_INT ? __int2float_rn((int)acc[2 * j + 1]) : __uint_as_float(acc[2 * j + 1]);
+        __nv_bfloat162 v = __floats2bfloat162_rn(f0, f1);
+        if (P.b_scale_first) {
+          if (has_b) v = __hmul2(v, sb2);
+          if (has_a) v = __hmul2(v, sa2);
+        } else {
+          if (has_a) v = __hmul2(v, sa2);
+          if (has_b) v = __hmul2(v, sb2);
+        }
+        pk[j] = *(const uint32_t*)&v;
+      }
+#pragma unroll
+      for (int v = 0; v < 2; ++v)
+        *(uint4*)(srow + (((h * 2 + v) ^ (lane & 7)) * 16)) =
+            make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+    }
+    if (P.tma_store) {
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0 && row0 < P.m)
+        tma_store_4d(tmO, stage, (int)(ncol0 + g * 64), (int)row0, (int)i1, (int)i0);
+    } else {
+      __syncwarp();
+      __nv_bfloat16* ob = (__nv_bfloat16*)P.out + i0 * P.o_b0 + i1 * P.o_b1 + ncol0 + g * 64;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int r = i * 4 + (lane >> 3), seg = lane & 7;
+        if (row0 + r < P.m) {
+          const uint4 v = *(const uint4*)(stage + r * kStagePitch + ((seg ^ (r & 7)) * 16));
+          *(uint4*)(ob + (row0 + r) * P.o_m + seg * 8) = v;
+        }
+      }
+    }
+  }
+}
+
+// Picks the epilogue for one 128-column slice (the choice is warp-uniform).
+template <bool IS_INT, int EPI>
+__device__ __forceinline__ void epilogue_slice(const GemmParams& P, const CUtensorMap* tmO,
+                                               uint32_t taddr, int lane, int64_t i0, int64_t i1,
+                                               int64_t row, int64_t ncol0, uint8_t* stage,
+                                               const EpiScales& sc) {
+  if constexpr (EPI == 1) {
+    if (P.stage_ok && P.acc_out == nullptr && P.out != nullptr && ncol0 + 128 <= P.n) {
+      epilogue_tile_bf16<IS_INT>(P, tmO, taddr, lane, i0, i1, row, ncol0, stage, sc);
+      return;
+    }
+  }
+  epilogue_tile<IS_INT, EPI>(P, taddr, lane, i0, i1, row, ncol0, stage, sc);
+}
+
 template <bool IS_INT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
-                    const __grid_constant__ CUtensorMap tmB, GemmParams P) {
+                    const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmO, GemmParams P) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* smem_a = smem;
@@ -441,7 +536,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ __align__(16) uint8_t epi_stage[EPI_WARPS][32 * kStagePitch];
+  __shared__ __align__(1024) uint8_t epi_stage[EPI_WARPS][32 * kStagePitch];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -536,12 +631,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       const int64_t row = mt * BM + quarter * 32 + lane;
       EpiScales sc;
       load_epi_scales<EPI>(P, lane, i0, i1, row, nt * BN + half * 128, sc);
-      int ok = mbar_wait_warp_idle(&tfull_bar[buf], aphase, abortp, lane) ? 1 : 0;
+      int ok = mbar_wait(&tfull_bar[buf], aphase, abortp) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
       tc_fence_after();
-      epilogue_tile<IS_INT, EPI>(
-          P, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128), lane,
+      epilogue_slice<IS_INT, EPI>(
+          P, &tmO, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128), lane,
           i0, i1, row, nt * BN + half * 128, epi_stage[warp - 2], sc);
       tc_fence_before();
       __syncwarp();
@@ -549,6 +644,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       buf ^= 1;
       if (buf == 0) aphase ^= 1;
     }
+    if (lane == 0) tma_store_wait_read();  // shared memory outlives its last store
     if (fail && lane == 0) { *abortp = 1; if (P.status) atomicCAS(P.status, 0, 3); }
   }
 
@@ -661,7 +757,8 @@ __device__ __forceinline__ void decode_tile2(const GemmParams& P, int64_t t, int
 template <bool IS_INT, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
-                         const __grid_constant__ CUtensorMap tmB, GemmParams P) {
+                         const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmO, GemmParams P) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* smem_a = smem;
@@ -672,7 +769,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   __shared__ __align__(8) uint64_t tempty_bar[2];       // used in the even CTA only
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ __align__(16) uint8_t epi_stage[EPI_WARPS][32 * kStagePitch];
+  __shared__ __align__(1024) uint8_t epi_stage[EPI_WARPS][32 * kStagePitch];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -781,12 +878,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       const int64_t row = mt * BM2 + rank * 128 + quarter * 32 + lane;
       EpiScales sc;
       load_epi_scales<EPI>(P, lane, i0, i1, row, nt * BN + half * 128, sc);
-      int ok = mbar_wait_warp_idle(&tfull_bar[buf], aphase, abortp, lane) ? 1 : 0;
+      int ok = mbar_wait(&tfull_bar[buf], aphase, abortp) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
       tc_fence_after();
-      epilogue_tile<IS_INT, EPI>(
-          P, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128), lane,
+      epilogue_slice<IS_INT, EPI>(
+          P, &tmO, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128), lane,
           i0, i1, row, nt * BN + half * 128, epi_stage[warp - 2], sc);
       tc_fence_before();
       __syncwarp();
@@ -794,6 +891,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       buf ^= 1;
       if (buf == 0) aphase ^= 1;
     }
+    if (lane == 0) tma_store_wait_read();  // shared memory outlives its last store
     if (fail && lane == 0) {
       *abortp = 1;
       st_cluster_u32(peer_abort, 1u);
@@ -810,6 +908,220 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
   __syncthreads();
   // Neither CTA may release its TMEM or leave while the other can still read
   // its shared memory or write its accumulators.
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Wide CTA-pair kernel: one 256 x 512 output tile per pair, held as two
+// 256-column accumulators that share every A slab. Per 128-byte k-slab each CTA
+// loads 128 rows of A and 2 x 128 rows of B (48 KB) for eight MMAs, a quarter
+// less operand traffic per flop than the 256 x 256 tile, which is what keeps the
+// tensor pipe fed without multicast loads. The price: both accumulators fill
+// all 512 TMEM columns, so the epilogue of a tile cannot overlap the mainloop
+// of the next one; the producer still runs ahead into the next tile, so only
+// the drain itself is exposed. Chosen for long contractions (see gemm_dequant).
+constexpr int STAGES3 = 4;
+constexpr int W_STAGE = A_STAGE + 2 * B_HALF;  // 48 KB per CTA per stage
+constexpr size_t GEMM3_SMEM = (size_t)STAGES3 * W_STAGE + 1024;
+constexpr int BNW = 512;
+// Shortest contraction (in 128-byte k-slabs) for which the exposed drain of the
+// wide tile costs less than the slower mainloop of the double-buffered one.
+constexpr int64_t WIDE_MIN_KB = 16;
+
+__device__ __forceinline__ void decode_tile3(const GemmParams& P, int64_t t, int64_t& i0,
+                                             int64_t& i1, int64_t& mt, int64_t& nt) {
+  const int64_t per_batch = P.m_tiles2 * P.n_tiles3;
+  int64_t b = t / per_batch, r = t % per_batch;
+  i1 = b % P.b1;
+  i0 = b / P.b1;
+  constexpr int64_t G = GROUP_M / 2;
+  const int64_t group = G * P.n_tiles3;
+  int64_t g = r / group, in = r % group;
+  int64_t first = g * G;
+  int64_t gm = min(G, P.m_tiles2 - first);
+  mt = first + in % gm;
+  nt = in / gm;
+}
+
+template <bool IS_INT, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
+                         const __grid_constant__ CUtensorMap tmB,
+                    const __grid_constant__ CUtensorMap tmO, GemmParams P) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t full_bar[STAGES3];   // used in the even CTA only
+  __shared__ __align__(8) uint64_t empty_bar[STAGES3];  // one per CTA
+  __shared__ __align__(8) uint64_t tfull_bar;           // one per CTA
+  __shared__ __align__(8) uint64_t tempty_bar[2];       // per accumulator; even CTA only
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  __shared__ __align__(1024) uint8_t epi_stage[EPI_WARPS][32 * kStagePitch];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const bool leader = rank == 0;
+  const int64_t cluster_id = blockIdx.x >> 1;
+  const int64_t num_clusters = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES3; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], 1);
+    }
+    mbar_init(&tfull_bar, 1);
+    mbar_init(&tempty_bar[0], 2 * EPI_WARPS);
+    mbar_init(&tempty_bar[1], 2 * EPI_WARPS);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abortp = &abort_flag;
+  const uint32_t peer_abort = map_to_cta(smem_u32(&abort_flag), rank ^ 1u);
+  int fail = 0;
+
+  if (warp == 0) {
+    // ---------------- TMA producer (both CTAs) ----------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int64_t t = cluster_id; t < P.total_tiles3 && !fail; t += num_clusters) {
+        int64_t i0, i1, mt, nt;
+        decode_tile3(P, t, i0, i1, mt, nt);
+        const bool two = nt * BNW + 256 < P.n;  // the second accumulator has columns
+        for (int64_t kb = 0; kb < P.num_kb; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
+          const uint32_t lbar = map_to_cta(smem_u32(&full_bar[stage]), 0);
+          uint8_t* sa = smem + stage * W_STAGE;
+          if (leader)
+            mbar_expect_tx(&full_bar[stage], 2 * (A_STAGE + (two ? 2 : 1) * B_HALF));
+          tma_load_4d_pair(sa, &tmA, lbar, (int)(kb * BK), (int)(mt * BM2 + rank * 128), (int)i1,
+                           (int)i0);
+          tma_load_4d_pair(sa + A_STAGE, &tmB, lbar, (int)(kb * BK),
+                           (int)(nt * BNW + rank * 128), (int)i1, (int)i0);
+          if (two)
+            tma_load_4d_pair(sa + A_STAGE + B_HALF, &tmB, lbar, (int)(kb * BK),
+                             (int)(nt * BNW + 256 + rank * 128), (int)i1, (int)i0);
+          if (++stage == STAGES3) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (fail) {
+        *abortp = 1;
+        st_cluster_u32(peer_abort, 1u);
+        if (P.status) atomicCAS(P.status, 0, 1);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (lane == 0 && leader) {
+      int stage = 0;
+      uint32_t phase = 0, aphase = 0;
+      for (int64_t t = cluster_id; t < P.total_tiles3 && !fail; t += num_clusters) {
+        int64_t i0, i1, mt, nt;
+        decode_tile3(P, t, i0, i1, mt, nt);
+        const bool two = nt * BNW + 256 < P.n;
+        for (int64_t kb = 0; kb < P.num_kb; ++kb) {
+          if (kb == 0) {
+            // Both accumulators must have been drained; the first one is
+            // released first, so its wait is the one that can still block.
+            if (!mbar_wait(&tempty_bar[0], aphase ^ 1, abortp)) { fail = 2; break; }
+            if (!mbar_wait(&tempty_bar[1], aphase ^ 1, abortp)) { fail = 2; break; }
+            tc_fence_after();
+          }
+          if (!mbar_wait(&full_bar[stage], phase, abortp)) { fail = 2; break; }
+          tc_fence_after();
+          const uint8_t* sa = smem + stage * W_STAGE;
+          const uint64_t ad = make_smem_desc(smem_u32(sa));
+          const uint64_t bd0 = make_smem_desc(smem_u32(sa + A_STAGE));
+          const uint64_t bd1 = make_smem_desc(smem_u32(sa + A_STAGE + B_HALF));
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k) {
+            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            tc_mma_pair<IS_INT>(tmem_base, ad + (uint64_t)(2 * k), bd0 + (uint64_t)(2 * k),
+                                P.idesc2, accum);
+            if (two)
+              tc_mma_pair<IS_INT>(tmem_base + 256u, ad + (uint64_t)(2 * k),
+                                  bd1 + (uint64_t)(2 * k), P.idesc2, accum);
+          }
+          tc_commit_pair(&empty_bar[stage]);
+          if (++stage == STAGES3) { stage = 0; phase ^= 1; }
+        }
+        if (fail) break;
+        tc_commit_pair(&tfull_bar);
+        aphase ^= 1;
+      }
+      if (fail) {
+        *abortp = 1;
+        st_cluster_u32(peer_abort, 1u);
+        if (P.status) atomicCAS(P.status, 0, 2);
+      }
+    }
+  } else {
+    // ---------------- epilogue (both CTAs, own 128 rows) ----------------
+    // All eight warps drain the first accumulator, hand it back, then drain
+    // the second: warp = (lane quarter, 128-column half of the accumulator).
+    const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    uint32_t aphase = 0;
+    for (int64_t t = cluster_id; t < P.total_tiles3; t += num_clusters) {
+      int64_t i0, i1, mt, nt;
+      decode_tile3(P, t, i0, i1, mt, nt);
+      const bool two = nt * BNW + 256 < P.n;
+      const int64_t row = mt * BM2 + rank * 128 + quarter * 32 + lane;
+      const int64_t col_a = nt * BNW + half * 128;
+      EpiScales sc;
+      load_epi_scales<EPI>(P, lane, i0, i1, row, col_a, sc);
+      int ok = mbar_wait(&tfull_bar, aphase, abortp) ? 1 : 0;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) { fail = 3; break; }
+      tc_fence_after();
+      const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int a = 0; a < 2; ++a) {
+        if (a == 0 || two) {
+          if (a == 1) load_epi_scales<EPI>(P, lane, i0, i1, row, col_a + 256, sc);
+          epilogue_slice<IS_INT, EPI>(P, &tmO, tlane + (uint32_t)(a * 256 + half * 128), lane, i0,
+                                     i1, row, col_a + a * 256, epi_stage[warp - 2], sc);
+          tc_fence_before();
+          __syncwarp();
+        }
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[a]), 0));
+      }
+      aphase ^= 1;
+    }
+    if (lane == 0) tma_store_wait_read();  // shared memory outlives its last store
+    if (fail && lane == 0) {
+      *abortp = 1;
+      st_cluster_u32(peer_abort, 1u);
+      if (P.status) atomicCAS(P.status, 0, 3);
+    }
+  }
+
+  __syncwarp();
+  if (*abortp) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { }
+  }
+  tc_fence_before();
+  __syncthreads();
   cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
@@ -961,6 +1273,16 @@ __global__ void __launch_bounds__(256) dequant_acc_kernel(GemmParams P, const ui
 // host side
 
 static int g_gemm_impl = 0;
+// AQTB200_TMA_STORE=0 in the environment keeps the epilogue on warp stores
+// (for A/B timing; results are identical).
+static bool tma_store_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("AQTB200_TMA_STORE");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
 static int g_sm_budget = 0;
 static int gemm_sms() {
   int n = sm_count();
@@ -1005,6 +1327,27 @@ static int make_operand_map(CUtensorMap* tm, const void* ptr, int64_t k, int64_t
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   AQT_REQUIRE(r == CUDA_SUCCESS, AQTB200_EDRIVER, "cuTensorMapEncodeTiled failed with %d", (int)r);
   return 0;
+}
+
+// 4-D map over a bf16 output [b0][b1][m][n] with n contiguous: 32 x 64 boxes
+// in the 128-byte swizzle the epilogue stages its rows in.
+static bool make_output_map(CUtensorMap* tm, void* ptr, int64_t n, int64_t m, int64_t b1,
+                            int64_t b0, int64_t s_m, int64_t s_b1, int64_t s_b0) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  if (b1 <= 1 || s_b1 == 0) s_b1 = s_m * m;
+  if (b0 <= 1 || s_b0 == 0) s_b0 = s_b1 * std::max<int64_t>(b1, 1);
+  if (((uintptr_t)ptr & 15) || s_m % 8 || s_b1 % 8 || s_b0 % 8 || s_m <= 0 || s_b1 <= 0 || s_b0 <= 0)
+    return false;
+  cuuint64_t dims[4] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)std::max<int64_t>(b1, 1),
+                        (cuuint64_t)std::max<int64_t>(b0, 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)s_m * 2, (cuuint64_t)s_b1 * 2, (cuuint64_t)s_b0 * 2};
+  cuuint32_t box[4] = {64, 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptr, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
 }
 
 static bool is_fp8(int dt) { return dt == AQTB200_E4M3 || dt == AQTB200_E5M2; }
@@ -1061,6 +1404,8 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
              ((uint32_t)(256 >> 4) << 24);
   P.m_tiles2 = (d->m + 255) / 256;
   P.total_tiles2 = d->b0 * d->b1 * P.m_tiles2 * P.n_tiles;
+  P.n_tiles3 = (d->n + 511) / 512;
+  P.total_tiles3 = d->b0 * d->b1 * P.m_tiles2 * P.n_tiles3;
 
   return 0;
 }
@@ -1080,7 +1425,9 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
 
   // CTA pairs pay off once a 256-row tile is mostly full; skinny problems keep
   // the single-CTA 128-row tiles. g_gemm_impl 2 / 3 force one or the other.
-  const bool pair = g_gemm_impl == 3 ? true : (g_gemm_impl == 2 ? false : d->m > 128);
+  const bool wide = g_gemm_impl == 4 ? true
+                    : (g_gemm_impl == 0 && d->m > 128 && d->n > 256 && P.num_kb >= WIDE_MIN_KB);
+  const bool pair = wide || (g_gemm_impl == 3 ? true : (g_gemm_impl == 2 ? false : d->m > 128));
   CUtensorMap tmA, tmB;
   int rc = make_operand_map(&tmA, d->a, d->k, d->m, d->b1, d->b0, d->lda, d->a_b1_stride,
                             d->a_b0_stride, BM);
@@ -1095,9 +1442,19 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   int epi = 0;
   if (d->dequant_dtype == AQTB200_BF16 && d->out_dtype == AQTB200_BF16 && sa_bf && sb_bf) epi = 1;
   if (d->dequant_dtype == AQTB200_F32 && d->out_dtype == AQTB200_F32 && sa_f && sb_f) epi = 2;
-  const int grid = pair ? 2 * std::max((int)std::min<int64_t>(P.total_tiles2, gemm_sms() / 2), 1)
+  // Outputs that qualify for the staged bf16 epilogue leave through the TMA
+  // unit when a tensor map can describe them (non-overlapping, ascending
+  // strides); otherwise the same staged rows are stored by the warps.
+  CUtensorMap tmO;
+  memset(&tmO, 0, sizeof(tmO));
+  P.tma_store = 0;
+  if (epi == 1 && P.stage_ok && tma_store_enabled())
+    P.tma_store = make_output_map(&tmO, d->out, d->n, d->m, d->b1, d->b0, d->out_m_stride,
+                                  d->out_b1_stride, d->out_b0_stride) ? 1 : 0;
+  const int64_t pair_tiles = wide ? P.total_tiles3 : P.total_tiles2;
+  const int grid = pair ? 2 * std::max((int)std::min<int64_t>(pair_tiles, gemm_sms() / 2), 1)
                         : (int)std::min<int64_t>(P.total_tiles, gemm_sms());
-  const size_t smem = pair ? GEMM2_SMEM : GEMM_SMEM;
+  const size_t smem = wide ? GEMM3_SMEM : (pair ? GEMM2_SMEM : GEMM_SMEM);
 #define AQT_LAUNCH_GEMM(KERNEL, I, E)                                                         \
   do {                                                                                        \
     static bool attr_done = false;                                                            \
@@ -1106,7 +1463,7 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
                                        (int)smem));                                           \
       attr_done = true;                                                                       \
     }                                                                                         \
-    KERNEL<I, E><<<grid, GEMM_THREADS, smem, st>>>(tmA, tmB, P);                              \
+    KERNEL<I, E><<<grid, GEMM_THREADS, smem, st>>>(tmA, tmB, tmO, P);                              \
   } while (0)
 #define AQT_LAUNCH_GEMM_E(KERNEL, I)                    \
   do {                                                  \
@@ -1114,7 +1471,10 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
     else if (epi == 2) AQT_LAUNCH_GEMM(KERNEL, I, 2);   \
     else AQT_LAUNCH_GEMM(KERNEL, I, 0);                 \
   } while (0)
-  if (pair) {
+  if (wide) {
+    if (P.is_int) AQT_LAUNCH_GEMM_E(gemm_tcgen05_wide_kernel, true);
+    else AQT_LAUNCH_GEMM_E(gemm_tcgen05_wide_kernel, false);
+  } else if (pair) {
     if (P.is_int) AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, true);
     else AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, false);
   } else {
@@ -1160,7 +1520,7 @@ int aqtb200_set_gemm_sm_budget(int max_sms) {
 }
 
 int aqtb200_set_gemm_impl(int impl) {
-  if (impl < 0 || impl > 3) return AQTB200_EINVAL;
+  if (impl < 0 || impl > 4) return AQTB200_EINVAL;
   aqtb200::g_gemm_impl = impl;
   return 0;
 }

@@ -73,8 +73,8 @@ def check_status():
 
 
 def set_gemm_impl(name: str):
-  """'tcgen05' (default), 'simt' (cross-check kernel), 'cta1' or 'cta2'."""
-  code = {'tcgen05': 0, 'simt': 1, 'cta1': 2, 'cta2': 3}[name]
+  """'tcgen05' (default), 'simt' (cross-check kernel), 'cta1', 'cta2', 'wide'."""
+  code = {'tcgen05': 0, 'simt': 1, 'cta1': 2, 'cta2': 3, 'wide': 4}[name]
   _lib.check(_lib.load().aqtb200_set_gemm_impl(code), 'set_gemm_impl')
 
 

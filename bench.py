@@ -54,7 +54,7 @@ def parse_args():
                  help='extra workloads only: replay the step from a CUDA graph '
                  '(removes host launch overhead from small problems)')
   p.add_argument('--gemm', default='tcgen05',
-                 choices=['tcgen05', 'cta1', 'cta2'],
+                 choices=['tcgen05', 'cta1', 'cta2', 'wide'],
                  help='tile shape of the tensor-core kernel (default: automatic)')
   return p.parse_args()
 

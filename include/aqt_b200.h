@@ -296,10 +296,13 @@ int aqtb200_device_sm_count(int* out);
 /* number of kernels this library has launched in this process (all threads);
  * lets a harness report how much of its timed region ran in these kernels. */
 int64_t aqtb200_kernel_launch_count(void);
-/* selects the contraction kernel: 0 = tcgen05, CTA pairs (cta_group::2,
- * 256 x 256 tiles) when M > 128 and single CTAs (128 x 256) otherwise
- * (default); 1 = plain CUDA-core reference kernel kept for cross-checking the
- * tensor-core path; 2 = always single CTAs; 3 = always CTA pairs. */
+/* selects the contraction kernel: 0 = tcgen05, chosen by shape: CTA pairs
+ * (cta_group::2) when M > 128 -- 256 x 512 tiles when also N > 256 and the
+ * contraction is at least 2048 bytes long, 256 x 256 tiles otherwise -- and
+ * single CTAs (128 x 256) for M <= 128 (default); 1 = plain CUDA-core
+ * reference kernel kept for cross-checking the tensor-core path; 2 = always
+ * single CTAs; 3 = always 256 x 256 CTA pairs; 4 = always 256 x 512 CTA
+ * pairs. */
 int aqtb200_set_gemm_impl(int impl);
 /* Caps the number of SMs the persistent GEMM kernels occupy (0 = all of them).
  * A caller that runs a collective concurrently with a GEMM leaves it room

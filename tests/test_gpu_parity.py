@@ -165,6 +165,55 @@ def test_tensor_core_kernel_agrees_with_cuda_core_kernel():
   assert torch.equal(a[2], b[2]) and torch.equal(a[0], b[0])
 
 
+@pytest.mark.parametrize('impl', ['cta1', 'cta2', 'wide'])
+@pytest.mark.parametrize('shape', [
+    (300, 1000, 520),    # ragged everywhere; second 256-column half partly filled
+    (256, 2048, 512),    # exact tiles
+    (130, 144, 200),     # one 512-column tile whose second half is empty
+    (513, 4096, 1030),   # several tiles per pair, long contraction
+    (64, 256, 256),      # fewer rows than a tile
+])
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+def test_every_tensor_core_kernel_agrees_with_cuda_core_kernel(impl, shape,
+                                                               np_dtype):
+  m, k, n = shape
+  rng = np.random.default_rng(m + n)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = _cuda(util.rand_normal(rng, (m, k), 1.0, np_dtype))
+  rhs = _cuda(util.rand_normal(rng, (k, n), 1.0, np_dtype))
+  raw = aqt.dot_general_raw_make(8, 8)
+  try:
+    engine.set_gemm_impl(impl)
+    a = engine.dg_raw(raw, lhs, rhs, None, None, dims, want_acc=True)
+    engine.set_gemm_impl('simt')
+    b = engine.dg_raw(raw, lhs, rhs, None, None, dims, want_acc=True)
+  finally:
+    engine.set_gemm_impl('tcgen05')
+  _sync()
+  assert torch.equal(a[2], b[2]), 'int32 accumulators'
+  assert torch.equal(a[0], b[0]), 'dequantized output'
+
+
+def test_wide_kernel_batched_and_transposed_output():
+  """The 256 x 512 kernel under batch dims and the drhs output transpose."""
+  rng = np.random.default_rng(11)
+  dims = (((2,), (2,)), ((0,), (0,)))
+  lhs = _cuda(util.rand_normal(rng, (3, 260, 384), 1.0, orc.bfloat16))
+  rhs = _cuda(util.rand_normal(rng, (3, 530, 384), 1.0, orc.bfloat16))
+  raw = aqt.dot_general_raw_make(8, 8)
+  try:
+    engine.set_gemm_impl('wide')
+    a = engine.dg_raw(raw, lhs, rhs, None, None, dims, want_acc=True,
+                      out_transpose_axes=(0, 2, 1))
+    engine.set_gemm_impl('simt')
+    b = engine.dg_raw(raw, lhs, rhs, None, None, dims, want_acc=True,
+                      out_transpose_axes=(0, 2, 1))
+  finally:
+    engine.set_gemm_impl('tcgen05')
+  _sync()
+  assert torch.equal(a[2], b[2]) and torch.equal(a[0], b[0])
+
+
 @pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e4m3', 'e4m3'),
                                      ('e5m2', 'e5m2')])
 @pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
