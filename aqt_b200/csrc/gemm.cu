@@ -949,20 +949,27 @@ __device__ __forceinline__ void decode_tile3(const GemmParams& P, int64_t t, int
   nt = in / gm;
 }
 
-template <bool IS_INT, int EPI>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+constexpr int WIDE_EPI_WARPS = 16;  // four per TMEM lane quarter: the drain is exposed, so it is spread wide
+constexpr int WIDE_THREADS = 32 * (2 + WIDE_EPI_WARPS);
+constexpr int kWidePitch = 64;  // bytes per staged row: 32 bf16 columns, 64-byte swizzle
+
+// Only the all-bf16 epilogue with a TMA-describable output runs here (the host
+// falls back to the 256 x 256 kernel otherwise), which keeps the register need
+// of the 18 warps under the 96 the register file allows them.
+template <bool IS_INT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WIDE_THREADS, 1)
 gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB,
-                    const __grid_constant__ CUtensorMap tmO, GemmParams P) {
+                         const __grid_constant__ CUtensorMap tmO, GemmParams P) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ __align__(8) uint64_t full_bar[STAGES3];   // used in the even CTA only
   __shared__ __align__(8) uint64_t empty_bar[STAGES3];  // one per CTA
-  __shared__ __align__(8) uint64_t tfull_bar;           // one per CTA
+  __shared__ __align__(8) uint64_t tfull_bar[2];        // per accumulator; one per CTA
   __shared__ __align__(8) uint64_t tempty_bar[2];       // per accumulator; even CTA only
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ __align__(1024) uint8_t epi_stage[EPI_WARPS][32 * kStagePitch];
+  __shared__ __align__(1024) uint8_t epi_stage[WIDE_EPI_WARPS][32 * kWidePitch];
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -975,9 +982,10 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
-    mbar_init(&tfull_bar, 1);
-    mbar_init(&tempty_bar[0], 2 * EPI_WARPS);
-    mbar_init(&tempty_bar[1], 2 * EPI_WARPS);
+    mbar_init(&tfull_bar[0], 1);
+    mbar_init(&tfull_bar[1], 1);
+    mbar_init(&tempty_bar[0], 2 * WIDE_EPI_WARPS);
+    mbar_init(&tempty_bar[1], 2 * WIDE_EPI_WARPS);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1038,14 +1046,67 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
         int64_t i0, i1, mt, nt;
         decode_tile3(P, t, i0, i1, mt, nt);
         const bool two = nt * BNW + 256 < P.n;
-        for (int64_t kb = 0; kb < P.num_kb; ++kb) {
-          if (kb == 0) {
-            // Both accumulators must have been drained; the first one is
-            // released first, so its wait is the one that can still block.
-            if (!mbar_wait(&tempty_bar[0], aphase ^ 1, abortp)) { fail = 2; break; }
-            if (!mbar_wait(&tempty_bar[1], aphase ^ 1, abortp)) { fail = 2; break; }
-            tc_fence_after();
+        // The two accumulators are staggered at both ends of the tile so the
+        // tensor pipe works through most of the drain. The first `head`
+        // k-slabs are issued accumulator by accumulator: all into the first
+        // one (handed back half way through the previous tile's drain), then
+        // all into the second. The last `tail` k-slabs likewise: the first
+        // accumulator finishes -- and its drain starts -- while the second is
+        // still being fed. The shared-memory stages of such a group are
+        // released after its second pass.
+        const int head = (int)min((int64_t)STAGES3, P.num_kb);
+        const int64_t rest = P.num_kb - head;
+        const int tail = (int)min((int64_t)STAGES3, rest);
+        const int64_t middle = rest - tail;
+        int stage_of[STAGES3];
+        // -- one staggered group of `cnt` k-slabs; first == the tile's first slabs
+        auto pass_a = [&](int cnt, bool first) {
+#pragma unroll
+          for (int q = 0; q < STAGES3; ++q) {
+            if (q < cnt && !fail) {
+              if (!mbar_wait(&full_bar[stage], phase, abortp)) { fail = 2; }
+              if (!fail) {
+                tc_fence_after();
+                const uint8_t* sa = smem + stage * W_STAGE;
+                const uint64_t ad = make_smem_desc(smem_u32(sa));
+                const uint64_t bd0 = make_smem_desc(smem_u32(sa + A_STAGE));
+#pragma unroll
+                for (int k = 0; k < BK / 32; ++k)
+                  tc_mma_pair<IS_INT>(tmem_base, ad + (uint64_t)(2 * k), bd0 + (uint64_t)(2 * k),
+                                      P.idesc2, (!first || q > 0 || k > 0) ? 1u : 0u);
+                stage_of[q] = stage;
+                if (++stage == STAGES3) { stage = 0; phase ^= 1; }
+              }
+            }
           }
+        };
+        auto pass_b = [&](int cnt, bool first) {
+#pragma unroll
+          for (int q = 0; q < STAGES3; ++q) {
+            if (q < cnt) {
+              if (two) {
+                const uint8_t* sa = smem + stage_of[q] * W_STAGE;
+                const uint64_t ad = make_smem_desc(smem_u32(sa));
+                const uint64_t bd1 = make_smem_desc(smem_u32(sa + A_STAGE + B_HALF));
+#pragma unroll
+                for (int k = 0; k < BK / 32; ++k)
+                  tc_mma_pair<IS_INT>(tmem_base + 256u, ad + (uint64_t)(2 * k),
+                                      bd1 + (uint64_t)(2 * k), P.idesc2,
+                                      (!first || q > 0 || k > 0) ? 1u : 0u);
+              }
+              tc_commit_pair(&empty_bar[stage_of[q]]);
+            }
+          }
+        };
+        if (!mbar_wait(&tempty_bar[0], aphase ^ 1, abortp)) { fail = 2; break; }
+        tc_fence_after();
+        pass_a(head, true);
+        if (fail) break;
+        if (rest == 0) tc_commit_pair(&tfull_bar[0]);
+        if (!mbar_wait(&tempty_bar[1], aphase ^ 1, abortp)) { fail = 2; break; }
+        tc_fence_after();
+        pass_b(head, true);
+        for (int64_t kb = 0; kb < middle; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abortp)) { fail = 2; break; }
           tc_fence_after();
           const uint8_t* sa = smem + stage * W_STAGE;
@@ -1054,18 +1115,23 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
           const uint64_t bd1 = make_smem_desc(smem_u32(sa + A_STAGE + B_HALF));
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {
-            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
             tc_mma_pair<IS_INT>(tmem_base, ad + (uint64_t)(2 * k), bd0 + (uint64_t)(2 * k),
-                                P.idesc2, accum);
+                                P.idesc2, 1u);
             if (two)
               tc_mma_pair<IS_INT>(tmem_base + 256u, ad + (uint64_t)(2 * k),
-                                  bd1 + (uint64_t)(2 * k), P.idesc2, accum);
+                                  bd1 + (uint64_t)(2 * k), P.idesc2, 1u);
           }
           tc_commit_pair(&empty_bar[stage]);
           if (++stage == STAGES3) { stage = 0; phase ^= 1; }
         }
         if (fail) break;
-        tc_commit_pair(&tfull_bar);
+        if (tail > 0) {
+          pass_a(tail, false);
+          if (fail) break;
+          tc_commit_pair(&tfull_bar[0]);
+          pass_b(tail, false);
+        }
+        tc_commit_pair(&tfull_bar[1]);
         aphase ^= 1;
       }
       if (fail) {
@@ -1076,34 +1142,119 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else {
     // ---------------- epilogue (both CTAs, own 128 rows) ----------------
-    // All eight warps drain the first accumulator, hand it back, then drain
-    // the second: warp = (lane quarter, 128-column half of the accumulator).
+    // warp = (TMEM lane quarter, 64-column slice). Each warp drains its slice
+    // of the first accumulator, hands that accumulator back, then drains its
+    // slice of the second. TMEM is read 16 columns at a time with the next
+    // read in flight during the conversion; every 32 columns the staged rows
+    // (64-byte swizzle of the output map) leave with one TMA store, which
+    // clips rows and columns past the matrix edge.
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int slice = (warp - 2) >> 2;
+    const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
+    const bool vary_b = has_b && P.sb_n != 0;
+    uint8_t* stage_rows = epi_stage[warp - 2];
+    uint8_t* srow = stage_rows + lane * kWidePitch;
+    const int swz = (lane >> 1) & 3;
     uint32_t aphase = 0;
     for (int64_t t = cluster_id; t < P.total_tiles3; t += num_clusters) {
       int64_t i0, i1, mt, nt;
       decode_tile3(P, t, i0, i1, mt, nt);
       const bool two = nt * BNW + 256 < P.n;
       const int64_t row = mt * BM2 + rank * 128 + quarter * 32 + lane;
-      const int64_t col_a = nt * BNW + half * 128;
-      EpiScales sc;
-      load_epi_scales<EPI>(P, lane, i0, i1, row, col_a, sc);
-      int ok = mbar_wait(&tfull_bar, aphase, abortp) ? 1 : 0;
+      const int64_t row0 = row - lane;
+      const int64_t col_s = nt * BNW + slice * 64;  // this warp's first column in accumulator 0
+      // scales do not depend on the accumulator: fetch them before waiting for it
+      float sa = 1.f;
+      if (has_a && row < P.m)
+        sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
+      const __nv_bfloat162 sa2 = __float2bfloat162_rn(sa);
+      uint32_t sbw[4];  // [accumulator * 2 + 32-column group]: lanes 0..15 hold column pairs
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        uint32_t w = 0x3f803f80u;  // (1.0, 1.0)
+        if (has_b) {
+          const unsigned short* sp = (const unsigned short*)P.b_scale + i0 * P.sb_b0 + i1 * P.sb_b1;
+          if (P.sb_n == 0) {
+            const uint32_t v = __ldg(sp);
+            w = v | (v << 16);
+          } else if (lane < 16) {
+            const int64_t cc = col_s + (q >> 1) * 256 + (q & 1) * 32 + 2 * lane;
+            const uint32_t lo = cc < P.n ? __ldg(sp + cc * P.sb_n) : 0x3f80u;
+            const uint32_t hi = cc + 1 < P.n ? __ldg(sp + (cc + 1) * P.sb_n) : 0x3f80u;
+            w = lo | (hi << 16);
+          }
+        }
+        sbw[q] = w;
+      }
+      int ok = mbar_wait(&tfull_bar[0], aphase, abortp) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
       tc_fence_after();
-      const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(slice * 64);
+      const int groups = two ? 4 : 2;  // 32-column groups: two per accumulator
+      uint32_t buf[2][16];
+      tc_ld16(tlane, buf[0]);
 #pragma unroll 1
-      for (int a = 0; a < 2; ++a) {
-        if (a == 0 || two) {
-          if (a == 1) load_epi_scales<EPI>(P, lane, i0, i1, row, col_a + 256, sc);
-          epilogue_slice<IS_INT, EPI>(P, &tmO, tlane + (uint32_t)(a * 256 + half * 128), lane, i0,
-                                     i1, row, col_a + a * 256, epi_stage[warp - 2], sc);
+      for (int g = 0; g < groups; ++g) {
+        const int a = g >> 1;
+        // the staging rows are free once the previous store has read them
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
+        const uint32_t sb_g = g < 2 ? (g ? sbw[1] : sbw[0]) : (g == 2 ? sbw[2] : sbw[3]);
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          tc_wait_ld();
+          const int pn = 2 * g + h + 1;  // next 16-column piece
+          if (pn < 2 * groups && pn != 4)  // piece 4 opens the second accumulator: see below
+            tc_ld16(tlane + (uint32_t)((pn >> 2) * 256 + (pn & 3) * 16), buf[h ^ 1]);
+          const uint32_t* acc = buf[h];
+          uint32_t pk[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            uint32_t w = vary_b ? __shfl_sync(0xffffffffu, sb_g, h * 8 + j) : sb_g;
+            const __nv_bfloat162 sb2 = *(const __nv_bfloat162*)&w;
+            const float f0 = IS_INT ? __int2float_rn((int)acc[2 * j]) : __uint_as_float(acc[2 * j]);
+            const float f1 =
+                IS_INT ? __int2float_rn((int)acc[2 * j + 1]) : __uint_as_float(acc[2 * j + 1]);
+            __nv_bfloat162 v = __floats2bfloat162_rn(f0, f1);
+            if (P.b_scale_first) {
+              if (has_b) v = __hmul2(v, sb2);
+              if (has_a) v = __hmul2(v, sa2);
+            } else {
+              if (has_a) v = __hmul2(v, sa2);
+              if (has_b) v = __hmul2(v, sb2);
+            }
+            pk[j] = *(const uint32_t*)&v;
+          }
+#pragma unroll
+          for (int v = 0; v < 2; ++v)
+            *(uint4*)(srow + (((h * 2 + v) ^ swz) * 16)) =
+                make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        const int64_t colg = col_s + a * 256 + (g & 1) * 32;
+        if (lane == 0 && row0 < P.m && colg < P.n)
+          tma_store_4d(&tmO, stage_rows, (int)colg, (int)row0, (int)i1, (int)i0);
+        if (g & 1) {
+          // this accumulator's columns have all been read (the read in flight,
+          // if any, belongs to the other accumulator)
           tc_fence_before();
           __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[a]), 0));
+          if (a == 0 && two) {
+            // the second accumulator finishes a little later than the first
+            int ok1 = mbar_wait(&tfull_bar[1], aphase, abortp) ? 1 : 0;
+            ok1 = __all_sync(0xffffffffu, ok1);
+            if (!ok1) { fail = 3; break; }
+            tc_fence_after();
+            tc_ld16(tlane + 256u, buf[0]);
+          }
         }
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[a]), 0));
+      }
+      if (fail) break;
+      if (!two) {
+        if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[1]), 0));
       }
       aphase ^= 1;
     }
@@ -1329,10 +1480,11 @@ static int make_operand_map(CUtensorMap* tm, const void* ptr, int64_t k, int64_t
   return 0;
 }
 
-// 4-D map over a bf16 output [b0][b1][m][n] with n contiguous: 32 x 64 boxes
-// in the 128-byte swizzle the epilogue stages its rows in.
+// 4-D map over a bf16 output [b0][b1][m][n] with n contiguous: boxes of 32 rows
+// by 64 columns in the 128-byte swizzle (or 32 columns in the 64-byte swizzle),
+// the layouts the epilogues stage their rows in.
 static bool make_output_map(CUtensorMap* tm, void* ptr, int64_t n, int64_t m, int64_t b1,
-                            int64_t b0, int64_t s_m, int64_t s_b1, int64_t s_b0) {
+                            int64_t b0, int64_t s_m, int64_t s_b1, int64_t s_b0, int box_cols) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return false;
   if (b1 <= 1 || s_b1 == 0) s_b1 = s_m * m;
@@ -1342,10 +1494,11 @@ static bool make_output_map(CUtensorMap* tm, void* ptr, int64_t n, int64_t m, in
   cuuint64_t dims[4] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)std::max<int64_t>(b1, 1),
                         (cuuint64_t)std::max<int64_t>(b0, 1)};
   cuuint64_t strides[3] = {(cuuint64_t)s_m * 2, (cuuint64_t)s_b1 * 2, (cuuint64_t)s_b0 * 2};
-  cuuint32_t box[4] = {64, 32, 1, 1};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, 32, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptr, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -1424,17 +1577,10 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   }
 
   // CTA pairs pay off once a 256-row tile is mostly full; skinny problems keep
-  // the single-CTA 128-row tiles. g_gemm_impl 2 / 3 force one or the other.
-  const bool wide = g_gemm_impl == 4 ? true
-                    : (g_gemm_impl == 0 && d->m > 128 && d->n > 256 && P.num_kb >= WIDE_MIN_KB);
-  const bool pair = wide || (g_gemm_impl == 3 ? true : (g_gemm_impl == 2 ? false : d->m > 128));
-  CUtensorMap tmA, tmB;
-  int rc = make_operand_map(&tmA, d->a, d->k, d->m, d->b1, d->b0, d->lda, d->a_b1_stride,
-                            d->a_b0_stride, BM);
-  if (rc) return rc;
-  rc = make_operand_map(&tmB, d->b, d->k, d->n, d->b1, d->b0, d->ldb, d->b_b1_stride,
-                        d->b_b0_stride, pair ? 128 : BN);
-  if (rc) return rc;
+  // the single-CTA 128-row tiles. Long contractions take the 256 x 512 pair
+  // tile. g_gemm_impl 2 / 3 / 4 force one kernel.
+  bool wide = g_gemm_impl == 4 ? true
+              : (g_gemm_impl == 0 && d->m > 128 && d->n > 256 && P.num_kb >= WIDE_MIN_KB);
   const bool sa_bf = d->a_scale == nullptr || d->a_scale_dtype == AQTB200_BF16;
   const bool sb_bf = d->b_scale == nullptr || d->b_scale_dtype == AQTB200_BF16;
   const bool sa_f = d->a_scale == nullptr || d->a_scale_dtype == AQTB200_F32;
@@ -1443,14 +1589,31 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   if (d->dequant_dtype == AQTB200_BF16 && d->out_dtype == AQTB200_BF16 && sa_bf && sb_bf) epi = 1;
   if (d->dequant_dtype == AQTB200_F32 && d->out_dtype == AQTB200_F32 && sa_f && sb_f) epi = 2;
   // Outputs that qualify for the staged bf16 epilogue leave through the TMA
-  // unit when a tensor map can describe them (non-overlapping, ascending
-  // strides); otherwise the same staged rows are stored by the warps.
+  // unit when a tensor map can describe them; otherwise the same staged rows
+  // are stored by the warps. The 256 x 512 kernel has only that epilogue, so
+  // without a map (or for other dtypes, or when the raw accumulator is wanted)
+  // the 256 x 256 kernel runs instead, whatever was asked for.
   CUtensorMap tmO;
   memset(&tmO, 0, sizeof(tmO));
   P.tma_store = 0;
-  if (epi == 1 && P.stage_ok && tma_store_enabled())
+  const bool can_map = epi == 1 && P.stage_ok && tma_store_enabled();
+  if (wide) {
+    wide = can_map && d->acc_out == nullptr &&
+           make_output_map(&tmO, d->out, d->n, d->m, d->b1, d->b0, d->out_m_stride,
+                           d->out_b1_stride, d->out_b0_stride, 32);
+    P.tma_store = wide ? 1 : 0;
+  }
+  if (!wide && can_map)
     P.tma_store = make_output_map(&tmO, d->out, d->n, d->m, d->b1, d->b0, d->out_m_stride,
-                                  d->out_b1_stride, d->out_b0_stride) ? 1 : 0;
+                                  d->out_b1_stride, d->out_b0_stride, 64) ? 1 : 0;
+  const bool pair = wide || (g_gemm_impl == 3 ? true : (g_gemm_impl == 2 ? false : d->m > 128));
+  CUtensorMap tmA, tmB;
+  int rc = make_operand_map(&tmA, d->a, d->k, d->m, d->b1, d->b0, d->lda, d->a_b1_stride,
+                            d->a_b0_stride, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tmB, d->b, d->k, d->n, d->b1, d->b0, d->ldb, d->b_b1_stride,
+                        d->b_b0_stride, pair ? 128 : BN);
+  if (rc) return rc;
   const int64_t pair_tiles = wide ? P.total_tiles3 : P.total_tiles2;
   const int grid = pair ? 2 * std::max((int)std::min<int64_t>(pair_tiles, gemm_sms() / 2), 1)
                         : (int)std::min<int64_t>(P.total_tiles, gemm_sms());
@@ -1472,8 +1635,20 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
     else AQT_LAUNCH_GEMM(KERNEL, I, 0);                 \
   } while (0)
   if (wide) {
-    if (P.is_int) AQT_LAUNCH_GEMM_E(gemm_tcgen05_wide_kernel, true);
-    else AQT_LAUNCH_GEMM_E(gemm_tcgen05_wide_kernel, false);
+    static bool attr_done[2] = {false, false};
+    if (!attr_done[P.is_int]) {
+      if (P.is_int)
+        AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<true>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      else
+        AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<false>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+      attr_done[P.is_int] = true;
+    }
+    if (P.is_int)
+      gemm_tcgen05_wide_kernel<true><<<grid, WIDE_THREADS, smem, st>>>(tmA, tmB, tmO, P);
+    else
+      gemm_tcgen05_wide_kernel<false><<<grid, WIDE_THREADS, smem, st>>>(tmA, tmB, tmO, P);
   } else if (pair) {
     if (P.is_int) AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, true);
     else AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, false);

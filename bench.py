@@ -415,7 +415,7 @@ def gemm_roofline(args, cfg, lhs, rhs, torch, engine):
   # is not re-measured here (nothing is timed under a profiler).
   traffic = 459.0e6 if (m, n, k) == (8192, 8192, 8192) else None
   return {'bound': 'tensor',
-          'kernel': 'gemm_tcgen05_pair_kernel (forward GEMM, 256x256 CTA-pair tiles)',
+          'kernel': 'gemm_tcgen05_wide_kernel (forward GEMM, 256x512 CTA-pair tiles)',
           'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s',
           'frac': achieved / peak, 'traffic': traffic,
           'algorithmic_bytes': float(m * k + n * k + 2 * m * n), 'ms_per_launch': ms,
