@@ -92,6 +92,14 @@ SYMBOLS = {
     'aqtb200_scale_from_amax': (C.c_int, [
         C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.POINTER(QuantSpec),
         C.c_void_p, C.c_void_p]),
+    'aqtb200_quantize_pair': (C.c_int, [
+        C.POINTER(View),
+        C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+        C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
+        C.c_int32, C.c_void_p]),
+    'aqtb200_requant_amax': (C.c_int, [
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.POINTER(QuantSpec),
+        C.c_void_p, C.c_void_p, C.c_void_p]),
     'aqtb200_round_up': (C.c_int64, [C.c_int64, C.c_int64]),
     'aqtb200_gemm_dequant': (C.c_int, [
         C.POINTER(GemmDesc), C.c_void_p, C.c_void_p]),

@@ -759,6 +759,167 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
 }
 
 // ---------------------------------------------------------------------------
+// One read, two fp8 quantizations (bf16 input, per-tensor scales): the
+// transposed one of quant_col_fast and one in the input's own orientation.
+// A training step needs each operand twice -- lhs as [M][K] for the forward
+// dot and as [K][M] for drhs, the cotangent as [M][N] for dlhs and [N][M] for
+// drhs -- and this way the operand is read from HBM once for both.
+// chain 0: both outputs quantize x; 1: the same-orientation output quantizes
+// the VALUES of the transposed one (x -> q_t -> q_s, the backward pass's
+// re-quantization of a stored forward operand); 2: the other way round.
+struct PairParams {
+  DView x;                 // rows contiguous (kept index of q_t), cols strided
+  const void* scale_t;     // one bf16 scale per output
+  const void* scale_s;
+  const void* pre_t;       // optional single bf16 / f32 prescale per output
+  const void* pre_s;
+  int pre_t_dtype, pre_s_dtype;
+  int qdtype_t, qdtype_s;
+  int chain;
+  uint8_t* q_t;            // [b][rows][ld_t]
+  uint8_t* q_s;            // [b][cols][ld_s]
+  int64_t ld_t, ld_s;
+};
+
+__device__ __forceinline__ uint32_t bf16_recip_pair(const void* scale) {
+  // round_bf16(1 / s), 1 where that overflows (aqt_tensor.py:151-153), in both halves
+  const float s = load1(scale, AQTB200_BF16, 0);
+  float inv = round_to(__fdiv_rn(1.f, s), AQTB200_BF16);
+  if (isinf(inv)) inv = 1.f;
+  return pack_bf16x2(inv, inv);
+}
+// two fp8 bytes -> their exact values as packed bf16
+__device__ __forceinline__ uint32_t fp8x2_to_bf16x2(uint32_t q2, __nv_fp8_interpretation_t k) {
+  const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)q2, k);
+  const float2 f = __half22float2(*(const __half2*)&h);
+  return pack_bf16x2(f.x, f.y);
+}
+
+__global__ void __launch_bounds__(256)
+quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_units) {
+  constexpr int EPV = 8, TR = 16 * EPV;
+  __shared__ __align__(16) uint32_t tile[TR][32];
+  const DView& x = P.x;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const uint32_t sinv_t = bf16_recip_pair(P.scale_t), sinv_s = bf16_recip_pair(P.scale_s);
+  const bool has_pre_t = P.pre_t != nullptr, has_pre_s = P.pre_s != nullptr;
+  uint32_t pre_t = 0, pre_s = 0;
+  if (has_pre_t) { const float p = round_to(load1(P.pre_t, P.pre_t_dtype, 0), AQTB200_BF16); pre_t = pack_bf16x2(p, p); }
+  if (has_pre_s) { const float p = round_to(load1(P.pre_s, P.pre_s_dtype, 0), AQTB200_BF16); pre_s = pack_bf16x2(p, p); }
+  const __nv_fp8_interpretation_t kt = P.qdtype_t == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
+  const __nv_fp8_interpretation_t ks = P.qdtype_s == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
+  const uint32_t one2 = 0u;
+  (void)one2;
+  for (int64_t uf = blockIdx.x; uf < total_units; uf += gridDim.x) {
+    const int64_t u = total_units - 1 - uf;  // back to front: the calibration pass's tail is still in L2
+    const int64_t ct = u % col_tiles;
+    int64_t t = u / col_tiles;
+    const int64_t rt = t % row_tiles;
+    const int64_t b = t / row_tiles;
+    const int64_t i1 = b % x.b1, i0 = b / x.b1;
+    const int64_t bidx = i0 * x.b1 + i1;
+    const int64_t r0 = rt * TR + tx * EPV;
+    const bool row_ok = r0 < x.rows;  // rows % 8 == 0: a vector is all in or all out
+    const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + (row_ok ? r0 : 0)) * 2;
+    uint4 raw[2][4];
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+        raw[i][e] = (row_ok && c < x.cols) ? ldg16(xp, c * x.sc * 2) : make_uint4(0u, 0u, 0u, 0u);
+      }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint32_t q4[4][2];  // transposed output: [column e][row group g]
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+        const bool in = row_ok && c < x.cols;
+        const uint32_t rw[4] = {raw[i][e].x, raw[i][e].y, raw[i][e].z, raw[i][e].w};
+        uint32_t qt[4], qs[4];  // two bytes each (rows 2j, 2j+1)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (P.chain == 1) {
+            qt[j] = bf16x2_to_fp8x2(rw[j], pre_t, has_pre_t, sinv_t, kt);
+            qs[j] = bf16x2_to_fp8x2(fp8x2_to_bf16x2(qt[j], kt), 0u, false, sinv_s, ks);
+          } else if (P.chain == 2) {
+            qs[j] = bf16x2_to_fp8x2(rw[j], pre_s, has_pre_s, sinv_s, ks);
+            qt[j] = bf16x2_to_fp8x2(fp8x2_to_bf16x2(qs[j], ks), 0u, false, sinv_t, kt);
+          } else {
+            qt[j] = bf16x2_to_fp8x2(rw[j], pre_t, has_pre_t, sinv_t, kt);
+            qs[j] = bf16x2_to_fp8x2(rw[j], pre_s, has_pre_s, sinv_s, ks);
+          }
+        }
+        q4[e][0] = in ? (qt[0] | (qt[1] << 16)) : 0u;
+        q4[e][1] = in ? (qt[2] | (qt[3] << 16)) : 0u;
+        if (in) {
+          // same orientation: rows r0..r0+7 of column c are 8 contiguous bytes
+          *(uint2*)(P.q_s + (bidx * x.cols + c) * P.ld_s + r0) =
+              make_uint2(qs[0] | (qs[1] << 16), qs[2] | (qs[3] << 16));
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const uint32_t cols4[4] = {q4[0][g], q4[1][g], q4[2][g], q4[3][g]};
+        uint32_t rows4[4];
+        transpose4x4(cols4, rows4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          tile[tx * EPV + 4 * g + j][(i * 16 + ty + 4 * tx) & 31] = rows4[j];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int s2 = 0; s2 < TR / 32; ++s2) {
+      const int id = tid + 256 * s2;
+      const int row = id >> 3, seg = id & 7;
+      const int64_t gr = rt * TR + row;
+      const int64_t gc = ct * 128 + seg * 16;
+      if (gr < x.rows && gc < P.ld_t) {
+        const uint4 o = *(const uint4*)&tile[row][(seg * 4 + 4 * (row / EPV)) & 31];
+        *(uint4*)(P.q_t + (bidx * x.rows + gr) * P.ld_t + gc) = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// |value of Q(amax)|: quantization is monotone and odd, so the largest
+// magnitude among the quantized values is the quantized largest magnitude and
+// the backward pass can calibrate a stored operand without reading it.
+struct RequantAmaxParams {
+  const uint32_t* amax;
+  const void* scale;
+  const void* pre;
+  int pre_dtype, t_dtype, s_dtype, kind, qdtype;
+  float clip_bound;
+  float* out;
+  int64_t n;
+};
+__global__ void requant_amax_kernel(RequantAmaxParams R) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= R.n) return;
+  float a = __uint_as_float(R.amax[i]);
+  if (R.pre != nullptr) a = apply_pre_abs(a, load1(R.pre, R.pre_dtype, 0), R.t_dtype);
+  const float s = load1(R.scale, R.s_dtype, i);
+  float inv = round_to(__fdiv_rn(1.f, s), R.s_dtype);
+  if (isinf(inv)) inv = 1.f;
+  const int y_dtype = (R.t_dtype == AQTB200_F32 || R.s_dtype == AQTB200_F32) ? AQTB200_F32 : AQTB200_BF16;
+  float y = round_to(__fmul_rn(a, inv), y_dtype);
+  y = fminf(fmaxf(y, -R.clip_bound), R.clip_bound);
+  float v;
+  if (R.kind == AQTB200_NUM_INT) {
+    v = (float)__float2int_rn(y);
+  } else {
+    const uint8_t q = (uint8_t)__nv_cvt_float_to_fp8(
+        y, __NV_SATFINITE, R.qdtype == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2);
+    v = fp8_to_float(q, R.qdtype);
+  }
+  R.out[i] = fabsf(v);
+}
+
+// ---------------------------------------------------------------------------
 // amax -> scale and rounded reciprocal (calibration.py:149-157,
 // aqt_tensor.py:151-153). All arithmetic in T, stored as S.
 struct FinalizeParams {
@@ -1338,6 +1499,72 @@ int aqtb200_scale_from_amax(const float* amax, int64_t n, const void* prescale,
   F.quant_bound = spec->quant_bound; F.clipping_scale = spec->clipping_scale;
   F.po2 = spec->po2_scale; F.pre = prescale; F.pre_dtype = prescale_dtype;
   finalize_scale_kernel<<<(int)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(F);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+int aqtb200_quantize_pair(const aqtb200_view* x,
+                          const aqtb200_quant_spec* spec_t, const void* scale_t,
+                          const void* prescale_t, int32_t prescale_t_dtype, void* q_t,
+                          const aqtb200_quant_spec* spec_s, const void* scale_s,
+                          const void* prescale_s, int32_t prescale_s_dtype, void* q_s,
+                          int32_t chain, void* stream) {
+  AQT_REQUIRE(x != nullptr && spec_t != nullptr && spec_s != nullptr && scale_t != nullptr &&
+                  scale_s != nullptr && q_t != nullptr && q_s != nullptr,
+              AQTB200_EINVAL, "null argument");
+  AQT_REQUIRE(chain >= 0 && chain <= 2, AQTB200_EINVAL, "chain must be 0, 1 or 2");
+  for (const aqtb200_quant_spec* sp : {spec_t, spec_s}) {
+    AQT_REQUIRE(sp->kind == AQTB200_NUM_FP8 && sp->per_tensor && sp->compute_dtype == AQTB200_BF16 &&
+                    sp->scale_dtype == AQTB200_BF16 &&
+                    (sp->qdtype == AQTB200_E4M3 || sp->qdtype == AQTB200_E5M2),
+                AQTB200_EUNSUPPORTED,
+                "aqtb200_quantize_pair: per-tensor fp8 with bf16 compute and scale dtype only");
+  }
+  AQT_REQUIRE(x->dtype == AQTB200_BF16, AQTB200_EUNSUPPORTED, "aqtb200_quantize_pair: bf16 input only");
+  if (prescale_t != nullptr) AQT_REQUIRE(is_float_dt(prescale_t_dtype), AQTB200_EINVAL, "prescale dtype");
+  if (prescale_s != nullptr) AQT_REQUIRE(is_float_dt(prescale_s_dtype), AQTB200_EINVAL, "prescale dtype");
+  AQT_REQUIRE(chain == 0 || (chain == 1 ? prescale_s == nullptr : prescale_t == nullptr), AQTB200_EINVAL,
+              "the chained output takes no prescale");
+  const int64_t nb = x->b0 * x->b1;
+  if (nb * x->rows * x->cols == 0) return 0;
+  PairParams P{};
+  P.x = to_dview(x);
+  AQT_REQUIRE(P.x.sr == 1 && x->rows % 16 == 0 && x->cols % 16 == 0 && col_fast_ok(P.x, x->rows, 8),
+              AQTB200_EUNSUPPORTED,
+              "aqtb200_quantize_pair: rows must be the contiguous index, both extents multiples of "
+              "16 and every stride a multiple of 16 bytes");
+  AQT_REQUIRE(aligned(q_t, 16) && aligned(q_s, 16), AQTB200_EINVAL, "outputs not 16-byte aligned");
+  P.scale_t = scale_t; P.scale_s = scale_s;
+  P.pre_t = prescale_t; P.pre_s = prescale_s;
+  P.pre_t_dtype = prescale_t_dtype; P.pre_s_dtype = prescale_s_dtype;
+  P.qdtype_t = spec_t->qdtype; P.qdtype_s = spec_s->qdtype;
+  P.chain = chain;
+  P.q_t = (uint8_t*)q_t; P.q_s = (uint8_t*)q_s;
+  P.ld_t = x->cols; P.ld_s = x->rows;
+  const int64_t rts = (x->rows + 127) / 128, cts = (x->cols + 127) / 128;
+  const int64_t units = nb * rts * cts;
+  quant_pair_kernel<<<grid_for(units, 4), 256, 0, (cudaStream_t)stream>>>(P, rts, cts, units);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+int aqtb200_requant_amax(const float* amax, int64_t n, const void* prescale, int32_t prescale_dtype,
+                         const aqtb200_quant_spec* spec, const void* scale, float* amax_q_out,
+                         void* stream) {
+  AQT_REQUIRE(amax != nullptr && spec != nullptr && scale != nullptr && amax_q_out != nullptr && n >= 0,
+              AQTB200_EINVAL, "null argument");
+  AQT_REQUIRE(is_float_dt(spec->compute_dtype) && is_float_dt(spec->scale_dtype), AQTB200_EINVAL,
+              "compute/scale dtype must be f32 or bf16");
+  AQT_REQUIRE(spec->kind == AQTB200_NUM_INT || spec->kind == AQTB200_NUM_FP8, AQTB200_EINVAL,
+              "numerics kind");
+  if (prescale != nullptr)
+    AQT_REQUIRE(is_float_dt(prescale_dtype), AQTB200_EINVAL, "prescale must be f32 or bf16");
+  if (n == 0) return 0;
+  RequantAmaxParams R{};
+  R.amax = (const uint32_t*)amax; R.scale = scale; R.pre = prescale; R.pre_dtype = prescale_dtype;
+  R.t_dtype = spec->compute_dtype; R.s_dtype = spec->scale_dtype; R.kind = spec->kind;
+  R.qdtype = spec->qdtype; R.clip_bound = spec->clip_bound; R.out = amax_q_out; R.n = n;
+  requant_amax_kernel<<<(int)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(R);
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   return 0;
 }

@@ -340,11 +340,15 @@ class DeferredDequant:
 
 
 def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
-           out_transpose_axes=None, want_acc=False, defer_dequant=False):
+           out_transpose_axes=None, want_acc=False, defer_dequant=False,
+           internal_qt=False):
   """DotGeneralRaw.__call__ on the device (aqt_dot_general.py:757-840).
 
   Returns (out, DotGeneralRes[, acc]). `out` is laid out as
   transpose(out, out_transpose_axes) would be, written by the epilogue.
+  internal_qt: the full QTensors passed in were made by this module from the
+  same operands (prequantize_for_training / cotangent_pair), so gradients
+  still flow to the operands as if they had been quantized here.
   """
   from aqt_b200.v2 import aqt_dot_general as adg
   from aqt_b200.v2 import aqt_tensor
@@ -652,9 +656,11 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
 
   res = adg.DotGeneralRes(
       lhs=adg.TensorRes(mt=adg.MultiTensor(x=lhs, qx=lhs_q_out),
-                        quant_grad=grad_fn(q.lhs, lhs, lhs_qv)),
+                        quant_grad=grad_fn(q.lhs, lhs,
+                                           None if internal_qt else lhs_qv)),
       rhs=adg.TensorRes(mt=adg.MultiTensor(x=rhs_float, qx=rhs_q_out),
-                        quant_grad=grad_fn(q.rhs, rhs_float, rhs_qv)))
+                        quant_grad=grad_fn(q.rhs, rhs_float,
+                                           None if internal_qt else rhs_qv)))
   if defer_dequant:
     return DeferredDequant(desc, acc_storage, out_t,
                            [lq, ls, rq, rs_, lsin, rsin]), res
@@ -921,6 +927,166 @@ def shared_cotangent_scales(cfg, res, g, reduce_max=None):
     out.append(aqt_tensor.QTensor(qvalue=None, scale=[scale], scale_t=None,
                                   bias=[], dequant_dtype=dd))
   return tuple(out)
+
+
+# ---------------------------------------------------------------------------
+# one read of an operand for both layouts a training step needs it in
+# (aqtb200_quantize_pair). Applies to 2-D bf16 matmuls whose quantizers are all
+# per-tensor fp8 without noise; everything else keeps the one-quantization-
+# per-dot flow of the reference.
+
+_BWD_COPY = '_aqt_b200_bwd_copy'  # attribute of the forward qvalue tensor
+
+
+def _pair_spec(quantizer):
+  """The per-tensor fp8/bf16 spec of `quantizer`, or None if it is anything else."""
+  if type(quantizer.numerics).__name__ != 'Fp8Numerics':
+    return None
+  if quantizer.calib_shared_axes != 'per_tensor':
+    return None
+  if getattr(quantizer.numerics, 'noise_fn', None) or getattr(
+      quantizer.numerics, 'stochastic_rounding', False):
+    return None
+  try:
+    spec = _make_spec(quantizer, _lib.BF16, True)
+  except NotImplementedError:
+    return None
+  if spec is None or spec.scale_dtype != _lib.BF16:
+    return None
+  return spec
+
+
+def _pair_matrix_ok(x):
+  return (isinstance(x, torch.Tensor) and x.ndim == 2 and
+          x.dtype == torch.bfloat16 and (x.is_cuda or _HOST_TEST_MODE) and
+          x.stride(1) == 1 and x.stride(0) == x.shape[1] and
+          x.shape[0] % 16 == 0 and x.shape[1] % 16 == 0 and x.numel() > 0 and
+          x.data_ptr() % 16 == 0)
+
+
+def _scale_of_amax(amax, spec, prescale=None):
+  out = torch.empty(1, dtype=_CODE_TORCH[spec.scale_dtype], device=amax.device)
+  pre_ptr, pre_code = None, 0
+  if prescale is not None:
+    pre_ptr, pre_code = prescale.data_ptr(), _code(prescale.dtype)
+  rc = _lib.load().aqtb200_scale_from_amax(
+      amax.data_ptr(), 1, pre_ptr, pre_code, C.byref(spec), out.data_ptr(),
+      _stream())
+  _lib.check(rc, 'aqtb200_scale_from_amax')
+  return out
+
+
+def _quantize_pair(x, spec_t, scale_t, pre_t, spec_s, scale_s, pre_s, chain):
+  """x: [C, R] row-major bf16. Returns (q_t [R][C], q_s [C][R]) buffers."""
+  c, r = x.shape
+  view = _view(x.data_ptr(), _lib.BF16, [1, 1], r, c, [0, 0], 1, r)
+  q_t = torch.empty((r, c), dtype=_CODE_TORCH[spec_t.qdtype], device=x.device)
+  q_s = torch.empty((c, r), dtype=_CODE_TORCH[spec_s.qdtype], device=x.device)
+  ptr = lambda t: (None, 0) if t is None else (t.data_ptr(), _code(t.dtype))
+  (pt, ptc), (ps, psc) = ptr(pre_t), ptr(pre_s)
+  rc = _lib.load().aqtb200_quantize_pair(
+      C.byref(view), C.byref(spec_t), scale_t.data_ptr(), pt, ptc,
+      q_t.data_ptr(), C.byref(spec_s), scale_s.data_ptr(), ps, psc,
+      q_s.data_ptr(), chain, _stream())
+  _lib.check(rc, 'aqtb200_quantize_pair')
+  return q_t, q_s
+
+
+def prequantize_for_training(cfg, lhs, rhs, dimension_numbers):
+  """Forward AND backward quantization of both operands of lhs[M,K] @ rhs[K,N].
+
+  The backward pass re-quantizes the stored forward values of each operand
+  along the other axis (aqt_dot_general.py:675-729, 1206-1217). Both copies
+  are fixed functions of the operand and of its maximum, so they are produced
+  together here, in one read. Returns full QTensors (lhs_qt, rhs_qt) for the
+  forward dot, each carrying the backward copy, or None when the
+  configuration is outside what aqtb200_quantize_pair covers.
+  """
+  from aqt_b200.v2 import aqt_tensor
+  (lca, rca), (lba, rba) = dimension_numbers
+  if list(lca) != [1] or list(rca) != [0] or list(lba) or list(rba):
+    return None
+  if not (_pair_matrix_ok(lhs) and _pair_matrix_ok(rhs)):
+    return None
+  for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
+    try:
+      _check_raw_supported(raw)
+    except NotImplementedError:
+      return None
+  if not (cfg.dlhs.rhs.use_fwd_quant and cfg.drhs.rhs.use_fwd_quant):
+    return None
+  specs = [_pair_spec(q) for q in (
+      cfg.fwd.dg_quantizer.lhs, cfg.fwd.dg_quantizer.rhs,
+      cfg.drhs.dg_quantizer.rhs, cfg.dlhs.dg_quantizer.rhs)]
+  if any(sp is None for sp in specs):
+    return None
+  f_lhs, f_rhs, b_lhs, b_rhs = specs
+  dd = utils.as_dtype(lhs.dtype)
+  lib = _lib.load()
+
+  def scales(x, spec1, spec2):
+    amax = absmax_raw(x)
+    s1 = _scale_of_amax(amax, spec1)
+    amax_q = torch.empty(1, dtype=torch.float32, device=x.device)
+    rc = lib.aqtb200_requant_amax(amax.data_ptr(), 1, None, 0, C.byref(spec1),
+                                  s1.data_ptr(), amax_q.data_ptr(), _stream())
+    _lib.check(rc, 'aqtb200_requant_amax')
+    return s1, _scale_of_amax(amax_q, spec2)
+
+  def qt(qvalue, scale):
+    return aqt_tensor.QTensor(qvalue=qvalue, scale=[scale.view(1, 1)],
+                              scale_t=None, bias=[], dequant_dtype=dd)
+
+  # lhs [M, K]: its own orientation is the forward copy (K contiguous); the
+  # transposed one, [K][M], is what drhs contracts over M.
+  s1, s2 = scales(lhs, f_lhs, b_lhs)
+  q_t, q_s = _quantize_pair(lhs, b_lhs, s2, None, f_lhs, s1, None, chain=2)
+  lhs_qt = qt(q_s, s1)
+  setattr(lhs_qt.qvalue, _BWD_COPY, qt(q_t.t(), s2))
+  # rhs [K, N]: the transposed copy, [N][K], is the forward one; its own
+  # orientation (N contiguous) is what dlhs contracts over.
+  s1, s2 = scales(rhs, f_rhs, b_rhs)
+  q_t, q_s = _quantize_pair(rhs, f_rhs, s1, None, b_rhs, s2, None, chain=1)
+  rhs_qt = qt(q_t.t(), s1)
+  setattr(rhs_qt.qvalue, _BWD_COPY, qt(q_s, s2))
+  return lhs_qt, rhs_qt
+
+
+def bwd_copy(qt):
+  """The backward-pass copy made by prequantize_for_training, if any.
+
+  QTensor is slotted, so the copy rides on the qvalue tensor object, which the
+  forward pass hands to the backward pass unchanged inside the residuals.
+  """
+  if qt is None or not isinstance(qt.qvalue, torch.Tensor):
+    return None
+  return getattr(qt.qvalue, _BWD_COPY, None)
+
+
+def cotangent_pair(cfg, res, g, shared):
+  """Both quantizations of the cotangent g[M,N] in one read.
+
+  `shared` are the two incomplete QTensors of shared_cotangent_scales (dlhs,
+  drhs). Returns full QTensors (g for dlhs, g for drhs) or None.
+  """
+  from aqt_b200.v2 import aqt_tensor
+  if shared is None or not _pair_matrix_ok(g):
+    return None
+  sp_dl = _pair_spec(cfg.dlhs.dg_quantizer.lhs)
+  sp_dr = _pair_spec(cfg.drhs.dg_quantizer.lhs)
+  if sp_dl is None or sp_dr is None:
+    return None
+  pres = []
+  for raw, mt in ((cfg.dlhs, res.rhs.mt), (cfg.drhs, res.lhs.mt)):
+    pres.append(mt.qx.scale[0] if raw.rhs.use_fwd_quant else None)
+  # g [M, N]: own orientation (N contiguous) feeds dlhs, the transposed copy
+  # [N][M] feeds drhs.
+  q_t, q_s = _quantize_pair(g, sp_dr, shared[1].scale[0], pres[1],
+                            sp_dl, shared[0].scale[0], pres[0], chain=0)
+  dd = utils.as_dtype(g.dtype)
+  mk = lambda qv, sc: aqt_tensor.QTensor(qvalue=qv, scale=[sc.view(1, 1)],
+                                         scale_t=None, bias=[], dequant_dtype=dd)
+  return mk(q_s, shared[0].scale[0]), mk(q_t.t(), shared[1].scale[0])
 
 
 def quantize_with_scale(x, scale, numerics, noise=None):

@@ -461,7 +461,17 @@ def dg_core_vjp_fwd(lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
       f'Unmatched lhs and rhs dtype: {lhs.dtype} vs {rhs.dtype}')
   for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
     _init_calibration_once(raw.dg_quantizer)
-  ret, res = cfg.fwd(lhs, rhs, lhs_qt, rhs_qt, dimension_numbers)
+  pre = None
+  if lhs_qt is None and rhs_qt is None:
+    from aqt_b200 import engine
+    # Training reads each operand once for its forward and backward copies
+    # when the configuration allows it (per-tensor fp8 matmuls).
+    pre = engine.prequantize_for_training(cfg, lhs, rhs, dimension_numbers)
+  if pre is not None:
+    ret, res = engine.dg_raw(cfg.fwd, lhs, rhs, pre[0], pre[1],
+                             dimension_numbers, internal_qt=True)
+  else:
+    ret, res = cfg.fwd(lhs, rhs, lhs_qt, rhs_qt, dimension_numbers)
   ret = ret.to(lhs.dtype)
   assert res is not None, 'res cannot be None in fwd pass.'
   qret = (res.lhs.mt.qx, res.rhs.mt.qx)
@@ -530,12 +540,22 @@ def dg_core_vjp_bwd(fwd_dimension_numbers, res, g):
     except NotImplementedError:
       shared = None
 
+  # ... and one read when both quantized copies can be written together.
+  pair = None
+  if shared is not None:
+    pair = engine.cotangent_pair(cfg, dg_res, g, shared)
+    if pair is not None:
+      shared = pair
+
   def grad_dot_general(y_res: TensorRes, quant_grad, dg_raw, y_is_lhs):
     dims, out_transpose_axes = _update_dimension_numbers_for_backward(
         fwd_dimension_numbers, y_is_lhs, g.ndim, y_res.mt.x.ndim)
     g_qt = None if shared is None else shared[1 if y_is_lhs else 0]
-    out = engine.dg_raw(dg_raw, g, y_res.mt, g_qt, None, dims,
-                        out_transpose_axes=out_transpose_axes)[0]
+    # the stored operand's backward copy, when the forward pass made one
+    y_qt = engine.bwd_copy(y_res.mt.qx) if dg_raw.rhs.use_fwd_quant else None
+    out = engine.dg_raw(dg_raw, g, y_res.mt, g_qt, y_qt, dims,
+                        out_transpose_axes=out_transpose_axes,
+                        internal_qt=True)[0]
     if isinstance(quant_grad, str):
       raise AssertionError(quant_grad)
     if quant_grad is not None:

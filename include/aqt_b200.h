@@ -186,6 +186,45 @@ int aqtb200_scale_from_amax(const float* amax, int64_t n, const void* prescale,
                             int32_t prescale_dtype, const aqtb200_quant_spec* spec,
                             void* scale_out, void* stream);
 
+/*
+ * One pass over an operand for the two layouts a training step needs it in.
+ * The reference quantizes every operand twice: lhs for the forward dot and,
+ * from the stored forward values, again for drhs; rhs likewise for dlhs
+ * (_maybe_use_fwd_quant, aqt_dot_general.py:675-729); the cotangent once per
+ * gradient dot (:1206-1217). The two contractions of one operand run along
+ * different axes, so the two quantized copies are transposes of each other in
+ * memory. aqtb200_quantize_pair reads the bf16 operand once and writes both:
+ *   q_t [b0][b1][rows][cols]  the strided index of x contiguous (as the
+ *                             transposing mode of aqtb200_quantize writes it);
+ *   q_s [b0][b1][cols][rows]  x's own orientation.
+ * x: row_stride == 1, col_stride != 1, rows and cols multiples of 16, every
+ * stride a multiple of 8 elements. Each output has its own spec (fp8,
+ * per_tensor, bf16 compute and scale dtype), its own one-element bf16 scale
+ * (an INPUT here) and an optional one-element prescale.
+ * chain = 0: both outputs quantize x (the cotangent);
+ * chain = 1: q_s quantizes the values of q_t (x -> q_t -> q_s: q_t is the
+ *            forward copy, q_s the backward re-quantization of it);
+ * chain = 2: q_t quantizes the values of q_s.
+ * Results are bit-identical to two aqtb200_quantize calls. Other dtypes,
+ * per-channel scales or noise: -2 (AQTB200_EUNSUPPORTED); call
+ * aqtb200_quantize twice.
+ *
+ * aqtb200_requant_amax supplies the calibration of the chained output without
+ * a pass over the data: quantization is monotone and odd, so the largest
+ * magnitude among the quantized values is amax_q[i] = |value(Q(amax[i]))|, from
+ * which aqtb200_scale_from_amax gives the second scale. `spec`, `scale` and
+ * `prescale` are those of the FIRST quantization.
+ */
+int aqtb200_quantize_pair(const aqtb200_view* x,
+                          const aqtb200_quant_spec* spec_t, const void* scale_t,
+                          const void* prescale_t, int32_t prescale_t_dtype, void* q_t,
+                          const aqtb200_quant_spec* spec_s, const void* scale_s,
+                          const void* prescale_s, int32_t prescale_s_dtype, void* q_s,
+                          int32_t chain, void* stream);
+int aqtb200_requant_amax(const float* amax, int64_t n, const void* prescale,
+                         int32_t prescale_dtype, const aqtb200_quant_spec* spec,
+                         const void* scale, float* amax_q_out, void* stream);
+
 int64_t aqtb200_round_up(int64_t v, int64_t multiple);
 
 /*

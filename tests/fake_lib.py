@@ -176,6 +176,85 @@ class FakeLib:
     _strided(scale_out, spec.scale_dtype, [n], [1], True)[...] = scale.astype(S)
     return 0
 
+  def aqtb200_requant_amax(self, amax, n, pre, pre_dtype, spec, scale, out,
+                           stream):
+    spec = _deref(spec, _lib.QuantSpec)
+    T = _NP[spec.compute_dtype]
+    a = np.array(_strided(amax, _lib.F32, [n], [1])).astype(T)
+    if pre:
+      p = np.array(_strided(pre, pre_dtype, [1], [1])).astype(np.float32).astype(T)
+      a = np.abs(orc.mul(a, p))
+    sc = np.array(_strided(scale, spec.scale_dtype, [n], [1]))
+    s_inv = orc.reciprocal(sc)
+    s_inv = np.where(np.isinf(s_inv.astype(np.float32)), np.ones_like(s_inv),
+                     s_inv)
+    y = orc.clip(orc.mul(a, s_inv), -spec.clip_bound, spec.clip_bound)
+    if spec.kind == _lib.NUM_INT:
+      v = np.rint(y.astype(np.float32))
+    else:
+      v = y.astype(np.float32).astype(_NP[spec.qdtype]).astype(np.float32)
+    _strided(out, _lib.F32, [n], [1], True)[...] = np.abs(v)
+    return 0
+
+  def aqtb200_quantize_pair(self, x, spec_t, scale_t, pre_t, pre_t_dtype, q_t,
+                            spec_s, scale_s, pre_s, pre_s_dtype, q_s, chain,
+                            stream):
+    self.calls.append(('quantize_pair', chain))
+    x = _deref(x, _lib.View)
+    spec_t = _deref(spec_t, _lib.QuantSpec)
+    spec_s = _deref(spec_s, _lib.QuantSpec)
+    if x.dtype != _lib.BF16 or x.row_stride != 1 or x.rows % 16 or x.cols % 16:
+      return self._fail(-2, 'quantize_pair: unsupported view')
+
+    def scalar_view(ptr, code):
+      if not ptr:
+        return None
+      v = _lib.View()
+      v.ptr, v.dtype = ptr, code
+      return v
+
+    def view(ptr, code, rows, cols, rs, cs):
+      v = _lib.View()
+      v.ptr, v.dtype = ptr, code
+      v.b0, v.b1, v.rows, v.cols = x.b0, x.b1, rows, cols
+      v.b0_stride = x.b1 * rows * cols
+      v.b1_stride = rows * cols
+      v.row_stride, v.col_stride = rs, cs
+      return v
+
+    # x transposed: rows = x.cols (strided), cols = x.rows (contiguous)
+    x_s = _lib.View()
+    x_s.ptr, x_s.dtype = x.ptr, x.dtype
+    x_s.b0, x_s.b1, x_s.rows, x_s.cols = x.b0, x.b1, x.cols, x.rows
+    x_s.b0_stride, x_s.b1_stride = x.b0_stride, x.b1_stride
+    x_s.row_stride, x_s.col_stride = x.col_stride, 1
+    T = _lib.BF16
+
+    def as_float(spec):
+      # the chained quantization sees the first one's values as bf16 numbers
+      sp = _lib.QuantSpec()
+      for f, _ in _lib.QuantSpec._fields_:
+        setattr(sp, f, getattr(spec, f))
+      sp.compute_dtype = T
+      return sp
+
+    if chain == 1:
+      rc = self._quantize(x, scalar_view(pre_t, pre_t_dtype), None, spec_t,
+                          scale_t, q_t, None)
+      src = view(q_t, spec_t.qdtype, x.cols, x.rows, 1, x.cols)
+      return rc or self._quantize(src, None, None, as_float(spec_s), scale_s,
+                                  q_s, None)
+    if chain == 2:
+      rc = self._quantize(x_s, scalar_view(pre_s, pre_s_dtype), None, spec_s,
+                          scale_s, q_s, None)
+      src = view(q_s, spec_s.qdtype, x.rows, x.cols, 1, x.rows)
+      return rc or self._quantize(src, None, None, as_float(spec_t), scale_t,
+                                  q_t, None)
+    rc = self._quantize(x, scalar_view(pre_t, pre_t_dtype), None, spec_t,
+                        scale_t, q_t, None)
+    return rc or self._quantize(x_s, scalar_view(pre_s, pre_s_dtype), None,
+                                spec_s, scale_s, q_s, None)
+
   # -- gemm
   def _gemm(self, g, acc_in=None):
     ext = [g.b0, g.b1]

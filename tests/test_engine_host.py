@@ -84,6 +84,38 @@ def test_fp8_per_tensor_matches_oracle(monkeypatch, fwd, bwd, np_dtype):
   _assert_same(dr, wr, 'drhs')
 
 
+@pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e5m2', 'e5m2')])
+def test_fp8_per_tensor_paired_quantization_matches_oracle(monkeypatch, fwd,
+                                                           bwd):
+  """bf16 matmul with extents that are multiples of 16: every operand is read
+  once for its two quantized copies (aqtb200_quantize_pair), and the results
+  are those of the reference's one-quantization-per-dot flow."""
+  fake = fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(3)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = util.rand_normal(rng, (32, 64), 1.0, orc.bfloat16)
+  rhs = util.rand_normal(rng, (64, 48), 0.1, orc.bfloat16)
+  g = util.rand_normal(rng, (32, 48), 1.0, orc.bfloat16)
+  cfg = config.fully_quantized(fwd_bits=fwd, bwd_bits=bwd,
+                               use_stochastic_rounding=False)
+  for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
+    raw.dg_quantizer.lhs.calib_shared_axes = 'per_tensor'
+    raw.dg_quantizer.rhs.calib_shared_axes = 'per_tensor'
+  tl, tr, tg = util.to_torch(lhs), util.to_torch(rhs), util.to_torch(g)
+  (out, (lq, rq)), vres = aqt.dg_core_vjp_fwd(tl, tr, None, None, dims, cfg)
+  dl, dr, *_ = aqt.dg_core_vjp_bwd(dims, vres, (tg, None))
+  assert [c for c in fake.calls if c[0] == 'quantize_pair'] == [
+      ('quantize_pair', 2), ('quantize_pair', 1), ('quantize_pair', 0)]
+  wo, wl, wr, res = orc.dg_fwd_bwd(cfg, lhs, rhs, g, dims)
+  _assert_same(lq.qvalue, res.lhs.qx.qvalue, 'q_lhs')
+  _assert_same(rq.qvalue, res.rhs.qx.qvalue, 'q_rhs')
+  _assert_same(lq.scale[0], res.lhs.qx.scale[0], 's_lhs')
+  _assert_same(rq.scale[0], res.rhs.qx.scale[0], 's_rhs')
+  _assert_same(out, wo, 'out')
+  _assert_same(dl, wl, 'dlhs')
+  _assert_same(dr, wr, 'drhs')
+
+
 def test_residual_qtensors_have_reference_layout(monkeypatch):
   fake_lib.install(monkeypatch)
   rng = np.random.default_rng(2)

@@ -165,6 +165,46 @@ def test_tensor_core_kernel_agrees_with_cuda_core_kernel():
   assert torch.equal(a[2], b[2]) and torch.equal(a[0], b[0])
 
 
+@pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e5m2', 'e4m3')])
+@pytest.mark.parametrize('shape', [(256, 512, 384), (16, 16, 16),
+                                   (272, 1040, 48)])
+def test_paired_quantization_equals_one_quantization_per_dot(monkeypatch, fwd,
+                                                             bwd, shape):
+  """aqtb200_quantize_pair / aqtb200_requant_amax (one read per operand) give
+  bit for bit what the reference's flow gives: each dot calibrating and
+  quantizing its own operands, the stored ones re-read in the backward pass."""
+  m, k, n = shape
+  rng = np.random.default_rng(m + k)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = _cuda(util.rand_normal(rng, (m, k), 1.0, orc.bfloat16))
+  rhs = _cuda(util.rand_normal(rng, (k, n), 0.05, orc.bfloat16))
+  g = _cuda(util.rand_normal(rng, (m, n), 1.0, orc.bfloat16))
+  cfg = config.fully_quantized(fwd_bits=fwd, bwd_bits=bwd,
+                               use_stochastic_rounding=False)
+  _per_tensor(cfg)
+
+  def run():
+    (out, (lq, rq)), vres = aqt.dg_core_vjp_fwd(lhs, rhs, None, None, dims, cfg)
+    dl, dr, *_ = aqt.dg_core_vjp_bwd(dims, vres, (g, None))
+    _sync()
+    return out, lq.qvalue, rq.qvalue, lq.scale[0], rq.scale[0], dl, dr
+
+  calls = []
+  real = engine._quantize_pair
+  monkeypatch.setattr(engine, '_quantize_pair',
+                      lambda *a, **kw: calls.append(kw.get('chain')) or real(*a, **kw))
+  paired = run()
+  assert calls == [2, 1, 0]
+  monkeypatch.setattr(engine, 'prequantize_for_training', lambda *a: None)
+  monkeypatch.setattr(engine, 'cotangent_pair', lambda *a: None)
+  single = run()
+  for a, b, what in zip(paired, single, ('out', 'q_lhs', 'q_rhs', 's_lhs',
+                                         's_rhs', 'dlhs', 'drhs')):
+    assert a.shape == b.shape, what
+    assert torch.equal(a.contiguous().view(torch.uint8),
+                       b.contiguous().view(torch.uint8)), what
+
+
 @pytest.mark.parametrize('impl', ['cta1', 'cta2', 'wide'])
 @pytest.mark.parametrize('shape', [
     (300, 1000, 520),    # ragged everywhere; second 256-column half partly filled
