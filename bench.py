@@ -451,9 +451,9 @@ def gemm_roofline(args, cfg, lhs, rhs, torch, engine):
     src = 'of fallback: 2 x 1.59 PFLOP/s bf16'
   peak = 2.0 * bf16
   # DRAM bytes (read + write) of one launch of this kernel at this shape, from
-  # the ncu capture summarised in profiles/gemm_tcgen05_pair_fp8_8192.md; it
+  # the ncu capture summarised in profiles/gemm_tcgen05_wide_fp8_8192.md; it
   # is not re-measured here (nothing is timed under a profiler).
-  traffic = 459.0e6 if (m, n, k) == (8192, 8192, 8192) else None
+  traffic = 537.0e6 if (m, n, k) == (8192, 8192, 8192) else None
   return {'bound': 'tensor',
           'kernel': 'gemm_tcgen05_wide_kernel (forward GEMM, 256x512 CTA-pair tiles)',
           'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s',
