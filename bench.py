@@ -152,63 +152,95 @@ def run_reference_arm(args, lines):
 
 
 class ClockSampler:
-  """Samples SM clock and throttle reasons DURING the timed region.
+  """Samples SM clock and clock event reasons DURING the timed region.
 
-  A separate `nvidia-smi -lms` process does the polling (read-only queries):
-  polling NVML from a thread of this process stalls kernel launches for
-  milliseconds per query and would distort the number being measured.
+  A separate process polls NVML (read-only queries) every few milliseconds and
+  time-stamps each sample; only samples between mark_begin() and mark_end()
+  are reported. Polling NVML from a thread of this process stalls kernel
+  launches for milliseconds per query and would distort the measurement.
   """
 
-  QUERY = ('clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,'
-           'clocks_event_reasons.hw_thermal_slowdown,'
-           'clocks_event_reasons.sw_thermal_slowdown,'
-           'clocks_event_reasons.sw_power_cap')
-  NAMES = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown',
-           'sw_power_cap')
+  # NVML bit masks of the clock event reasons the contract asks about
+  MASKS = {'sw_power_cap': 0x4, 'hw_slowdown': 0x8, 'sw_thermal_slowdown': 0x20,
+           'hw_thermal_slowdown': 0x40}
+  POLLER = r"""
+import sys, time
+import pynvml as N
+N.nvmlInit()
+h = N.nvmlDeviceGetHandleByIndex(int(sys.argv[1]))
+mx = N.nvmlDeviceGetMaxClockInfo(h, N.NVML_CLOCK_SM)
+period = float(sys.argv[2])
+print('ready', mx, flush=True)
+while True:
+  t = time.time()
+  c = N.nvmlDeviceGetClockInfo(h, N.NVML_CLOCK_SM)
+  try:
+    r = N.nvmlDeviceGetCurrentClocksEventReasons(h)
+  except Exception:
+    r = N.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+  print(t, c, r, flush=True)
+  time.sleep(period)
+"""
 
-  def __init__(self, index, period_ms=50):
+  def __init__(self, index, period_ms=4):
     self.index, self.period_ms = index, period_ms
     self.proc = None
+    self.mx = None
+    self.t0 = self.t1 = None
 
   def start(self):
+    """Starts a separate polling process (NVML, every few ms). An in-process
+    poller would share the interpreter with the thread that launches kernels."""
     import subprocess
     try:
       self.proc = subprocess.Popen(
-          ['nvidia-smi', '-i', str(self.index), f'--query-gpu={self.QUERY}',
-           '--format=csv,noheader,nounits', '-lms', str(self.period_ms)],
+          [sys.executable, '-c', self.POLLER, str(self.index),
+           str(self.period_ms / 1e3)],
           stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-      # wait for the first line so that polling is under way before timing
-      self.first = self.proc.stdout.readline()
+      first = self.proc.stdout.readline().split()
+      if not first or first[0] != 'ready':
+        raise RuntimeError('poller did not start')
+      self.mx = int(first[1])
     except Exception:  # pylint: disable=broad-except
       self.proc = None
+
+  def mark_begin(self):
+    self.t0 = time.time()
+
+  def mark_end(self):
+    self.t1 = time.time()
 
   def stop(self):
     if self.proc is None:
       return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': [], 'samples': 0}
-    time.sleep(self.period_ms / 1e3)
+    if self.t1 is None:
+      self.t1 = time.time()
+    time.sleep(2 * self.period_ms / 1e3)
     self.proc.terminate()
     try:
       rest, _ = self.proc.communicate(timeout=5)
     except Exception:  # pylint: disable=broad-except
       self.proc.kill()
       rest = ''
-    # the line read before the timed region started is not a sample under load
-    clocks, reasons, mx = [], set(), None
+    clocks, bits = [], 0
     for line in rest.splitlines():
-      parts = [x.strip() for x in line.split(',')]
-      if len(parts) < 6:
+      parts = line.split()
+      if len(parts) != 3:
         continue
       try:
-        clocks.append(int(parts[0]))
-        mx = int(parts[1])
+        t, c, r = float(parts[0]), int(parts[1]), int(parts[2])
       except ValueError:
         continue
-      for name, flag in zip(self.NAMES, parts[2:6]):
-        if flag.lower().startswith('active'):
-          reasons.add(name)
+      # only samples taken while the timed region was running count
+      if self.t0 is not None and not self.t0 <= t <= self.t1:
+        continue
+      clocks.append(c)
+      bits |= r
     clocks.sort()
+    reasons = sorted(k for k, m in self.MASKS.items() if bits & m)
     return {'sm_mhz': clocks[len(clocks) // 2] if clocks else None,
-            'sm_max_mhz': mx, 'reasons': sorted(reasons),
+            'sm_min_mhz': clocks[0] if clocks else None,
+            'sm_max_mhz': self.mx, 'reasons': reasons,
             'samples': len(clocks)}
 
 
@@ -306,6 +338,7 @@ def run_ours(args, lines):
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   sampler.start()
   barrier()
+  sampler.mark_begin()
   e0.record()
   t_host = time.perf_counter()
   for _ in range(args.steps):
@@ -313,6 +346,7 @@ def run_ours(args, lines):
   host_ms = (time.perf_counter() - t_host) * 1e3 / args.steps
   e1.record()
   barrier()
+  sampler.mark_end()
   clocks = sampler.stop()
   launches = lib.aqtb200_kernel_launch_count() - launches0
   if launches_per_step is not None:
@@ -568,11 +602,14 @@ def run_extra_workload(args, lines):
   e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   sampler = ClockSampler(0)
   sampler.start()
+  torch.cuda.synchronize()
+  sampler.mark_begin()
   e0.record()
   for _ in range(args.steps):
     step()
   e1.record()
   torch.cuda.synchronize()
+  sampler.mark_end()
   clocks = sampler.stop()
   engine.check_status()
   ms = e0.elapsed_time(e1) / args.steps
