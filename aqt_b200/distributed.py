@@ -44,11 +44,17 @@ def _calib_kwargs(quantizer):
 class ShardedDotGeneral:
   """cfg.vjp for row-sharded operands (see module docstring)."""
 
-  def __init__(self, cfg: adg.DotGeneral, group=None, overlap_sms: int = 32):
+  def __init__(self, cfg: adg.DotGeneral, group=None, overlap_sms: int = 32,
+               drhs_slices: int = 2, slice_multiple: int = 256):
     self.cfg = cfg
     self.group = group
-    # SMs left to the all-reduce kernel while the dlhs GEMM runs beside it.
+    # SMs left to the all-reduce kernel while a GEMM runs beside it.
     self.overlap_sms = overlap_sms
+    # drhs is computed in this many column slices so that the all-reduce of
+    # one slice's accumulators runs under the next slice's GEMM.
+    self.drhs_slices = drhs_slices
+    # a slice is a whole number of GEMM tiles wide
+    self.slice_multiple = slice_multiple
 
   # -- collectives -----------------------------------------------------------
   def _max(self, t):
@@ -100,8 +106,17 @@ class ShardedDotGeneral:
     cfg.assert_config_validity()
     for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
       adg._init_calibration_once(raw.dg_quantizer)  # pylint: disable=protected-access
-    lhs_qt = self._global_scale(cfg.fwd.dg_quantizer.lhs, lhs, [1], 0)
-    out, res = engine.dg_raw(cfg.fwd, lhs, rhs, lhs_qt, None, dims)
+    # Per-tensor fp8 matmuls: each operand is read once for its forward and
+    # backward copies; lhs's maximum is agreed across ranks first, which fixes
+    # every scale of lhs on every rank without a further collective.
+    pre = engine.prequantize_for_training(cfg, lhs, rhs, dims,
+                                          reduce_max_lhs=self._max)
+    if pre is not None:
+      out, res = engine.dg_raw(cfg.fwd, lhs, rhs, pre[0], pre[1], dims,
+                               internal_qt=True)
+    else:
+      lhs_qt = self._global_scale(cfg.fwd.dg_quantizer.lhs, lhs, [1], 0)
+      out, res = engine.dg_raw(cfg.fwd, lhs, rhs, lhs_qt, None, dims)
     out = out.to(lhs.dtype)
 
     def backprop(g):
@@ -153,33 +168,94 @@ class ShardedDotGeneral:
             fwd_scale_r.reshape(1, 1))
       g_qt_dlhs = self._global_scale(cfg.dlhs.dg_quantizer.lhs, g, [1], 0,
                                      prescale=pre_r)
-    x_qt = self._global_scale(cfg.drhs.dg_quantizer.rhs, other, [0], 0,
-                              compute_dtype=other_dt)
+    # One read of the cotangent for both of its copies, and the stored
+    # operands' backward copies from the forward pass, when they exist.
+    pair = engine.cotangent_pair(cfg, res, g, shared)
+    if pair is not None:
+      g_qt_dlhs, g_qt = pair
+    x_qt = engine.bwd_copy(res.lhs.mt.qx) if cfg.drhs.rhs.use_fwd_quant else None
+    y_qt = engine.bwd_copy(res.rhs.mt.qx) if cfg.dlhs.rhs.use_fwd_quant else None
+    internal = pair is not None or x_qt is not None or y_qt is not None
+    if x_qt is None:
+      x_qt = self._global_scale(cfg.drhs.dg_quantizer.rhs, other, [0], 0,
+                                compute_dtype=other_dt)
 
     deferred, work, drhs = None, None, None
-    if g_qt is None and x_qt is None:  # unquantized gradient dot
+    sliced = self._drhs_sliced(g, res, g_qt, x_qt, r_dims, r_perm, internal)
+    if sliced is not None:
+      pass
+    elif g_qt is None and x_qt is None:  # unquantized gradient dot
       drhs = engine.dg_raw(cfg.drhs, g, res.lhs.mt, None, None, r_dims,
                            out_transpose_axes=r_perm)[0].contiguous()
       work = self._sum_async(drhs)
     else:
       deferred, _ = engine.dg_raw(cfg.drhs, g, res.lhs.mt, g_qt, x_qt, r_dims,
                                   out_transpose_axes=r_perm,
-                                  defer_dequant=True)
+                                  defer_dequant=True, internal_qt=internal)
       work = self._sum_async(deferred.acc)
 
     # dlhs = g[M,N] . rhs'[K,N]^T : rows of g sharded, contraction over N local
     g_qt = g_qt_dlhs
+    if sliced is not None:
+      work = sliced[1][-1]
     if work is not None and self.overlap_sms and not engine._HOST_TEST_MODE:  # pylint: disable=protected-access
       engine.set_gemm_sm_budget(max(engine.sm_count() - self.overlap_sms, 2))
     try:
-      dlhs = engine.dg_raw(cfg.dlhs, g, res.rhs.mt, g_qt, None, d_dims,
-                           out_transpose_axes=d_perm)[0]
+      dlhs = engine.dg_raw(cfg.dlhs, g, res.rhs.mt, g_qt, y_qt, d_dims,
+                           out_transpose_axes=d_perm, internal_qt=internal)[0]
     finally:
       if work is not None and self.overlap_sms and not engine._HOST_TEST_MODE:  # pylint: disable=protected-access
         engine.set_gemm_sm_budget(0)
 
+    if sliced is not None:
+      drhs, works, parts = sliced
+      for w, d in zip(works, parts):
+        if w is not None:
+          w.wait()
+        d.finish()
+      return dlhs, drhs
     if work is not None:
       work.wait()
     if deferred is not None:
       drhs = deferred.finish()
     return dlhs, drhs
+
+  def _drhs_sliced(self, g, res, g_qt, x_qt, r_dims, r_perm, internal):
+    """drhs in column slices, each slice's accumulators all-reduced while the
+    next slice's GEMM runs. Needs both operands already quantized (full
+    QTensors), so that a slice costs one GEMM and nothing else. Returns
+    (drhs, [work handles], [DeferredDequant]) or None."""
+    s = self.drhs_slices
+    if not (s and s > 1 and g_qt is not None and x_qt is not None and
+            g_qt.is_full() and x_qt.is_full()):
+      return None
+    if not (dist.is_initialized() and dist.get_world_size(self.group) > 1):
+      return None
+    n = g.shape[1]
+    if n % (s * self.slice_multiple) != 0:
+      return None
+    cfg = self.cfg
+    k = res.lhs.mt.x.shape[1]
+    out_dtype = g.dtype
+    drhs = torch.empty((k, n), dtype=out_dtype, device=g.device)
+    works, parts = [], []
+    budget = self.overlap_sms and not engine._HOST_TEST_MODE  # pylint: disable=protected-access
+    try:
+      for i in range(s):
+        sl = slice(i * (n // s), (i + 1) * (n // s))
+        g_slice_qt = aqt_tensor.QTensor(
+            qvalue=g_qt.qvalue[:, sl], scale=g_qt.scale, scale_t=None, bias=[],
+            dequant_dtype=g_qt.dequant_dtype)
+        if i == 1 and budget:
+          # from the second slice on an all-reduce is in flight beside the GEMM
+          engine.set_gemm_sm_budget(max(engine.sm_count() - self.overlap_sms, 2))
+        d, _ = engine.dg_raw(cfg.drhs, g[:, sl], res.lhs.mt, g_slice_qt, x_qt,
+                             r_dims, out_transpose_axes=r_perm,
+                             defer_dequant=True, internal_qt=internal,
+                             out=drhs[:, sl])
+        parts.append(d)
+        works.append(self._sum_async(d.acc))
+    finally:
+      if budget:
+        engine.set_gemm_sm_budget(0)
+    return drhs, works, parts

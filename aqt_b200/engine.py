@@ -341,7 +341,7 @@ class DeferredDequant:
 
 def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
            out_transpose_axes=None, want_acc=False, defer_dequant=False,
-           internal_qt=False):
+           internal_qt=False, out=None):
   """DotGeneralRaw.__call__ on the device (aqt_dot_general.py:757-840).
 
   Returns (out, DotGeneralRes[, acc]). `out` is laid out as
@@ -349,6 +349,8 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
   internal_qt: the full QTensors passed in were made by this module from the
   same operands (prequantize_for_training / cotangent_pair), so gradients
   still flow to the operands as if they had been quantized here.
+  out: optional preallocated result (any strides, e.g. a slice of a larger
+  tensor) of the transposed result's shape and the result dtype.
   """
   from aqt_b200.v2 import aqt_dot_general as adg
   from aqt_b200.v2 import aqt_tensor
@@ -443,8 +445,13 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
   perm = list(out_transpose_axes) if out_transpose_axes is not None else list(
       range(len(raw_shape)))
   out_dtype = _CODE_TORCH[d_code]
-  out_t = torch.empty([raw_shape[p] for p in perm], dtype=out_dtype,
-                      device=lhs.device)
+  out_shape = [raw_shape[p] for p in perm]
+  if out is not None:
+    assert list(out.shape) == out_shape and out.dtype == out_dtype, (
+        f'out must be {out_shape} {out_dtype}, got {list(out.shape)} {out.dtype}')
+    out_t = out
+  else:
+    out_t = torch.empty(out_shape, dtype=out_dtype, device=lhs.device)
   raw_strides = [0] * len(raw_shape)
   for i, p in enumerate(perm):
     raw_strides[p] = out_t.stride(i)
@@ -956,8 +963,15 @@ def _pair_spec(quantizer):
   return spec
 
 
+def _pair_enabled():
+  # AQTB200_PAIR=0 keeps the reference's one-quantization-per-dot flow (for
+  # A/B timing; results are identical).
+  import os
+  return os.environ.get('AQTB200_PAIR', '1') != '0'
+
+
 def _pair_matrix_ok(x):
-  return (isinstance(x, torch.Tensor) and x.ndim == 2 and
+  return (_pair_enabled() and isinstance(x, torch.Tensor) and x.ndim == 2 and
           x.dtype == torch.bfloat16 and (x.is_cuda or _HOST_TEST_MODE) and
           x.stride(1) == 1 and x.stride(0) == x.shape[1] and
           x.shape[0] % 16 == 0 and x.shape[1] % 16 == 0 and x.numel() > 0 and
@@ -992,7 +1006,8 @@ def _quantize_pair(x, spec_t, scale_t, pre_t, spec_s, scale_s, pre_s, chain):
   return q_t, q_s
 
 
-def prequantize_for_training(cfg, lhs, rhs, dimension_numbers):
+def prequantize_for_training(cfg, lhs, rhs, dimension_numbers,
+                             reduce_max_lhs=None):
   """Forward AND backward quantization of both operands of lhs[M,K] @ rhs[K,N].
 
   The backward pass re-quantizes the stored forward values of each operand
@@ -1001,6 +1016,8 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers):
   together here, in one read. Returns full QTensors (lhs_qt, rhs_qt) for the
   forward dot, each carrying the backward copy, or None when the
   configuration is outside what aqtb200_quantize_pair covers.
+  reduce_max_lhs, if given, is applied to lhs's raw maximum (a cross-rank max
+  when the rows of lhs are sharded); every scale of lhs follows from it.
   """
   from aqt_b200.v2 import aqt_tensor
   (lca, rca), (lba, rba) = dimension_numbers
@@ -1024,8 +1041,10 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers):
   dd = utils.as_dtype(lhs.dtype)
   lib = _lib.load()
 
-  def scales(x, spec1, spec2):
+  def scales(x, spec1, spec2, reduce_max=None):
     amax = absmax_raw(x)
+    if reduce_max is not None:
+      amax = reduce_max(amax)
     s1 = _scale_of_amax(amax, spec1)
     amax_q = torch.empty(1, dtype=torch.float32, device=x.device)
     rc = lib.aqtb200_requant_amax(amax.data_ptr(), 1, None, 0, C.byref(spec1),
@@ -1039,7 +1058,7 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers):
 
   # lhs [M, K]: its own orientation is the forward copy (K contiguous); the
   # transposed one, [K][M], is what drhs contracts over M.
-  s1, s2 = scales(lhs, f_lhs, b_lhs)
+  s1, s2 = scales(lhs, f_lhs, b_lhs, reduce_max_lhs)
   q_t, q_s = _quantize_pair(lhs, b_lhs, s2, None, f_lhs, s1, None, chain=2)
   lhs_qt = qt(q_s, s1)
   setattr(lhs_qt.qvalue, _BWD_COPY, qt(q_t.t(), s2))

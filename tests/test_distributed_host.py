@@ -39,18 +39,22 @@ def _make_cfg(kind, per_tensor, use_fwd_quant):
   return cfg
 
 
-def _data():
+def _data(np_dtype=np.float32):
   rng = np.random.default_rng(0)
-  lhs = util.rand_normal(rng, (32, 48), 1.0, np.float32)
-  rhs = util.rand_normal(rng, (48, 40), 0.2, np.float32)
-  g = util.rand_normal(rng, (32, 40), 1.0, np.float32)
+  # bf16 with extents that are multiples of 16 per shard takes the
+  # one-read-per-operand path (aqtb200_quantize_pair)
+  n = 48 if np_dtype != np.float32 else 40
+  lhs = util.rand_normal(rng, (32, 48), 1.0, np_dtype)
+  rhs = util.rand_normal(rng, (48, n), 0.2, np_dtype)
+  g = util.rand_normal(rng, (32, n), 1.0, np_dtype)
   # make the two shards' maxima differ clearly
   lhs[20, 3] = 7.0
   g[5, 7] = -9.0
   return lhs, rhs, g
 
 
-def _worker(rank, world, port, kind, per_tensor, use_fwd_quant, ret):
+def _worker(rank, world, port, kind, per_tensor, use_fwd_quant, ret,
+            np_dtype=np.float32):
   os.environ['MASTER_ADDR'] = '127.0.0.1'
   os.environ['MASTER_PORT'] = str(port)
   dist.init_process_group('gloo', rank=rank, world_size=world)
@@ -62,11 +66,15 @@ def _worker(rank, world, port, kind, per_tensor, use_fwd_quant, ret):
     fake = fake_lib.FakeLib()
     with mock.patch.object(_lib, 'load', lambda: fake), \
          mock.patch.object(engine, '_HOST_TEST_MODE', True):
-      lhs, rhs, g = _data()
+      lhs, rhs, g = _data(np_dtype)
       rows = lhs.shape[0] // world
       sl = slice(rank * rows, (rank + 1) * rows)
+      kw = {}
+      if np_dtype != np.float32:
+        # exercise the sliced drhs with its per-slice all-reduces
+        kw = dict(drhs_slices=2, slice_multiple=8)
       op = aqt_dist.ShardedDotGeneral(_make_cfg(kind, per_tensor,
-                                                use_fwd_quant))
+                                                use_fwd_quant), **kw)
       out, bp = op.vjp(util.to_torch(lhs[sl]), util.to_torch(rhs), DIMS)
       dl, dr = bp(util.to_torch(g[sl]))
       ret[rank] = (util.to_numpy(out), util.to_numpy(dl), util.to_numpy(dr))
@@ -104,3 +112,27 @@ def test_two_ranks_equal_one_device(kind, per_tensor, use_fwd_quant):
       np.testing.assert_array_equal(ret[r][2], wr)
     else:  # f32 partial sums are added in a different order
       np.testing.assert_allclose(ret[r][2], wr, rtol=1e-5, atol=1e-6)
+
+
+def test_two_ranks_paired_quantization_equal_one_device():
+  """bf16 / per-tensor fp8: every rank reads each operand once for both of its
+  copies; the raw maxima of lhs and of the cotangent are the only things
+  agreed across ranks besides the accumulator sum."""
+  world = 2
+  mgr = mp.Manager()
+  ret = mgr.dict()
+  mp.spawn(_worker, args=(world, _free_port(), 'fp8', True, True, ret,
+                          orc.bfloat16), nprocs=world, join=True)
+  lhs, rhs, g = _data(orc.bfloat16)
+  cfg = _make_cfg('fp8', True, True)
+  wo, wl, wr, _ = orc.dg_fwd_bwd(cfg, lhs, rhs, g, DIMS)
+  f32 = lambda a: np.asarray(a, np.float32)
+  out = np.concatenate([f32(ret[r][0]) for r in range(world)], axis=0)
+  dl = np.concatenate([f32(ret[r][1]) for r in range(world)], axis=0)
+  np.testing.assert_array_equal(out, f32(wo))
+  np.testing.assert_array_equal(dl, f32(wl))
+  for r in range(world):
+    # the f32 partial sums of the two ranks are added in a different order
+    # than one device's single sum: at most one bf16 ulp after rounding
+    got, want = f32(ret[r][2]), f32(wr)
+    assert np.all(np.abs(got - want) <= np.abs(want) * 2.0 ** -7 + 1e-6)
