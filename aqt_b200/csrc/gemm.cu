@@ -29,6 +29,7 @@ constexpr int BM = 128;
 constexpr int BN = 256;
 constexpr int BK = 128;  // bytes (= elements) of k per stage: one 128B swizzle row
 constexpr int STAGES = 4;
+constexpr int MAX_STAGES1 = 12;  // single-CTA kernel, narrow B tiles: up to this many stages
 constexpr int A_STAGE = BM * BK;
 constexpr int B_STAGE = BN * BK;
 constexpr int GROUP_M = 16;
@@ -54,6 +55,7 @@ struct GemmParams {
   int64_t m_tiles, n_tiles, total_tiles, num_kb;
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
   int64_t n_tiles3, total_tiles3;  // 512-column tiles of the wide CTA-pair kernel
+  int stages1, b_stage;  // single-CTA kernel: ring depth and bytes of one B tile
   int stage_ok;  // output rows can be written as aligned 16-byte pieces
   int tma_store;  // a tensor map of the bf16 output exists: staged rows leave through the TMA unit
   int32_t* status;
@@ -529,9 +531,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint8_t* smem_a = smem;
-  uint8_t* smem_b = smem + STAGES * A_STAGE;
-  __shared__ __align__(8) uint64_t full_bar[STAGES];
-  __shared__ __align__(8) uint64_t empty_bar[STAGES];
+  // The B tile holds as many rows as the MMAs are wide (P.b_stage bytes), and
+  // the ring is as deep as shared memory allows (P.stages1): a narrow problem
+  // streams its big A operand with far more bytes in flight.
+  uint8_t* smem_b = smem + P.stages1 * A_STAGE;
+  __shared__ __align__(8) uint64_t full_bar[MAX_STAGES1];
+  __shared__ __align__(8) uint64_t empty_bar[MAX_STAGES1];
   __shared__ __align__(8) uint64_t tfull_bar[2];
   __shared__ __align__(8) uint64_t tempty_bar[2];
   __shared__ uint32_t tmem_slot;
@@ -541,7 +546,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
+    for (int s = 0; s < P.stages1; ++s) {
       mbar_init(&full_bar[s], 1);
       mbar_init(&empty_bar[s], 1);
     }
@@ -577,12 +582,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         decode_tile(P, t, i0, i1, mt, nt);
         for (int64_t kb = 0; kb < P.num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
-          mbar_expect_tx(&full_bar[stage], A_STAGE + B_STAGE);
+          mbar_expect_tx(&full_bar[stage], A_STAGE + P.b_stage);
           tma_load_4d(smem_a + stage * A_STAGE, &tmA, &full_bar[stage], (int)(kb * BK),
                       (int)(mt * BM), (int)i1, (int)i0);
-          tma_load_4d(smem_b + stage * B_STAGE, &tmB, &full_bar[stage], (int)(kb * BK),
+          tma_load_4d(smem_b + stage * P.b_stage, &tmB, &full_bar[stage], (int)(kb * BK),
                       (int)(nt * BN), (int)i1, (int)i0);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == P.stages1) { stage = 0; phase ^= 1; }
         }
       }
       if (fail) { *abortp = 1; if (P.status) atomicCAS(P.status, 0, 1); }
@@ -602,7 +607,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           if (!mbar_wait(&full_bar[stage], phase, abortp)) { fail = 2; break; }
           tc_fence_after();
           const uint64_t ad = make_smem_desc(smem_u32(smem_a + stage * A_STAGE));
-          const uint64_t bd = make_smem_desc(smem_u32(smem_b + stage * B_STAGE));
+          const uint64_t bd = make_smem_desc(smem_u32(smem_b + stage * P.b_stage));
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k) {
             // advance 32 bytes of k inside the swizzle row: +2 in 16-byte units
@@ -610,7 +615,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
                            (kb > 0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++stage == P.stages1) { stage = 0; phase ^= 1; }
         }
         if (fail) break;
         tc_commit(&tfull_bar[buf]);
@@ -1551,8 +1556,16 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   const uint32_t cfmt = ints ? 2u : 1u;
   const uint32_t afmt = ints ? 1u : (d->a_dtype == AQTB200_E5M2 ? 1u : 0u);
   const uint32_t bfmt = ints ? 1u : (d->b_dtype == AQTB200_E5M2 ? 1u : 0u);
-  P.idesc = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
+  // A problem at most one tile wide lets the single-CTA kernel issue MMAs only
+  // as wide as the columns that exist (a multiple of 16): the tensor pipe's
+  // time scales with N, which is what makes a skinny GEMM -- a few tokens
+  // against many weight rows, with the weights on the row side -- stream its
+  // big operand at memory speed instead of multiplying zero columns.
+  const int64_t n_mma = d->n < BN ? std::max<int64_t>(16, (d->n + 15) / 16 * 16) : BN;
+  P.idesc = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(n_mma >> 3) << 17) |
             ((uint32_t)(BM >> 4) << 24);
+  P.b_stage = (int)(n_mma * BK);
+  P.stages1 = (int)std::min<int64_t>(MAX_STAGES1, (int64_t)(GEMM_SMEM - 1024) / (A_STAGE + P.b_stage));
   P.idesc2 = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
              ((uint32_t)(256 >> 4) << 24);
   P.m_tiles2 = (d->m + 255) / 256;
@@ -1606,13 +1619,15 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   if (!wide && can_map)
     P.tma_store = make_output_map(&tmO, d->out, d->n, d->m, d->b1, d->b0, d->out_m_stride,
                                   d->out_b1_stride, d->out_b0_stride, 64) ? 1 : 0;
-  const bool pair = wide || (g_gemm_impl == 3 ? true : (g_gemm_impl == 2 ? false : d->m > 128));
+  // fewer than 128 columns: the single-CTA kernel with narrow MMAs (see fill_params)
+  const bool pair = wide || (g_gemm_impl == 3 ? true
+                                              : (g_gemm_impl == 2 ? false : d->m > 128 && d->n >= 128));
   CUtensorMap tmA, tmB;
   int rc = make_operand_map(&tmA, d->a, d->k, d->m, d->b1, d->b0, d->lda, d->a_b1_stride,
                             d->a_b0_stride, BM);
   if (rc) return rc;
   rc = make_operand_map(&tmB, d->b, d->k, d->n, d->b1, d->b0, d->ldb, d->b_b1_stride,
-                        d->b_b0_stride, pair ? 128 : BN);
+                        d->b_b0_stride, pair ? 128 : P.b_stage / BK);
   if (rc) return rc;
   const int64_t pair_tiles = wide ? P.total_tiles3 : P.total_tiles2;
   const int grid = pair ? 2 * std::max((int)std::min<int64_t>(pair_tiles, gemm_sms() / 2), 1)

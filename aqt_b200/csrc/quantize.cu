@@ -367,13 +367,13 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *(const uint32_t*)&t;
 }
 
-constexpr int kFastRowChunk = 8192;  // elements of one (row, chunk) work unit
+constexpr int kFastRowChunk = 8192;  // most elements of one (row, chunk) work unit
 
 // absmax, contraction contiguous, one warp per (batch-row, chunk).
 // PRE: 0 none, 1 constant over the row (applied to the maximum), 2 per column.
 template <int EPV, int PRE>
 __global__ void __launch_bounds__(256)
-absmax_row_fast(QParams P, int64_t chunks_per_row, int64_t total_units) {
+absmax_row_fast(QParams P, int64_t chunks_per_row, int64_t total_units, int chunk_elems) {
   constexpr int ES = 16 / EPV;
   constexpr int U = 4;
   __shared__ float red[32];
@@ -386,8 +386,8 @@ absmax_row_fast(QParams P, int64_t chunks_per_row, int64_t total_units) {
     const int64_t brow = u / chunks_per_row, chunk = u % chunks_per_row;
     int64_t i0, i1, r;
     decode_brow(x, brow, i0, i1, r);
-    const int64_t c0 = chunk * kFastRowChunk;
-    const int64_t nvec = (min(x.cols, c0 + (int64_t)kFastRowChunk) - c0) / EPV;
+    const int64_t c0 = chunk * chunk_elems;
+    const int64_t nvec = (min(x.cols, c0 + (int64_t)chunk_elems) - c0) / EPV;
     const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + r * x.sr + c0) * ES;
     const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
     uint4 run = make_uint4(0u, 0u, 0u, 0u);
@@ -1328,10 +1328,16 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
     AQT_CUDA_OK(cudaMemsetAsync(P.amax, 0, (size_t)ns * 4, st));
     if (total > 0) {
       if (fast_row && (pre_kind != 2 || P.pre_vec)) {
-        int64_t chunks = (xv->cols + kFastRowChunk - 1) / kFastRowChunk;
+        // a (row, chunk) unit is one warp's work: shorter chunks when the whole
+        // tensor would otherwise occupy a handful of warps (decode-time activations)
+        int chunk_elems = kFastRowChunk;
+        while (chunk_elems > 1024 &&
+               nbrow * ((xv->cols + chunk_elems - 1) / chunk_elems) < (int64_t)sm_count() * 8)
+          chunk_elems /= 2;
+        int64_t chunks = (xv->cols + chunk_elems - 1) / chunk_elems;
         int64_t units = nbrow * chunks;
         int grid = grid_for((units + 7) / 8, 8);
-        AQT_DISPATCH_EPV_PRE(absmax_row_fast, grid, 256, P, chunks, units);
+        AQT_DISPATCH_EPV_PRE(absmax_row_fast, grid, 256, P, chunks, units, chunk_elems);
       } else if (row_mode) {
         int64_t chunks = (xv->cols + kRowChunk - 1) / kRowChunk;
         int64_t units = nbrow * chunks;

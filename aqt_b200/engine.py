@@ -604,6 +604,11 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
   # Put the operand whose kept index is contiguous in the OUTPUT on the
   # column side of the tile so the epilogue stores rows of the result.
   swap = (ns[1] != 1 and ms[1] == 1 and N > 1)
+  # A few rows against many (decode-time serving: tokens x weight rows): the
+  # many go on the row side of the tile whatever the output layout, so the
+  # MMAs are only as wide as the few (see fill_params in csrc/gemm.cu).
+  if M <= 64 and N >= 8 * max(M, 16):
+    swap = True
   desc.swap_ab = 1 if swap else 0
   desc.dequant_dtype = d_code
   desc.out = out_t.data_ptr()

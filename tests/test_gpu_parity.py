@@ -234,6 +234,32 @@ def test_every_tensor_core_kernel_agrees_with_cuda_core_kernel(impl, shape,
   assert torch.equal(a[0], b[0]), 'dequantized output'
 
 
+@pytest.mark.parametrize('shape', [(16, 512, 1024), (1, 256, 4096),
+                                   (64, 1040, 520), (40, 144, 2048)])
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+def test_skinny_lhs_uses_narrow_mmas_and_agrees(shape, np_dtype):
+  """A few rows against many: the planner puts the many on the tile's row side
+  and the kernel issues MMAs as wide as the few."""
+  m, k, n = shape
+  rng = np.random.default_rng(m * n)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = _cuda(util.rand_normal(rng, (m, k), 1.0, np_dtype))
+  rhs = _cuda(util.rand_normal(rng, (k, n), 1.0, np_dtype))
+  raw = aqt.dot_general_raw_make(8, 8)
+  try:
+    a = engine.dg_raw(raw, lhs, rhs, None, None, dims, want_acc=True)
+    engine.set_gemm_impl('simt')
+    b = engine.dg_raw(raw, lhs, rhs, None, None, dims, want_acc=True)
+  finally:
+    engine.set_gemm_impl('tcgen05')
+  _sync()
+  assert torch.equal(a[2], b[2]), 'int32 accumulators'
+  assert torch.equal(a[0], b[0]), 'dequantized output'
+  want, _ = orc.dg_raw(raw, util.to_numpy(lhs), util.to_numpy(rhs), None, None,
+                       dims)
+  _exact(a[0], want, 'out vs oracle')
+
+
 def test_wide_kernel_batched_and_transposed_output():
   """The 256 x 512 kernel under batch dims and the drhs output transpose."""
   rng = np.random.default_rng(11)
