@@ -33,6 +33,7 @@ struct QParams {
   int pre_vec, noise_vec;  // vector loads allowed on prescale / noise
   int use_lut;    // 1-byte input, one scale and one prescale for the whole call: byte -> byte table
   int fast_bf16;  // bf16 in, bf16 scale, fp8 out, no noise: packed bf16 arithmetic
+  int pre_bf16;   // bf16 input, bf16 prescale, bf16 compute dtype: x * pre as packed bf16 multiplies
   uint32_t* amax;
   float* sinv;
   uint8_t* q;
@@ -401,6 +402,28 @@ absmax_row_fast(QParams P, int64_t chunks_per_row, int64_t total_units, int chun
       }
 #pragma unroll
       for (int k = 0; k < U; ++k) {
+        if constexpr (PRE == 2 && EPV == 8) {
+          if (P.pre_bf16 && P.pre_vec) {
+            // round_bf16(x * p) is the packed bf16 multiply; its magnitude bits
+            // order like unsigned integers
+            const int64_t idx = i + 32 * k;
+            if (idx < nvec) {
+              const uint4 pw = ldg16(P.pre.ptr, (pbase + c0 + idx * EPV) * 2);
+              const uint32_t xw[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+              const uint32_t pp[4] = {pw.x, pw.y, pw.z, pw.w};
+              uint32_t r[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const __nv_bfloat162 v = __hmul2(*(const __nv_bfloat162*)&xw[j],
+                                                 *(const __nv_bfloat162*)&pp[j]);
+                r[j] = *(const uint32_t*)&v & 0x7fff7fffu;
+              }
+              run.x = __vmaxu2(run.x, r[0]); run.y = __vmaxu2(run.y, r[1]);
+              run.z = __vmaxu2(run.z, r[2]); run.w = __vmaxu2(run.w, r[3]);
+            }
+            continue;
+          }
+        }
         if constexpr (PRE == 2) {
           const int64_t idx = i + 32 * k;
           if (idx < nvec) {
@@ -415,7 +438,7 @@ absmax_row_fast(QParams P, int64_t chunks_per_row, int64_t total_units, int chun
         }
       }
     }
-    float m = PRE == 2 ? fm : packed_hmax<EPV>(run, x.dtype);
+    float m = PRE == 2 ? fmaxf(fm, packed_hmax<EPV>(run, x.dtype)) : packed_hmax<EPV>(run, x.dtype);
     if constexpr (PRE == 1)
       m = apply_pre_abs(m, load1(P.pre.ptr, P.pre.dtype, pbase), P.t_dtype);
     if (P.per_tensor) {
@@ -470,6 +493,26 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
         }
 #pragma unroll
         for (int k = 0; k < U; ++k) {
+          if constexpr (PRE == 2 && EPV == 8) {
+            if (P.pre_bf16) {
+              const int64_t ck = c + 8 * k;
+              if (ck < cend) {
+                const float p = load1(P.pre.ptr, P.pre.dtype, pbase + ck * P.pre.sc);
+                const uint32_t p2 = pack_bf16x2(p, p);
+                const uint32_t xw[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+                uint32_t r[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const __nv_bfloat162 v = __hmul2(*(const __nv_bfloat162*)&xw[j],
+                                                   *(const __nv_bfloat162*)&p2);
+                  r[j] = *(const uint32_t*)&v & 0x7fff7fffu;
+                }
+                run.x = __vmaxu2(run.x, r[0]); run.y = __vmaxu2(run.y, r[1]);
+                run.z = __vmaxu2(run.z, r[2]); run.w = __vmaxu2(run.w, r[3]);
+              }
+              continue;
+            }
+          }
           if constexpr (PRE == 2) {
             const int64_t ck = c + 8 * k;
             if (ck < cend) {
@@ -487,8 +530,10 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
     }
     float m[EPV];
     if constexpr (PRE == 2) {
+      float pm[EPV];
+      packed_to_floats<EPV>(run, x.dtype, pm);  // the packed-bf16 path's maxima (zero otherwise)
 #pragma unroll
-      for (int j = 0; j < EPV; ++j) m[j] = fm[j];
+      for (int j = 0; j < EPV; ++j) m[j] = fmaxf(fm[j], pm[j]);
     } else {
       packed_to_floats<EPV>(run, x.dtype, m);
       if constexpr (PRE == 1) {
@@ -1302,6 +1347,8 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
   P.fast_bf16 = P.x.dtype == AQTB200_BF16 && P.t_dtype == AQTB200_BF16 &&
                 P.s_dtype == AQTB200_BF16 && P.kind == AQTB200_NUM_FP8 && P.noise.ptr == nullptr &&
                 (P.pre.ptr == nullptr || P.pre.dtype == AQTB200_BF16 || true);
+  P.pre_bf16 = P.pre.ptr != nullptr && P.x.dtype == AQTB200_BF16 && P.pre.dtype == AQTB200_BF16 &&
+               P.t_dtype == AQTB200_BF16;
   // prescale class: 0 none, 1 constant along the contraction index, 2 varying
   const int pre_kind = P.pre.ptr == nullptr ? 0 : (P.pre.sc == 0 || xv->cols <= 1 ? 1 : 2);
   const bool fast_row = row_mode && row_vec_ok(P.x, xv->cols);
