@@ -857,10 +857,20 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
   (void)one2;
   for (int64_t uf = blockIdx.x; uf < total_units; uf += gridDim.x) {
     const int64_t u = total_units - 1 - uf;  // back to front: the calibration pass's tail is still in L2
+#ifdef AQT_PAIR_CT_FAST
     const int64_t ct = u % col_tiles;
     int64_t t = u / col_tiles;
     const int64_t rt = t % row_tiles;
     const int64_t b = t / row_tiles;
+#else
+    // Neighbouring blocks take neighbouring tiles along the CONTIGUOUS index of
+    // the input, so the blocks in flight together stream whole rows of it (and
+    // of the same-orientation output) instead of a 256-byte strip of every row.
+    const int64_t rt = u % row_tiles;
+    int64_t t = u / row_tiles;
+    const int64_t ct = t % col_tiles;
+    const int64_t b = t / col_tiles;
+#endif
     const int64_t i1 = b % x.b1, i0 = b / x.b1;
     const int64_t bidx = i0 * x.b1 + i1;
     const int64_t r0 = rt * TR + tx * EPV;
@@ -980,6 +990,27 @@ struct FinalizeParams {
   int pre_dtype;
 };
 
+// scale = where(a == 0, 1, a) [* clipping_scale] / quant_bound, in T, stored as S
+__device__ __forceinline__ float scale_of_amax(float a, int t_dtype, int s_dtype, float quant_bound,
+                                               float clipping_scale, int po2) {
+  if (a == 0.f) a = 1.f;
+  float bound = clipping_scale != 0.f ? round_to(__fmul_rn(a, clipping_scale), t_dtype) : a;
+  float s = round_to(__fdiv_rn(bound, quant_bound), t_dtype);
+  if (po2) {
+    // 1 / 2**floor(log2(1/s)); the exponent is read off the float directly.
+    float r = round_to(__fdiv_rn(1.f, s), t_dtype);
+    int e;
+    frexpf(r, &e);  // r = m * 2**e, m in [0.5, 1)
+    float p = round_to(ldexpf(1.f, e - 1), t_dtype);
+    s = round_to(__fdiv_rn(1.f, p), t_dtype);
+  }
+  return round_to(s, s_dtype);
+}
+__device__ __forceinline__ float recip_of_scale(float s, int s_dtype) {
+  float inv = round_to(__fdiv_rn(1.f, s), s_dtype);
+  return isinf(inv) ? 1.f : inv;
+}
+
 __global__ void finalize_scale_kernel(FinalizeParams F) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= F.n) return;
@@ -989,20 +1020,7 @@ __global__ void finalize_scale_kernel(FinalizeParams F) {
   } else {
     float a = __uint_as_float(F.amax[i]);
     if (F.pre != nullptr) a = apply_pre_abs(a, load1(F.pre, F.pre_dtype, 0), F.t_dtype);
-    if (a == 0.f) a = 1.f;
-    float bound = F.clipping_scale != 0.f
-                      ? round_to(__fmul_rn(a, F.clipping_scale), F.t_dtype)
-                      : a;
-    s = round_to(__fdiv_rn(bound, F.quant_bound), F.t_dtype);
-    if (F.po2) {
-      // 1 / 2**floor(log2(1/s)); the exponent is read off the float directly.
-      float r = round_to(__fdiv_rn(1.f, s), F.t_dtype);
-      int e;
-      frexpf(r, &e);  // r = m * 2**e, m in [0.5, 1)
-      float p = round_to(ldexpf(1.f, e - 1), F.t_dtype);
-      s = round_to(__fdiv_rn(1.f, p), F.t_dtype);
-    }
-    s = round_to(s, F.s_dtype);
+    s = scale_of_amax(a, F.t_dtype, F.s_dtype, F.quant_bound, F.clipping_scale, F.po2);
   }
   if (F.scale_out != nullptr && F.scale_out != F.scale_in) {
     if (F.s_dtype == AQTB200_BF16)
@@ -1011,9 +1029,86 @@ __global__ void finalize_scale_kernel(FinalizeParams F) {
       ((float*)F.scale_out)[i] = s;
   }
   if (F.sinv == nullptr) return;
-  float inv = round_to(__fdiv_rn(1.f, s), F.s_dtype);
-  if (isinf(inv)) inv = 1.f;
-  F.sinv[i] = inv;
+  F.sinv[i] = recip_of_scale(s, F.s_dtype);
+}
+
+// ---------------------------------------------------------------------------
+// Calibrate and quantize in ONE pass, for per-row scales when a row fits in a
+// block's registers (up to 256 threads x 4 vectors): each block takes whole
+// rows, keeps the row in registers between the maximum and the quantization,
+// so the operand is read once and three launches become one. Same arithmetic
+// as absmax_row_fast + finalize_scale_kernel + quant_row_fast (no prescale
+// that varies along the row, no noise).
+struct OnePassParams {
+  QParams q;
+  float quant_bound, clipping_scale;
+  int po2;
+  void* scale_out;
+};
+
+template <int EPV, int PRE>
+__global__ void __launch_bounds__(256)
+quant_row_onepass(OnePassParams O, int64_t nbrow) {
+  constexpr int ES = 16 / EPV;
+  constexpr int NV = 16 / EPV;   // input vectors per 16 outputs
+  constexpr int UMAX = 4 / NV > 0 ? 4 / NV : 1;  // 16-output units per thread
+  __shared__ float red[32];
+  const QParams& P = O.q;
+  const DView& x = P.x;
+  const int64_t units = P.ldq / 16;  // per row; cols % 16 == 0 here
+  for (int64_t brow = blockIdx.x; brow < nbrow; brow += gridDim.x) {
+    int64_t i0, i1, r;
+    decode_brow(x, brow, i0, i1, r);
+    const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + r * x.sr) * ES;
+    uint4 raw[UMAX][NV];
+    uint4 run = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int k = 0; k < UMAX; ++k) {
+      const int64_t u = threadIdx.x + 256 * k;
+#pragma unroll
+      for (int n = 0; n < NV; ++n) {
+        raw[k][n] = u < units ? ldg16(xp, (u * NV + n) * 16) : make_uint4(0u, 0u, 0u, 0u);
+        packed_absmax<EPV>(run, raw[k][n], x.dtype);
+      }
+    }
+    float m = packed_hmax<EPV>(run, x.dtype);
+    const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+    float pconst = 0.f;
+    if constexpr (PRE == 1) pconst = load1(P.pre.ptr, P.pre.dtype, pbase);
+    m = block_max(m, red);
+    if (threadIdx.x == 0) red[0] = m;
+    __syncthreads();
+    m = red[0];
+    __syncthreads();
+    if constexpr (PRE == 1) m = apply_pre_abs(m, pconst, P.t_dtype);
+    const float s = scale_of_amax(m, P.t_dtype, P.s_dtype, O.quant_bound, O.clipping_scale, O.po2);
+    if (threadIdx.x == 0) {
+      if (P.s_dtype == AQTB200_BF16) ((__nv_bfloat16*)O.scale_out)[brow] = __float2bfloat16_rn(s);
+      else ((float*)O.scale_out)[brow] = s;
+    }
+    const float sinv = recip_of_scale(s, P.s_dtype);
+    const float sinv4[4] = {sinv, sinv, sinv, sinv};
+    const float nz[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int k = 0; k < UMAX; ++k) {
+      const int64_t u = threadIdx.x + 256 * k;
+      if (u >= units) continue;
+      uint32_t outw[4];
+#pragma unroll
+      for (int n = 0; n < NV; ++n) {
+        float v[EPV];
+        unpack<EPV>(raw[k][n], x.dtype, v);
+        if constexpr (PRE == 1) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) v[j] = apply_pre(v[j], pconst, P.t_dtype);
+        }
+#pragma unroll
+        for (int g = 0; g < EPV / 4; ++g)
+          outw[(n * EPV) / 4 + g] = quant4(v + 4 * g, sinv4, nz, false, P);
+      }
+      *(uint4*)(P.q + brow * P.ldq + u * 16) = make_uint4(outw[0], outw[1], outw[2], outw[3]);
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1371,6 +1466,29 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
     }                                                                                    \
   } while (0)
 
+  // Per-row scales over rows that fit in a block: one kernel, one read.
+  {
+    const int nv = epv == 16 ? 1 : 16 / epv;     // input vectors per 16 outputs
+    const int umax = 4 / nv > 0 ? 4 / nv : 1;    // 16-output units per thread
+    if (scale_in == nullptr && want_q && amax_only_out == nullptr && fast_row && epv != 16 &&
+        !P.per_tensor && P.noise.ptr == nullptr && pre_kind != 2 && xv->cols >= 1024 &&
+        xv->cols % 16 == 0 && xv->cols / 16 <= 256 * (int64_t)umax && nbrow > 0) {
+      OnePassParams O{};
+      O.q = P;
+      O.quant_bound = spec->quant_bound; O.clipping_scale = spec->clipping_scale;
+      O.po2 = spec->po2_scale; O.scale_out = scale_out;
+      const int grid = grid_for(nbrow, 8);
+      if (epv == 4) {
+        if (pre_kind == 0) quant_row_onepass<4, 0><<<grid, 256, 0, st>>>(O, nbrow);
+        else quant_row_onepass<4, 1><<<grid, 256, 0, st>>>(O, nbrow);
+      } else {
+        if (pre_kind == 0) quant_row_onepass<8, 0><<<grid, 256, 0, st>>>(O, nbrow);
+        else quant_row_onepass<8, 1><<<grid, 256, 0, st>>>(O, nbrow);
+      }
+      AQT_CUDA_OK(cudaGetLastError()); count_launch();
+      return 0;
+    }
+  }
   if (scale_in == nullptr) {
     AQT_CUDA_OK(cudaMemsetAsync(P.amax, 0, (size_t)ns * 4, st));
     if (total > 0) {
