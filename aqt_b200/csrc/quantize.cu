@@ -819,7 +819,8 @@ struct PairParams {
   const void* pre_t;       // optional single bf16 / f32 prescale per output
   const void* pre_s;
   int pre_t_dtype, pre_s_dtype;
-  int qdtype_t, qdtype_s;
+  int qdtype_t, qdtype_s;   // e4m3 / e5m2 / s8
+  float clip_t, clip_s;     // int8 outputs: clip bound
   int chain;
   uint8_t* q_t;            // [b][rows][ld_t]
   uint8_t* q_s;            // [b][cols][ld_s]
@@ -840,6 +841,25 @@ __device__ __forceinline__ uint32_t fp8x2_to_bf16x2(uint32_t q2, __nv_fp8_interp
   return pack_bf16x2(f.x, f.y);
 }
 
+// Two bf16 values -> two quantized bytes (fp8, or int8 with clip and RNE), and back.
+__device__ __forceinline__ uint32_t bf16x2_to_q8x2(uint32_t w, uint32_t pre2, bool has_pre,
+                                                   uint32_t sinv2, bool is_int, float clip,
+                                                   __nv_fp8_interpretation_t k) {
+  if (!is_int) return bf16x2_to_fp8x2(w, pre2, has_pre, sinv2, k);
+  __nv_bfloat162 v = *(const __nv_bfloat162*)&w;
+  if (has_pre) v = __hmul2(v, *(const __nv_bfloat162*)&pre2);
+  v = __hmul2(v, *(const __nv_bfloat162*)&sinv2);
+  const uint32_t r = *(const uint32_t*)&v;
+  const float lo = fminf(fmaxf(bf16lo(r), -clip), clip);
+  const float hi = fminf(fmaxf(bf16hi(r), -clip), clip);
+  return ((uint32_t)__float2int_rn(lo) & 0xffu) | (((uint32_t)__float2int_rn(hi) & 0xffu) << 8);
+}
+__device__ __forceinline__ uint32_t q8x2_to_bf16x2(uint32_t q2, bool is_int,
+                                                   __nv_fp8_interpretation_t k) {
+  if (!is_int) return fp8x2_to_bf16x2(q2, k);
+  return pack_bf16x2((float)(signed char)(q2 & 0xffu), (float)(signed char)((q2 >> 8) & 0xffu));
+}
+
 __global__ void __launch_bounds__(256)
 quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_units) {
   constexpr int EPV = 8, TR = 16 * EPV;
@@ -853,8 +873,7 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
   if (has_pre_s) { const float p = round_to(load1(P.pre_s, P.pre_s_dtype, 0), AQTB200_BF16); pre_s = pack_bf16x2(p, p); }
   const __nv_fp8_interpretation_t kt = P.qdtype_t == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
   const __nv_fp8_interpretation_t ks = P.qdtype_s == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
-  const uint32_t one2 = 0u;
-  (void)one2;
+  const bool int_t = P.qdtype_t == AQTB200_S8, int_s = P.qdtype_s == AQTB200_S8;
   for (int64_t uf = blockIdx.x; uf < total_units; uf += gridDim.x) {
     const int64_t u = total_units - 1 - uf;  // back to front: the calibration pass's tail is still in L2
 #ifdef AQT_PAIR_CT_FAST
@@ -896,14 +915,16 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (P.chain == 1) {
-            qt[j] = bf16x2_to_fp8x2(rw[j], pre_t, has_pre_t, sinv_t, kt);
-            qs[j] = bf16x2_to_fp8x2(fp8x2_to_bf16x2(qt[j], kt), 0u, false, sinv_s, ks);
+            qt[j] = bf16x2_to_q8x2(rw[j], pre_t, has_pre_t, sinv_t, int_t, P.clip_t, kt);
+            qs[j] = bf16x2_to_q8x2(q8x2_to_bf16x2(qt[j], int_t, kt), 0u, false, sinv_s, int_s,
+                                   P.clip_s, ks);
           } else if (P.chain == 2) {
-            qs[j] = bf16x2_to_fp8x2(rw[j], pre_s, has_pre_s, sinv_s, ks);
-            qt[j] = bf16x2_to_fp8x2(fp8x2_to_bf16x2(qs[j], ks), 0u, false, sinv_t, kt);
+            qs[j] = bf16x2_to_q8x2(rw[j], pre_s, has_pre_s, sinv_s, int_s, P.clip_s, ks);
+            qt[j] = bf16x2_to_q8x2(q8x2_to_bf16x2(qs[j], int_s, ks), 0u, false, sinv_t, int_t,
+                                   P.clip_t, kt);
           } else {
-            qt[j] = bf16x2_to_fp8x2(rw[j], pre_t, has_pre_t, sinv_t, kt);
-            qs[j] = bf16x2_to_fp8x2(rw[j], pre_s, has_pre_s, sinv_s, ks);
+            qt[j] = bf16x2_to_q8x2(rw[j], pre_t, has_pre_t, sinv_t, int_t, P.clip_t, kt);
+            qs[j] = bf16x2_to_q8x2(rw[j], pre_s, has_pre_s, sinv_s, int_s, P.clip_s, ks);
           }
         }
         q4[e][0] = in ? (qt[0] | (qt[1] << 16)) : 0u;
@@ -1685,11 +1706,13 @@ int aqtb200_quantize_pair(const aqtb200_view* x,
               AQTB200_EINVAL, "null argument");
   AQT_REQUIRE(chain >= 0 && chain <= 2, AQTB200_EINVAL, "chain must be 0, 1 or 2");
   for (const aqtb200_quant_spec* sp : {spec_t, spec_s}) {
-    AQT_REQUIRE(sp->kind == AQTB200_NUM_FP8 && sp->per_tensor && sp->compute_dtype == AQTB200_BF16 &&
-                    sp->scale_dtype == AQTB200_BF16 &&
-                    (sp->qdtype == AQTB200_E4M3 || sp->qdtype == AQTB200_E5M2),
+    const bool fp8 = sp->kind == AQTB200_NUM_FP8 &&
+                     (sp->qdtype == AQTB200_E4M3 || sp->qdtype == AQTB200_E5M2);
+    const bool i8 = sp->kind == AQTB200_NUM_INT && sp->qdtype == AQTB200_S8;
+    AQT_REQUIRE((fp8 || i8) && sp->per_tensor && sp->compute_dtype == AQTB200_BF16 &&
+                    sp->scale_dtype == AQTB200_BF16,
                 AQTB200_EUNSUPPORTED,
-                "aqtb200_quantize_pair: per-tensor fp8 with bf16 compute and scale dtype only");
+                "aqtb200_quantize_pair: per-tensor fp8 or int8 with bf16 compute and scale dtype only");
   }
   AQT_REQUIRE(x->dtype == AQTB200_BF16, AQTB200_EUNSUPPORTED, "aqtb200_quantize_pair: bf16 input only");
   if (prescale_t != nullptr) AQT_REQUIRE(is_float_dt(prescale_t_dtype), AQTB200_EINVAL, "prescale dtype");
@@ -1709,6 +1732,7 @@ int aqtb200_quantize_pair(const aqtb200_view* x,
   P.pre_t = prescale_t; P.pre_s = prescale_s;
   P.pre_t_dtype = prescale_t_dtype; P.pre_s_dtype = prescale_s_dtype;
   P.qdtype_t = spec_t->qdtype; P.qdtype_s = spec_s->qdtype;
+  P.clip_t = spec_t->clip_bound; P.clip_s = spec_s->clip_bound;
   P.chain = chain;
   P.q_t = (uint8_t*)q_t; P.q_s = (uint8_t*)q_s;
   P.ld_t = x->cols; P.ld_s = x->rows;

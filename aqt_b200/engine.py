@@ -944,15 +944,15 @@ def shared_cotangent_scales(cfg, res, g, reduce_max=None):
 # ---------------------------------------------------------------------------
 # one read of an operand for both layouts a training step needs it in
 # (aqtb200_quantize_pair). Applies to 2-D bf16 matmuls whose quantizers are all
-# per-tensor fp8 without noise; everything else keeps the one-quantization-
+# per-tensor fp8 or int8 without noise; everything else keeps the one-quantization-
 # per-dot flow of the reference.
 
 _BWD_COPY = '_aqt_b200_bwd_copy'  # attribute of the forward qvalue tensor
 
 
 def _pair_spec(quantizer):
-  """The per-tensor fp8/bf16 spec of `quantizer`, or None if it is anything else."""
-  if type(quantizer.numerics).__name__ != 'Fp8Numerics':
+  """The per-tensor fp8 or int8 / bf16 spec of `quantizer`, or None if it is anything else."""
+  if type(quantizer.numerics).__name__ not in ('Fp8Numerics', 'IntSymmetric'):
     return None
   if quantizer.calib_shared_axes != 'per_tensor':
     return None
@@ -964,6 +964,8 @@ def _pair_spec(quantizer):
   except NotImplementedError:
     return None
   if spec is None or spec.scale_dtype != _lib.BF16:
+    return None
+  if spec.kind == _lib.NUM_INT and spec.qdtype != _lib.S8:
     return None
   return spec
 

@@ -198,7 +198,7 @@ int aqtb200_scale_from_amax(const float* amax, int64_t n, const void* prescale,
  *                             transposing mode of aqtb200_quantize writes it);
  *   q_s [b0][b1][cols][rows]  x's own orientation.
  * x: row_stride == 1, col_stride != 1, rows and cols multiples of 16, every
- * stride a multiple of 8 elements. Each output has its own spec (fp8,
+ * stride a multiple of 8 elements. Each output has its own spec (fp8 or int8,
  * per_tensor, bf16 compute and scale dtype), its own one-element bf16 scale
  * (an INPUT here) and an optional one-element prescale.
  * chain = 0: both outputs quantize x (the cotangent);

@@ -84,7 +84,8 @@ def test_fp8_per_tensor_matches_oracle(monkeypatch, fwd, bwd, np_dtype):
   _assert_same(dr, wr, 'drhs')
 
 
-@pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e5m2', 'e5m2')])
+@pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e5m2', 'e5m2'),
+                                     (8, 8), (4, 8)])
 def test_fp8_per_tensor_paired_quantization_matches_oracle(monkeypatch, fwd,
                                                            bwd):
   """bf16 matmul with extents that are multiples of 16: every operand is read

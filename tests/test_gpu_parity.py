@@ -165,7 +165,8 @@ def test_tensor_core_kernel_agrees_with_cuda_core_kernel():
   assert torch.equal(a[2], b[2]) and torch.equal(a[0], b[0])
 
 
-@pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e5m2', 'e4m3')])
+@pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e5m2', 'e4m3'),
+                                     (8, 8), (4, 8)])
 @pytest.mark.parametrize('shape', [(256, 512, 384), (16, 16, 16),
                                    (272, 1040, 48)])
 def test_paired_quantization_equals_one_quantization_per_dot(monkeypatch, fwd,
