@@ -860,6 +860,9 @@ __device__ __forceinline__ uint32_t q8x2_to_bf16x2(uint32_t q2, bool is_int,
   return pack_bf16x2((float)(signed char)(q2 & 0xffu), (float)(signed char)((q2 >> 8) & 0xffu));
 }
 
+// IS_INT: both outputs int8 (else both fp8); CHAIN as PairParams::chain. Compile-
+// time, because the kernel is bound by issue slots, not by memory.
+template <bool IS_INT, int CHAIN>
 __global__ void __launch_bounds__(256)
 quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_units) {
   constexpr int EPV = 8, TR = 16 * EPV;
@@ -873,15 +876,9 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
   if (has_pre_s) { const float p = round_to(load1(P.pre_s, P.pre_s_dtype, 0), AQTB200_BF16); pre_s = pack_bf16x2(p, p); }
   const __nv_fp8_interpretation_t kt = P.qdtype_t == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
   const __nv_fp8_interpretation_t ks = P.qdtype_s == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
-  const bool int_t = P.qdtype_t == AQTB200_S8, int_s = P.qdtype_s == AQTB200_S8;
+  constexpr bool int_t = IS_INT, int_s = IS_INT;
   for (int64_t uf = blockIdx.x; uf < total_units; uf += gridDim.x) {
     const int64_t u = total_units - 1 - uf;  // back to front: the calibration pass's tail is still in L2
-#ifdef AQT_PAIR_CT_FAST
-    const int64_t ct = u % col_tiles;
-    int64_t t = u / col_tiles;
-    const int64_t rt = t % row_tiles;
-    const int64_t b = t / row_tiles;
-#else
     // Neighbouring blocks take neighbouring tiles along the CONTIGUOUS index of
     // the input, so the blocks in flight together stream whole rows of it (and
     // of the same-orientation output) instead of a 256-byte strip of every row.
@@ -889,12 +886,12 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
     int64_t t = u / row_tiles;
     const int64_t ct = t % col_tiles;
     const int64_t b = t / col_tiles;
-#endif
     const int64_t i1 = b % x.b1, i0 = b / x.b1;
     const int64_t bidx = i0 * x.b1 + i1;
     const int64_t r0 = rt * TR + tx * EPV;
     const bool row_ok = r0 < x.rows;  // rows % 8 == 0: a vector is all in or all out
     const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + (row_ok ? r0 : 0)) * 2;
+    uint8_t* qs_base = P.q_s + (bidx * x.cols + ct * 128 + ty * 4) * P.ld_s + r0;
     uint4 raw[2][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
@@ -914,11 +911,11 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
         uint32_t qt[4], qs[4];  // two bytes each (rows 2j, 2j+1)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-          if (P.chain == 1) {
+          if constexpr (CHAIN == 1) {
             qt[j] = bf16x2_to_q8x2(rw[j], pre_t, has_pre_t, sinv_t, int_t, P.clip_t, kt);
             qs[j] = bf16x2_to_q8x2(q8x2_to_bf16x2(qt[j], int_t, kt), 0u, false, sinv_s, int_s,
                                    P.clip_s, ks);
-          } else if (P.chain == 2) {
+          } else if constexpr (CHAIN == 2) {
             qs[j] = bf16x2_to_q8x2(rw[j], pre_s, has_pre_s, sinv_s, int_s, P.clip_s, ks);
             qt[j] = bf16x2_to_q8x2(q8x2_to_bf16x2(qs[j], int_s, ks), 0u, false, sinv_t, int_t,
                                    P.clip_t, kt);
@@ -931,7 +928,7 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
         q4[e][1] = in ? (qt[2] | (qt[3] << 16)) : 0u;
         if (in) {
           // same orientation: rows r0..r0+7 of column c are 8 contiguous bytes
-          *(uint2*)(P.q_s + (bidx * x.cols + c) * P.ld_s + r0) =
+          *(uint2*)(qs_base + (int64_t)(i * 64 + e) * P.ld_s) =
               make_uint2(qs[0] | (qs[1] << 16), qs[2] | (qs[3] << 16));
         }
       }
@@ -1738,7 +1735,19 @@ int aqtb200_quantize_pair(const aqtb200_view* x,
   P.ld_t = x->cols; P.ld_s = x->rows;
   const int64_t rts = (x->rows + 127) / 128, cts = (x->cols + 127) / 128;
   const int64_t units = nb * rts * cts;
-  quant_pair_kernel<<<grid_for(units, 4), 256, 0, (cudaStream_t)stream>>>(P, rts, cts, units);
+  const bool ints = spec_t->kind == AQTB200_NUM_INT;
+  AQT_REQUIRE(ints == (spec_s->kind == AQTB200_NUM_INT), AQTB200_EUNSUPPORTED,
+              "aqtb200_quantize_pair: both outputs int8 or both fp8");
+  const int grid = grid_for(units, 4);
+  cudaStream_t st = (cudaStream_t)stream;
+#define AQT_PAIR(I)                                                                   \
+  do {                                                                                \
+    if (chain == 0) quant_pair_kernel<I, 0><<<grid, 256, 0, st>>>(P, rts, cts, units);      \
+    else if (chain == 1) quant_pair_kernel<I, 1><<<grid, 256, 0, st>>>(P, rts, cts, units); \
+    else quant_pair_kernel<I, 2><<<grid, 256, 0, st>>>(P, rts, cts, units);                 \
+  } while (0)
+  if (ints) AQT_PAIR(true); else AQT_PAIR(false);
+#undef AQT_PAIR
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   return 0;
 }
