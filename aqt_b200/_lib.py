@@ -96,7 +96,7 @@ SYMBOLS = {
         C.POINTER(View),
         C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
         C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
-        C.c_int32, C.c_void_p]),
+        C.c_int32, C.c_void_p, C.c_void_p]),
     'aqtb200_requant_amax': (C.c_int, [
         C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.POINTER(QuantSpec),
         C.c_void_p, C.c_void_p, C.c_void_p]),

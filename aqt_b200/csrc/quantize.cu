@@ -803,6 +803,27 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
   }
 }
 
+// scale = where(a == 0, 1, a) [* clipping_scale] / quant_bound, in T, stored as S
+__device__ __forceinline__ float scale_of_amax(float a, int t_dtype, int s_dtype, float quant_bound,
+                                               float clipping_scale, int po2) {
+  if (a == 0.f) a = 1.f;
+  float bound = clipping_scale != 0.f ? round_to(__fmul_rn(a, clipping_scale), t_dtype) : a;
+  float s = round_to(__fdiv_rn(bound, quant_bound), t_dtype);
+  if (po2) {
+    // 1 / 2**floor(log2(1/s)); the exponent is read off the float directly.
+    float r = round_to(__fdiv_rn(1.f, s), t_dtype);
+    int e;
+    frexpf(r, &e);  // r = m * 2**e, m in [0.5, 1)
+    float p = round_to(ldexpf(1.f, e - 1), t_dtype);
+    s = round_to(__fdiv_rn(1.f, p), t_dtype);
+  }
+  return round_to(s, s_dtype);
+}
+__device__ __forceinline__ float recip_of_scale(float s, int s_dtype) {
+  float inv = round_to(__fdiv_rn(1.f, s), s_dtype);
+  return isinf(inv) ? 1.f : inv;
+}
+
 // ---------------------------------------------------------------------------
 // One read, two fp8 quantizations (bf16 input, per-tensor scales): the
 // transposed one of quant_col_fast and one in the input's own orientation.
@@ -814,14 +835,19 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
 // re-quantization of a stored forward operand); 2: the other way round.
 struct PairParams {
   DView x;                 // rows contiguous (kept index of q_t), cols strided
-  const void* scale_t;     // one bf16 scale per output
-  const void* scale_s;
+  void* scale_t;           // one bf16 scale per output (read, or written when amax is given)
+  void* scale_s;
   const void* pre_t;       // optional single bf16 / f32 prescale per output
   const void* pre_s;
   int pre_t_dtype, pre_s_dtype;
   int qdtype_t, qdtype_s;   // e4m3 / e5m2 / s8
   float clip_t, clip_s;     // int8 outputs: clip bound
   int chain;
+  // amax != null: the scales are computed here from amax[0] and written out
+  // (block 0), instead of being read
+  const uint32_t* amax;
+  float qb_t, qb_s, cs_t, cs_s;  // quant_bound / clipping_scale per output
+  int po2_t, po2_s;
   uint8_t* q_t;            // [b][rows][ld_t]
   uint8_t* q_s;            // [b][cols][ld_s]
   int64_t ld_t, ld_s;
@@ -839,6 +865,20 @@ __device__ __forceinline__ uint32_t fp8x2_to_bf16x2(uint32_t q2, __nv_fp8_interp
   const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)q2, k);
   const float2 f = __half22float2(*(const __half2*)&h);
   return pack_bf16x2(f.x, f.y);
+}
+
+// |value of Q(a)| for a >= 0 already prescaled: the largest magnitude among the
+// quantized values of a tensor whose largest magnitude is a.
+__device__ __forceinline__ float requant_abs(float a, float s, int t_dtype, int s_dtype, int kind,
+                                             int qdtype, float clip_bound) {
+  const float inv = recip_of_scale(s, s_dtype);
+  const int y_dtype = (t_dtype == AQTB200_F32 || s_dtype == AQTB200_F32) ? AQTB200_F32 : AQTB200_BF16;
+  float y = round_to(__fmul_rn(a, inv), y_dtype);
+  y = fminf(fmaxf(y, -clip_bound), clip_bound);
+  if (kind == AQTB200_NUM_INT) return fabsf((float)__float2int_rn(y));
+  const uint8_t q = (uint8_t)__nv_cvt_float_to_fp8(y, __NV_SATFINITE,
+                                                   qdtype == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2);
+  return fabsf(fp8_to_float(q, qdtype));
 }
 
 // Two bf16 values -> two quantized bytes (fp8, or int8 with clip and RNE), and back.
@@ -869,11 +909,44 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
   __shared__ __align__(16) uint32_t tile[TR][32];
   const DView& x = P.x;
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
-  const uint32_t sinv_t = bf16_recip_pair(P.scale_t), sinv_s = bf16_recip_pair(P.scale_s);
   const bool has_pre_t = P.pre_t != nullptr, has_pre_s = P.pre_s != nullptr;
   uint32_t pre_t = 0, pre_s = 0;
-  if (has_pre_t) { const float p = round_to(load1(P.pre_t, P.pre_t_dtype, 0), AQTB200_BF16); pre_t = pack_bf16x2(p, p); }
-  if (has_pre_s) { const float p = round_to(load1(P.pre_s, P.pre_s_dtype, 0), AQTB200_BF16); pre_s = pack_bf16x2(p, p); }
+  float pre_t_f = 1.f, pre_s_f = 1.f;
+  if (has_pre_t) { pre_t_f = round_to(load1(P.pre_t, P.pre_t_dtype, 0), AQTB200_BF16); pre_t = pack_bf16x2(pre_t_f, pre_t_f); }
+  if (has_pre_s) { pre_s_f = round_to(load1(P.pre_s, P.pre_s_dtype, 0), AQTB200_BF16); pre_s = pack_bf16x2(pre_s_f, pre_s_f); }
+  uint32_t sinv_t, sinv_s;
+  if (P.amax != nullptr) {
+    // Every block derives the two scales from the maximum (a few dozen scalar
+    // operations); block 0 also publishes them for the dequantizing epilogue.
+    constexpr int B = AQTB200_BF16;
+    constexpr int kind = IS_INT ? AQTB200_NUM_INT : AQTB200_NUM_FP8;
+    const float a = __uint_as_float(P.amax[0]);
+    const float a_t = has_pre_t ? apply_pre_abs(a, pre_t_f, B) : a;
+    const float a_s = has_pre_s ? apply_pre_abs(a, pre_s_f, B) : a;
+    float s_t, s_s;
+    if constexpr (CHAIN == 1) {
+      s_t = scale_of_amax(a_t, B, B, P.qb_t, P.cs_t, P.po2_t);
+      s_s = scale_of_amax(requant_abs(a_t, s_t, B, B, kind, P.qdtype_t, P.clip_t), B, B, P.qb_s,
+                          P.cs_s, P.po2_s);
+    } else if constexpr (CHAIN == 2) {
+      s_s = scale_of_amax(a_s, B, B, P.qb_s, P.cs_s, P.po2_s);
+      s_t = scale_of_amax(requant_abs(a_s, s_s, B, B, kind, P.qdtype_s, P.clip_s), B, B, P.qb_t,
+                          P.cs_t, P.po2_t);
+    } else {
+      s_t = scale_of_amax(a_t, B, B, P.qb_t, P.cs_t, P.po2_t);
+      s_s = scale_of_amax(a_s, B, B, P.qb_s, P.cs_s, P.po2_s);
+    }
+    if (blockIdx.x == 0 && tid == 0) {
+      *(__nv_bfloat16*)P.scale_t = __float2bfloat16_rn(s_t);
+      *(__nv_bfloat16*)P.scale_s = __float2bfloat16_rn(s_s);
+    }
+    const float it = recip_of_scale(s_t, B), is = recip_of_scale(s_s, B);
+    sinv_t = pack_bf16x2(it, it);
+    sinv_s = pack_bf16x2(is, is);
+  } else {
+    sinv_t = bf16_recip_pair(P.scale_t);
+    sinv_s = bf16_recip_pair(P.scale_s);
+  }
   const __nv_fp8_interpretation_t kt = P.qdtype_t == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
   const __nv_fp8_interpretation_t ks = P.qdtype_s == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
   constexpr bool int_t = IS_INT, int_s = IS_INT;
@@ -976,20 +1049,7 @@ __global__ void requant_amax_kernel(RequantAmaxParams R) {
   float a = __uint_as_float(R.amax[i]);
   if (R.pre != nullptr) a = apply_pre_abs(a, load1(R.pre, R.pre_dtype, 0), R.t_dtype);
   const float s = load1(R.scale, R.s_dtype, i);
-  float inv = round_to(__fdiv_rn(1.f, s), R.s_dtype);
-  if (isinf(inv)) inv = 1.f;
-  const int y_dtype = (R.t_dtype == AQTB200_F32 || R.s_dtype == AQTB200_F32) ? AQTB200_F32 : AQTB200_BF16;
-  float y = round_to(__fmul_rn(a, inv), y_dtype);
-  y = fminf(fmaxf(y, -R.clip_bound), R.clip_bound);
-  float v;
-  if (R.kind == AQTB200_NUM_INT) {
-    v = (float)__float2int_rn(y);
-  } else {
-    const uint8_t q = (uint8_t)__nv_cvt_float_to_fp8(
-        y, __NV_SATFINITE, R.qdtype == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2);
-    v = fp8_to_float(q, R.qdtype);
-  }
-  R.out[i] = fabsf(v);
+  R.out[i] = requant_abs(a, s, R.t_dtype, R.s_dtype, R.kind, R.qdtype, R.clip_bound);
 }
 
 // ---------------------------------------------------------------------------
@@ -1007,27 +1067,6 @@ struct FinalizeParams {
   const void* pre;  // optional single prescale applied to the maximum
   int pre_dtype;
 };
-
-// scale = where(a == 0, 1, a) [* clipping_scale] / quant_bound, in T, stored as S
-__device__ __forceinline__ float scale_of_amax(float a, int t_dtype, int s_dtype, float quant_bound,
-                                               float clipping_scale, int po2) {
-  if (a == 0.f) a = 1.f;
-  float bound = clipping_scale != 0.f ? round_to(__fmul_rn(a, clipping_scale), t_dtype) : a;
-  float s = round_to(__fdiv_rn(bound, quant_bound), t_dtype);
-  if (po2) {
-    // 1 / 2**floor(log2(1/s)); the exponent is read off the float directly.
-    float r = round_to(__fdiv_rn(1.f, s), t_dtype);
-    int e;
-    frexpf(r, &e);  // r = m * 2**e, m in [0.5, 1)
-    float p = round_to(ldexpf(1.f, e - 1), t_dtype);
-    s = round_to(__fdiv_rn(1.f, p), t_dtype);
-  }
-  return round_to(s, s_dtype);
-}
-__device__ __forceinline__ float recip_of_scale(float s, int s_dtype) {
-  float inv = round_to(__fdiv_rn(1.f, s), s_dtype);
-  return isinf(inv) ? 1.f : inv;
-}
 
 __global__ void finalize_scale_kernel(FinalizeParams F) {
   int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -1693,11 +1732,11 @@ int aqtb200_scale_from_amax(const float* amax, int64_t n, const void* prescale,
 }
 
 int aqtb200_quantize_pair(const aqtb200_view* x,
-                          const aqtb200_quant_spec* spec_t, const void* scale_t,
+                          const aqtb200_quant_spec* spec_t, void* scale_t,
                           const void* prescale_t, int32_t prescale_t_dtype, void* q_t,
-                          const aqtb200_quant_spec* spec_s, const void* scale_s,
+                          const aqtb200_quant_spec* spec_s, void* scale_s,
                           const void* prescale_s, int32_t prescale_s_dtype, void* q_s,
-                          int32_t chain, void* stream) {
+                          int32_t chain, const float* amax, void* stream) {
   AQT_REQUIRE(x != nullptr && spec_t != nullptr && spec_s != nullptr && scale_t != nullptr &&
                   scale_s != nullptr && q_t != nullptr && q_s != nullptr,
               AQTB200_EINVAL, "null argument");
@@ -1730,6 +1769,10 @@ int aqtb200_quantize_pair(const aqtb200_view* x,
   P.pre_t_dtype = prescale_t_dtype; P.pre_s_dtype = prescale_s_dtype;
   P.qdtype_t = spec_t->qdtype; P.qdtype_s = spec_s->qdtype;
   P.clip_t = spec_t->clip_bound; P.clip_s = spec_s->clip_bound;
+  P.amax = (const uint32_t*)amax;
+  P.qb_t = spec_t->quant_bound; P.qb_s = spec_s->quant_bound;
+  P.cs_t = spec_t->clipping_scale; P.cs_s = spec_s->clipping_scale;
+  P.po2_t = spec_t->po2_scale; P.po2_s = spec_s->po2_scale;
   P.chain = chain;
   P.q_t = (uint8_t*)q_t; P.q_s = (uint8_t*)q_s;
   P.ld_t = x->cols; P.ld_s = x->rows;

@@ -145,12 +145,17 @@ class ShardedDotGeneral:
           fwd_scale.reshape(1, 1))
     # Per-tensor scales everywhere: one pass over g and one max-all-reduce give
     # the cotangent's scale for both gradient dots.
-    shared = None
+    shared, pair = None, None
     try:
-      shared = engine.shared_cotangent_scales(cfg, res, g,
-                                              reduce_max=self._max)
+      # one read of the cotangent for both of its copies where that applies
+      pair = engine.cotangent_pair(cfg, res, g, reduce_max=self._max)
+      if pair is None:
+        shared = engine.shared_cotangent_scales(cfg, res, g,
+                                                reduce_max=self._max)
     except NotImplementedError:
       shared = None
+    if pair is not None:
+      shared = pair
     d_dims, d_perm = upd(dims, False, g.ndim, res.rhs.mt.x.ndim)
     if shared is not None:
       g_qt_dlhs, g_qt = shared
@@ -168,11 +173,7 @@ class ShardedDotGeneral:
             fwd_scale_r.reshape(1, 1))
       g_qt_dlhs = self._global_scale(cfg.dlhs.dg_quantizer.lhs, g, [1], 0,
                                      prescale=pre_r)
-    # One read of the cotangent for both of its copies, and the stored
-    # operands' backward copies from the forward pass, when they exist.
-    pair = engine.cotangent_pair(cfg, res, g, shared)
-    if pair is not None:
-      g_qt_dlhs, g_qt = pair
+    # The stored operands' backward copies from the forward pass, when they exist.
     x_qt = engine.bwd_copy(res.lhs.mt.qx) if cfg.drhs.rhs.use_fwd_quant else None
     y_qt = engine.bwd_copy(res.rhs.mt.qx) if cfg.dlhs.rhs.use_fwd_quant else None
     internal = pair is not None or x_qt is not None or y_qt is not None

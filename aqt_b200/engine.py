@@ -997,8 +997,13 @@ def _scale_of_amax(amax, spec, prescale=None):
   return out
 
 
-def _quantize_pair(x, spec_t, scale_t, pre_t, spec_s, scale_s, pre_s, chain):
-  """x: [C, R] row-major bf16. Returns (q_t [R][C], q_s [C][R]) buffers."""
+def _quantize_pair(x, spec_t, scale_t, pre_t, spec_s, scale_s, pre_s, chain,
+                   amax=None):
+  """x: [C, R] row-major bf16. Returns (q_t [R][C], q_s [C][R]) buffers.
+
+  With `amax` (the raw maximum of x) the kernel computes both scales itself
+  and writes them into scale_t / scale_s; otherwise it reads them.
+  """
   c, r = x.shape
   view = _view(x.data_ptr(), _lib.BF16, [1, 1], r, c, [0, 0], 1, r)
   q_t = torch.empty((r, c), dtype=_CODE_TORCH[spec_t.qdtype], device=x.device)
@@ -1008,7 +1013,8 @@ def _quantize_pair(x, spec_t, scale_t, pre_t, spec_s, scale_s, pre_s, chain):
   rc = _lib.load().aqtb200_quantize_pair(
       C.byref(view), C.byref(spec_t), scale_t.data_ptr(), pt, ptc,
       q_t.data_ptr(), C.byref(spec_s), scale_s.data_ptr(), ps, psc,
-      q_s.data_ptr(), chain, _stream())
+      q_s.data_ptr(), chain, None if amax is None else amax.data_ptr(),
+      _stream())
   _lib.check(rc, 'aqtb200_quantize_pair')
   return q_t, q_s
 
@@ -1046,18 +1052,14 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers,
     return None
   f_lhs, f_rhs, b_lhs, b_rhs = specs
   dd = utils.as_dtype(lhs.dtype)
-  lib = _lib.load()
 
-  def scales(x, spec1, spec2, reduce_max=None):
+  def new_scales(x):
+    mk = lambda: torch.empty(1, dtype=torch.bfloat16, device=x.device)
+    return mk(), mk()
+
+  def amax_of(x, reduce_max=None):
     amax = absmax_raw(x)
-    if reduce_max is not None:
-      amax = reduce_max(amax)
-    s1 = _scale_of_amax(amax, spec1)
-    amax_q = torch.empty(1, dtype=torch.float32, device=x.device)
-    rc = lib.aqtb200_requant_amax(amax.data_ptr(), 1, None, 0, C.byref(spec1),
-                                  s1.data_ptr(), amax_q.data_ptr(), _stream())
-    _lib.check(rc, 'aqtb200_requant_amax')
-    return s1, _scale_of_amax(amax_q, spec2)
+    return reduce_max(amax) if reduce_max is not None else amax
 
   def qt(qvalue, scale):
     return aqt_tensor.QTensor(qvalue=qvalue, scale=[scale.view(1, 1)],
@@ -1065,14 +1067,16 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers,
 
   # lhs [M, K]: its own orientation is the forward copy (K contiguous); the
   # transposed one, [K][M], is what drhs contracts over M.
-  s1, s2 = scales(lhs, f_lhs, b_lhs, reduce_max_lhs)
-  q_t, q_s = _quantize_pair(lhs, b_lhs, s2, None, f_lhs, s1, None, chain=2)
+  s1, s2 = new_scales(lhs)
+  q_t, q_s = _quantize_pair(lhs, b_lhs, s2, None, f_lhs, s1, None, chain=2,
+                            amax=amax_of(lhs, reduce_max_lhs))
   lhs_qt = qt(q_s, s1)
   setattr(lhs_qt.qvalue, _BWD_COPY, qt(q_t.t(), s2))
   # rhs [K, N]: the transposed copy, [N][K], is the forward one; its own
   # orientation (N contiguous) is what dlhs contracts over.
-  s1, s2 = scales(rhs, f_rhs, b_rhs)
-  q_t, q_s = _quantize_pair(rhs, f_rhs, s1, None, b_rhs, s2, None, chain=1)
+  s1, s2 = new_scales(rhs)
+  q_t, q_s = _quantize_pair(rhs, f_rhs, s1, None, b_rhs, s2, None, chain=1,
+                            amax=amax_of(rhs))
   rhs_qt = qt(q_t.t(), s1)
   setattr(rhs_qt.qvalue, _BWD_COPY, qt(q_s, s2))
   return lhs_qt, rhs_qt
@@ -1089,30 +1093,40 @@ def bwd_copy(qt):
   return getattr(qt.qvalue, _BWD_COPY, None)
 
 
-def cotangent_pair(cfg, res, g, shared):
-  """Both quantizations of the cotangent g[M,N] in one read.
-
-  `shared` are the two incomplete QTensors of shared_cotangent_scales (dlhs,
-  drhs). Returns full QTensors (g for dlhs, g for drhs) or None.
-  """
+def cotangent_pair(cfg, res, g, reduce_max=None):
+  """Both quantizations of the cotangent g[M,N] in one read (plus one pass for
+  its maximum). Returns full QTensors (g for dlhs, g for drhs) or None when
+  the configuration is outside what aqtb200_quantize_pair covers.
+  `reduce_max`, if given, is applied to the raw maximum (cross-rank max)."""
   from aqt_b200.v2 import aqt_tensor
-  if shared is None or not _pair_matrix_ok(g):
+  if not _pair_matrix_ok(g):
     return None
   sp_dl = _pair_spec(cfg.dlhs.dg_quantizer.lhs)
   sp_dr = _pair_spec(cfg.drhs.dg_quantizer.lhs)
-  if sp_dl is None or sp_dr is None:
+  if sp_dl is None or sp_dr is None or sp_dl.kind != sp_dr.kind:
     return None
   pres = []
   for raw, mt in ((cfg.dlhs, res.rhs.mt), (cfg.drhs, res.lhs.mt)):
-    pres.append(mt.qx.scale[0] if raw.rhs.use_fwd_quant else None)
+    if raw.rhs.use_fwd_quant:
+      if mt.qx.scale is None or len(mt.qx.scale) != 1 or (
+          mt.qx.scale[0].numel() != 1):
+        return None
+      pres.append(mt.qx.scale[0])
+    else:
+      pres.append(None)
+  amax = absmax_raw(g)
+  if reduce_max is not None:
+    amax = reduce_max(amax)
+  mk = lambda: torch.empty(1, dtype=torch.bfloat16, device=g.device)
+  s_dl, s_dr = mk(), mk()
   # g [M, N]: own orientation (N contiguous) feeds dlhs, the transposed copy
   # [N][M] feeds drhs.
-  q_t, q_s = _quantize_pair(g, sp_dr, shared[1].scale[0], pres[1],
-                            sp_dl, shared[0].scale[0], pres[0], chain=0)
+  q_t, q_s = _quantize_pair(g, sp_dr, s_dr, pres[1], sp_dl, s_dl, pres[0],
+                            chain=0, amax=amax)
   dd = utils.as_dtype(g.dtype)
-  mk = lambda qv, sc: aqt_tensor.QTensor(qvalue=qv, scale=[sc.view(1, 1)],
+  qt = lambda qv, sc: aqt_tensor.QTensor(qvalue=qv, scale=[sc.view(1, 1)],
                                          scale_t=None, bias=[], dequant_dtype=dd)
-  return mk(q_s, shared[0].scale[0]), mk(q_t.t(), shared[1].scale[0])
+  return qt(q_s, s_dl), qt(q_t.t(), s_dr)
 
 
 def quantize_with_scale(x, scale, numerics, noise=None):

@@ -531,21 +531,18 @@ def dg_core_vjp_bwd(fwd_dimension_numbers, res, g):
   g = g[0]  # g[1] would be the gradient w.r.t. the returned QTensors.
 
   from aqt_b200 import engine
-  # One pass over the cotangent can serve both of its quantizations when all
-  # the scales involved are per-tensor; otherwise each raw dot calibrates it.
+  # One read of the cotangent gives both of its quantized copies when all the
+  # scales involved are per-tensor (and the kernel covers the dtypes); failing
+  # that, one pass over it can still serve both calibrations; otherwise each
+  # raw dot calibrates and quantizes it on its own.
   shared = None
   if cfg.dlhs.local_aqt is None and cfg.drhs.local_aqt is None:
     try:
-      shared = engine.shared_cotangent_scales(cfg, dg_res, g)
+      shared = engine.cotangent_pair(cfg, dg_res, g)
+      if shared is None:
+        shared = engine.shared_cotangent_scales(cfg, dg_res, g)
     except NotImplementedError:
       shared = None
-
-  # ... and one read when both quantized copies can be written together.
-  pair = None
-  if shared is not None:
-    pair = engine.cotangent_pair(cfg, dg_res, g, shared)
-    if pair is not None:
-      shared = pair
 
   def grad_dot_general(y_res: TensorRes, quant_grad, dg_raw, y_is_lhs):
     dims, out_transpose_axes = _update_dimension_numbers_for_backward(

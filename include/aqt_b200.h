@@ -200,7 +200,12 @@ int aqtb200_scale_from_amax(const float* amax, int64_t n, const void* prescale,
  * x: row_stride == 1, col_stride != 1, rows and cols multiples of 16, every
  * stride a multiple of 8 elements. Each output has its own spec (fp8 or int8,
  * per_tensor, bf16 compute and scale dtype), its own one-element bf16 scale
- * (an INPUT here) and an optional one-element prescale.
+ * and an optional one-element prescale. With amax == NULL the scales are
+ * INPUTS. With amax given (one f32, the operand's raw maximum from
+ * aqtb200_absmax_raw, max-reduced across ranks if the operand is sharded) they
+ * are OUTPUTS: the kernel derives them as aqtb200_scale_from_amax and, for the
+ * chained output, aqtb200_requant_amax would, so an operand costs two
+ * launches in all.
  * chain = 0: both outputs quantize x (the cotangent);
  * chain = 1: q_s quantizes the values of q_t (x -> q_t -> q_s: q_t is the
  *            forward copy, q_s the backward re-quantization of it);
@@ -216,11 +221,11 @@ int aqtb200_scale_from_amax(const float* amax, int64_t n, const void* prescale,
  * `prescale` are those of the FIRST quantization.
  */
 int aqtb200_quantize_pair(const aqtb200_view* x,
-                          const aqtb200_quant_spec* spec_t, const void* scale_t,
+                          const aqtb200_quant_spec* spec_t, void* scale_t,
                           const void* prescale_t, int32_t prescale_t_dtype, void* q_t,
-                          const aqtb200_quant_spec* spec_s, const void* scale_s,
+                          const aqtb200_quant_spec* spec_s, void* scale_s,
                           const void* prescale_s, int32_t prescale_s_dtype, void* q_s,
-                          int32_t chain, void* stream);
+                          int32_t chain, const float* amax, void* stream);
 int aqtb200_requant_amax(const float* amax, int64_t n, const void* prescale,
                          int32_t prescale_dtype, const aqtb200_quant_spec* spec,
                          const void* scale, float* amax_q_out, void* stream);

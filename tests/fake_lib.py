@@ -198,11 +198,32 @@ class FakeLib:
 
   def aqtb200_quantize_pair(self, x, spec_t, scale_t, pre_t, pre_t_dtype, q_t,
                             spec_s, scale_s, pre_s, pre_s_dtype, q_s, chain,
-                            stream):
+                            amax, stream):
     self.calls.append(('quantize_pair', chain))
     x = _deref(x, _lib.View)
     spec_t = _deref(spec_t, _lib.QuantSpec)
     spec_s = _deref(spec_s, _lib.QuantSpec)
+    if amax:
+      # the scales are outputs: derive them as the separate entry points would
+      tmp = (C.c_float * 1)()
+      tp = C.addressof(tmp)
+      if chain == 1:
+        self.aqtb200_scale_from_amax(amax, 1, pre_t, pre_t_dtype, spec_t,
+                                     scale_t, None)
+        self.aqtb200_requant_amax(amax, 1, pre_t, pre_t_dtype, spec_t, scale_t,
+                                  tp, None)
+        self.aqtb200_scale_from_amax(tp, 1, None, 0, spec_s, scale_s, None)
+      elif chain == 2:
+        self.aqtb200_scale_from_amax(amax, 1, pre_s, pre_s_dtype, spec_s,
+                                     scale_s, None)
+        self.aqtb200_requant_amax(amax, 1, pre_s, pre_s_dtype, spec_s, scale_s,
+                                  tp, None)
+        self.aqtb200_scale_from_amax(tp, 1, None, 0, spec_t, scale_t, None)
+      else:
+        self.aqtb200_scale_from_amax(amax, 1, pre_t, pre_t_dtype, spec_t,
+                                     scale_t, None)
+        self.aqtb200_scale_from_amax(amax, 1, pre_s, pre_s_dtype, spec_s,
+                                     scale_s, None)
     if x.dtype != _lib.BF16 or x.row_stride != 1 or x.rows % 16 or x.cols % 16:
       return self._fail(-2, 'quantize_pair: unsupported view')
 
