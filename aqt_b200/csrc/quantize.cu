@@ -373,7 +373,7 @@ constexpr int kFastRowChunk = 8192;  // most elements of one (row, chunk) work u
 // absmax, contraction contiguous, one warp per (batch-row, chunk).
 // PRE: 0 none, 1 constant over the row (applied to the maximum), 2 per column.
 template <int EPV, int PRE>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, PRE == 2 ? 4 : (EPV == 16 ? 6 : 8))
 absmax_row_fast(QParams P, int64_t chunks_per_row, int64_t total_units, int chunk_elems) {
   constexpr int ES = 16 / EPV;
   constexpr int U = 4;
