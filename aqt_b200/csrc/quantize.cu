@@ -34,6 +34,7 @@ struct QParams {
   int use_lut;    // 1-byte input, one scale and one prescale for the whole call: byte -> byte table
   int fast_bf16;  // bf16 in, bf16 scale, fp8 out, no noise: packed bf16 arithmetic
   int pre_bf16;   // bf16 input, bf16 prescale, bf16 compute dtype: x * pre as packed bf16 multiplies
+  int int_bf16;   // bf16 in, bf16 scale and prescale, int8 out (with or without noise): packed bf16 arithmetic
   uint32_t* amax;
   float* sinv;
   uint8_t* q;
@@ -368,6 +369,33 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   return *(const uint32_t*)&t;
 }
 
+// Four bf16 values (two raw words) -> four int8 bytes, arithmetic in packed
+// bf16: round_bf16(x * pre), round_bf16(. * sinv), optionally
+// round_bf16(f32(.) + noise), clip, round half to even.
+__device__ __forceinline__ uint32_t bf16x4_to_s8x4(uint32_t w0, uint32_t w1, uint32_t p0, uint32_t p1,
+                                                   bool has_pre, uint32_t s0, uint32_t s1,
+                                                   const float* nz, bool has_noise, float clip) {
+  uint32_t out = 0;
+  const uint32_t ws[2] = {w0, w1}, ps[2] = {p0, p1}, ss[2] = {s0, s1};
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    __nv_bfloat162 v = *(const __nv_bfloat162*)&ws[h];
+    if (has_pre) v = __hmul2(v, *(const __nv_bfloat162*)&ps[h]);
+    v = __hmul2(v, *(const __nv_bfloat162*)&ss[h]);
+    uint32_t r = *(const uint32_t*)&v;
+    float lo = bf16lo(r), hi = bf16hi(r);
+    if (has_noise) {
+      r = pack_bf16x2(__fadd_rn(lo, nz[2 * h]), __fadd_rn(hi, nz[2 * h + 1]));
+      lo = bf16lo(r); hi = bf16hi(r);
+    }
+    lo = fminf(fmaxf(lo, -clip), clip);
+    hi = fminf(fmaxf(hi, -clip), clip);
+    out |= (((uint32_t)__float2int_rn(lo) & 0xffu) | (((uint32_t)__float2int_rn(hi) & 0xffu) << 8))
+           << (16 * h);
+  }
+  return out;
+}
+
 constexpr int kFastRowChunk = 8192;  // most elements of one (row, chunk) work unit
 
 // absmax, contraction contiguous, one warp per (batch-row, chunk).
@@ -641,6 +669,27 @@ quant_row_fast(QParams P, int64_t units_per_row, int64_t total_units) {
             outw[(n * 2 + g) & 3] = lo | (hi << 16);
           }
         }
+      } else if (EPV == 8 && P.int_bf16 && (PRE != 2 || P.pre_vec) && (!has_noise || P.noise_vec)) {
+        const uint32_t sinv2 = pack_bf16x2(s, s);
+#pragma unroll
+        for (int n = 0; n < NV; ++n) {
+          const uint32_t rw[4] = {raw[k][n].x, raw[k][n].y, raw[k][n].z, raw[k][n].w};
+          const int64_t c = col[k] + n * EPV;
+          uint32_t pw[4] = {0u, 0u, 0u, 0u};
+          if constexpr (PRE == 1) {
+            pw[0] = pw[1] = pw[2] = pw[3] = pack_bf16x2(pconst, pconst);
+          } else if constexpr (PRE == 2) {
+            const uint4 pv = ldg16(P.pre.ptr, (pbase + c) * 2);
+            pw[0] = pv.x; pw[1] = pv.y; pw[2] = pv.z; pw[3] = pv.w;
+          }
+#pragma unroll
+          for (int g = 0; g < 2; ++g) {
+            float nz[4] = {0.f, 0.f, 0.f, 0.f};
+            if (has_noise) loadN<4>(P.noise.ptr, AQTB200_F32, nbase + c + 4 * g, nz);
+            outw[(n * 2 + g) & 3] = bf16x4_to_s8x4(rw[2 * g], rw[2 * g + 1], pw[2 * g], pw[2 * g + 1],
+                                                   PRE != 0, sinv2, sinv2, nz, has_noise, P.clip_bound);
+          }
+        }
       } else {
 #pragma unroll
       for (int n = 0; n < NV; ++n) {
@@ -751,6 +800,22 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
             const uint32_t hi = bf16x2_to_fp8x2(rw[(2 * g + 1) & 3], pre2, PRE != 0,
                                                 pack_bf16x2(sinv[(4 * g + 2) % EPV], sinv[(4 * g + 3) % EPV]), f8k);
             q4[e][g] = in ? (lo | (hi << 16)) : 0u;
+          }
+        } else if (EPV == 8 && P.int_bf16 && (!has_noise || P.noise_vec)) {
+          float p = pconst;
+          if constexpr (PRE == 2) p = in ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
+          const uint32_t pre2 = pack_bf16x2(p, p);
+#pragma unroll
+          for (int g = 0; g < EPV / 4; ++g) {
+            float nz[4] = {0.f, 0.f, 0.f, 0.f};
+            if (has_noise && in)
+              loadN<4>(P.noise.ptr, AQTB200_F32, nbase + c * P.noise.sc + r0 + 4 * g, nz);
+            const uint32_t q = bf16x4_to_s8x4(
+                rw[(2 * g) & 3], rw[(2 * g + 1) & 3], pre2, pre2, PRE != 0,
+                pack_bf16x2(sinv[(4 * g) % EPV], sinv[(4 * g + 1) % EPV]),
+                pack_bf16x2(sinv[(4 * g + 2) % EPV], sinv[(4 * g + 3) % EPV]), nz, has_noise,
+                P.clip_bound);
+            q4[e][g] = in ? q : 0u;
           }
         } else {
           float v[EPV];
@@ -1501,6 +1566,8 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
                 (P.pre.ptr == nullptr || P.pre.dtype == AQTB200_BF16 || true);
   P.pre_bf16 = P.pre.ptr != nullptr && P.x.dtype == AQTB200_BF16 && P.pre.dtype == AQTB200_BF16 &&
                P.t_dtype == AQTB200_BF16;
+  P.int_bf16 = P.x.dtype == AQTB200_BF16 && P.t_dtype == AQTB200_BF16 && P.s_dtype == AQTB200_BF16 &&
+               P.kind == AQTB200_NUM_INT && (P.pre.ptr == nullptr || P.pre.dtype == AQTB200_BF16);
   // prescale class: 0 none, 1 constant along the contraction index, 2 varying
   const int pre_kind = P.pre.ptr == nullptr ? 0 : (P.pre.sc == 0 || xv->cols <= 1 ? 1 : 2);
   const bool fast_row = row_mode && row_vec_ok(P.x, xv->cols);
