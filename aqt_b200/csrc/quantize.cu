@@ -482,6 +482,65 @@ absmax_row_fast(QParams P, int64_t chunks_per_row, int64_t total_units, int chun
   }
 }
 
+// absmax, contraction contiguous, rows of at most 32 vectors (a power of two
+// of them): one lane per vector, 32 / nvec rows per warp and load, the row
+// maximum by a segmented butterfly. absmax_row_fast gives such rows a whole
+// warp each and leaves most lanes idle.
+template <int EPV, int PRE>
+__global__ void __launch_bounds__(256, 5)
+absmax_shortrow_fast(QParams P, int64_t nbrow, int nvec) {
+  constexpr int ES = 16 / EPV;
+  constexpr int U = 4;
+  __shared__ float red[32];
+  const int lane = threadIdx.x & 31;
+  const int rows_per_warp = 32 / nvec;
+  const int sub = lane / nvec, vi = lane % nvec;
+  const int64_t warp_g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const DView& x = P.x;
+  float tmax = 0.f;
+  const int64_t groups = (nbrow + rows_per_warp - 1) / rows_per_warp;
+  for (int64_t g0 = warp_g * U; g0 < groups; g0 += nwarps * U) {
+    uint4 raw[U];
+    int64_t brow[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      brow[k] = (g0 + k) * rows_per_warp + sub;
+      raw[k] = make_uint4(0u, 0u, 0u, 0u);
+      if (g0 + k < groups && brow[k] < nbrow) {
+        int64_t i0, i1, r;
+        decode_brow(x, brow[k], i0, i1, r);
+        raw[k] = ldg16(x.ptr, ((i0 * x.sb0 + i1 * x.sb1 + r * x.sr) * ES) + (int64_t)vi * 16);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      uint4 run = make_uint4(0u, 0u, 0u, 0u);
+      packed_absmax<EPV>(run, raw[k], x.dtype);
+      float m = packed_hmax<EPV>(run, x.dtype);
+      for (int o = nvec >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const bool ok = g0 + k < groups && brow[k] < nbrow;
+      if constexpr (PRE == 1) {
+        if (ok) {
+          int64_t i0, i1, r;
+          decode_brow(x, brow[k], i0, i1, r);
+          m = apply_pre_abs(m, load1(P.pre.ptr, P.pre.dtype, i0 * P.pre.sb0 + i1 * P.pre.sb1),
+                            P.t_dtype);
+        }
+      }
+      if (P.per_tensor) {
+        if (ok) tmax = fmaxf(tmax, m);
+      } else if (ok && vi == 0) {
+        P.amax[brow[k]] = __float_as_uint(m);  // the whole row is in this group: no atomic needed
+      }
+    }
+  }
+  if (P.per_tensor) {
+    tmax = block_max(tmax, red);
+    if (threadIdx.x == 0 && tmax > 0.f) atomic_max_nonneg(P.amax, tmax);
+  }
+}
+
 // absmax, kept index contiguous. Block (32 x 8): thread (tx, ty) owns the EPV
 // kept rows of one 16-byte vector and strides over a chunk of the contraction
 // index. PRE: 0 none, 1 constant over the contraction index, 2 varying with it.
@@ -1616,7 +1675,22 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
   if (scale_in == nullptr) {
     AQT_CUDA_OK(cudaMemsetAsync(P.amax, 0, (size_t)ns * 4, st));
     if (total > 0) {
-      if (fast_row && (pre_kind != 2 || P.pre_vec)) {
+      const int64_t row_vecs = xv->cols / (16 / dtype_size(P.x.dtype));
+      if (fast_row && pre_kind != 2 && xv->cols % (16 / dtype_size(P.x.dtype)) == 0 &&
+          row_vecs >= 1 && row_vecs <= 16 && (row_vecs & (row_vecs - 1)) == 0) {
+        const int64_t groups = (nbrow + (32 / row_vecs) - 1) / (32 / row_vecs);
+        const int grid = grid_for((groups + 31) / 32, 8);
+        if (epv == 4) {
+          if (pre_kind == 0) absmax_shortrow_fast<4, 0><<<grid, 256, 0, st>>>(P, nbrow, (int)row_vecs);
+          else absmax_shortrow_fast<4, 1><<<grid, 256, 0, st>>>(P, nbrow, (int)row_vecs);
+        } else if (epv == 8) {
+          if (pre_kind == 0) absmax_shortrow_fast<8, 0><<<grid, 256, 0, st>>>(P, nbrow, (int)row_vecs);
+          else absmax_shortrow_fast<8, 1><<<grid, 256, 0, st>>>(P, nbrow, (int)row_vecs);
+        } else {
+          if (pre_kind == 0) absmax_shortrow_fast<16, 0><<<grid, 256, 0, st>>>(P, nbrow, (int)row_vecs);
+          else absmax_shortrow_fast<16, 1><<<grid, 256, 0, st>>>(P, nbrow, (int)row_vecs);
+        }
+      } else if (fast_row && (pre_kind != 2 || P.pre_vec)) {
         // a (row, chunk) unit is one warp's work: shorter chunks when the whole
         // tensor would otherwise occupy a handful of warps (decode-time activations)
         int chunk_elems = kFastRowChunk;

@@ -261,6 +261,26 @@ def test_skinny_lhs_uses_narrow_mmas_and_agrees(shape, np_dtype):
   _exact(a[0], want, 'out vs oracle')
 
 
+@pytest.mark.parametrize('k', [16, 32, 64, 128])
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+def test_short_contraction_rows(k, np_dtype):
+  """Rows of at most 32 sixteen-byte vectors take the several-rows-per-warp
+  absmax kernel; batched, as the attention-score einsum uses it."""
+  rng = np.random.default_rng(k)
+  dims = (((3,), (3,)), ((0, 2), (0, 2)))
+  lhs = util.rand_normal(rng, (2, 70, 3, k), 1.0, np_dtype)
+  rhs = util.rand_normal(rng, (2, 50, 3, k), 1.0, np_dtype)
+  lhs[1, 5, 2, :] = 0  # an all-zero row: scale 1
+  raw = aqt.dot_general_raw_make(8, 8)
+  got, res = engine.dg_raw(raw, _cuda(lhs), _cuda(rhs), None, None, dims)
+  _sync()
+  want, wres = orc.dg_raw(raw, lhs, rhs, None, None, dims)
+  _exact(res.lhs.mt.qx.scale[0], wres.lhs.qx.scale[0], 's_lhs')
+  _exact(res.rhs.mt.qx.scale[0], wres.rhs.qx.scale[0], 's_rhs')
+  _exact(res.lhs.mt.qx.qvalue, wres.lhs.qx.qvalue, 'q_lhs')
+  _exact(got, want, 'out')
+
+
 def test_wide_kernel_batched_and_transposed_output():
   """The 256 x 512 kernel under batch dims and the drhs output transpose."""
   rng = np.random.default_rng(11)
