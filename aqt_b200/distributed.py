@@ -62,6 +62,14 @@ class ShardedDotGeneral:
       dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
     return t
 
+  def _max_async(self, t):
+    """Starts a max-all-reduce of t in place; returns (t, wait) or t."""
+    if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+      work = dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group,
+                             async_op=True)
+      return t, work.wait
+    return t
+
   def _sum(self, t):
     if dist.is_initialized() and dist.get_world_size(self.group) > 1:
       dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
@@ -110,7 +118,7 @@ class ShardedDotGeneral:
     # backward copies; lhs's maximum is agreed across ranks first, which fixes
     # every scale of lhs on every rank without a further collective.
     pre = engine.prequantize_for_training(cfg, lhs, rhs, dims,
-                                          reduce_max_lhs=self._max)
+                                          reduce_max_lhs=self._max_async)
     if pre is not None:
       out, res = engine.dg_raw(cfg.fwd, lhs, rhs, pre[0], pre[1], dims,
                                internal_qt=True)

@@ -1065,13 +1065,13 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers,
     return aqt_tensor.QTensor(qvalue=qvalue, scale=[scale.view(1, 1)],
                               scale_t=None, bias=[], dequant_dtype=dd)
 
-  # lhs [M, K]: its own orientation is the forward copy (K contiguous); the
-  # transposed one, [K][M], is what drhs contracts over M.
-  s1, s2 = new_scales(lhs)
-  q_t, q_s = _quantize_pair(lhs, b_lhs, s2, None, f_lhs, s1, None, chain=2,
-                            amax=amax_of(lhs, reduce_max_lhs))
-  lhs_qt = qt(q_s, s1)
-  setattr(lhs_qt.qvalue, _BWD_COPY, qt(q_t.t(), s2))
+  # lhs's maximum first: when it has to be agreed across ranks, that exchange
+  # (reduce_max_lhs may return (tensor, wait) for one in flight) runs while
+  # rhs, which is replicated, is calibrated and quantized.
+  lhs_amax = amax_of(lhs, reduce_max_lhs)
+  lhs_wait = None
+  if isinstance(lhs_amax, tuple):
+    lhs_amax, lhs_wait = lhs_amax
   # rhs [K, N]: the transposed copy, [N][K], is the forward one; its own
   # orientation (N contiguous) is what dlhs contracts over.
   s1, s2 = new_scales(rhs)
@@ -1079,6 +1079,15 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers,
                             amax=amax_of(rhs))
   rhs_qt = qt(q_t.t(), s1)
   setattr(rhs_qt.qvalue, _BWD_COPY, qt(q_s, s2))
+  # lhs [M, K]: its own orientation is the forward copy (K contiguous); the
+  # transposed one, [K][M], is what drhs contracts over M.
+  if lhs_wait is not None:
+    lhs_wait()
+  s1, s2 = new_scales(lhs)
+  q_t, q_s = _quantize_pair(lhs, b_lhs, s2, None, f_lhs, s1, None, chain=2,
+                            amax=lhs_amax)
+  lhs_qt = qt(q_s, s1)
+  setattr(lhs_qt.qvalue, _BWD_COPY, qt(q_t.t(), s2))
   return lhs_qt, rhs_qt
 
 

@@ -106,7 +106,7 @@ def test_fp8_per_tensor_paired_quantization_matches_oracle(monkeypatch, fwd,
   (out, (lq, rq)), vres = aqt.dg_core_vjp_fwd(tl, tr, None, None, dims, cfg)
   dl, dr, *_ = aqt.dg_core_vjp_bwd(dims, vres, (tg, None))
   assert [c for c in fake.calls if c[0] == 'quantize_pair'] == [
-      ('quantize_pair', 2), ('quantize_pair', 1), ('quantize_pair', 0)]
+      ('quantize_pair', 1), ('quantize_pair', 2), ('quantize_pair', 0)]
   wo, wl, wr, res = orc.dg_fwd_bwd(cfg, lhs, rhs, g, dims)
   _assert_same(lq.qvalue, res.lhs.qx.qvalue, 'q_lhs')
   _assert_same(rq.qvalue, res.rhs.qx.qvalue, 'q_rhs')
