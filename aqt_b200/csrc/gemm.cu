@@ -32,7 +32,7 @@ constexpr int STAGES = 4;
 constexpr int MAX_STAGES1 = 12;  // single-CTA kernel, narrow B tiles: up to this many stages
 constexpr int A_STAGE = BM * BK;
 constexpr int B_STAGE = BN * BK;
-constexpr int GROUP_M = 16;
+constexpr int GROUP_M = 32;
 constexpr int EPI_WARPS = 8;     // two per TMEM lane quarter, each draining half the columns
 constexpr int GEMM_THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
