@@ -497,7 +497,7 @@ def gemm_roofline(args, cfg, lhs, rhs, torch, engine):
   # DRAM bytes (read + write) of one launch of this kernel at this shape, from
   # the ncu capture summarised in profiles/gemm_tcgen05_wide_fp8_8192.md; it
   # is not re-measured here (nothing is timed under a profiler).
-  traffic = 537.0e6 if (m, n, k) == (8192, 8192, 8192) else None
+  traffic = 446.0e6 if (m, n, k) == (8192, 8192, 8192) else None
   return {'bound': 'tensor',
           'kernel': 'gemm_tcgen05_wide_kernel (forward GEMM, 256x512 CTA-pair tiles)',
           'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s',
