@@ -51,7 +51,7 @@ class GemmDesc(C.Structure):
       ('out', C.c_void_p), ('out_dtype', C.c_int32), ('reserved', C.c_int32),
       ('out_b0_stride', C.c_int64), ('out_b1_stride', C.c_int64),
       ('out_m_stride', C.c_int64), ('out_n_stride', C.c_int64),
-      ('acc_out', C.c_void_p),
+      ('acc_out', C.c_void_p), ('amax_out', C.c_void_p),
   ]
 
 
@@ -69,7 +69,7 @@ class DgRawDesc(C.Structure):
       ('out', C.c_void_p), ('out_dtype', C.c_int32), ('reserved', C.c_int32),
       ('out_b0_stride', C.c_int64), ('out_b1_stride', C.c_int64),
       ('out_m_stride', C.c_int64), ('out_n_stride', C.c_int64),
-      ('acc_out', C.c_void_p),
+      ('acc_out', C.c_void_p), ('amax_out', C.c_void_p),
   ]
 
 

@@ -113,6 +113,7 @@ static void fill_gemm_desc(const aqtb200_dg_raw_desc* d, const Side& L, const Si
   g.out_m_stride = d->swap_ab ? d->out_n_stride : d->out_m_stride;
   g.out_n_stride = d->swap_ab ? d->out_m_stride : d->out_n_stride;
   g.acc_out = d->acc_out;
+  g.amax_out = d->amax_out;
 }
 
 }  // namespace aqtb200

@@ -51,6 +51,7 @@ struct GemmParams {
   void* out;
   int64_t o_b0, o_b1, o_m, o_n;
   void* acc_out;
+  uint32_t* amax_out;  // optional: max |out| as f32 bits (atomic max)
   uint32_t idesc, idesc2;
   int64_t m_tiles, n_tiles, total_tiles, num_kb;
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
@@ -218,6 +219,24 @@ __device__ __forceinline__ float scale_mul(float r, float s, int& cur, int sdt) 
   return round_to(__fmul_rn(r, s), cur);
 }
 
+// Running max |v| of an epilogue thread, as f32 bits (non-negative floats order
+// like their bit patterns; a NaN pattern ranks above infinity and so survives).
+__device__ __forceinline__ void amax_f32(uint32_t& run, float v) {
+  run = max(run, __float_as_uint(v) & 0x7fffffffu);
+}
+// eight packed bf16 pairs
+__device__ __forceinline__ void amax_bf16x2(uint32_t& run, const uint32_t* pk, int n) {
+  uint32_t m2 = 0;
+  for (int j = 0; j < n; ++j) m2 = __vmaxu2(m2, pk[j] & 0x7fff7fffu);
+  run = max(run, max(m2 & 0xffffu, m2 >> 16) << 16);
+}
+// Folds the epilogue threads' maxima of one warp into the caller's cell.
+__device__ __forceinline__ void amax_publish(uint32_t* cell, uint32_t run, int lane) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) run = max(run, __shfl_xor_sync(0xffffffffu, run, o));
+  if (lane == 0 && run != 0) atomicMax(cell, run);
+}
+
 // Drains one 128 x BN accumulator tile: TMEM -> registers -> dequantizing chain
 // -> global. `taddr` addresses this warp's 32 lanes and the tile's first column.
 // Scales of one output tile, fetched BEFORE the warp waits for the
@@ -270,7 +289,8 @@ __device__ __forceinline__ void load_epi_scales(const GemmParams& P, int lane, i
 template <bool IS_INT, int EPI>
 __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t taddr, int lane,
                                               int64_t i0, int64_t i1, int64_t row, int64_t ncol0,
-                                              uint8_t* stage, const EpiScales& sc) {
+                                              uint8_t* stage, const EpiScales& sc,
+                                              uint32_t& amax) {
   if (P.tma_store && stage != nullptr) {
     // an earlier tile of this warp may have left through the TMA unit
     if (lane == 0) tma_store_wait_read();
@@ -342,6 +362,25 @@ __device__ __forceinline__ void epilogue_tile(const GemmParams& P, uint32_t tadd
           r = round_to(r, P.d_dtype);
           res[j] = round_to(r, P.out_dtype);
         }
+      }
+    }
+    if (row_ok && P.amax_out != nullptr && P.out != nullptr) {
+      // rows and columns past the matrix edge hold products of fill zeros
+      // with stand-in scales: leave them out
+      if constexpr (EPI == 1) {
+        if (col0 + 32 <= P.n) {
+          amax_bf16x2(amax, pk, 16);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            if (col0 + 2 * j < P.n) amax_f32(amax, bf16lo(pk[j]));
+            if (col0 + 2 * j + 1 < P.n) amax_f32(amax, bf16hi(pk[j]));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (col0 + j < P.n) amax_f32(amax, res[j]);
       }
     }
     if (row_ok && P.acc_out != nullptr) {
@@ -447,9 +486,11 @@ template <bool IS_INT>
 __device__ __forceinline__ void epilogue_tile_bf16(const GemmParams& P, const CUtensorMap* tmO,
                                                    uint32_t taddr, int lane, int64_t i0,
                                                    int64_t i1, int64_t row, int64_t ncol0,
-                                                   uint8_t* stage, const EpiScales& sc) {
+                                                   uint8_t* stage, const EpiScales& sc,
+                                                   uint32_t& amax) {
   const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
   const bool vary_b = has_b && P.sb_n != 0;
+  const bool want_amax = P.amax_out != nullptr && row < P.m;
   const __nv_bfloat162 sa2 = __float2bfloat162_rn(sc.sa);
   const int64_t row0 = row - lane;
   uint8_t* srow = stage + lane * kStagePitch;
@@ -483,6 +524,7 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmParams& P, const CU
         }
         pk[j] = *(const uint32_t*)&v;
       }
+      if (want_amax) amax_bf16x2(amax, pk, 8);
 #pragma unroll
       for (int v = 0; v < 2; ++v)
         *(uint4*)(srow + (((h * 2 + v) ^ (lane & 7)) * 16)) =
@@ -513,14 +555,14 @@ template <bool IS_INT, int EPI>
 __device__ __forceinline__ void epilogue_slice(const GemmParams& P, const CUtensorMap* tmO,
                                                uint32_t taddr, int lane, int64_t i0, int64_t i1,
                                                int64_t row, int64_t ncol0, uint8_t* stage,
-                                               const EpiScales& sc) {
+                                               const EpiScales& sc, uint32_t& amax) {
   if constexpr (EPI == 1) {
     if (P.stage_ok && P.acc_out == nullptr && P.out != nullptr && ncol0 + 128 <= P.n) {
-      epilogue_tile_bf16<IS_INT>(P, tmO, taddr, lane, i0, i1, row, ncol0, stage, sc);
+      epilogue_tile_bf16<IS_INT>(P, tmO, taddr, lane, i0, i1, row, ncol0, stage, sc, amax);
       return;
     }
   }
-  epilogue_tile<IS_INT, EPI>(P, taddr, lane, i0, i1, row, ncol0, stage, sc);
+  epilogue_tile<IS_INT, EPI>(P, taddr, lane, i0, i1, row, ncol0, stage, sc, amax);
 }
 
 template <bool IS_INT, int EPI>
@@ -630,6 +672,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     const int half = (warp - 2) >> 2;      // which 128 columns of the tile it drains
     int buf = 0;
     uint32_t aphase = 0;
+    uint32_t amax = 0;
     for (int64_t t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
       int64_t i0, i1, mt, nt;
       decode_tile(P, t, i0, i1, mt, nt);
@@ -642,13 +685,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       tc_fence_after();
       epilogue_slice<IS_INT, EPI>(
           P, &tmO, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128), lane,
-          i0, i1, row, nt * BN + half * 128, epi_stage[warp - 2], sc);
+          i0, i1, row, nt * BN + half * 128, epi_stage[warp - 2], sc, amax);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
       buf ^= 1;
       if (buf == 0) aphase ^= 1;
     }
+    if (P.amax_out != nullptr) amax_publish(P.amax_out, amax, lane);
     if (lane == 0) tma_store_wait_read();  // shared memory outlives its last store
     if (fail && lane == 0) { *abortp = 1; if (P.status) atomicCAS(P.status, 0, 3); }
   }
@@ -877,6 +921,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     const int half = (warp - 2) >> 2;
     int buf = 0;
     uint32_t aphase = 0;
+    uint32_t amax = 0;
     for (int64_t t = cluster_id; t < P.total_tiles2; t += num_clusters) {
       int64_t i0, i1, mt, nt;
       decode_tile2(P, t, i0, i1, mt, nt);
@@ -889,13 +934,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       tc_fence_after();
       epilogue_slice<IS_INT, EPI>(
           P, &tmO, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128), lane,
-          i0, i1, row, nt * BN + half * 128, epi_stage[warp - 2], sc);
+          i0, i1, row, nt * BN + half * 128, epi_stage[warp - 2], sc, amax);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
       buf ^= 1;
       if (buf == 0) aphase ^= 1;
     }
+    if (P.amax_out != nullptr) amax_publish(P.amax_out, amax, lane);
     if (lane == 0) tma_store_wait_read();  // shared memory outlives its last store
     if (fail && lane == 0) {
       *abortp = 1;
@@ -961,7 +1007,12 @@ constexpr int kWidePitch = 64;  // bytes per staged row: 32 bf16 columns, 64-byt
 // Only the all-bf16 epilogue with a TMA-describable output runs here (the host
 // falls back to the 256 x 256 kernel otherwise), which keeps the register need
 // of the 18 warps under the 96 the register file allows them.
-template <bool IS_INT>
+// RAW: instead of the dequantized bf16 result the epilogue writes the raw
+// 32-bit accumulators (tmO then maps the contiguous [b0][b1][m][n] int32 / f32
+// accumulator tensor, boxes of 32 rows x 16 columns in the 64-byte swizzle):
+// the form a contraction sharded over several GPUs needs, whose partial sums
+// are added across ranks before the one dequantization.
+template <bool IS_INT, bool RAW>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(WIDE_THREADS, 1)
 gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
                          const __grid_constant__ CUtensorMap tmB,
@@ -1161,6 +1212,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
     uint8_t* srow = stage_rows + lane * kWidePitch;
     const int swz = (lane >> 1) & 3;
     uint32_t aphase = 0;
+    uint32_t amax = 0;
     for (int64_t t = cluster_id; t < P.total_tiles3; t += num_clusters) {
       int64_t i0, i1, mt, nt;
       decode_tile3(P, t, i0, i1, mt, nt);
@@ -1170,27 +1222,29 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
       const int64_t col_s = nt * BNW + slice * 64;  // this warp's first column in accumulator 0
       // scales do not depend on the accumulator: fetch them before waiting for it
       float sa = 1.f;
-      if (has_a && row < P.m)
-        sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
-      const __nv_bfloat162 sa2 = __float2bfloat162_rn(sa);
       uint32_t sbw[4];  // [accumulator * 2 + 32-column group]: lanes 0..15 hold column pairs
+      if constexpr (!RAW) {
+        if (has_a && row < P.m)
+          sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        uint32_t w = 0x3f803f80u;  // (1.0, 1.0)
-        if (has_b) {
-          const unsigned short* sp = (const unsigned short*)P.b_scale + i0 * P.sb_b0 + i1 * P.sb_b1;
-          if (P.sb_n == 0) {
-            const uint32_t v = __ldg(sp);
-            w = v | (v << 16);
-          } else if (lane < 16) {
-            const int64_t cc = col_s + (q >> 1) * 256 + (q & 1) * 32 + 2 * lane;
-            const uint32_t lo = cc < P.n ? __ldg(sp + cc * P.sb_n) : 0x3f80u;
-            const uint32_t hi = cc + 1 < P.n ? __ldg(sp + (cc + 1) * P.sb_n) : 0x3f80u;
-            w = lo | (hi << 16);
+        for (int q = 0; q < 4; ++q) {
+          uint32_t w = 0x3f803f80u;  // (1.0, 1.0)
+          if (has_b) {
+            const unsigned short* sp = (const unsigned short*)P.b_scale + i0 * P.sb_b0 + i1 * P.sb_b1;
+            if (P.sb_n == 0) {
+              const uint32_t v = __ldg(sp);
+              w = v | (v << 16);
+            } else if (lane < 16) {
+              const int64_t cc = col_s + (q >> 1) * 256 + (q & 1) * 32 + 2 * lane;
+              const uint32_t lo = cc < P.n ? __ldg(sp + cc * P.sb_n) : 0x3f80u;
+              const uint32_t hi = cc + 1 < P.n ? __ldg(sp + (cc + 1) * P.sb_n) : 0x3f80u;
+              w = lo | (hi << 16);
+            }
           }
+          sbw[q] = w;
         }
-        sbw[q] = w;
       }
+      const __nv_bfloat162 sa2 = __float2bfloat162_rn(sa);
       int ok = mbar_wait(&tfull_bar[0], aphase, abortp) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
@@ -1202,10 +1256,14 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
 #pragma unroll 1
       for (int g = 0; g < groups; ++g) {
         const int a = g >> 1;
-        // the staging rows are free once the previous store has read them
-        if (lane == 0) tma_store_wait_read();
-        __syncwarp();
-        const uint32_t sb_g = g < 2 ? (g ? sbw[1] : sbw[0]) : (g == 2 ? sbw[2] : sbw[3]);
+        const int64_t colg = col_s + a * 256 + (g & 1) * 32;
+        if constexpr (!RAW) {
+          // the staging rows are free once the previous store has read them
+          if (lane == 0) tma_store_wait_read();
+          __syncwarp();
+        }
+        uint32_t sb_g = 0;
+        if constexpr (!RAW) sb_g = g < 2 ? (g ? sbw[1] : sbw[0]) : (g == 2 ? sbw[2] : sbw[3]);
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           tc_wait_ld();
@@ -1213,34 +1271,63 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
           if (pn < 2 * groups && pn != 4)  // piece 4 opens the second accumulator: see below
             tc_ld16(tlane + (uint32_t)((pn >> 2) * 256 + (pn & 3) * 16), buf[h ^ 1]);
           const uint32_t* acc = buf[h];
-          uint32_t pk[8];
+          if constexpr (RAW) {
+            // one piece = 16 accumulators = the 64 bytes of a staged row
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            uint32_t w = vary_b ? __shfl_sync(0xffffffffu, sb_g, h * 8 + j) : sb_g;
-            const __nv_bfloat162 sb2 = *(const __nv_bfloat162*)&w;
-            const float f0 = IS_INT ? __int2float_rn((int)acc[2 * j]) : __uint_as_float(acc[2 * j]);
-            const float f1 =
-                IS_INT ? __int2float_rn((int)acc[2 * j + 1]) : __uint_as_float(acc[2 * j + 1]);
-            __nv_bfloat162 v = __floats2bfloat162_rn(f0, f1);
-            if (P.b_scale_first) {
-              if (has_b) v = __hmul2(v, sb2);
-              if (has_a) v = __hmul2(v, sa2);
-            } else {
-              if (has_a) v = __hmul2(v, sa2);
-              if (has_b) v = __hmul2(v, sb2);
+            for (int v = 0; v < 4; ++v)
+              *(uint4*)(srow + ((v ^ swz) * 16)) =
+                  make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]);
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
+            if (lane == 0 && row0 < P.m && colg + h * 16 < P.n)
+              tma_store_4d(&tmO, stage_rows, (int)(colg + h * 16), (int)row0, (int)i1, (int)i0);
+          } else {
+            uint32_t pk[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              uint32_t w = vary_b ? __shfl_sync(0xffffffffu, sb_g, h * 8 + j) : sb_g;
+              const __nv_bfloat162 sb2 = *(const __nv_bfloat162*)&w;
+              const float f0 = IS_INT ? __int2float_rn((int)acc[2 * j]) : __uint_as_float(acc[2 * j]);
+              const float f1 =
+                  IS_INT ? __int2float_rn((int)acc[2 * j + 1]) : __uint_as_float(acc[2 * j + 1]);
+              __nv_bfloat162 v = __floats2bfloat162_rn(f0, f1);
+              if (P.b_scale_first) {
+                if (has_b) v = __hmul2(v, sb2);
+                if (has_a) v = __hmul2(v, sa2);
+              } else {
+                if (has_a) v = __hmul2(v, sa2);
+                if (has_b) v = __hmul2(v, sb2);
+              }
+              pk[j] = *(const uint32_t*)&v;
             }
-            pk[j] = *(const uint32_t*)&v;
-          }
+            if (P.amax_out != nullptr && row < P.m) {
+              // columns past the matrix edge hold products of fill zeros with
+              // stand-in scales: leave them out
+              const int64_t cp = colg + h * 16;
+              if (cp + 16 <= P.n) {
+                amax_bf16x2(amax, pk, 8);
+              } else {
 #pragma unroll
-          for (int v = 0; v < 2; ++v)
-            *(uint4*)(srow + (((h * 2 + v) ^ swz) * 16)) =
-                make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+                for (int j = 0; j < 8; ++j) {
+                  if (cp + 2 * j < P.n) amax_f32(amax, bf16lo(pk[j]));
+                  if (cp + 2 * j + 1 < P.n) amax_f32(amax, bf16hi(pk[j]));
+                }
+              }
+            }
+#pragma unroll
+            for (int v = 0; v < 2; ++v)
+              *(uint4*)(srow + (((h * 2 + v) ^ swz) * 16)) =
+                  make_uint4(pk[4 * v], pk[4 * v + 1], pk[4 * v + 2], pk[4 * v + 3]);
+          }
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        __syncwarp();
-        const int64_t colg = col_s + a * 256 + (g & 1) * 32;
-        if (lane == 0 && row0 < P.m && colg < P.n)
-          tma_store_4d(&tmO, stage_rows, (int)colg, (int)row0, (int)i1, (int)i0);
+        if constexpr (!RAW) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+          __syncwarp();
+          if (lane == 0 && row0 < P.m && colg < P.n)
+            tma_store_4d(&tmO, stage_rows, (int)colg, (int)row0, (int)i1, (int)i0);
+        }
         if (g & 1) {
           // this accumulator's columns have all been read (the read in flight,
           // if any, belongs to the other accumulator)
@@ -1262,6 +1349,9 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
         if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[1]), 0));
       }
       aphase ^= 1;
+    }
+    if constexpr (!RAW) {
+      if (P.amax_out != nullptr) amax_publish(P.amax_out, amax, lane);
     }
     if (lane == 0) tma_store_wait_read();  // shared memory outlives its last store
     if (fail && lane == 0) {
@@ -1333,6 +1423,7 @@ __global__ void gemm_simt_kernel(GemmParams P) {
     r = round_to(round_to(r, P.d_dtype), P.out_dtype);
     const int64_t oi = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m + col * P.o_n;
     if (P.out == nullptr) continue;
+    if (P.amax_out != nullptr) atomicMax(P.amax_out, __float_as_uint(r) & 0x7fffffffu);
     if (P.out_dtype == AQTB200_BF16)
       ((__nv_bfloat16*)P.out)[oi] = __float2bfloat16_rn(r);
     else
@@ -1366,6 +1457,7 @@ __global__ void __launch_bounds__(256) dequant_acc_kernel(GemmParams P, const ui
   const int64_t nq = P.n / W;
   const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
   const int es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
+  uint32_t amax = 0;
   for (int64_t i0u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0u < total;
        i0u += nthreads * UU) {
     uint32_t raw[UU][W];
@@ -1401,6 +1493,7 @@ __global__ void __launch_bounds__(256) dequant_acc_kernel(GemmParams P, const ui
                                            i0 * P.sb_b0 + i1 * P.sb_b1 + (col + j) * P.sb_n)
                                    : 1.f;
         res[j] = dequant_one(P, raw[k][j], sa, sb);
+        amax_f32(amax, res[j]);
       }
       const int64_t oi = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m + col * P.o_n;
       if (VEC && P.o_n == 1 && ((((uintptr_t)P.out) + (size_t)oi * es) & (4 * es - 1)) == 0) {
@@ -1423,22 +1516,14 @@ __global__ void __launch_bounds__(256) dequant_acc_kernel(GemmParams P, const ui
       }
     }
   }
+  // (every thread reaches this point: the loops above have no early exit)
+  if (P.amax_out != nullptr) amax_publish(P.amax_out, amax, threadIdx.x & 31);
 }
 
 // ---------------------------------------------------------------------------
 // host side
 
 static int g_gemm_impl = 0;
-// AQTB200_TMA_STORE=0 in the environment keeps the epilogue on warp stores
-// (for A/B timing; results are identical).
-static bool tma_store_enabled() {
-  static int v = -1;
-  if (v < 0) {
-    const char* e = getenv("AQTB200_TMA_STORE");
-    v = (e != nullptr && e[0] == '0') ? 0 : 1;
-  }
-  return v != 0;
-}
 static int g_sm_budget = 0;
 static int gemm_sms() {
   int n = sm_count();
@@ -1508,6 +1593,23 @@ static bool make_output_map(CUtensorMap* tm, void* ptr, int64_t n, int64_t m, in
   return r == CUDA_SUCCESS;
 }
 
+// 4-D map over the contiguous 32-bit accumulator tensor [b0][b1][m][n]: boxes
+// of 32 rows by 16 columns (64 bytes) in the 64-byte swizzle.
+static bool make_acc_map(CUtensorMap* tm, void* ptr, int64_t n, int64_t m, int64_t b1, int64_t b0) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr || ((uintptr_t)ptr & 15) || n % 4 != 0) return false;
+  b1 = std::max<int64_t>(b1, 1);
+  b0 = std::max<int64_t>(b0, 1);
+  cuuint64_t dims[4] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)b1, (cuuint64_t)b0};
+  cuuint64_t strides[3] = {(cuuint64_t)n * 4, (cuuint64_t)n * m * 4, (cuuint64_t)n * m * b1 * 4};
+  cuuint32_t box[4] = {16, 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, ptr, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 static bool is_fp8(int dt) { return dt == AQTB200_E4M3 || dt == AQTB200_E5M2; }
 
 static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& P, bool* empty) {
@@ -1541,6 +1643,7 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   P.out = d->out; P.o_b0 = d->out_b0_stride; P.o_b1 = d->out_b1_stride;
   P.o_m = d->out_m_stride; P.o_n = d->out_n_stride;
   P.acc_out = d->acc_out;
+  P.amax_out = (uint32_t*)d->amax_out;
   P.stage_ok = d->out != nullptr && d->out_dtype == AQTB200_BF16 && d->out_n_stride == 1 &&
                (((uintptr_t)d->out) & 15) == 0 && d->out_m_stride % 8 == 0 &&
                d->out_b0_stride % 8 == 0 && d->out_b1_stride % 8 == 0;
@@ -1603,17 +1706,23 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   if (d->dequant_dtype == AQTB200_F32 && d->out_dtype == AQTB200_F32 && sa_f && sb_f) epi = 2;
   // Outputs that qualify for the staged bf16 epilogue leave through the TMA
   // unit when a tensor map can describe them; otherwise the same staged rows
-  // are stored by the warps. The 256 x 512 kernel has only that epilogue, so
-  // without a map (or for other dtypes, or when the raw accumulator is wanted)
-  // the 256 x 256 kernel runs instead, whatever was asked for.
+  // are stored by the warps. The 256 x 512 kernel has only that epilogue and
+  // one that writes the raw accumulators alone (no dequantized output); for
+  // anything else (no map, other dtypes, both outputs wanted) the 256 x 256
+  // kernel runs instead, whatever was asked for.
   CUtensorMap tmO;
   memset(&tmO, 0, sizeof(tmO));
   P.tma_store = 0;
-  const bool can_map = epi == 1 && P.stage_ok && tma_store_enabled();
+  const bool can_map = epi == 1 && P.stage_ok;
+  bool wide_raw = false;
   if (wide) {
-    wide = can_map && d->acc_out == nullptr &&
-           make_output_map(&tmO, d->out, d->n, d->m, d->b1, d->b0, d->out_m_stride,
-                           d->out_b1_stride, d->out_b0_stride, 32);
+    if (d->out == nullptr && d->acc_out != nullptr) {
+      wide_raw = wide = make_acc_map(&tmO, d->acc_out, d->n, d->m, d->b1, d->b0);
+    } else {
+      wide = can_map && d->acc_out == nullptr &&
+             make_output_map(&tmO, d->out, d->n, d->m, d->b1, d->b0, d->out_m_stride,
+                             d->out_b1_stride, d->out_b0_stride, 32);
+    }
     P.tma_store = wide ? 1 : 0;
   }
   if (!wide && can_map)
@@ -1633,13 +1742,17 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   const int grid = pair ? 2 * std::max((int)std::min<int64_t>(pair_tiles, gemm_sms() / 2), 1)
                         : (int)std::min<int64_t>(P.total_tiles, gemm_sms());
   const size_t smem = wide ? GEMM3_SMEM : (pair ? GEMM2_SMEM : GEMM_SMEM);
+  // the shared-memory opt-in is a per-device attribute of each kernel
+  int dev = 0;
+  AQT_CUDA_OK(cudaGetDevice(&dev));
+  dev = dev & 63;
 #define AQT_LAUNCH_GEMM(KERNEL, I, E)                                                         \
   do {                                                                                        \
-    static bool attr_done = false;                                                            \
-    if (!attr_done) {                                                                         \
+    static bool attr_done[64] = {false};                                                      \
+    if (!attr_done[dev]) {                                                                    \
       AQT_CUDA_OK(cudaFuncSetAttribute(KERNEL<I, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                                        (int)smem));                                           \
-      attr_done = true;                                                                       \
+      attr_done[dev] = true;                                                                  \
     }                                                                                         \
     KERNEL<I, E><<<grid, GEMM_THREADS, smem, st>>>(tmA, tmB, tmO, P);                              \
   } while (0)
@@ -1650,20 +1763,19 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
     else AQT_LAUNCH_GEMM(KERNEL, I, 0);                 \
   } while (0)
   if (wide) {
-    static bool attr_done[2] = {false, false};
-    if (!attr_done[P.is_int]) {
-      if (P.is_int)
-        AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<true>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      else
-        AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<false>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-      attr_done[P.is_int] = true;
-    }
-    if (P.is_int)
-      gemm_tcgen05_wide_kernel<true><<<grid, WIDE_THREADS, smem, st>>>(tmA, tmB, tmO, P);
-    else
-      gemm_tcgen05_wide_kernel<false><<<grid, WIDE_THREADS, smem, st>>>(tmA, tmB, tmO, P);
+#define AQT_LAUNCH_WIDE(I, R)                                                                  \
+  do {                                                                                         \
+    static bool attr_done[64] = {false};                                                       \
+    if (!attr_done[dev]) {                                                                     \
+      AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<I, R>,                         \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      attr_done[dev] = true;                                                                   \
+    }                                                                                          \
+    gemm_tcgen05_wide_kernel<I, R><<<grid, WIDE_THREADS, smem, st>>>(tmA, tmB, tmO, P);        \
+  } while (0)
+    if (P.is_int) { if (wide_raw) AQT_LAUNCH_WIDE(true, true); else AQT_LAUNCH_WIDE(true, false); }
+    else { if (wide_raw) AQT_LAUNCH_WIDE(false, true); else AQT_LAUNCH_WIDE(false, false); }
+#undef AQT_LAUNCH_WIDE
   } else if (pair) {
     if (P.is_int) AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, true);
     else AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, false);

@@ -1480,17 +1480,20 @@ __global__ void dequant_kernel(DeqParams D, int64_t total) {
 // ---------------------------------------------------------------------------
 // host side
 
-static int g_sm_count = 0;
+// SM count of the CURRENT device (a process may drive several).
+static int g_sm_count[64] = {0};
 int sm_count() {
-  if (g_sm_count == 0) {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) == cudaSuccess &&
-        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
-      g_sm_count = n;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+  dev &= 63;
+  if (g_sm_count[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) == cudaSuccess && n > 0)
+      g_sm_count[dev] = n;
     else
-      g_sm_count = 148;
+      g_sm_count[dev] = 148;
   }
-  return g_sm_count;
+  return g_sm_count[dev];
 }
 
 static bool is_float_dt(int dt) { return dt == AQTB200_F32 || dt == AQTB200_BF16; }

@@ -12,12 +12,22 @@ concatenated lhs -- bit for bit for int8, to f32 summation order for fp8:
     (aqt_dot_general.py:645-653). The scale is a monotone function of the
     absolute maximum, so max(scale_r) == scale(max_r amax);
   * drhs sums raw int32 / f32 accumulators across ranks before the single
-    dequantizing epilogue (engine.DeferredDequant).
+    dequantizing epilogue. Where both operands are already quantized (the
+    one-read flow) the sum is a reduce-scatter: every rank receives the total
+    of its band of drhs rows only, dequantizes that band, and an all-gather
+    of the finished (bf16 / f32) bands completes the result -- fewer bytes on
+    the links than an all-reduce of the accumulators and 1/N of the
+    dequantizing traffic per rank. drhs is produced in row slices so that
+    the exchange of one slice runs under the next slice's GEMM and under
+    dlhs. Otherwise the accumulators are all-reduced and dequantized whole.
 
 Only a 2-D contraction lhs[M,K] . rhs[K,N] is handled; that is the projection
 layer the reference's data-parallel users shard. The reference itself has no
 collective on this path (cross-replica statistics raise NotImplementedError,
 flax/aqt_flax_calibration.py:161-164).
+
+Every collective and stream dependency is issued through engine.tape_op, so a
+sharded step can be recorded and replayed by engine.TracedStep.
 """
 
 from __future__ import annotations
@@ -41,6 +51,21 @@ def _calib_kwargs(quantizer):
   return kw
 
 
+class _StreamCtx:
+  """`with` block that makes `stream` current (a no-op for stream None)."""
+
+  def __init__(self, stream):
+    self._ctx = torch.cuda.stream(stream) if stream is not None else None
+
+  def __enter__(self):
+    if self._ctx is not None:
+      self._ctx.__enter__()
+
+  def __exit__(self, *exc):
+    if self._ctx is not None:
+      self._ctx.__exit__(*exc)
+
+
 class ShardedDotGeneral:
   """cfg.vjp for row-sharded operands (see module docstring)."""
 
@@ -48,38 +73,62 @@ class ShardedDotGeneral:
                drhs_slices: int = 2, slice_multiple: int = 256):
     self.cfg = cfg
     self.group = group
-    # SMs left to the all-reduce kernel while a GEMM runs beside it.
+    # SMs left to the collective's kernel while a GEMM runs beside it.
     self.overlap_sms = overlap_sms
-    # drhs is computed in this many column slices so that the all-reduce of
-    # one slice's accumulators runs under the next slice's GEMM.
+    # drhs is computed in this many row slices so that the exchange of one
+    # slice's accumulators runs under the next slice's GEMM.
     self.drhs_slices = drhs_slices
-    # a slice is a whole number of GEMM tiles wide
+    # a slice (and a rank's band of it) is a whole number of GEMM tile rows
     self.slice_multiple = slice_multiple
+    self._side = {}
+
+  # -- plumbing ----------------------------------------------------------------
+  def _world(self):
+    if not dist.is_initialized():
+      return 1
+    return dist.get_world_size(self.group)
+
+  def _side_stream(self, device):
+    """A second stream per device for the dequantize-and-gather half of the
+    drhs exchange (None for host tensors, which have no streams)."""
+    if device.type != 'cuda':
+      return None
+    key = str(device)
+    if key not in self._side:
+      self._side[key] = torch.cuda.Stream(device=device)
+    return self._side[key]
 
   # -- collectives -----------------------------------------------------------
   def _max(self, t):
-    if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-      dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group)
+    if self._world() > 1:
+      engine.tape_op(lambda: dist.all_reduce(t, op=dist.ReduceOp.MAX,
+                                             group=self.group))
     return t
 
   def _max_async(self, t):
     """Starts a max-all-reduce of t in place; returns (t, wait) or t."""
-    if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-      work = dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group,
-                             async_op=True)
-      return t, work.wait
-    return t
+    if self._world() > 1:
+      box = {}
 
-  def _sum(self, t):
-    if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-      dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+      def start():
+        box['w'] = dist.all_reduce(t, op=dist.ReduceOp.MAX, group=self.group,
+                                   async_op=True)
+
+      engine.tape_op(start)
+      return t, lambda: engine.tape_op(lambda: box['w'].wait())
     return t
 
   def _sum_async(self, t):
-    """Starts a sum-all-reduce of t in place; returns a handle or None."""
-    if dist.is_initialized() and dist.get_world_size(self.group) > 1:
-      return dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group,
-                             async_op=True)
+    """Starts a sum-all-reduce of t in place; returns a wait callable or None."""
+    if self._world() > 1:
+      box = {}
+
+      def start():
+        box['w'] = dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group,
+                                   async_op=True)
+
+      engine.tape_op(start)
+      return lambda: engine.tape_op(lambda: box['w'].wait())
     return None
 
   # -- scales ------------------------------------------------------------------
@@ -143,7 +192,7 @@ class ShardedDotGeneral:
     upd = adg._update_dimension_numbers_for_backward  # pylint: disable=protected-access
 
     # drhs = g[M,N]^T . lhs'[M,K] : contraction over the sharded rows. It runs
-    # first so that the all-reduce of its accumulators overlaps with dlhs.
+    # first so that the exchange of its accumulators overlaps with dlhs.
     r_dims, r_perm = upd(dims, True, g.ndim, res.lhs.mt.x.ndim)
     other, fwd_scale, other_dt = self._other_operand(cfg.drhs, res.lhs.mt)
     pre = None
@@ -170,7 +219,7 @@ class ShardedDotGeneral:
     else:
       g_qt = self._global_scale(cfg.drhs.dg_quantizer.lhs, g, [0], 0,
                                 prescale=pre)
-      # Every cross-rank scale is agreed on BEFORE the big all-reduce starts:
+      # Every cross-rank scale is agreed on BEFORE the big exchange starts:
       # a small collective queued behind it on the same communicator would
       # wait for it and serialise the dlhs pass after it.
       _, fwd_scale_r, _ = self._other_operand(cfg.dlhs, res.rhs.mt)
@@ -189,82 +238,117 @@ class ShardedDotGeneral:
       x_qt = self._global_scale(cfg.drhs.dg_quantizer.rhs, other, [0], 0,
                                 compute_dtype=other_dt)
 
-    deferred, work, drhs = None, None, None
+    deferred, wait, drhs = None, None, None
     sliced = self._drhs_sliced(g, res, g_qt, x_qt, r_dims, r_perm, internal)
     if sliced is not None:
       pass
     elif g_qt is None and x_qt is None:  # unquantized gradient dot
       drhs = engine.dg_raw(cfg.drhs, g, res.lhs.mt, None, None, r_dims,
                            out_transpose_axes=r_perm)[0].contiguous()
-      work = self._sum_async(drhs)
+      wait = self._sum_async(drhs)
     else:
       deferred, _ = engine.dg_raw(cfg.drhs, g, res.lhs.mt, g_qt, x_qt, r_dims,
                                   out_transpose_axes=r_perm,
                                   defer_dequant=True, internal_qt=internal)
-      work = self._sum_async(deferred.acc)
+      wait = self._sum_async(deferred.acc)
+    overlapped = sliced is not None or wait is not None
 
     # dlhs = g[M,N] . rhs'[K,N]^T : rows of g sharded, contraction over N local
-    g_qt = g_qt_dlhs
-    if sliced is not None:
-      work = sliced[1][-1]
-    if work is not None and self.overlap_sms and not engine._HOST_TEST_MODE:  # pylint: disable=protected-access
+    if overlapped and self.overlap_sms:
       engine.set_gemm_sm_budget(max(engine.sm_count() - self.overlap_sms, 2))
     try:
-      dlhs = engine.dg_raw(cfg.dlhs, g, res.rhs.mt, g_qt, y_qt, d_dims,
+      dlhs = engine.dg_raw(cfg.dlhs, g, res.rhs.mt, g_qt_dlhs, y_qt, d_dims,
                            out_transpose_axes=d_perm, internal_qt=internal)[0]
     finally:
-      if work is not None and self.overlap_sms and not engine._HOST_TEST_MODE:  # pylint: disable=protected-access
+      if overlapped and self.overlap_sms:
         engine.set_gemm_sm_budget(0)
 
     if sliced is not None:
-      drhs, works, parts = sliced
-      for w, d in zip(works, parts):
-        if w is not None:
-          w.wait()
-        d.finish()
+      drhs, join = sliced
+      join()
       return dlhs, drhs
-    if work is not None:
-      work.wait()
+    if wait is not None:
+      wait()
     if deferred is not None:
       drhs = deferred.finish()
     return dlhs, drhs
 
   def _drhs_sliced(self, g, res, g_qt, x_qt, r_dims, r_perm, internal):
-    """drhs in column slices, each slice's accumulators all-reduced while the
-    next slice's GEMM runs. Needs both operands already quantized (full
-    QTensors), so that a slice costs one GEMM and nothing else. Returns
-    (drhs, [work handles], [DeferredDequant]) or None."""
+    """drhs in row slices; per slice: GEMM into raw accumulators, reduce-scatter
+    of the accumulators, dequantization of this rank's band, all-gather of the
+    finished bands. The reduce-scatter is issued from the compute stream right
+    behind its GEMM; the dequantization and the all-gather run on a second
+    stream, so the compute stream goes straight on to the next slice's GEMM.
+    Needs both operands already quantized (full QTensors), so that a slice
+    costs one GEMM and nothing else. Returns (drhs, join) or None; join()
+    makes the compute stream wait for the whole exchange."""
     s = self.drhs_slices
-    if not (s and s > 1 and g_qt is not None and x_qt is not None and
-            g_qt.is_full() and x_qt.is_full()):
+    world = self._world()
+    if not (s and s >= 1 and world > 1 and g_qt is not None and
+            x_qt is not None and g_qt.is_full() and x_qt.is_full()):
       return None
-    if not (dist.is_initialized() and dist.get_world_size(self.group) > 1):
-      return None
+    k = res.lhs.mt.x.shape[1]
     n = g.shape[1]
-    if n % (s * self.slice_multiple) != 0:
+    if k % (s * world) != 0 or (k // (s * world)) % self.slice_multiple != 0:
       return None
     cfg = self.cfg
-    k = res.lhs.mt.x.shape[1]
-    out_dtype = g.dtype
-    drhs = torch.empty((k, n), dtype=out_dtype, device=g.device)
-    works, parts = [], []
-    budget = self.overlap_sms and not engine._HOST_TEST_MODE  # pylint: disable=protected-access
+    rank = dist.get_rank(self.group)
+    rows = k // s
+    band = rows // world
+    drhs = engine._empty((k, n), g.dtype, g.device)  # pylint: disable=protected-access
+    side = self._side_stream(g.device)
+    mt = res.lhs.mt
+    keep, gathers = [], []
+    budget = self.overlap_sms
     try:
       for i in range(s):
-        sl = slice(i * (n // s), (i + 1) * (n // s))
-        g_slice_qt = aqt_tensor.QTensor(
-            qvalue=g_qt.qvalue[:, sl], scale=g_qt.scale, scale_t=None, bias=[],
-            dequant_dtype=g_qt.dequant_dtype)
+        sl = slice(i * rows, (i + 1) * rows)
+        mt_i = adg.MultiTensor(
+            x=mt.x[:, sl], qx=mt.qx.replace(qvalue=mt.qx.qvalue[:, sl]))
+        x_i = x_qt.replace(qvalue=x_qt.qvalue[:, sl])
         if i == 1 and budget:
-          # from the second slice on an all-reduce is in flight beside the GEMM
-          engine.set_gemm_sm_budget(max(engine.sm_count() - self.overlap_sms, 2))
-        d, _ = engine.dg_raw(cfg.drhs, g[:, sl], res.lhs.mt, g_slice_qt, x_qt,
-                             r_dims, out_transpose_axes=r_perm,
-                             defer_dequant=True, internal_qt=internal,
-                             out=drhs[:, sl])
-        parts.append(d)
-        works.append(self._sum_async(d.acc))
+          # from the second slice on a collective is in flight beside the GEMM
+          engine.set_gemm_sm_budget(max(engine.sm_count() - budget, 2))
+        d, _ = engine.dg_raw(cfg.drhs, g, mt_i, g_qt, x_i, r_dims,
+                             out_transpose_axes=r_perm, defer_dequant=True,
+                             internal_qt=internal, out=drhs[sl])
+        acc = d.acc.reshape(rows, n)
+        assert acc.is_contiguous() and acc.data_ptr() == d.acc.data_ptr(), (
+            'drhs accumulators are expected as [rows of drhs][columns]')
+        mine = engine._empty((band, n), acc.dtype, g.device)  # pylint: disable=protected-access
+        keep += [d, acc, mine]
+        box = {}
+
+        def scatter(box=box, mine=mine, acc=acc):
+          box['rs'] = dist.reduce_scatter_tensor(
+              mine, acc, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+
+        engine.tape_op(scatter)
+
+        def wait_scatter(box=box):
+          with _StreamCtx(side):
+            box['rs'].wait()
+
+        engine.tape_op(wait_scatter)
+        with _StreamCtx(side):
+          d.finish_rows(rank * band, band, mine)
+        out_i = drhs[sl]
+
+        def gather(box=box, out_i=out_i):
+          with _StreamCtx(side):
+            box['ag'] = dist.all_gather_into_tensor(
+                out_i, out_i[rank * band:(rank + 1) * band], group=self.group,
+                async_op=True)
+
+        engine.tape_op(gather)
+        gathers.append(box)
     finally:
       if budget:
         engine.set_gemm_sm_budget(0)
-    return drhs, works, parts
+
+    def join():
+      for box in gathers:
+        engine.tape_op(lambda box=box: box['ag'].wait())
+      del keep[:]
+
+    return drhs, join

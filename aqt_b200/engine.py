@@ -32,6 +32,11 @@ _FLOAT_CODES = (_lib.F32, _lib.BF16)
 
 def _code(dtype) -> int:
   if isinstance(dtype, torch.dtype):
+    if dtype == torch.float16:
+      raise NotImplementedError(
+          'float16 operands: the reference admits them '
+          '(aqt_dot_general.py:986-987), the sm_100a kernels compute in '
+          'float32 and bfloat16 only; cast the operands')
     if dtype not in _TORCH_CODE:
       raise NotImplementedError(f'dtype {dtype} is not handled on the device')
     return _TORCH_CODE[dtype]
@@ -41,15 +46,57 @@ def _code(dtype) -> int:
   return d.code
 
 
-# Set only by the CPU test-suite, together with a stand-in for the shared
-# library, to exercise the stride planner on host tensors.
-_HOST_TEST_MODE = False
-
-
 def _stream() -> int:
-  if _HOST_TEST_MODE:
-    return 0
   return torch.cuda.current_stream().cuda_stream
+
+
+def _on_device(*tensors) -> bool:
+  """True when every tensor lives in GPU memory (there is no CPU path)."""
+  return all(t.is_cuda for t in tensors)
+
+
+# ---------------------------------------------------------------------------
+# Recording a step once and replaying it (see TracedStep below). While a tape
+# is open every call into the shared library, and every buffer handed to one,
+# is noted on it.
+
+
+class _Tape:
+
+  def __init__(self):
+    # in issue order: (library entry point, its arguments), whose return code
+    # is checked on replay, or (host action, None)
+    self.ops = []
+    self.keep = []   # buffers the recorded calls point into
+
+
+_tape = None
+
+
+def _call(fn, *args):
+  """Calls one entry point of the shared library; notes it on an open tape."""
+  rc = fn(*args)
+  if _tape is not None:
+    _tape.ops.append((fn, args))
+  return rc
+
+
+def tape_op(op):
+  """Runs a host-side action that belongs to the step (a collective, a stream
+  wait) and notes it on an open tape, so that a replay repeats it in place."""
+  ret = op()
+  if _tape is not None:
+    _tape.ops.append((op, None))
+  return ret
+
+
+def _empty(shape, dtype, device):
+  """Uninitialised device buffer; while a tape is open it is held for the
+  tape's lifetime, because the recorded calls carry its address."""
+  t = torch.empty(shape, dtype=dtype, device=device)
+  if _tape is not None:
+    _tape.keep.append(t)
+  return t
 
 
 _status = {}
@@ -75,12 +122,12 @@ def check_status():
 def set_gemm_impl(name: str):
   """'tcgen05' (default), 'simt' (cross-check kernel), 'cta1', 'cta2', 'wide'."""
   code = {'tcgen05': 0, 'simt': 1, 'cta1': 2, 'cta2': 3, 'wide': 4}[name]
-  _lib.check(_lib.load().aqtb200_set_gemm_impl(code), 'set_gemm_impl')
+  _lib.check(_call(_lib.load().aqtb200_set_gemm_impl, code), 'set_gemm_impl')
 
 
 def set_gemm_sm_budget(max_sms: int):
   """Caps the SMs the persistent GEMM grids take (0 = all)."""
-  _lib.check(_lib.load().aqtb200_set_gemm_sm_budget(int(max_sms)),
+  _lib.check(_call(_lib.load().aqtb200_set_gemm_sm_budget, int(max_sms)),
              'set_gemm_sm_budget')
 
 
@@ -320,28 +367,61 @@ def _logical_q(buf, op: _Operand, k: int):
   return t.permute(*inv)
 
 
+def _copy_struct(d):
+  return type(d).from_buffer_copy(d)
+
+
 class DeferredDequant:
   """Accumulators of a raw dot whose dequantization has been postponed.
 
-  `acc` is the raw int32 / f32 accumulator tensor (sum it across ranks when
-  the contraction index is sharded); finish() applies the dequantizing
-  epilogue once and returns the output.
+  `acc` is the raw int32 / f32 accumulator tensor, contiguous
+  [batch][tile rows][tile columns] (sum it across ranks when the contraction
+  index is sharded); finish() applies the dequantizing epilogue once and
+  returns the output. finish_rows() does so for a band of accumulator rows
+  that sit in a buffer of their own (one rank's share after a
+  reduce-scatter).
   """
 
   def __init__(self, desc, acc, out, keep):
     self._desc, self.acc, self._out, self._keep = desc, acc, out, keep
 
   def finish(self):
-    self._desc.out = self._out.data_ptr()
-    rc = _lib.load().aqtb200_dot_general_raw_dequant(C.byref(self._desc),
-                                                     _stream())
+    desc = _copy_struct(self._desc)
+    desc.out = self._out.data_ptr()
+    rc = _call(_lib.load().aqtb200_dot_general_raw_dequant, C.byref(desc),
+               _stream())
+    _lib.check(rc, 'aqtb200_dot_general_raw_dequant')
+    return self._out
+
+  def finish_rows(self, start: int, count: int, acc_band):
+    """Dequantizes accumulator rows [start, start + count), read from
+    `acc_band` ([count][columns], contiguous), into their place in the output."""
+    desc = _copy_struct(self._desc)
+    assert desc.lhs.b0 * desc.lhs.b1 == 1, 'finish_rows: unbatched dots only'
+    swap = bool(desc.swap_ab)
+    side = desc.rhs if swap else desc.lhs
+    spec = desc.rhs_spec if swap else desc.lhs_spec
+    assert 0 <= start and start + count <= side.rows
+    side.rows = count
+    stride = desc.out_n_stride if swap else desc.out_m_stride
+    desc.out = self._out.data_ptr() + start * stride * self._out.element_size()
+    desc.acc_out = acc_band.data_ptr()
+    if not spec.per_tensor:
+      off = start * (2 if spec.scale_dtype == _lib.BF16 else 4)
+      for name in (('rhs_scale', 'rhs_scale_in') if swap else
+                   ('lhs_scale', 'lhs_scale_in')):
+        ptr = getattr(desc, name)
+        if ptr:
+          setattr(desc, name, ptr + off)
+    rc = _call(_lib.load().aqtb200_dot_general_raw_dequant, C.byref(desc),
+               _stream())
     _lib.check(rc, 'aqtb200_dot_general_raw_dequant')
     return self._out
 
 
 def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
            out_transpose_axes=None, want_acc=False, defer_dequant=False,
-           internal_qt=False, out=None):
+           internal_qt=False, out=None, _regrouped=False, _noise=None):
   """DotGeneralRaw.__call__ on the device (aqt_dot_general.py:757-840).
 
   Returns (out, DotGeneralRes[, acc]). `out` is laid out as
@@ -377,7 +457,7 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
     else:
       rhs_float = rhs.x
   assert isinstance(lhs, torch.Tensor) and isinstance(rhs_float, torch.Tensor)
-  if not (lhs.is_cuda and rhs_float.is_cuda) and not _HOST_TEST_MODE:
+  if not _on_device(lhs, rhs_float):
     raise _lib.AqtB200Error('operands must be CUDA tensors (no CPU path)')
 
   lra = utils.get_remaining_axes(lhs.ndim, lca, lba)
@@ -429,8 +509,13 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
   lhs_qv, lhs_sin = split_qt(lhs_qt)
   rhs_qv, rhs_sin = split_qt(rhs_qt)
 
-  noise_l = None if lhs_qv is not None else _noise_for(q.lhs, lhs.shape, lhs.device)
-  noise_r = None if rhs_qv is not None else _noise_for(q.rhs, rhs_float.shape, lhs.device)
+  if _noise is not None:  # drawn by the caller in its own axis order
+    noise_l, noise_r = _noise
+  else:
+    noise_l = None if lhs_qv is not None else _noise_for(q.lhs, lhs.shape,
+                                                         lhs.device)
+    noise_r = None if rhs_qv is not None else _noise_for(
+        q.rhs, rhs_float.shape, lhs.device)
   if noise_l is not None and lhs_spec.kind != _lib.NUM_INT:
     raise NotImplementedError('noise_fn with fp8 numerics')
 
@@ -451,7 +536,7 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
         f'out must be {out_shape} {out_dtype}, got {list(out.shape)} {out.dtype}')
     out_t = out
   else:
-    out_t = torch.empty(out_shape, dtype=out_dtype, device=lhs.device)
+    out_t = _empty(out_shape, out_dtype, lhs.device)
   raw_strides = [0] * len(raw_shape)
   for i, p in enumerate(perm):
     raw_strides[p] = out_t.stride(i)
@@ -512,8 +597,12 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
             f'forward scale shape {tuple(pre_t.shape)} does not line up with '
             'the cotangent; set use_fwd_quant=False')
   except _Unmergeable:
+    if _regrouped or defer_dequant:
+      raise NotImplementedError(
+          f'dimension_numbers {dimension_numbers} with these strides cannot '
+          'be expressed as one strided batched GEMM')
     return _dg_raw_via_copies(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
-                              out_transpose_axes, want_acc)
+                              out_transpose_axes, want_acc, out)
 
   def pad(dims, n, nt):
     dims = list(dims)
@@ -576,9 +665,8 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
       # pre-quantized operand: must already be contraction-contiguous
       qbuf = None
     else:
-      qbuf = torch.empty((nB, rows, ldk), dtype=_CODE_TORCH[spec.qdtype],
-                         device=dev)
-    sbuf = torch.empty(n_sc, dtype=s_dtype, device=dev)
+      qbuf = _empty((nB, rows, ldk), _CODE_TORCH[spec.qdtype], dev)
+    sbuf = _empty(n_sc, s_dtype, dev)
     sin_c = None
     if sin is not None:
       sin_c = _as_scale_compact(sin, op, bool(spec.per_tensor),
@@ -621,8 +709,7 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
     want_acc = True
   if want_acc:
     acc_shape = (nB, N, M) if swap else (nB, M, N)
-    acc = torch.empty(acc_shape, device=dev,
-                      dtype=torch.int32 if ints[0] else torch.float32)
+    acc = _empty(acc_shape, torch.int32 if ints[0] else torch.float32, dev)
     desc.acc_out = acc.data_ptr()
     acc_storage = acc
     if swap:
@@ -632,10 +719,10 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
 
   lib = _lib.load()
   ws_bytes = lib.aqtb200_dot_general_raw_workspace_bytes(C.byref(desc))
-  ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=dev)
+  ws = _empty(max(ws_bytes, 256), torch.uint8, dev)
   status = _status_buf(dev)
-  rc = lib.aqtb200_dot_general_raw(C.byref(desc), ws.data_ptr(), ws.numel(),
-                                   status.data_ptr(), _stream())
+  rc = _call(lib.aqtb200_dot_general_raw, C.byref(desc), ws.data_ptr(),
+             ws.numel(), status.data_ptr(), _stream())
   _lib.check(rc, f'aqtb200_dot_general_raw[{raw.jax_scope_name}]')
   del keep  # buffers stay alive until here; frees are stream-ordered
 
@@ -733,41 +820,90 @@ def _dg_raw_unquantized(raw, lhs, rhs, lhs_qt, rhs_qt, dims,
 
 
 def _dg_raw_via_copies(raw, lhs, rhs, lhs_qt, rhs_qt, dims,
-                       out_transpose_axes, want_acc):
+                       out_transpose_axes, want_acc, out=None):
   """Strides the kernels cannot express: regroup axes with copies, then retry.
 
-  Operands are permuted to (batch, kept, contraction) order and made
-  contiguous, the dot runs on the regrouped tensors, and the result is
-  returned as a permuted view.
+  Operands (and, in the backward pass, the stored quantized operand with its
+  scale) are permuted to (batch, kept, contraction) order and made contiguous,
+  the dot runs on the regrouped tensors into a contiguous raw-order result, and
+  everything handed back -- the result, the residual operands, the QTensors --
+  is a permuted view with the caller's own axis order, so the backward pass
+  can keep using the forward dimension numbers.
   """
   from aqt_b200.v2 import aqt_dot_general as adg
-  if lhs_qt is not None or rhs_qt is not None:
-    raise NotImplementedError(
-        'caller-supplied QTensors with dimension_numbers that need a '
-        'regrouping copy')
+  from aqt_b200.v2 import aqt_tensor
   (lca, rca), (lba, rba) = dims
-  if isinstance(rhs, adg.MultiTensor) and raw.rhs.use_fwd_quant:
-    raise NotImplementedError(
-        'use_fwd_quant with dimension_numbers that need a regrouping copy')
-  rhs_x = rhs.x if isinstance(rhs, adg.MultiTensor) else rhs
+  lca, rca, lba, rba = list(lca), list(rca), list(lba), list(rba)
+  is_mt = isinstance(rhs, adg.MultiTensor)
+  rhs_x = rhs.x if is_mt else rhs
   lra = utils.get_remaining_axes(lhs.ndim, lca, lba)
   rra = utils.get_remaining_axes(rhs_x.ndim, rca, rba)
-  l2 = lhs.permute(*lba, *lra, *lca).contiguous()
-  r2 = rhs_x.permute(*rba, *rra, *rca).contiguous()
+  l_order, r_order = lba + lra + lca, rba + rra + rca
+  l_inv = [l_order.index(i) for i in range(lhs.ndim)]
+  r_inv = [r_order.index(i) for i in range(rhs_x.ndim)]
+  regroup_l = lambda t: t.permute(*l_order).contiguous()
+  regroup_r = lambda t: t.permute(*r_order).contiguous()
+
+  def regroup_qt(qt, regroup, what):
+    """An incomplete (scale-only) caller QTensor follows its operand."""
+    if qt is None:
+      return None
+    if qt.is_full():
+      raise NotImplementedError(
+          f'a pre-quantized {what} with dimension_numbers that need a '
+          'regrouping copy')
+    return qt.replace(scale=[regroup(s) if s.numel() > 1 else
+                             s.reshape([1] * s.ndim) for s in qt.scale])
+
+  l2 = regroup_l(lhs)
+  if is_mt:
+    qx = rhs.qx
+    if qx is not None and isinstance(qx.qvalue, torch.Tensor):
+      qx = qx.replace(
+          qvalue=regroup_r(qx.qvalue),
+          scale=[regroup_r(s) for s in (qx.scale or [])])
+    r2 = adg.MultiTensor(x=regroup_r(rhs_x), qx=qx)
+  else:
+    r2 = regroup_r(rhs_x)
   nb, nm, nn, nk = len(lba), len(lra), len(rra), len(lca)
-  if l2.data_ptr() == lhs.data_ptr() and r2.data_ptr() == rhs_x.data_ptr() and (
-      l2.stride() == lhs.stride() and r2.stride() == rhs_x.stride()):
-    raise NotImplementedError(
-        f'dimension_numbers {dims} with these strides cannot be expressed as '
-        'one strided batched GEMM')
   dims2 = ((tuple(range(nb + nm, nb + nm + nk)),
             tuple(range(nb + nn, nb + nn + nk))),
            (tuple(range(nb)), tuple(range(nb))))
-  got = dg_raw(raw, l2, r2, None, None, dims2, None, want_acc)
-  out = got[0]
+  # Stochastic-rounding noise pairs with the operand's elements in the
+  # caller's axis order: draw it there, then regroup it like the operand.
+  q = raw.dg_quantizer
+  noise = (None, None)
+  if hasattr(q, 'lhs'):
+    nl = _noise_for(q.lhs, lhs.shape, lhs.device) if lhs_qt is None or (
+        not lhs_qt.is_full()) else None
+    nr = _noise_for(q.rhs, rhs_x.shape, lhs.device) if rhs_qt is None or (
+        not rhs_qt.is_full()) else None
+    noise = (None if nl is None else regroup_l(nl),
+             None if nr is None else regroup_r(nr))
+  got = dg_raw(raw, l2, r2, regroup_qt(lhs_qt, regroup_l, 'lhs'),
+               regroup_qt(rhs_qt, regroup_r, 'rhs'), dims2, None, want_acc,
+               _regrouped=True, _noise=noise)
+  res2 = got[1]
+
+  def back(mt, x_orig, inv):
+    qx = mt.qx
+    if qx is not None and isinstance(qx.qvalue, torch.Tensor):
+      qx = qx.replace(qvalue=qx.qvalue.permute(*inv),
+                      scale=[s.permute(*inv) for s in (qx.scale or [])])
+    return adg.MultiTensor(x=x_orig, qx=qx)
+
+  res = adg.DotGeneralRes(
+      lhs=adg.TensorRes(mt=back(res2.lhs.mt, lhs, l_inv),
+                        quant_grad=res2.lhs.quant_grad),
+      rhs=adg.TensorRes(mt=back(res2.rhs.mt, rhs_x, r_inv),
+                        quant_grad=res2.rhs.quant_grad))
+  result = got[0]
   if out_transpose_axes is not None:
-    out = out.permute(*out_transpose_axes)
-  return (out,) + tuple(got[1:])
+    result = result.permute(*out_transpose_axes)
+  if out is not None:
+    out.copy_(result)
+    result = out
+  return (result, res) + tuple(got[2:])
 
 
 # ---------------------------------------------------------------------------
@@ -850,10 +986,11 @@ def absmax_scale(x, shared_axes, numerics, scale_dtype=None,
                      cols, [0, 0], 0, pcs)
   lib = _lib.load()
   n = 1 if per_tensor else rows
-  sbuf = torch.empty(n, dtype=_CODE_TORCH[spec.scale_dtype], device=x.device)
+  sbuf = _empty(n, _CODE_TORCH[spec.scale_dtype], x.device)
   ws_bytes = lib.aqtb200_quantize_workspace_bytes(C.byref(view), C.byref(spec))
-  ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=x.device)
-  rc = lib.aqtb200_absmax_scale(
+  ws = _empty(max(ws_bytes, 256), torch.uint8, x.device)
+  rc = _call(
+      lib.aqtb200_absmax_scale,
       C.byref(view), C.byref(pre_view) if pre_view is not None else None,
       C.byref(spec), sbuf.data_ptr(), ws.data_ptr(), ws.numel(), _stream())
   _lib.check(rc, 'aqtb200_absmax_scale')
@@ -863,9 +1000,9 @@ def absmax_scale(x, shared_axes, numerics, scale_dtype=None,
 def absmax_raw(x):
   """max |x| over the whole tensor as a 1-element f32 device tensor."""
   op, view, rows, cols = _single_operand(x, list(range(x.ndim)))
-  out = torch.empty(1, dtype=torch.float32, device=x.device)
-  rc = _lib.load().aqtb200_absmax_raw(C.byref(view), 1, out.data_ptr(),
-                                      _stream())
+  out = _empty(1, torch.float32, x.device)
+  rc = _call(_lib.load().aqtb200_absmax_raw, C.byref(view), 1, out.data_ptr(),
+             _stream())
   _lib.check(rc, 'aqtb200_absmax_raw')
   return out
 
@@ -880,12 +1017,13 @@ def scale_from_amax(amax, numerics, compute_dtype, scale_dtype=None,
   """
   code = _code(compute_dtype)
   spec = _spec_for(numerics, code, scale_dtype, True, clipping_scale, po2_scale)
-  out = torch.empty(1, dtype=_CODE_TORCH[spec.scale_dtype], device=amax.device)
+  out = _empty(1, _CODE_TORCH[spec.scale_dtype], amax.device)
   pre_ptr, pre_code = None, 0
   if prescale is not None:
     assert prescale.numel() == 1
     pre_ptr, pre_code = prescale.data_ptr(), _code(prescale.dtype)
-  rc = _lib.load().aqtb200_scale_from_amax(
+  rc = _call(
+      _lib.load().aqtb200_scale_from_amax,
       amax.data_ptr(), 1, pre_ptr, pre_code, C.byref(spec), out.data_ptr(),
       _stream())
   _lib.check(rc, 'aqtb200_scale_from_amax')
@@ -970,27 +1108,21 @@ def _pair_spec(quantizer):
   return spec
 
 
-def _pair_enabled():
-  # AQTB200_PAIR=0 keeps the reference's one-quantization-per-dot flow (for
-  # A/B timing; results are identical).
-  import os
-  return os.environ.get('AQTB200_PAIR', '1') != '0'
-
-
 def _pair_matrix_ok(x):
-  return (_pair_enabled() and isinstance(x, torch.Tensor) and x.ndim == 2 and
-          x.dtype == torch.bfloat16 and (x.is_cuda or _HOST_TEST_MODE) and
+  return (isinstance(x, torch.Tensor) and x.ndim == 2 and
+          x.dtype == torch.bfloat16 and _on_device(x) and
           x.stride(1) == 1 and x.stride(0) == x.shape[1] and
           x.shape[0] % 16 == 0 and x.shape[1] % 16 == 0 and x.numel() > 0 and
           x.data_ptr() % 16 == 0)
 
 
 def _scale_of_amax(amax, spec, prescale=None):
-  out = torch.empty(1, dtype=_CODE_TORCH[spec.scale_dtype], device=amax.device)
+  out = _empty(1, _CODE_TORCH[spec.scale_dtype], amax.device)
   pre_ptr, pre_code = None, 0
   if prescale is not None:
     pre_ptr, pre_code = prescale.data_ptr(), _code(prescale.dtype)
-  rc = _lib.load().aqtb200_scale_from_amax(
+  rc = _call(
+      _lib.load().aqtb200_scale_from_amax,
       amax.data_ptr(), 1, pre_ptr, pre_code, C.byref(spec), out.data_ptr(),
       _stream())
   _lib.check(rc, 'aqtb200_scale_from_amax')
@@ -1006,12 +1138,13 @@ def _quantize_pair(x, spec_t, scale_t, pre_t, spec_s, scale_s, pre_s, chain,
   """
   c, r = x.shape
   view = _view(x.data_ptr(), _lib.BF16, [1, 1], r, c, [0, 0], 1, r)
-  q_t = torch.empty((r, c), dtype=_CODE_TORCH[spec_t.qdtype], device=x.device)
-  q_s = torch.empty((c, r), dtype=_CODE_TORCH[spec_s.qdtype], device=x.device)
+  q_t = _empty((r, c), _CODE_TORCH[spec_t.qdtype], x.device)
+  q_s = _empty((c, r), _CODE_TORCH[spec_s.qdtype], x.device)
   ptr = lambda t: (None, 0) if t is None else (t.data_ptr(), _code(t.dtype))
   (pt, ptc), (ps, psc) = ptr(pre_t), ptr(pre_s)
-  rc = _lib.load().aqtb200_quantize_pair(
-      C.byref(view), C.byref(spec_t), scale_t.data_ptr(), pt, ptc,
+  rc = _call(
+      _lib.load().aqtb200_quantize_pair, C.byref(view), C.byref(spec_t),
+      scale_t.data_ptr(), pt, ptc,
       q_t.data_ptr(), C.byref(spec_s), scale_s.data_ptr(), ps, psc,
       q_s.data_ptr(), chain, None if amax is None else amax.data_ptr(),
       _stream())
@@ -1054,7 +1187,7 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers,
   dd = utils.as_dtype(lhs.dtype)
 
   def new_scales(x):
-    mk = lambda: torch.empty(1, dtype=torch.bfloat16, device=x.device)
+    mk = lambda: _empty(1, torch.bfloat16, x.device)
     return mk(), mk()
 
   def amax_of(x, reduce_max=None):
@@ -1126,7 +1259,7 @@ def cotangent_pair(cfg, res, g, reduce_max=None):
   amax = absmax_raw(g)
   if reduce_max is not None:
     amax = reduce_max(amax)
-  mk = lambda: torch.empty(1, dtype=torch.bfloat16, device=g.device)
+  mk = lambda: _empty(1, torch.bfloat16, g.device)
   s_dl, s_dr = mk(), mk()
   # g [M, N]: own orientation (N contiguous) feeds dlhs, the transposed copy
   # [N][M] feeds drhs.
@@ -1149,8 +1282,7 @@ def quantize_with_scale(x, scale, numerics, noise=None):
   spec = _spec_for(numerics, x_code, utils.as_dtype(scale.dtype), per_tensor)
   sin = _as_scale_compact(scale, op, per_tensor, spec.scale_dtype)
   ldk = (cols + 15) // 16 * 16
-  qbuf = torch.empty((1, rows, ldk), dtype=_CODE_TORCH[spec.qdtype],
-                     device=x.device)
+  qbuf = _empty((1, rows, ldk), _CODE_TORCH[spec.qdtype], x.device)
   nview = None
   if noise is not None:
     if not isinstance(noise, torch.Tensor):
@@ -1166,12 +1298,11 @@ def quantize_with_scale(x, scale, numerics, noise=None):
       nop, nview, _, _ = _single_operand(noise, shared)
   lib = _lib.load()
   ws_bytes = lib.aqtb200_quantize_workspace_bytes(C.byref(view), C.byref(spec))
-  ws = torch.empty(max(ws_bytes, 256), dtype=torch.uint8, device=x.device)
-  rc = lib.aqtb200_quantize(C.byref(view), None,
-                            C.byref(nview) if nview is not None else None,
-                            C.byref(spec), sin.data_ptr(), qbuf.data_ptr(),
-                            sin.data_ptr(), ws.data_ptr(), ws.numel(),
-                            _stream())
+  ws = _empty(max(ws_bytes, 256), torch.uint8, x.device)
+  rc = _call(lib.aqtb200_quantize, C.byref(view), None,
+             C.byref(nview) if nview is not None else None,
+             C.byref(spec), sin.data_ptr(), qbuf.data_ptr(),
+             sin.data_ptr(), ws.data_ptr(), ws.numel(), _stream())
   _lib.check(rc, 'aqtb200_quantize')
   return _logical_q(qbuf, op, cols)
 
@@ -1194,8 +1325,7 @@ def dequant(qvalue, scales, dequant_dtype):
   if len(scales) > 1:
     raise NotImplementedError('dequant with more than one scale')
   d_code = _code(dequant_dtype)
-  out = torch.empty(qvalue.shape, dtype=_CODE_TORCH[d_code],
-                    device=qvalue.device)
+  out = _empty(qvalue.shape, _CODE_TORCH[d_code], qvalue.device)
   if not scales:
     return out.copy_(qvalue)
   scale = scales[0].expand(qvalue.shape)
@@ -1210,10 +1340,88 @@ def dequant(qvalue, scales, dequant_dtype):
              qs[:2], qs[2], qs[3])
   sv = _view(scale.data_ptr(), _code(scale.dtype), ext[:2], ext[2], ext[3],
              ss[:2], ss[2], ss[3])
-  rc = _lib.load().aqtb200_dequantize(C.byref(qv), C.byref(sv), d_code,
-                                      out.data_ptr(), _stream())
+  rc = _call(_lib.load().aqtb200_dequantize, C.byref(qv), C.byref(sv), d_code,
+             out.data_ptr(), _stream())
   _lib.check(rc, 'aqtb200_dequantize')
   return out
+
+
+# ---------------------------------------------------------------------------
+# record once, replay many times
+
+
+def _flat_tensors(x):
+  if isinstance(x, torch.Tensor):
+    return [x]
+  if isinstance(x, (tuple, list)):
+    return [t for e in x for t in _flat_tensors(e)]
+  return []
+
+
+class TracedStep:
+  """A step function recorded once and replayed call by call.
+
+  The reference runs under jax.jit: Python builds the computation once and
+  every later step only launches it. This is the same idea at the level of
+  the C ABI. `fn(*inputs)` is run with a tape open; every call it makes into
+  the shared library (with its filled descriptors and buffer addresses) and
+  every host action registered through tape_op() -- collectives, stream waits
+  -- lands on the tape, and the buffers those calls point into are held.
+  Calling the object replays the tape: the same kernels on the same buffers,
+  for the cost of one foreign call each instead of the planner's work.
+
+  Like a jitted function with donated buffers it is tied to the tensors it was
+  traced with: the inputs must be the same tensors (new values are copied into
+  them by the caller), the results are the same tensors every time. Anything
+  the step does outside the library and tape_op() is NOT replayed; with
+  `verify` (the default) the first replay is compared bit for bit with an
+  eager run, so a step that cannot be traced is refused instead of silently
+  going wrong.
+  """
+
+  def __init__(self, fn, *inputs, verify: bool = True):
+    global _tape
+    assert _tape is None, 'a step is already being traced'
+    self._inputs = inputs
+    self._stream = _stream()
+    want = _flat_tensors(fn(*inputs)) if verify else None
+    _tape = tape = _Tape()
+    try:
+      self.outputs = fn(*inputs)
+    finally:
+      _tape = None
+    self._tape = tape
+    if verify:
+      self()
+      got = _flat_tensors(self.outputs)
+      assert len(got) == len(want)
+      for i, (a, b) in enumerate(zip(got, want)):
+        same = a.shape == b.shape and a.dtype == b.dtype and torch.equal(
+            a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8))
+        if not same:
+          raise _lib.AqtB200Error(
+              f'TracedStep: result {i} of the replay differs from the eager '
+              'run; the step does work outside the C ABI and tape_op()')
+
+  @property
+  def n_ops(self) -> int:
+    return len(self._tape.ops)
+
+  def __call__(self, *inputs):
+    for a, b in zip(inputs, self._inputs):
+      assert a is b or (isinstance(a, torch.Tensor) and a.data_ptr() ==
+                        b.data_ptr() and a.shape == b.shape), (
+          'a traced step runs on the tensors it was traced with')
+    assert _stream() == self._stream, (
+        'a traced step replays on the stream it was traced on')
+    for fn, args in self._tape.ops:
+      if args is None:
+        fn()
+      else:
+        rc = fn(*args)
+        if rc != 0:
+          _lib.check(rc, 'replayed call')
+    return self.outputs
 
 
 # ---------------------------------------------------------------------------

@@ -133,22 +133,57 @@ class AqtEinsum:
     self.rhs_quant_mode = rhs_quant_mode
     self.rngs = rngs
     self.name = name
-    self._dg = None
+    # One inner AqtDotGeneral per operand order, built on first use and kept:
+    # it owns the frozen QTensors of CONVERT/SERVE and the position in the rng
+    # stream, both of which must survive from one call to the next.
+    self._dgs = {}
+
+  def _inner(self, swap: bool) -> AqtDotGeneral:
+    if swap not in self._dgs:
+      cfg = copy.deepcopy(self.cfg)
+      lhs_mode, rhs_mode = self.lhs_quant_mode, self.rhs_quant_mode
+      if cfg is not None and swap:
+        # reference :684-704
+        cfg.fwd.dg_quantizer.swap_lhs_and_rhs()
+        cfg.fwd.lhs, cfg.fwd.rhs = cfg.fwd.rhs, cfg.fwd.lhs
+        cfg.dlhs, cfg.drhs = cfg.drhs, cfg.dlhs
+        lhs_mode, rhs_mode = rhs_mode, lhs_mode
+      self._dgs[swap] = AqtDotGeneral(cfg, prng_name=self.prng_name,
+                                      lhs_quant_mode=lhs_mode,
+                                      rhs_quant_mode=rhs_mode, rngs=self.rngs,
+                                      name=self.name)
+    return self._dgs[swap]
+
+  def _frozen(self, which: str):
+    """Frozen QTensor of the FIRST (`lhs`) or SECOND (`rhs`) einsum argument,
+    wherever the operand order put it."""
+    for swap, dg in self._dgs.items():
+      attr = ('rhs' if which == 'lhs' else 'lhs') if swap else which
+      qt = getattr(dg, attr + '_qtensor')
+      if qt is not None:
+        return qt
+    return getattr(self, '_pending_' + which, None)
+
+  def _set_frozen(self, which: str, qt):
+    setattr(self, '_pending_' + which, qt)
+    for swap, dg in self._dgs.items():
+      attr = ('rhs' if which == 'lhs' else 'lhs') if swap else which
+      setattr(dg, attr + '_qtensor', qt)
+
+  lhs_qtensor = property(lambda self: self._frozen('lhs'),
+                         lambda self, qt: self._set_frozen('lhs', qt))
+  rhs_qtensor = property(lambda self: self._frozen('rhs'),
+                         lambda self, qt: self._set_frozen('rhs', qt))
 
   def __call__(self, eqn, lhs_g, rhs_g):
     _, _, swap = aqt_dot_general.einsum_to_dot_general(eqn, lhs_g.ndim,
                                                        rhs_g.ndim)
-    cfg = copy.deepcopy(self.cfg)
-    lhs_mode, rhs_mode = self.lhs_quant_mode, self.rhs_quant_mode
-    if cfg is not None and swap:
-      # reference :684-704
-      cfg.fwd.dg_quantizer.swap_lhs_and_rhs()
-      cfg.fwd.lhs, cfg.fwd.rhs = cfg.fwd.rhs, cfg.fwd.lhs
-      cfg.dlhs, cfg.drhs = cfg.drhs, cfg.dlhs
-      lhs_mode, rhs_mode = rhs_mode, lhs_mode
-    if self._dg is None or self._dg.cfg is not cfg:
-      self._dg = AqtDotGeneral(cfg, prng_name=self.prng_name,
-                               lhs_quant_mode=lhs_mode,
-                               rhs_quant_mode=rhs_mode, rngs=self.rngs,
-                               name=self.name)
-    return aqt_dot_general.einsum(eqn, lhs_g, rhs_g, self._dg)
+    new = swap not in self._dgs
+    dg = self._inner(swap)
+    if new:  # frozen tensors assigned before the first call
+      for which in ('lhs', 'rhs'):
+        qt = getattr(self, '_pending_' + which, None)
+        if qt is not None:
+          attr = ('rhs' if which == 'lhs' else 'lhs') if swap else which
+          setattr(dg, attr + '_qtensor', qt)
+    return aqt_dot_general.einsum(eqn, lhs_g, rhs_g, dg)

@@ -265,9 +265,18 @@ typedef struct aqtb200_gemm_desc {
   int32_t out_dtype; /* F32|BF16 */
   int32_t reserved;
   int64_t out_b0_stride, out_b1_stride, out_m_stride, out_n_stride;
-  /* optional raw accumulator dump, contiguous [b0][b1][m][n], int32 or f32;
-     for parity checks of the tensor-core result. NULL in production. */
+  /* optional raw accumulators, contiguous [b0][b1][m][n], int32 or f32: for
+     parity checks of the tensor-core result, and -- with out == NULL -- for a
+     contraction sharded over several GPUs, whose partial sums are added
+     across ranks before the one dequantization (aqtb200_dot_general_raw_dequant). */
   void* acc_out;
+  /* optional: one f32 cell, zeroed by the caller, that receives max |out| over
+     everything this call writes (of the values as stored, i.e. after the last
+     rounding), by atomic max on the bit pattern. A consumer that quantizes this
+     output with a per-tensor scale -- the next layer, or a delayed-scaling
+     calibrator (flax/delayed_scaling_calibration.py:119-124) -- then needs no
+     pass of its own over it. NULL = not wanted. */
+  float* amax_out;
 } aqtb200_gemm_desc;
 
 /* status: device int32[4], zeroed by the caller before first use; a kernel
@@ -309,6 +318,7 @@ typedef struct aqtb200_dg_raw_desc {
   int32_t reserved;
   int64_t out_b0_stride, out_b1_stride, out_m_stride, out_n_stride;
   void* acc_out;
+  float* amax_out;  /* as aqtb200_gemm_desc.amax_out */
 } aqtb200_dg_raw_desc;
 
 size_t aqtb200_dot_general_raw_workspace_bytes(const aqtb200_dg_raw_desc* desc);

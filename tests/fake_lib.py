@@ -313,6 +313,10 @@ class FakeLib:
     r = r.astype(D).astype(_NP[g.out_dtype])
     if not g.out:
       return 0
+    if g.amax_out:
+      cell = _strided(g.amax_out, _lib.F32, [1], [1], True)
+      cell[0] = max(float(cell[0]), float(np.abs(r.astype(np.float32)).max(
+          initial=0.0)))
     _strided(g.out, g.out_dtype, ext + [g.m, g.n],
              [g.out_b0_stride, g.out_b1_stride, g.out_m_stride,
               g.out_n_stride], True)[...] = r
@@ -375,6 +379,7 @@ class FakeLib:
     g.out_m_stride = d.out_n_stride if d.swap_ab else d.out_m_stride
     g.out_n_stride = d.out_m_stride if d.swap_ab else d.out_n_stride
     g.acc_out = d.acc_out
+    g.amax_out = d.amax_out
     return self._gemm(g, acc_in=d.acc_out if dequant_only else None)
 
   # -- dequantize
@@ -397,5 +402,6 @@ def install(monkeypatch):
   from aqt_b200 import engine
   fake = FakeLib()
   monkeypatch.setattr(_lib, 'load', lambda: fake)
-  monkeypatch.setattr(engine, '_HOST_TEST_MODE', True)
+  monkeypatch.setattr(engine, '_stream', lambda: 0)
+  monkeypatch.setattr(engine, '_on_device', lambda *t: True)
   return fake

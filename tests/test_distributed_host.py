@@ -54,7 +54,7 @@ def _data(np_dtype=np.float32):
 
 
 def _worker(rank, world, port, kind, per_tensor, use_fwd_quant, ret,
-            np_dtype=np.float32):
+            np_dtype=np.float32, traced=False):
   os.environ['MASTER_ADDR'] = '127.0.0.1'
   os.environ['MASTER_PORT'] = str(port)
   dist.init_process_group('gloo', rank=rank, world_size=world)
@@ -65,18 +65,36 @@ def _worker(rank, world, port, kind, per_tensor, use_fwd_quant, ret,
     from tests import fake_lib
     fake = fake_lib.FakeLib()
     with mock.patch.object(_lib, 'load', lambda: fake), \
-         mock.patch.object(engine, '_HOST_TEST_MODE', True):
+         mock.patch.object(engine, '_stream', lambda: 0), \
+         mock.patch.object(engine, '_on_device', lambda *t: True):
       lhs, rhs, g = _data(np_dtype)
       rows = lhs.shape[0] // world
       sl = slice(rank * rows, (rank + 1) * rows)
       kw = {}
       if np_dtype != np.float32:
-        # exercise the sliced drhs with its per-slice all-reduces
-        kw = dict(drhs_slices=2, slice_multiple=8)
+        # exercise the sliced drhs: reduce-scatter, band dequantization and
+        # all-gather per slice (48 rows of drhs = 2 slices x 2 ranks x 12)
+        kw = dict(drhs_slices=2, slice_multiple=4)
       op = aqt_dist.ShardedDotGeneral(_make_cfg(kind, per_tensor,
                                                 use_fwd_quant), **kw)
-      out, bp = op.vjp(util.to_torch(lhs[sl]), util.to_torch(rhs), DIMS)
-      dl, dr = bp(util.to_torch(g[sl]))
+      tl, tr, tg = (util.to_torch(lhs[sl]), util.to_torch(rhs),
+                    util.to_torch(g[sl]))
+      if traced:
+        calls = []
+        if kw:
+          real = op._drhs_sliced
+          op._drhs_sliced = lambda *a: calls.append(1) or real(*a)
+
+        def step(a, b, c):
+          out, bp = op.vjp(a, b, DIMS)
+          return (out,) + tuple(bp(c))
+
+        replay = engine.TracedStep(step, tl, tr, tg)  # verifies itself
+        assert not kw or calls, 'the sliced drhs exchange did not run'
+        out, dl, dr = replay(tl, tr, tg)
+      else:
+        out, bp = op.vjp(tl, tr, DIMS)
+        dl, dr = bp(tg)
       ret[rank] = (util.to_numpy(out), util.to_numpy(dl), util.to_numpy(dr))
   finally:
     dist.destroy_process_group()
@@ -114,15 +132,18 @@ def test_two_ranks_equal_one_device(kind, per_tensor, use_fwd_quant):
       np.testing.assert_allclose(ret[r][2], wr, rtol=1e-5, atol=1e-6)
 
 
-def test_two_ranks_paired_quantization_equal_one_device():
+@pytest.mark.parametrize('traced', [False, True])
+def test_two_ranks_paired_quantization_equal_one_device(traced):
   """bf16 / per-tensor fp8: every rank reads each operand once for both of its
   copies; the raw maxima of lhs and of the cotangent are the only things
-  agreed across ranks besides the accumulator sum."""
+  agreed across ranks besides the accumulator sum. drhs goes through the
+  sliced reduce-scatter / all-gather exchange. `traced`: the step is recorded
+  and replayed (engine.TracedStep), collectives included."""
   world = 2
   mgr = mp.Manager()
   ret = mgr.dict()
   mp.spawn(_worker, args=(world, _free_port(), 'fp8', True, True, ret,
-                          orc.bfloat16), nprocs=world, join=True)
+                          orc.bfloat16, traced), nprocs=world, join=True)
   lhs, rhs, g = _data(orc.bfloat16)
   cfg = _make_cfg('fp8', True, True)
   wo, wl, wr, _ = orc.dg_fwd_bwd(cfg, lhs, rhs, g, DIMS)

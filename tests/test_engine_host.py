@@ -41,6 +41,10 @@ CASES = [
     ((((1,), (1,)), ((), ())), (8, 20), (10, 20)),
     ((((0,), (0,)), ((), ())), (20, 8), (20, 10)),
     ((((2,), (0,)), ((), ())), (4, 6, 32), (32, 12)),
+    # kept axes of lhs on both sides of its contraction axis ('bkh,kd->bhd'):
+    # no single strided view exists, the planner regroups with copies
+    ((((1,), (0,)), ((), ())), (4, 32, 6), (32, 10)),
+    ((((1,), (0,)), ((), ())), (4, 6, 6), (6, 5)),
 ]
 
 
@@ -184,3 +188,44 @@ def test_unsupported_configs_raise(monkeypatch):
     cfg(x, y, dims, precision='highest')
   with pytest.raises(AssertionError):
     cfg(x, y.to(torch.bfloat16), dims)
+
+
+@pytest.mark.parametrize('kind', ['int8_per_channel', 'fp8_per_tensor'])
+def test_traced_step_replays_the_same_calls(monkeypatch, kind):
+  """engine.TracedStep: record once, replay; new input VALUES written into the
+  traced tensors give the new step's results."""
+  from aqt_b200 import engine
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(5)
+  dims = (((1,), (0,)), ((), ()))
+  dt = np.float32 if kind == 'int8_per_channel' else orc.bfloat16
+  if kind == 'int8_per_channel':
+    cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                                 use_stochastic_rounding=False)
+  else:
+    cfg = config.fully_quantized(fwd_bits='e4m3', bwd_bits='e5m2',
+                                 use_stochastic_rounding=False)
+    for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
+      raw.dg_quantizer.lhs.calib_shared_axes = 'per_tensor'
+      raw.dg_quantizer.rhs.calib_shared_axes = 'per_tensor'
+  mk = lambda shape, std: util.rand_normal(rng, shape, std, dt)
+  lhs, rhs, g = mk((32, 48), 1.0), mk((48, 16), 0.2), mk((32, 16), 1.0)
+  tl, tr, tg = util.to_torch(lhs), util.to_torch(rhs), util.to_torch(g)
+
+  def step(a, b, c):
+    out, bp = cfg.vjp(a, b, dims)
+    return (out,) + tuple(bp(c))
+
+  traced = engine.TracedStep(step, tl, tr, tg)
+  assert traced.n_ops >= 3
+  # second step: other values in the same tensors
+  lhs2, g2 = mk((32, 48), 2.0), mk((32, 16), 0.5)
+  tl.copy_(util.to_torch(lhs2))
+  tg.copy_(util.to_torch(g2))
+  out, dl, dr = traced(tl, tr, tg)
+  wo, wl, wr, _ = orc.dg_fwd_bwd(cfg, lhs2, rhs, g2, dims)
+  _assert_same(out, wo, 'out')
+  _assert_same(dl, wl, 'dlhs')
+  _assert_same(dr, wr, 'drhs')
+  with pytest.raises(AssertionError):
+    traced(tl.clone(), tr, tg)

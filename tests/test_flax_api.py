@@ -75,3 +75,50 @@ def test_convert_then_serve_is_bit_identical(monkeypatch):
   serve.rhs_qtensor = frozen
   got = serve(x, torch.zeros_like(w), dims)  # the float weights are unused
   np.testing.assert_array_equal(util.to_numpy(got), util.to_numpy(train))
+
+
+def test_aqt_einsum_convert_then_serve(monkeypatch):
+  # the frozen weights live on the AqtEinsum object from one call to the
+  # next, also when the einsum swaps its operands ('ab,bc->ca')
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(3)
+  x = util.to_torch(util.rand_normal(rng, (8, 32), 1.0, np.float32))
+  w = util.to_torch(util.rand_normal(rng, (32, 16), 0.2, np.float32))
+  cfg = config.fully_quantized(use_stochastic_rounding=False)
+  for eqn in ('ab,bc->ac', 'ab,bc->ca'):
+    train = aqt_flax.AqtEinsum(cfg)(eqn, x, w)
+    conv = aqt_flax.AqtEinsum(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
+    conv(eqn, x, w)
+    frozen = conv.rhs_qtensor
+    assert frozen is not None and frozen.qvalue.dtype == torch.int8
+    assert tuple(frozen.qvalue.shape) == (32, 16), eqn
+    assert conv.lhs_qtensor is None
+    serve = aqt_flax.AqtEinsum(cfg, rhs_quant_mode=utils.QuantMode.SERVE)
+    serve.rhs_qtensor = frozen
+    for _ in range(2):
+      got = serve(eqn, x, torch.zeros_like(w))
+      np.testing.assert_array_equal(util.to_numpy(got), util.to_numpy(train))
+
+
+def test_aqt_einsum_draws_fresh_noise_every_call(monkeypatch):
+  fake_lib.install(monkeypatch)
+  from aqt_b200.v2 import stochastic_rounding as sr
+  rng = np.random.default_rng(4)
+  x = util.to_torch(util.rand_normal(rng, (8, 32), 1.0, np.float32))
+  w = util.to_torch(util.rand_normal(rng, (32, 16), 0.2, np.float32))
+  g = util.to_torch(util.rand_normal(rng, (8, 16), 1.0, np.float32))
+  keys = []
+  cfg = config.fully_quantized(use_stochastic_rounding=True)
+
+  def noise_fn(shape, key):
+    keys.append((int(key[0]), int(key[1])))
+    return torch.zeros(shape)
+
+  for raw in (cfg.dlhs, cfg.drhs):
+    raw.dg_quantizer.lhs.numerics.noise_fn = noise_fn
+    raw.dg_quantizer.rhs.numerics.noise_fn = noise_fn
+  es = aqt_flax.AqtEinsum(cfg, rngs={'params': sr.PRNGKey(7)})
+  for _ in range(2):
+    xx, ww = x.clone().requires_grad_(), w.clone().requires_grad_()
+    es('ab,bc->ac', xx, ww).backward(g)
+  assert len(keys) == 8 and len(set(keys)) == 8, keys

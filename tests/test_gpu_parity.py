@@ -78,6 +78,10 @@ CASES = [
     ((((1,), (1,)), ((), ())), (8, 20), (10, 20)),
     ((((0,), (0,)), ((), ())), (20, 8), (20, 10)),
     ((((2,), (0,)), ((), ())), (4, 6, 32), (32, 12)),
+    # kept axes of lhs on both sides of its contraction axis ('bkh,kd->bhd'):
+    # no single strided view exists, the planner regroups with copies
+    ((((1,), (0,)), ((), ())), (4, 32, 6), (32, 10)),
+    ((((1,), (0,)), ((), ())), (4, 6, 6), (6, 5)),
     ((((1,), (0,)), ((), ())), (1, 17), (17, 1)),
 ]
 
