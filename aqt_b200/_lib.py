@@ -117,6 +117,7 @@ SYMBOLS = {
     'aqtb200_kernel_launch_count': (C.c_int64, []),
     'aqtb200_set_gemm_impl': (C.c_int, [C.c_int]),
     'aqtb200_set_gemm_sm_budget': (C.c_int, [C.c_int]),
+    'aqtb200_mma_peak': (C.c_int, [C.c_int32, C.c_int64, C.c_void_p, C.c_void_p]),
 }
 
 _lib = None

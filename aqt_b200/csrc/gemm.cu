@@ -1378,6 +1378,83 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
 }
 
 // ---------------------------------------------------------------------------
+// Tensor-pipe ceiling: nothing but tcgen05.mma issue. Each CTA (one per SM)
+// fills one 128 x 128-byte A slab and one 256 x 128-byte B slab in shared
+// memory with pseudo-random bytes (no global traffic at all), then one thread
+// issues 128 x 256 x 32 MMAs into two alternating TMEM accumulators, a commit
+// every 16 MMAs, never more than two such batches in flight. No epilogue: the
+// accumulators are dropped. What this measures is the rate the tensor pipe
+// retires 8-bit MMAs of the shape the GEMM kernels use, on this GPU at the
+// clock the power cap allows -- the denominator of their roofline.
+constexpr int PEAK_BATCH = 16;
+
+template <bool IS_INT>
+__global__ void __launch_bounds__(128, 1)
+mma_peak_kernel(int64_t batches, uint32_t idesc, int32_t* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) uint64_t done_bar[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // int8: any byte is a value. fp8: keep the exponent field away from all-ones
+  // (NaN / infinity encodings) by clearing the top exponent bit.
+  uint32_t x = 0x9e3779b9u * (threadIdx.x + 1) + 0x85ebca6bu * (blockIdx.x + 1);
+  for (int i = threadIdx.x; i < (A_STAGE + B_STAGE) / 4; i += blockDim.x) {
+    x ^= x << 13; x ^= x >> 17; x ^= x << 5;
+    ((uint32_t*)smem)[i] = IS_INT ? x : (x & 0xbfbfbfbfu);
+  }
+  if (threadIdx.x == 0) {
+    mbar_init(&done_bar[0], 1);
+    mbar_init(&done_bar[1], 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(&tmem_slot)),
+                 "r"(TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  if (warp == 0 && lane == 0) {
+    const uint64_t ad = make_smem_desc(smem_u32(smem));
+    const uint64_t bd = make_smem_desc(smem_u32(smem + A_STAGE));
+    volatile int* abortp = &abort_flag;
+    bool ok = true;
+    for (int64_t b = 0; b < batches && ok; ++b) {
+      const int slot = (int)(b & 1);
+      // batch b reuses the barrier of batch b - 2: wait for that one first
+      if (b >= 2) ok = mbar_wait(&done_bar[slot], (uint32_t)(((b - 2) >> 1) & 1), abortp);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll
+      for (int i = 0; i < PEAK_BATCH; ++i)
+        tc_mma<IS_INT>(tmem_base + (uint32_t)(slot * BN), ad + (uint64_t)(2 * (i & 3)),
+                       bd + (uint64_t)(2 * (i & 3)), idesc, i > 0 ? 1u : 0u);
+      tc_commit(&done_bar[slot]);
+    }
+    // drain: the last two batches
+    for (int64_t b = batches > 2 ? batches - 2 : 0; b < batches && ok; ++b)
+      ok = mbar_wait(&done_bar[b & 1], (uint32_t)((b >> 1) & 1), abortp);
+    if (!ok && status != nullptr) atomicCAS(status, 0, 4);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"(TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Plain CUDA-core kernel with the same epilogue; selected only through
 // aqtb200_set_gemm_impl(1) to cross-check the tensor-core kernel.
 __device__ __forceinline__ float qval(const uint8_t* p, int dt, int64_t i) {
@@ -1813,6 +1890,29 @@ extern "C" {
 
 int aqtb200_gemm_dequant(const aqtb200_gemm_desc* desc, int32_t* status, void* stream) {
   return aqtb200::gemm_dequant(desc, status, (cudaStream_t)stream);
+}
+
+int aqtb200_mma_peak(int32_t is_int, int64_t mmas_per_sm, int32_t* status, void* stream) {
+  using namespace aqtb200;
+  AQT_REQUIRE(mmas_per_sm > 0 && mmas_per_sm < ((int64_t)1 << 40), AQTB200_EINVAL,
+              "mmas_per_sm out of range");
+  const int64_t batches = (mmas_per_sm + PEAK_BATCH - 1) / PEAK_BATCH;
+  const uint32_t cfmt = is_int ? 2u : 1u, abfmt = is_int ? 1u : 0u;  // s8 x s8 -> s32, e4m3 x e4m3 -> f32
+  const uint32_t idesc = (cfmt << 4) | (abfmt << 7) | (abfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
+                         ((uint32_t)(BM >> 4) << 24);
+  const size_t smem = A_STAGE + B_STAGE + 1024;
+  if (is_int) {
+    AQT_CUDA_OK(cudaFuncSetAttribute(mma_peak_kernel<true>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mma_peak_kernel<true><<<sm_count(), 128, smem, (cudaStream_t)stream>>>(batches, idesc, status);
+  } else {
+    AQT_CUDA_OK(cudaFuncSetAttribute(mma_peak_kernel<false>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    mma_peak_kernel<false><<<sm_count(), 128, smem, (cudaStream_t)stream>>>(batches, idesc, status);
+  }
+  AQT_CUDA_OK(cudaGetLastError());
+  count_launch();
+  return 0;
 }
 
 int aqtb200_set_gemm_sm_budget(int max_sms) {

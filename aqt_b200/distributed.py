@@ -78,7 +78,7 @@ class ShardedDotGeneral:
     # drhs is computed in this many row slices so that the exchange of one
     # slice's accumulators runs under the next slice's GEMM.
     self.drhs_slices = drhs_slices
-    # a slice (and a rank's band of it) is a whole number of GEMM tile rows
+    # a slice is a whole number of GEMM tile rows
     self.slice_multiple = slice_multiple
     self._side = {}
 
@@ -289,7 +289,7 @@ class ShardedDotGeneral:
       return None
     k = res.lhs.mt.x.shape[1]
     n = g.shape[1]
-    if k % (s * world) != 0 or (k // (s * world)) % self.slice_multiple != 0:
+    if k % (s * world) != 0 or (k // s) % self.slice_multiple != 0 or n % 4:
       return None
     cfg = self.cfg
     rank = dist.get_rank(self.group)

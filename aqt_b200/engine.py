@@ -421,7 +421,8 @@ class DeferredDequant:
 
 def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
            out_transpose_axes=None, want_acc=False, defer_dequant=False,
-           internal_qt=False, out=None, _regrouped=False, _noise=None):
+           internal_qt=False, out=None, amax_out=None, _regrouped=False,
+           _noise=None):
   """DotGeneralRaw.__call__ on the device (aqt_dot_general.py:757-840).
 
   Returns (out, DotGeneralRes[, acc]). `out` is laid out as
@@ -431,6 +432,8 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
   still flow to the operands as if they had been quantized here.
   out: optional preallocated result (any strides, e.g. a slice of a larger
   tensor) of the transposed result's shape and the result dtype.
+  amax_out: optional one-element f32 device tensor, zeroed by the caller, that
+  receives max |out| from the GEMM epilogue (atomic max).
   """
   from aqt_b200.v2 import aqt_dot_general as adg
   from aqt_b200.v2 import aqt_tensor
@@ -716,6 +719,9 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
       acc = acc.transpose(1, 2)
   if defer_dequant:
     desc.out = None
+  if amax_out is not None:
+    assert amax_out.dtype == torch.float32 and amax_out.numel() == 1
+    desc.amax_out = amax_out.data_ptr()
 
   lib = _lib.load()
   ws_bytes = lib.aqtb200_dot_general_raw_workspace_bytes(C.byref(desc))

@@ -11,13 +11,18 @@ quantization kernels included.
 
 Prints ONE JSON line (rank 0). `value` is whole-job TOPS with inputs resident
 in HBM; `e2e` is the same metric through the public API with pinned host
-buffers, host->device and device->host copies inside the timed region.
-`--impl reference` times the CPU restatement of the reference (the reference
-itself needs jax, which is not installed here) on a bounded sample.
+buffers, host->device and device->host copies inside the timed region;
+`sustained` repeats the device-resident measurement for seconds instead of
+milliseconds (the part is power-capped, so a short burst runs at a higher
+clock than a long loop); `extras` (1 GPU only) time the other BASELINE.json
+configurations. `--impl reference` times the CPU restatement of the reference
+(the reference itself needs jax, which is not installed here) on a bounded
+sample, with every host core.
 """
 
 import argparse
 import json
+import math
 import os
 import sys
 import time
@@ -28,6 +33,7 @@ if ROOT not in sys.path:
 
 METRIC = 'quantized_dot_general_fwd_bwd_tops'
 UNIT = 'TOPS'
+DIMS = (((1,), (0,)), ((), ()))
 
 
 def parse_args():
@@ -40,25 +46,30 @@ def parse_args():
   p.add_argument('--size', type=int, default=8192)
   p.add_argument('--kind', default='fp8', choices=['fp8', 'int8'])
   p.add_argument('--cpu-sample-rows', type=int, default=0,
-                 help='rows of lhs/cotangent the CPU arm processes (0 = all: '
-                 'the whole workload, which keeps the ratio of contraction to '
-                 'quantization work of the real problem)')
+                 help='rows of lhs/cotangent the CPU leg processes (0 = all '
+                 'for the one-pass baseline of the default run; the reference '
+                 'arm sizes its sample from --steps/--warmup)')
   p.add_argument('--no-cpu-baseline', action='store_true')
   p.add_argument('--no-e2e', action='store_true')
-  p.add_argument('--workload', default='c2', choices=['c1', 'c2', 'c3', 'c4'],
-                 help='BASELINE.json config to time; c2 is the headline '
-                 'workload, the others are extra single-GPU measurements')
+  p.add_argument('--no-extras', action='store_true',
+                 help='skip the other BASELINE.json configurations (1 GPU)')
+  p.add_argument('--sustained-seconds', type=float, default=2.0,
+                 help='length of the second, long timed region (0 = skip)')
+  p.add_argument('--workload', default='c2',
+                 choices=['c1', 'c2', 'c3', 'c4', 'int8', 'stack'],
+                 help='c2 is the headline workload (with the others as '
+                 '`extras` in its line); naming another one times that alone')
   p.add_argument('--m', type=int, default=16,
                  help='rows of the activation for --workload c4')
   p.add_argument('--eager', action='store_true',
-                 help='main workload at 1 GPU: launch every kernel from Python '
-                      'each step instead of replaying the step from a CUDA graph')
-  p.add_argument('--graph', action='store_true',
-                 help='extra workloads only: replay the step from a CUDA graph '
-                 '(removes host launch overhead from small problems)')
+                 help='launch every kernel from Python each step instead of '
+                 'replaying a recorded step (CUDA graph at 1 GPU, call tape '
+                 'at several)')
   p.add_argument('--gemm', default='tcgen05',
                  choices=['tcgen05', 'cta1', 'cta2', 'wide'],
                  help='tile shape of the tensor-core kernel (default: automatic)')
+  p.add_argument('--drhs-slices', type=int, default=2)
+  p.add_argument('--overlap-sms', type=int, default=32)
   return p.parse_args()
 
 
@@ -76,16 +87,52 @@ def make_cfg(kind):
   return cfg
 
 
-DIMS = (((1,), (0,)), ((), ()))
-
-
 def workload_name(args):
   return (f'{args.kind} dot_general {args.size}x{args.size}x{args.size} '
           'fwd+dlhs+drhs, bf16 in/out, per-tensor absmax scales')
 
 
+def config_dict(args, world):
+  """The `config` object of the JSON line; both arms print the same one."""
+  n = args.size
+  m_local = n if args.scaling == 'weak' else n // world
+  return {
+      'workload': workload_name(args),
+      'rows_per_gpu': m_local, 'global_rows': m_local * world,
+      'parallelism': f'rows sharded over {world} GPU(s)',
+      'l2': 'inputs (3 x 134 MB bf16 + quantized copies) exceed the 126 MB L2',
+  }
+
+
+def measured_peaks():
+  path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+  if os.path.exists(path):
+    with open(path) as f:
+      d = json.load(f)
+    return {'hbm_gbs': d['hbm_gbs'], 'bf16': d['bf16_tflops'],
+            'bf16_sustained': d.get('bf16_tflops_sustained', d['bf16_tflops']),
+            'src': 'of measured (MEASURED_PEAKS.json)'}
+  return {'hbm_gbs': 6650.0, 'bf16': 1590.0, 'bf16_sustained': 1400.0,
+          'src': 'of fallback (6.65 TB/s, 1.59 PFLOP/s bf16)'}
+
+
 # ---------------------------------------------------------------------------
-# CPU arm: the oracle on a bounded sample
+# CPU legs: the oracle on a bounded sample
+
+
+def use_all_host_cores():
+  """BLAS threads = host cores (a launcher may have exported OMP_NUM_THREADS=1
+  before numpy was loaded). Returns the thread count in effect."""
+  n = os.cpu_count() or 1
+  try:
+    import numpy as np  # the BLAS behind it must be loaded before it is asked
+    import threadpoolctl
+    np.ones((8, 8), np.float32) @ np.ones((8, 8), np.float32)
+    threadpoolctl.threadpool_limits(limits=n)
+    infos = threadpoolctl.threadpool_info()
+    return max([i.get('num_threads', 1) for i in infos] + [1])
+  except Exception:  # pylint: disable=broad-except
+    return n
 
 
 def cpu_sample(args, rows):
@@ -105,40 +152,49 @@ def cpu_sample(args, rows):
   return ops / dt / 1e12, dt
 
 
-def blas_threads():
-  try:
-    import threadpoolctl
-    infos = threadpoolctl.threadpool_info()
-    return max([i.get('num_threads', 1) for i in infos] + [1])
-  except Exception:  # pylint: disable=broad-except
-    return os.cpu_count() or 1
-
-
 def run_reference_arm(args, lines):
+  """The reference's CPU path (its numpy restatement) on this box's host
+  cores: --warmup + --steps passes, each over a sample of the workload's rows
+  sized so that the whole run stays within a few minutes."""
   rank = int(os.environ.get('RANK', '0'))
   if rank != 0:
     return
-  rows = args.cpu_sample_rows or args.size
-  for _ in range(min(args.warmup, 1)):
+  cores = use_all_host_cores()
+  n = args.size
+  if args.cpu_sample_rows:
+    rows = args.cpu_sample_rows
+  else:
+    # cost model t(rows) = fixed (the rhs side) + per_row * rows from two probes
+    r1, r2 = min(256, n), min(512, n)
+    _, t1 = cpu_sample(args, r1)
+    _, t2 = cpu_sample(args, r2)
+    per_row = max((t2 - t1) / max(r2 - r1, 1), 1e-6)
+    fixed = max(t1 - per_row * r1, 0.0)
+    budget = 150.0 / max(args.steps + args.warmup, 1)
+    rows = int((budget - fixed) / per_row) if budget > fixed else r1
+    rows = max(r1, min(n, rows // 256 * 256))
+  for _ in range(args.warmup):
     cpu_sample(args, rows)
-  steps = max(1, min(args.steps, 3))
   vals, times = [], []
-  for _ in range(steps):
+  for _ in range(args.steps):
     v, dt = cpu_sample(args, rows)
     vals.append(v)
     times.append(dt)
   value = sum(vals) / len(vals)
-  sample = (f'{rows} of {args.size} lhs/cotangent rows against the full '
-            f'{args.size}x{args.size} rhs, numpy+ml_dtypes restatement '
-            '(jax is not installed, so the reference itself cannot run)')
+  sample = (f'{rows} of {n} lhs/cotangent rows against the full {n}x{n} rhs '
+            f'per step, {args.steps} steps after {args.warmup} warm-up; '
+            'numpy+ml_dtypes restatement on all host cores (jax is not '
+            'installed, so the reference itself cannot run); TOPS counts the '
+            'operations of the sampled rows')
+  world = int(os.environ.get('WORLD_SIZE', str(args.gpus)))
   line = {
       'impl': 'reference', 'metric': METRIC, 'value': value, 'unit': UNIT,
-      'n_gpus': args.gpus, 'steps': steps, 'warmup': min(args.warmup, 1),
+      'n_gpus': args.gpus, 'steps': args.steps, 'warmup': args.warmup,
       'ms_per_step': 1e3 * sum(times) / len(times), 'higher_is_better': True,
-      'scaling': args.scaling, 'vs_baseline': None, 'dtype': args.kind,
-      'data': 'synthetic',
-      'config': {'workload': workload_name(args), 'sample': sample},
-      'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': blas_threads(),
+      'scaling': args.scaling, 'vs_baseline': None,
+      'dtype': 'f8e4m3/f8e5m2->f32' if args.kind == 'fp8' else 's8->s32',
+      'data': 'synthetic', 'config': config_dict(args, max(world, args.gpus)),
+      'cpu_baseline': {'value': value, 'unit': UNIT, 'cores': cores,
                        'kind': 'port', 'sample': sample},
       'e2e': {'value': value, 'unit': UNIT, 'h2d_bytes_per_step': 0,
               'd2h_bytes_per_step': 0},
@@ -244,6 +300,234 @@ while True:
             'samples': len(clocks)}
 
 
+def timed_region(torch, step, steps, device_index, barrier=None):
+  """`steps` calls of step() between two events on the current stream, with
+  the clocks sampled meanwhile. Returns (ms per step, clocks, host ms per step)."""
+  barrier = barrier or torch.cuda.synchronize
+  sampler = ClockSampler(device_index)
+  e0 = torch.cuda.Event(enable_timing=True)
+  e1 = torch.cuda.Event(enable_timing=True)
+  sampler.start()
+  barrier()
+  sampler.mark_begin()
+  e0.record()
+  t_host = time.perf_counter()
+  for _ in range(steps):
+    step()
+  host_ms = (time.perf_counter() - t_host) * 1e3 / steps
+  e1.record()
+  barrier()
+  sampler.mark_end()
+  clocks = sampler.stop()
+  return e0.elapsed_time(e1) / steps, clocks, host_ms
+
+
+def capture_graph(torch, step, barrier=None):
+  """Captures step() in a CUDA graph; returns (replay, outputs of the capture)."""
+  barrier = barrier or torch.cuda.synchronize
+  side = torch.cuda.Stream()
+  side.wait_stream(torch.cuda.current_stream())
+  with torch.cuda.stream(side):
+    step()
+  torch.cuda.current_stream().wait_stream(side)
+  barrier()
+  graph = torch.cuda.CUDAGraph()
+  with torch.cuda.graph(graph):
+    outs = step()
+  for _ in range(3):
+    graph.replay()
+  barrier()
+  return graph.replay, outs, graph
+
+
+# ---------------------------------------------------------------------------
+# parity of the sharded step against the unsharded one (outside any timing)
+
+
+def sharded_parity_check(torch, dist, rank, world, dev, m_local=2048, k=1024,
+                         n=1024, traced=True):
+  """Runs a small row-sharded step and, on every rank, the same problem
+  unsharded; returns a dict of 'ok' / 'MISMATCH' per case. int8: bit for bit.
+  fp8: out and dlhs bit for bit (rows are independent given the agreed
+  scales), drhs within max(1 bf16 ulp, 1e-5 * sum |g||lhs|) because the
+  ranks' f32 partial sums are added in another order than one device's."""
+  from aqt_b200 import distributed as aqt_dist
+  from aqt_b200 import engine
+  result = {}
+  for kind in ('int8', 'fp8'):
+    for per_tensor in (True, False):
+      cfg = make_cfg(kind)
+      if not per_tensor:
+        for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
+          raw.dg_quantizer.lhs.calib_shared_axes = None
+          raw.dg_quantizer.rhs.calib_shared_axes = None
+      gen = torch.Generator(device=dev)
+      gen.manual_seed(7)
+      m = m_local * world
+      lhs = torch.randn(m, k, device=dev, generator=gen).to(torch.bfloat16)
+      rhs = (torch.randn(k, n, device=dev, generator=gen) * 0.03).to(
+          torch.bfloat16)
+      g = torch.randn(m, n, device=dev, generator=gen).to(torch.bfloat16)
+      sl = slice(rank * m_local, (rank + 1) * m_local)
+      a, c = lhs[sl].contiguous(), g[sl].contiguous()
+      op = aqt_dist.ShardedDotGeneral(cfg)
+
+      def step(a_, b_, c_, op=op):
+        out, bp = op.vjp(a_, b_, DIMS)
+        return (out,) + tuple(bp(c_))
+
+      if traced and per_tensor:
+        out, dl, dr = engine.TracedStep(step, a, rhs, c)(a, rhs, c)
+      else:
+        out, dl, dr = step(a, rhs, c)
+      wo, wbp = cfg.vjp(lhs, rhs, DIMS)
+      wl, wr = wbp(g)
+      torch.cuda.synchronize()
+      engine.check_status()
+      same = torch.equal(out, wo[sl]) and torch.equal(dl, wl[sl])
+      if kind == 'int8':
+        same = same and torch.equal(dr, wr)
+      else:
+        want = wr.double()
+        ulp = 2.0 ** (torch.floor(torch.log2(want.abs().clamp_min(1e-38))) - 7)
+        bound = 2.0 * (lhs.float().abs().t() @ g.float().abs()).double()
+        tol = torch.maximum(ulp, 1e-5 * bound)
+        same = same and bool(((dr.double() - want).abs() <= tol).all())
+      flag = torch.tensor([1 if same else 0], device=dev)
+      dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+      result[f'{kind}_{"per_tensor" if per_tensor else "per_channel"}'] = (
+          'ok' if int(flag.item()) else 'MISMATCH')
+  return result
+
+
+# ---------------------------------------------------------------------------
+# the other BASELINE.json configurations (1 GPU, device-resident)
+
+
+def build_workload(name, args, torch, dev):
+  """Returns (step, ops per step, minimum HBM bytes per step, description,
+  bound) for one of: c1, c3, c4 (with args.m), int8 (the 8192^3 step in
+  int8), stack (one Llama-3-8B-shaped decoder layer's seven projections)."""
+  from aqt_b200.v2 import aqt_dot_general as adg
+  from aqt_b200.v2 import config
+  from aqt_b200.v2 import stochastic_rounding as sr
+  from aqt_b200.v2 import utils
+  from aqt_b200.v2.flax import aqt_flax
+  gen = torch.Generator(device=dev)
+  gen.manual_seed(0)
+  rn = lambda shape, std, dt: (torch.randn(shape, device=dev, generator=gen)
+                               * std).to(dt)
+  if name == 'c1':
+    lhs = rn((1024, 4096), 1.0, torch.float32)
+    rhs = rn((4096, 4096), 1.0 / 64, torch.float32)
+    g = rn((1024, 4096), 1.0, torch.float32)
+    cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                                 use_stochastic_rounding=False)
+
+    def step():
+      out, bp = cfg.vjp(lhs, rhs, DIMS)
+      return out, bp(g)
+
+    return (step, 3 * 2 * 1024 * 4096 * 4096, 201e6,
+            'config 1: int8 [1024,4096]x[4096,4096] f32 in/out, per-channel '
+            'absmax, RNE, fwd+dlhs+drhs', 'hbm')
+  if name == 'int8':
+    n = args.size
+    lhs = rn((n, n), 1.0, torch.bfloat16)
+    rhs = rn((n, n), n ** -0.5, torch.bfloat16)
+    g = rn((n, n), 1.0, torch.bfloat16)
+    cfg = make_cfg('int8')
+
+    def step():
+      out, bp = cfg.vjp(lhs, rhs, DIMS)
+      return out, bp(g)
+
+    return (step, 3 * 2 * n ** 3, 6 * 2 * n * n,
+            f'int8 dot_general {n}^3 fwd+dlhs+drhs, bf16 in/out, per-tensor '
+            'absmax scales (config 2 in int8)', 'tensor')
+  if name == 'c3':
+    b, t, h, d = 8, 2048, 32, 128
+    q = rn((b, t, h, d), 1.0, torch.bfloat16)
+    k = rn((b, t, h, d), 1.0, torch.bfloat16)
+    g = rn((b, h, t, t), 1.0, torch.bfloat16)
+    cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                                 use_stochastic_rounding=True)
+    noise = {}
+
+    def noise_fn(shape, key):
+      kk = (tuple(shape), int(key[0]), int(key[1]))
+      if kk not in noise:
+        noise[kk] = torch.rand(shape, device=dev, generator=gen) - 0.5
+      return noise[kk]
+
+    for raw in (cfg.dlhs, cfg.drhs):
+      raw.dg_quantizer.lhs.numerics.noise_fn = noise_fn
+      raw.dg_quantizer.rhs.numerics.noise_fn = noise_fn
+    cfg = config.set_context(cfg, key=sr.PRNGKey(1), train_step=None)
+    dims = (((3,), (3,)), ((0, 2), (0, 2)))
+
+    def step():
+      out, bp = cfg.vjp(q, k, dims)
+      return out, bp(g)
+
+    return (step, 3 * 2 * b * h * t * t * d, 5.1e9,
+            "config 3: int8 einsum 'bthd,bshd->bhts' B8 H32 T=S=2048 D128, "
+            'bf16, per-token scales, fwd + both gradients, stochastic '
+            'rounding from 4 given f32 noise tensors (2 x 4.29 GB + 2 x 0.27 GB '
+            'read on top of the minimum bytes)', 'hbm')
+  if name == 'c4':
+    m, kk, n = args.m, 8192, 28672
+    x = rn((m, kk), 1.0, torch.bfloat16)
+    w = rn((kk, n), kk ** -0.5, torch.bfloat16)
+    cfg = adg.dot_general_make(lhs_bits=8, rhs_bits=4)
+    cfg.fwd.dg_quantizer.rhs.numerics.dtype = utils.int8
+    conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
+    conv(x, w, DIMS)
+    rhs_qt = conv.rhs_qtensor
+    del conv
+
+    def step():
+      # dg_core is what AqtDotGeneral calls after copying its config; calling
+      # it directly keeps the per-call deepcopy out of a serving loop. The
+      # float weights are not read in SERVE mode.
+      return cfg.dg_core(x, w, None, rhs_qt, DIMS)[0]
+
+    return (step, 2 * m * kk * n,
+            kk * n + m * kk * 2 + m * n * 2 + 2 * n + 2 * m,
+            f'config 4: serving GEMM M={m} K=8192 N=28672, int8 activations '
+            'per token x int4-in-int8 frozen weights per channel, bf16 out',
+            'hbm' if m <= 256 else 'tensor')
+  raise ValueError(name)
+
+
+def time_workload(name, args, torch, dev, lib, engine, peaks, steps=None):
+  step, ops, min_bytes, desc, bound = build_workload(name, args, torch, dev)
+  for _ in range(3):
+    step()
+  torch.cuda.synchronize()
+  engine.check_status()
+  l0 = lib.aqtb200_kernel_launch_count()
+  replay, keep, graph = capture_graph(torch, step)
+  launches = (lib.aqtb200_kernel_launch_count() - l0) // 2  # two passes: dry run, capture
+  steps = steps or args.steps
+  ms, clocks, _ = timed_region(torch, replay, steps, dev.index or 0)
+  engine.check_status()
+  tops = ops / (ms * 1e-3) / 1e12
+  gbs = min_bytes / (ms * 1e-3) / 1e9
+  rec = {'workload': desc, 'ms_per_step': ms, 'tops': tops,
+         'min_bytes_gbs': gbs, 'bound': bound, 'launches_per_step': launches,
+         'steps': steps, 'launch': 'cuda_graph replay', 'sm_mhz': clocks['sm_mhz'],
+         'reasons': clocks['reasons']}
+  if bound == 'tensor':
+    rec['frac'] = tops / (2.0 * peaks['bf16'])
+    rec['frac_of'] = '2 x bf16_tflops, ' + peaks['src']
+  else:
+    rec['frac'] = gbs / peaks['hbm_gbs']
+    rec['frac_of'] = 'minimum bytes / time over hbm_gbs, ' + peaks['src']
+  del keep, graph
+  return rec
+
+
 # ---------------------------------------------------------------------------
 # our arm
 
@@ -265,6 +549,7 @@ def run_ours(args, lines):
     dist.init_process_group('nccl', device_id=dev)
   lib = _lib.load()
   engine.set_gemm_impl(args.gemm)
+  peaks = measured_peaks()
 
   n = args.size
   m_local = n if args.scaling == 'weak' else n // world
@@ -282,9 +567,10 @@ def run_ours(args, lines):
   op = None
   if world > 1:
     from aqt_b200 import distributed as aqt_dist
-    op = aqt_dist.ShardedDotGeneral(cfg)
+    op = aqt_dist.ShardedDotGeneral(cfg, drhs_slices=args.drhs_slices,
+                                    overlap_sms=args.overlap_sms)
 
-  def step(a, b, c):
+  def eager_step(a, b, c):
     if op is not None:
       out, bp = op.vjp(a, b, DIMS)
     else:
@@ -298,73 +584,85 @@ def run_ours(args, lines):
     torch.cuda.synchronize()
 
   for _ in range(args.warmup):
-    step(lhs, rhs, g)
+    eager_step(lhs, rhs, g)
   barrier()
   engine.check_status()
 
-  # One GPU: the step (17 kernels behind a Python planner) is captured once and
-  # replayed, as a compiled training step would be; operands keep their
-  # addresses, results land in the graph's own buffers. Several GPUs: eager,
-  # the collectives stay outside graphs.
-  use_graph = world == 1 and not args.eager
+  # The step is recorded once and replayed, as a compiled training step would
+  # be. One GPU: a CUDA graph of its kernels. Several GPUs: the call tape of
+  # engine.TracedStep (kernels AND collectives re-issued from a flat list, the
+  # collectives stay outside graphs); its first replay is compared bit for bit
+  # with an eager step.
+  launch = 'eager'
   launches_per_step = None
-  eager_step = step
-  if use_graph:
-   try:
-    run_step = step
-    side = torch.cuda.Stream()
-    side.wait_stream(torch.cuda.current_stream())
-    with torch.cuda.stream(side):
-      run_step(lhs, rhs, g)
-    torch.cuda.current_stream().wait_stream(side)
-    barrier()
-    graph = torch.cuda.CUDAGraph()
-    l0 = lib.aqtb200_kernel_launch_count()
-    with torch.cuda.graph(graph):
-      graph_outs = run_step(lhs, rhs, g)
-    launches_per_step = lib.aqtb200_kernel_launch_count() - l0
+  outs = eager_step(lhs, rhs, g)
+  step = lambda: eager_step(lhs, rhs, g)
+  if not args.eager:
+    try:
+      l0 = lib.aqtb200_kernel_launch_count()
+      if world == 1:
+        step, outs, graph = capture_graph(torch, step, barrier)
+        launches_per_step = (lib.aqtb200_kernel_launch_count() - l0) // 2
+        launch = 'cuda_graph replay of the whole step'
+      else:
+        traced = engine.TracedStep(eager_step, lhs, rhs, g)
+        outs = traced.outputs
+        step = lambda: traced(lhs, rhs, g)
+        launch = (f'call tape replay ({traced.n_ops} recorded calls: kernels '
+                  'and collectives), first replay verified bit for bit '
+                  'against an eager step')
+        for _ in range(3):
+          step()
+      barrier()
+      engine.check_status()
+    except Exception as e:  # pylint: disable=broad-except
+      # recording is an optimisation of the launch path only: run eagerly
+      print(f'step recording failed ({type(e).__name__}: {e}); eager',
+            file=sys.stderr)
+      launch, launches_per_step = 'eager', None
+      step = lambda: eager_step(lhs, rhs, g)
+      torch.cuda.synchronize()
 
-    def step(a, b, c):  # pylint: disable=function-redefined
-      assert a is lhs and b is rhs and c is g
-      graph.replay()
-      return graph_outs
-
-    for _ in range(3):
-      step(lhs, rhs, g)
-    barrier()
-    engine.check_status()
-   except Exception as e:  # pylint: disable=broad-except
-    # capture is an optimisation of the launch path only: run eagerly instead
-    print(f'CUDA graph capture failed ({type(e).__name__}: {e}); eager', file=sys.stderr)
-    use_graph, launches_per_step, step = False, None, eager_step
-    torch.cuda.synchronize()
-
-  sampler = ClockSampler(local_rank)
   launches0 = lib.aqtb200_kernel_launch_count()
-  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  sampler.start()
-  barrier()
-  sampler.mark_begin()
-  e0.record()
-  t_host = time.perf_counter()
-  for _ in range(args.steps):
-    outs = step(lhs, rhs, g)
-  host_ms = (time.perf_counter() - t_host) * 1e3 / args.steps
-  e1.record()
-  barrier()
-  sampler.mark_end()
-  clocks = sampler.stop()
+  ms, clocks, host_ms = timed_region(torch, step, args.steps, local_rank,
+                                     barrier)
   launches = lib.aqtb200_kernel_launch_count() - launches0
   if launches_per_step is not None:
     launches = launches_per_step * args.steps  # replayed, not re-issued
   engine.check_status()
-  ms = e0.elapsed_time(e1) / args.steps
-  if world > 1:
-    t = torch.tensor([ms], device=dev, dtype=torch.float64)
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    ms = float(t.item())
+
+  def max_over_ranks(v):
+    if world > 1:
+      t = torch.tensor([v], device=dev, dtype=torch.float64)
+      dist.all_reduce(t, op=dist.ReduceOp.MAX)
+      return float(t.item())
+    return v
+
+  ms = max_over_ranks(ms)
   ops_step = 3 * 2 * m_global * n * n
   value = ops_step / (ms * 1e-3) / 1e12
+
+  # ---- the same measurement over seconds instead of milliseconds
+  sustained = None
+  if args.sustained_seconds > 0:
+    k_long = max(args.steps, int(math.ceil(args.sustained_seconds * 1e3 / ms)))
+    sms, sclocks, _ = timed_region(torch, step, k_long, local_rank, barrier)
+    sms = max_over_ranks(sms)
+    sval = ops_step / (sms * 1e-3) / 1e12
+    sustained = {
+        'value': sval, 'unit': UNIT, 'ms_per_step': sms, 'steps': k_long,
+        'seconds': sms * k_long * 1e-3, 'clocks': sclocks,
+        'step_frac': sval / world / (2.0 * peaks['bf16_sustained']),
+        'step_frac_of': '2 x bf16_tflops_sustained, ' + peaks['src']}
+    engine.check_status()
+
+  # ---- sharded against unsharded results, outside any timed region
+  parity = None
+  if world > 1:
+    try:
+      parity = sharded_parity_check(torch, dist, rank, world, dev)
+    except Exception as e:  # pylint: disable=broad-except
+      parity = {'error': f'{type(e).__name__}: {e}'}
 
   # ---- end to end through the public API with pinned host buffers
   e2e = None
@@ -383,43 +681,62 @@ def run_ours(args, lines):
     pipe.drain()
     barrier()
     k = max(3, min(args.steps, 10))
+    e0 = torch.cuda.Event(enable_timing=True)
+    e1 = torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(k):
       pipe.submit(h, ho)
     pipe.drain()
     e1.record()
     barrier()
-    ems = e0.elapsed_time(e1) / k
-    if world > 1:
-      t = torch.tensor([ems], device=dev, dtype=torch.float64)
-      dist.all_reduce(t, op=dist.ReduceOp.MAX)
-      ems = float(t.item())
+    ems = max_over_ranks(e0.elapsed_time(e1) / k)
     e2e = {'value': ops_step / (ems * 1e-3) / 1e12, 'unit': UNIT,
            'h2d_bytes_per_step': sum(t.numel() * t.element_size() for t in h),
            'd2h_bytes_per_step': sum(t.numel() * t.element_size() for t in ho),
            'ms_per_step': ems,
            'path': 'aqt_b200.host_io.HostStepPipeline (pinned host buffers, '
                    'copies of neighbouring steps overlap compute)'}
+    del pipe, h, ho
 
   # ---- roofline of the dominant kernel: the tcgen05 GEMM, timed alone
   roof = None
   if rank == 0:
-    roof = gemm_roofline(args, cfg, lhs, rhs, torch, engine)
+    roof = gemm_roofline(args, cfg, lhs, rhs, torch, engine, peaks)
     # the whole step (calibration, quantization and the three GEMMs) against
-    # the same tensor peak, per GPU
+    # the same tensor peaks, per GPU
     roof['step_achieved'] = value / world
     roof['step_frac'] = value / world / roof['peak']
+    roof['step_frac_2x_bf16'] = value / world / roof['peak_2x_bf16']
 
   if rank != 0:
     if world > 1:
       dist.destroy_process_group()
     return
 
+  extras = None
+  if world == 1 and not args.no_extras and args.size == 8192:
+    del outs
+    extras = {}
+    todo = [('int8', None), ('c1', None), ('c3', None), ('c4', 16), ('c4', 256),
+            ('c4', 4096)]
+    if args.kind == 'int8':
+      todo = todo[1:]
+    for name, m in todo:
+      key = name if m is None else f'{name}_m{m}'
+      try:
+        if m is not None:
+          args.m = m
+        extras[key] = time_workload(name, args, torch, dev, lib, engine, peaks)
+      except Exception as e:  # pylint: disable=broad-except
+        extras[key] = {'error': f'{type(e).__name__}: {e}'}
+      torch.cuda.empty_cache()
+
   cpu = None
   if not args.no_cpu_baseline and world == 1:
+    cores = use_all_host_cores()
     cpu_rows = args.cpu_sample_rows or n
     v, dt = cpu_sample(args, cpu_rows)
-    cpu = {'value': v, 'unit': UNIT, 'cores': blas_threads(), 'kind': 'port',
+    cpu = {'value': v, 'unit': UNIT, 'cores': cores, 'kind': 'port',
            'sample': (f'{cpu_rows} of {n} lhs/cotangent rows against '
                       f'the full rhs, one pass, {dt:.1f} s; numpy+ml_dtypes '
                       'restatement (jax not installed)')}
@@ -429,28 +746,71 @@ def run_ours(args, lines):
       'higher_is_better': True, 'scaling': args.scaling, 'vs_baseline': None,
       'dtype': 'f8e4m3/f8e5m2->f32' if args.kind == 'fp8' else 's8->s32',
       'data': 'synthetic',
-      'config': {
-          'workload': workload_name(args),
-          'rows_per_gpu': m_local, 'global_rows': m_global,
-          'parallelism': f'rows sharded over {world} GPU(s)',
-          'launch': 'cuda_graph replay of the whole step' if use_graph else 'eager',
-          'l2': 'inputs (3 x 134 MB bf16 + quantized copies) exceed the 126 MB L2',
-      },
+      'config': config_dict(args, world),
+      'launch': launch,
       'clocks': clocks,
       'e2e': e2e,
       'gpu_launches': int(launches),
       'host_issue_ms_per_step': host_ms,
+      'sustained': sustained,
       'roofline': roof,
       'cpu_baseline': cpu,
   }
+  if parity is not None:
+    line['parity_check'] = parity
+  if extras is not None:
+    line['extras'] = extras
   lines.append(json.dumps(line))
   if world > 1:
     dist.destroy_process_group()
 
 
-def gemm_roofline(args, cfg, lhs, rhs, torch, engine):
+def mma_peak(args, torch, lib, mmas_per_sm=40000, reps=3):
+  """8-bit tensor-pipe ceiling of this GPU, measured now: nothing but MMA issue
+  from shared memory (aqtb200_mma_peak), a few milliseconds per launch."""
+  from aqt_b200 import _lib
+  stream = torch.cuda.current_stream().cuda_stream
+  status = torch.zeros(4, dtype=torch.int32, device='cuda')
+  is_int = 1 if args.kind == 'int8' else 0
+  _lib.check(lib.aqtb200_mma_peak(is_int, 2000, status.data_ptr(), stream),
+             'mma_peak')
+  torch.cuda.synchronize()
+  if int(status[0].item()):
+    return None
+  sampler = ClockSampler(torch.cuda.current_device(), period_ms=2)
+  sampler.start()
+  e0 = torch.cuda.Event(enable_timing=True)
+  e1 = torch.cuda.Event(enable_timing=True)
+  torch.cuda.synchronize()
+  sampler.mark_begin()
+  e0.record()
+  for _ in range(reps):
+    lib.aqtb200_mma_peak(is_int, mmas_per_sm, status.data_ptr(), stream)
+  e1.record()
+  torch.cuda.synchronize()
+  sampler.mark_end()
+  clocks = sampler.stop()
+  if int(status[0].item()):
+    return None
+  ms = e0.elapsed_time(e1) / reps
+  sms = ctypes_sm_count(lib)
+  launched = (mmas_per_sm + 15) // 16 * 16
+  ops = sms * launched * 2.0 * 128 * 256 * 32
+  return {'tops': ops / (ms * 1e-3) / 1e12, 'ms_per_launch': ms,
+          'sm_mhz': clocks['sm_mhz'], 'reasons': clocks['reasons'],
+          'kind': 'kind::i8' if is_int else 'kind::f8f6f4 (e4m3 x e4m3)'}
+
+
+def ctypes_sm_count(lib):
+  import ctypes as C
+  n = C.c_int(0)
+  lib.aqtb200_device_sm_count(C.byref(n))
+  return n.value
+
+
+def gemm_roofline(args, cfg, lhs, rhs, torch, engine, peaks):
   """Average duration of the forward GEMM launch alone (CUDA events on the
-  launching stream) against the measured tensor peak."""
+  launching stream) against the 8-bit tensor peak measured in the same run."""
   import ctypes as C
   from aqt_b200 import _lib
   lib = _lib.load()
@@ -485,153 +845,53 @@ def gemm_roofline(args, cfg, lhs, rhs, torch, engine):
   torch.cuda.synchronize()
   ms = e0.elapsed_time(e1) / reps
   achieved = 2.0 * m * n * k / (ms * 1e-3) / 1e12
-  peaks_path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
-  if os.path.exists(peaks_path):
-    with open(peaks_path) as f:
-      bf16 = json.load(f)['bf16_tflops']
-    src = 'of measured: 2 x bf16_tflops (burst) from MEASURED_PEAKS.json'
+  peak2 = 2.0 * peaks['bf16']
+  measured = None
+  try:
+    measured = mma_peak(args, torch, lib)
+  except Exception as e:  # pylint: disable=broad-except
+    print(f'mma peak measurement failed: {e}', file=sys.stderr)
+  if measured is not None:
+    peak = measured['tops']
+    src = ('measured in this run: tcgen05.mma issue only, operands in shared '
+           f"memory, {measured['kind']}, {measured['ms_per_launch']:.2f} ms per "
+           f"launch at {measured['sm_mhz']} MHz")
   else:
-    bf16 = 1590.0
-    src = 'of fallback: 2 x 1.59 PFLOP/s bf16'
-  peak = 2.0 * bf16
-  # DRAM bytes (read + write) of one launch of this kernel at this shape, from
-  # the ncu capture summarised in profiles/gemm_tcgen05_wide_fp8_8192.md; it
-  # is not re-measured here (nothing is timed under a profiler).
+    peak, src = peak2, '2 x bf16_tflops (burst), ' + peaks['src']
+  # DRAM bytes (read + write) of one launch of this kernel at this shape come
+  # from an ncu capture of the same kernel (profiles/), not from this run:
+  # nothing here is timed under a profiler.
   traffic = 446.0e6 if (m, n, k) == (8192, 8192, 8192) else None
   return {'bound': 'tensor',
           'kernel': 'gemm_tcgen05_wide_kernel (forward GEMM, 256x512 CTA-pair tiles)',
           'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s',
-          'frac': achieved / peak, 'traffic': traffic,
-          'algorithmic_bytes': float(m * k + n * k + 2 * m * n), 'ms_per_launch': ms,
-          'peak_source': src + '; 8-bit operands run at twice the bf16 rate'}
+          'frac': achieved / peak, 'peak_source': src,
+          'peak_2x_bf16': peak2, 'frac_2x_bf16': achieved / peak2,
+          'peak_2x_bf16_source': '2 x bf16_tflops (burst), ' + peaks['src'],
+          'mma_peak': measured,
+          'traffic': traffic, 'traffic_source': 'from profile (ncu, same kernel and shape)',
+          'algorithmic_bytes': float(m * k + n * k + 2 * m * n), 'ms_per_launch': ms}
 
 
-def run_extra_workload(args, lines):
-  """Single-GPU timing of BASELINE configs 1, 3 and 4 (device-resident)."""
-  import numpy as np
+def run_single_workload(args, lines):
+  """--workload other than c2: that configuration alone, 1 GPU."""
   import torch
   from aqt_b200 import _lib
   from aqt_b200 import engine
-  from aqt_b200.v2 import aqt_dot_general as adg
-  from aqt_b200.v2 import config
-  from aqt_b200.v2 import stochastic_rounding as sr
-  from aqt_b200.v2 import utils
-  from aqt_b200.v2.flax import aqt_flax
   torch.cuda.set_device(0)
   dev = torch.device('cuda', 0)
   lib = _lib.load()
   engine.set_gemm_impl(args.gemm)
-  gen = torch.Generator(device=dev)
-  gen.manual_seed(0)
-  rn = lambda shape, std, dt: (torch.randn(shape, device=dev, generator=gen)
-                               * std).to(dt)
-  extra = {}
-  if args.workload == 'c1':
-    lhs = rn((1024, 4096), 1.0, torch.float32)
-    rhs = rn((4096, 4096), 1.0 / 64, torch.float32)
-    g = rn((1024, 4096), 1.0, torch.float32)
-    cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
-                                 use_stochastic_rounding=False)
-    ops = 3 * 2 * 1024 * 4096 * 4096
-    min_bytes = 201e6
-    name = ('config 1: int8 [1024,4096]x[4096,4096] f32 in/out, per-channel '
-            'absmax, RNE, fwd+dlhs+drhs')
-
-    def step():
-      out, bp = cfg.vjp(lhs, rhs, DIMS)
-      return out, bp(g)
-  elif args.workload == 'c3':
-    b, t, h, d = 8, 2048, 32, 128
-    q = rn((b, t, h, d), 1.0, torch.bfloat16)
-    k = rn((b, t, h, d), 1.0, torch.bfloat16)
-    g = rn((b, h, t, t), 1.0, torch.bfloat16)
-    cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
-                                 use_stochastic_rounding=True)
-    noise = {}
-
-    def noise_fn(shape, key):
-      kk = (tuple(shape), int(key[0]), int(key[1]))
-      if kk not in noise:
-        noise[kk] = torch.rand(shape, device=dev, generator=gen) - 0.5
-      return noise[kk]
-
-    for raw in (cfg.dlhs, cfg.drhs):
-      raw.dg_quantizer.lhs.numerics.noise_fn = noise_fn
-      raw.dg_quantizer.rhs.numerics.noise_fn = noise_fn
-    cfg = config.set_context(cfg, key=sr.PRNGKey(1), train_step=None)
-    dims = (((3,), (3,)), ((0, 2), (0, 2)))
-    ops = 3 * 2 * b * h * t * t * d
-    min_bytes = 5.1e9
-    name = ("config 3: int8 einsum 'bthd,bshd->bhts' B8 H32 T=S=2048 D128, "
-            'bf16, per-token scales, fwd + both gradients, stochastic '
-            'rounding from 4 given f32 noise tensors (2 x 4.29 GB + 2 x 0.27 GB '
-            'read on top of the minimum bytes)')
-
-    def step():
-      out, bp = cfg.vjp(q, k, dims)
-      return out, bp(g)
-  else:
-    m, kk, n = args.m, 8192, 28672
-    x = rn((m, kk), 1.0, torch.bfloat16)
-    w = rn((kk, n), kk ** -0.5, torch.bfloat16)
-    cfg = adg.dot_general_make(lhs_bits=8, rhs_bits=4)
-    cfg.fwd.dg_quantizer.rhs.numerics.dtype = utils.int8
-    conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
-    conv(x, w, DIMS)
-    serve = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE)
-    serve.rhs_qtensor = conv.rhs_qtensor
-    del conv
-    wz = torch.empty(0, device=dev)
-    dummy_w = w  # the float weights are not read in SERVE mode
-    ops = 2 * m * kk * n
-    min_bytes = kk * n + m * kk * 2 + m * n * 2 + 2 * n + 2 * m
-    name = (f'config 4: serving GEMM M={m} K=8192 N=28672, int8 activations '
-            'per token x int4-in-int8 frozen weights per channel, bf16 out')
-    del wz
-
-    rhs_qt = serve.rhs_qtensor
-
-    def step():
-      # dg_core is what AqtDotGeneral calls after copying its config; calling
-      # it directly keeps the per-call deepcopy out of a serving loop.
-      return cfg.dg_core(x, dummy_w, None, rhs_qt, DIMS)[0]
-  for _ in range(max(args.warmup, 3)):
-    step()
-  torch.cuda.synchronize()
-  engine.check_status()
-  if args.graph:
-    eager_step = step
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
-      keep = eager_step()
-    step = graph.replay
-    for _ in range(3):
-      step()
-    torch.cuda.synchronize()
-  l0 = lib.aqtb200_kernel_launch_count()
-  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  sampler = ClockSampler(0)
-  sampler.start()
-  torch.cuda.synchronize()
-  sampler.mark_begin()
-  e0.record()
-  for _ in range(args.steps):
-    step()
-  e1.record()
-  torch.cuda.synchronize()
-  sampler.mark_end()
-  clocks = sampler.stop()
-  engine.check_status()
-  ms = e0.elapsed_time(e1) / args.steps
+  peaks = measured_peaks()
+  rec = time_workload(args.workload, args, torch, dev, lib, engine, peaks)
   lines.append(json.dumps({
-      'metric': METRIC, 'value': ops / (ms * 1e-3) / 1e12, 'unit': UNIT,
-      'n_gpus': 1, 'steps': args.steps, 'warmup': max(args.warmup, 3),
-      'ms_per_step': ms, 'higher_is_better': True, 'scaling': 'weak',
-      'vs_baseline': None, 'dtype': 's8->s32', 'data': 'synthetic',
-      'config': {'workload': name, 'cuda_graph': bool(args.graph)},
-      'min_bytes_gbs': min_bytes / (ms * 1e-3) / 1e9,
-      'clocks': clocks,
-      'gpu_launches': int(lib.aqtb200_kernel_launch_count() - l0),
+      'metric': METRIC, 'value': rec['tops'], 'unit': UNIT,
+      'n_gpus': 1, 'steps': args.steps, 'warmup': 3,
+      'ms_per_step': rec['ms_per_step'], 'higher_is_better': True,
+      'scaling': 'weak', 'vs_baseline': None, 'dtype': 's8->s32',
+      'data': 'synthetic', 'config': {'workload': rec['workload']},
+      'detail': rec,
+      'gpu_launches': int(rec['launches_per_step'] * args.steps),
   }))
 
 
@@ -645,8 +905,11 @@ def main():
   try:
     if args.impl == 'reference':
       run_reference_arm(args, lines)
+    elif args.workload == 'stack':
+      from aqt_b200 import layer_stack
+      layer_stack.bench_main(args, lines)
     elif args.workload != 'c2':
-      run_extra_workload(args, lines)
+      run_single_workload(args, lines)
     else:
       run_ours(args, lines)
   finally:

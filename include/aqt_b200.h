@@ -364,6 +364,18 @@ int aqtb200_set_gemm_impl(int impl);
  * collective's kernel (or the GEMM's last CTAs) wait for a free SM. */
 int aqtb200_set_gemm_sm_budget(int max_sms);
 
+/*
+ * aqtb200_mma_peak: measurement helper, no counterpart in the reference.
+ * Launches one CTA per SM that issues `mmas_per_sm` (rounded up to a multiple
+ * of 16) tcgen05 MMAs of 128 x 256 x 32 -- kind::i8 when is_int, else
+ * kind::f8f6f4 on e4m3 -- from operands that stay in shared memory, with no
+ * loads from global memory and no epilogue. Timed with events around it, it
+ * gives the 8-bit tensor-pipe ceiling of the device it runs on:
+ *   ops = SMs * launched MMAs per SM * 2 * 128 * 256 * 32.
+ * status as for aqtb200_gemm_dequant.
+ */
+int aqtb200_mma_peak(int32_t is_int, int64_t mmas_per_sm, int32_t* status, void* stream);
+
 #ifdef __cplusplus
 } /* extern "C" */
 #endif

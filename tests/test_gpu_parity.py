@@ -305,6 +305,80 @@ def test_wide_kernel_batched_and_transposed_output():
   assert torch.equal(a[2], b[2]) and torch.equal(a[0], b[0])
 
 
+@pytest.mark.parametrize('impl', ['cta1', 'cta2', 'wide', 'simt'])
+@pytest.mark.parametrize('shape', [(300, 2048, 1030), (256, 2048, 512),
+                                   (64, 256, 256)])
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+def test_amax_out_is_the_maximum_of_the_output(impl, shape, np_dtype):
+  """The optional amax_out of the GEMM epilogues: max |out| over what was
+  stored, ragged edges left out."""
+  m, k, n = shape
+  rng = np.random.default_rng(m + k)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = _cuda(util.rand_normal(rng, (m, k), 1.0, np_dtype))
+  rhs = _cuda(util.rand_normal(rng, (k, n), 1.0, np_dtype))
+  raw = aqt.dot_general_raw_make(8, 8)
+  amax = torch.zeros(1, dtype=torch.float32, device=DEV)
+  try:
+    engine.set_gemm_impl(impl)
+    out, _ = engine.dg_raw(raw, lhs, rhs, None, None, dims, amax_out=amax)
+  finally:
+    engine.set_gemm_impl('tcgen05')
+  _sync()
+  assert amax.item() == out.float().abs().max().item()
+
+
+@pytest.mark.parametrize('kind', ['int8', 'fp8'])
+@pytest.mark.parametrize('shape', [(300, 2048, 1032), (512, 4096, 512)])
+def test_wide_kernel_raw_accumulators_and_band_dequantization(kind, shape):
+  """The 256 x 512 kernel writing raw accumulators only (the form a sharded
+  contraction sums across ranks), then the dequantizing pass over them, whole
+  and by bands of rows."""
+  m, k, n = shape
+  rng = np.random.default_rng(n)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = _cuda(util.rand_normal(rng, (m, k), 1.0, orc.bfloat16))
+  rhs = _cuda(util.rand_normal(rng, (k, n), 1.0, orc.bfloat16))
+  raw = aqt.dot_general_raw_make(8, 8) if kind == 'int8' else (
+      aqt.dot_general_raw_make('e4m3', 'e4m3'))
+  try:
+    engine.set_gemm_impl('wide')
+    want, _ = engine.dg_raw(raw, lhs, rhs, None, None, dims)
+    d, _ = engine.dg_raw(raw, lhs, rhs, None, None, dims, defer_dequant=True)
+    engine.set_gemm_impl('simt')
+    _, _, acc_simt = engine.dg_raw(raw, lhs, rhs, None, None, dims,
+                                   want_acc=True)
+  finally:
+    engine.set_gemm_impl('tcgen05')
+  acc = d.acc.reshape(m, n).clone()
+  whole = d.finish().clone()
+  _sync()
+  if kind == 'int8':
+    assert torch.equal(acc, acc_simt.reshape(m, n))
+  else:  # the CUDA-core kernel sums in f64
+    bound = lhs.float().abs() @ rhs.float().abs()
+    assert ((acc - acc_simt.reshape(m, n)).abs() <= 1e-5 * bound + 1e-30).all()
+  assert torch.equal(whole, want)
+  # bands: rows [0, 128) and [128, m) from copies of the accumulator rows
+  d._out.zero_()
+  d.finish_rows(0, 128, acc[:128].contiguous())
+  d.finish_rows(128, m - 128, acc[128:].contiguous())
+  _sync()
+  assert torch.equal(d._out, want)
+
+
+def test_mma_peak_kernel_runs():
+  from aqt_b200 import _lib
+  lib = _lib.load()
+  status = torch.zeros(4, dtype=torch.int32, device=DEV)
+  for is_int in (1, 0):
+    rc = lib.aqtb200_mma_peak(is_int, 4096, status.data_ptr(),
+                              torch.cuda.current_stream().cuda_stream)
+    assert rc == 0, lib.aqtb200_last_error()
+  torch.cuda.synchronize()
+  assert status[0].item() == 0
+
+
 @pytest.mark.parametrize('fwd,bwd', [('e4m3', 'e5m2'), ('e4m3', 'e4m3'),
                                      ('e5m2', 'e5m2')])
 @pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
