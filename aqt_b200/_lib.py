@@ -70,6 +70,7 @@ class DgRawDesc(C.Structure):
       ('out_b0_stride', C.c_int64), ('out_b1_stride', C.c_int64),
       ('out_m_stride', C.c_int64), ('out_n_stride', C.c_int64),
       ('acc_out', C.c_void_p), ('amax_out', C.c_void_p),
+      ('scope_name', C.c_char_p),
   ]
 
 

@@ -4,6 +4,8 @@
 #include <cstdarg>
 #include <cstdio>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 
 namespace aqtb200 {
@@ -154,6 +156,14 @@ int aqtb200_dot_general_raw(const aqtb200_dg_raw_desc* d, void* workspace, size_
               AQTB200_EWORKSPACE, "workspace: need %zu bytes, 256-byte aligned (got %zu)", need,
               workspace_bytes);
   size_t lhs_ws = align256(aqtb200_quantize_workspace_bytes(&d->lhs, &d->lhs_spec));
+  // NVTX range around the pass (a no-op unless a profiler is attached)
+  struct Scope {
+    bool on;
+    explicit Scope(const char* name) : on(name != nullptr && name[0] != 0) {
+      if (on) nvtxRangePushA(name);
+    }
+    ~Scope() { if (on) nvtxRangePop(); }
+  } scope(d->scope_name);
   Side L{}, R{};
   int rc = prepare_side(d->lhs, d->lhs_prescale, d->lhs_noise, d->lhs_spec, d->lhs_scale_in,
                         d->lhs_is_quantized, d->lhs_q, d->lhs_scale, workspace, lhs_ws, st, &L);

@@ -168,6 +168,16 @@ class _Unmergeable(Exception):
   pass
 
 
+_SCOPES = {}
+
+
+def _scope_bytes(name: str) -> bytes:
+  """NUL-terminated name for a descriptor, kept alive for the process."""
+  if name not in _SCOPES:
+    _SCOPES[name] = name.encode()
+  return _SCOPES[name]
+
+
 def _view(ptr, code, b, rows, cols, bs, rs, cs) -> _lib.View:
   v = _lib.View()
   v.ptr = ptr
@@ -722,6 +732,8 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
   if amax_out is not None:
     assert amax_out.dtype == torch.float32 and amax_out.numel() == 1
     desc.amax_out = amax_out.data_ptr()
+  if getattr(raw, 'jax_scope_name', None):
+    desc.scope_name = _scope_bytes(raw.jax_scope_name)
 
   lib = _lib.load()
   ws_bytes = lib.aqtb200_dot_general_raw_workspace_bytes(C.byref(desc))

@@ -154,11 +154,15 @@ def _each_quantizer(cfg: DotGeneral):
 
 
 def set_constant_calibration(cfg: DotGeneral, bound: float = 1.0, bias=None):
-  _assert_default_quantizers(cfg)
-  cls = functools.partial(calibration.ConstantCalibration, bound=bound,
-                          bias=bias)
-  for quantizer in _each_quantizer(cfg):
-    quantizer.calibration = cls
+  """Reference: config.py:142-168. Constant bounds are not among the
+  calibrations the sm_100a kernels implement (AbsMax and delayed scaling
+  are), so the request is refused here, when the configuration is built,
+  rather than at the first dot."""
+  del cfg, bound, bias
+  raise NotImplementedError(
+      'ConstantCalibration (set_constant_calibration, use_dummy_static_bound) '
+      'is outside the sm_100a hot path; use AbsMaxCalibration or '
+      'DelayedScalingCalibration')
 
 
 def set_local_aqt(cfg: DotGeneral, fwd_local_aqt, dlhs_local_aqt,

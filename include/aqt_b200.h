@@ -319,6 +319,11 @@ typedef struct aqtb200_dg_raw_desc {
   int64_t out_b0_stride, out_b1_stride, out_m_stride, out_n_stride;
   void* acc_out;
   float* amax_out;  /* as aqtb200_gemm_desc.amax_out */
+  /* optional NUL-terminated name ("aqt_fwd", "aqt_dlhs", "aqt_drhs": the
+     reference's DotGeneralRaw.jax_scope_name, entered as jax.named_scope at
+     aqt_dot_general.py:767). The call's kernels are enclosed in an NVTX range
+     of that name, so a profiler timeline shows the three passes. */
+  const char* scope_name;
 } aqtb200_dg_raw_desc;
 
 size_t aqtb200_dot_general_raw_workspace_bytes(const aqtb200_dg_raw_desc* desc);
