@@ -118,6 +118,17 @@ SYMBOLS = {
     'aqtb200_kernel_launch_count': (C.c_int64, []),
     'aqtb200_set_gemm_impl': (C.c_int, [C.c_int]),
     'aqtb200_set_gemm_sm_budget': (C.c_int, [C.c_int]),
+    'aqtb200_delayed_scaling_scale': (C.c_int, [
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.POINTER(QuantSpec),
+        C.c_void_p, C.c_void_p]),
+    'aqtb200_delayed_scaling_push': (C.c_int, [
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p]),
+    'aqtb200_prescale_amax': (C.c_int, [
+        C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.c_int32, C.c_void_p,
+        C.c_void_p]),
+    'aqtb200_jax_noise': (C.c_int, [
+        C.c_uint32, C.c_uint32, C.c_int64, C.c_int32, C.c_int32, C.c_float,
+        C.c_void_p, C.c_void_p]),
     'aqtb200_mma_peak': (C.c_int, [C.c_int32, C.c_int64, C.c_void_p, C.c_void_p]),
 }
 

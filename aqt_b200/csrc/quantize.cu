@@ -1176,6 +1176,12 @@ __global__ void requant_amax_kernel(RequantAmaxParams R) {
   R.out[i] = requant_abs(a, s, R.t_dtype, R.s_dtype, R.kind, R.qdtype, R.clip_bound);
 }
 
+__global__ void prescale_amax_kernel(const uint32_t* amax, int64_t n, const void* pre, int pre_dtype,
+                                     int t_dtype, float* out) {
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = apply_pre_abs(__uint_as_float(amax[i]), load1(pre, pre_dtype, 0), t_dtype);
+}
+
 // ---------------------------------------------------------------------------
 // amax -> scale and rounded reciprocal (calibration.py:149-157,
 // aqt_tensor.py:151-153). All arithmetic in T, stored as S.
@@ -1211,6 +1217,81 @@ __global__ void finalize_scale_kernel(FinalizeParams F) {
   }
   if (F.sinv == nullptr) return;
   F.sinv[i] = recip_of_scale(s, F.s_dtype);
+}
+
+// ---------------------------------------------------------------------------
+// Delayed scaling (flax/delayed_scaling_calibration.py:28-124): the bound comes
+// from a history of earlier maxima, not from the tensor being quantized, so
+// the quantization of a step does not wait for a reduction over its operand.
+//   new_bound = max(history) if that is > 0 and finite, else the previous bound
+//   scale     = cast_S(new_bound / quant_bound [-> power of two])       (f32 math)
+//   history   = roll(history, -1) with element 0 replaced by max |x|
+struct DelayedParams {
+  float* history;
+  int64_t len;
+  float* bound;
+  int update_bound;
+  float quant_bound;
+  int po2, s_dtype;
+  void* scale_out;
+  const float* amax;
+};
+
+// one block; history lengths up to 4096
+__global__ void __launch_bounds__(1024) delayed_scale_kernel(DelayedParams D) {
+  __shared__ float red[32];
+  float m = -INFINITY;
+  bool nan = false;
+  for (int64_t i = threadIdx.x; i < D.len; i += blockDim.x) {
+    const float h = D.history[i];
+    nan |= h != h;
+    m = fmaxf(m, h);
+  }
+  // jnp.max propagates NaN
+  m = nan ? NAN : m;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float other = __shfl_xor_sync(0xffffffffu, m, o);
+    m = (m != m || other != other) ? NAN : fmaxf(m, other);
+  }
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float a = red[0];
+    const int nw = (blockDim.x + 31) >> 5;
+    for (int w = 1; w < nw; ++w) a = (a != a || red[w] != red[w]) ? NAN : fmaxf(a, red[w]);
+    const float prev = D.bound[0];
+    float nb = a > 0.0f ? a : prev;
+    nb = isfinite(a) ? nb : prev;
+    if (D.update_bound) D.bound[0] = nb;
+    float s = __fdiv_rn(nb, D.quant_bound);
+    if (D.po2) {
+      // calibration.ceil_to_po2 in f32: 1 / 2**floor(log2(1/s))
+      const float r = __fdiv_rn(1.f, s);
+      int e;
+      frexpf(r, &e);
+      s = __fdiv_rn(1.f, ldexpf(1.f, e - 1));
+    }
+    if (D.s_dtype == AQTB200_BF16) ((__nv_bfloat16*)D.scale_out)[0] = __float2bfloat16_rn(s);
+    else ((float*)D.scale_out)[0] = s;
+  }
+}
+
+__global__ void __launch_bounds__(1024) delayed_push_kernel(DelayedParams D) {
+  // every element is read before any is written: one block, values in registers
+  float v[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int64_t i = threadIdx.x + 1024 * k;
+    v[k] = i < D.len ? D.history[(i + 1) % D.len] : 0.f;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int64_t i = threadIdx.x + 1024 * k;
+    if (i < D.len) D.history[i] = i == 0 ? D.amax[0] : v[k];
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -1956,6 +2037,48 @@ int aqtb200_requant_amax(const float* amax, int64_t n, const void* prescale, int
   R.t_dtype = spec->compute_dtype; R.s_dtype = spec->scale_dtype; R.kind = spec->kind;
   R.qdtype = spec->qdtype; R.clip_bound = spec->clip_bound; R.out = amax_q_out; R.n = n;
   requant_amax_kernel<<<(int)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(R);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+int aqtb200_prescale_amax(const float* amax, int64_t n, const void* prescale, int32_t prescale_dtype,
+                          int32_t compute_dtype, float* out, void* stream) {
+  AQT_REQUIRE(amax != nullptr && prescale != nullptr && out != nullptr && n >= 0, AQTB200_EINVAL,
+              "null argument");
+  AQT_REQUIRE(is_float_dt(prescale_dtype) && is_float_dt(compute_dtype), AQTB200_EINVAL,
+              "prescale / compute dtype must be f32 or bf16");
+  if (n == 0) return 0;
+  prescale_amax_kernel<<<(int)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      (const uint32_t*)amax, n, prescale, prescale_dtype, compute_dtype, out);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+int aqtb200_delayed_scaling_scale(const float* history, int64_t len, float* bound,
+                                  int32_t update_bound, const aqtb200_quant_spec* spec,
+                                  void* scale_out, void* stream) {
+  AQT_REQUIRE(history != nullptr && bound != nullptr && spec != nullptr && scale_out != nullptr,
+              AQTB200_EINVAL, "null argument");
+  AQT_REQUIRE(len >= 1 && len <= 4096, AQTB200_EUNSUPPORTED,
+              "amax history length %lld: 1 ... 4096 elements", (long long)len);
+  AQT_REQUIRE(is_float_dt(spec->scale_dtype), AQTB200_EINVAL, "scale dtype must be f32 or bf16");
+  AQT_REQUIRE(spec->quant_bound > 0.f, AQTB200_EINVAL, "quant_bound must be positive");
+  DelayedParams D{};
+  D.history = const_cast<float*>(history); D.len = len; D.bound = bound;
+  D.update_bound = update_bound; D.quant_bound = spec->quant_bound; D.po2 = spec->po2_scale;
+  D.s_dtype = spec->scale_dtype; D.scale_out = scale_out;
+  delayed_scale_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(D);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+int aqtb200_delayed_scaling_push(float* history, int64_t len, const float* amax, void* stream) {
+  AQT_REQUIRE(history != nullptr && amax != nullptr, AQTB200_EINVAL, "null argument");
+  AQT_REQUIRE(len >= 1 && len <= 4096, AQTB200_EUNSUPPORTED,
+              "amax history length %lld: 1 ... 4096 elements", (long long)len);
+  DelayedParams D{};
+  D.history = history; D.len = len; D.amax = amax;
+  delayed_push_kernel<<<1, 1024, 0, (cudaStream_t)stream>>>(D);
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   return 0;
 }

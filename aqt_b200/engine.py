@@ -199,14 +199,29 @@ def _calibration_kwargs(quantizer):
   if isinstance(cal, functools.partial):
     kw = dict(cal.keywords)
     cal = cal.func
-  if cal is None or cal.__name__ != 'AbsMaxCalibration':
+  name = None if cal is None else cal.__name__
+  if name == 'DelayedScalingCalibration':
+    extra = set(kw) - {'dtype', 'po2_scale', 'amax_history_length', 'stats'}
+    if extra:
+      raise NotImplementedError(
+          f'DelayedScalingCalibration options {sorted(extra)}')
+    return kw
+  if name != 'AbsMaxCalibration':
     raise NotImplementedError(
         f'calibration {cal} is outside the sm_100a hot path '
-        '(AbsMaxCalibration only)')
+        '(AbsMaxCalibration and DelayedScalingCalibration)')
   extra = set(kw) - {'dtype', 'clipping_scale', 'po2_scale'}
   if extra:
     raise NotImplementedError(f'AbsMaxCalibration options {sorted(extra)}')
   return kw
+
+
+def _delayed(quantizer):
+  """The quantizer's DelayedScalingCalibration instance, or None."""
+  cal = getattr(quantizer, '_calibrator', None)
+  if type(cal).__name__ == 'DelayedScalingCalibration':
+    return cal
+  return None
 
 
 def _round_to_dtype(value: float, code: int) -> float:
@@ -254,7 +269,9 @@ def _make_spec(quantizer, compute_code: int, contraction_axes_ok: bool):
   spec.qdtype = qcode
   spec.quant_bound = qb
   spec.clip_bound = cb
-  spec.per_tensor = 1 if csa == 'per_tensor' else 0
+  # delayed scaling keeps one bound per tensor whatever the axes
+  # (flax/delayed_scaling_calibration.py:66-75)
+  spec.per_tensor = 1 if csa == 'per_tensor' or _delayed(quantizer) else 0
   spec.compute_dtype = compute_code
   spec.scale_dtype = compute_code if scale_dtype is None else _code(scale_dtype)
   if spec.scale_dtype not in _FLOAT_CODES:
@@ -521,6 +538,32 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
 
   lhs_qv, lhs_sin = split_qt(lhs_qt)
   rhs_qv, rhs_sin = split_qt(rhs_qt)
+
+  # Delayed scaling: the scale comes from the calibrator's history; max |x|
+  # (after the cotangent's prescale, which must then be one value) goes into
+  # the history beside the quantization, not before it.
+  def delayed_scale(quantizer, x, pre, t_code):
+    cal = _delayed(quantizer)
+    if cal is None:
+      return None
+
+    def amax_fn():
+      amax = absmax_raw(x)
+      if pre is not None:
+        if pre.numel() != 1:
+          raise NotImplementedError(
+              'delayed scaling of a cotangent that carries a per-channel '
+              'forward scale; set use_fwd_quant=False or per-tensor scales')
+        amax = prescale_amax(amax, pre, t_code)
+      return amax
+
+    return cal.device_scale(x, quantizer.numerics, quantizer.context,
+                            amax_fn=amax_fn, compute_dtype=_CODE_TORCH[t_code])
+
+  if lhs_qv is None and lhs_sin is None:
+    lhs_sin = delayed_scale(q.lhs, lhs, prescale, t_code_l)
+  if rhs_qv is None and rhs_sin is None:
+    rhs_sin = delayed_scale(q.rhs, rhs_float, None, t_code_r)
 
   if _noise is not None:  # drawn by the caller in its own axis order
     noise_l, noise_r = _noise
@@ -1025,6 +1068,18 @@ def absmax_raw(x):
   return out
 
 
+def prescale_amax(amax, prescale, compute_code: int):
+  """|round_T(amax * round_T(prescale))|: the maximum of a tensor after one
+  prescale value has been folded into it (rounding is monotone)."""
+  assert prescale.numel() == 1
+  out = _empty(1, torch.float32, amax.device)
+  rc = _call(_lib.load().aqtb200_prescale_amax, amax.data_ptr(), 1,
+             prescale.data_ptr(), _code(prescale.dtype), compute_code,
+             out.data_ptr(), _stream())
+  _lib.check(rc, 'aqtb200_prescale_amax')
+  return out
+
+
 def scale_from_amax(amax, numerics, compute_dtype, scale_dtype=None,
                     clipping_scale=None, po2_scale=False, prescale=None,
                     ndim=2):
@@ -1052,7 +1107,7 @@ def _per_tensor_absmax(quantizer):
   """Calibration keywords if the quantizer is per-tensor AbsMax, else None."""
   if type(quantizer.numerics).__name__ == 'NoNumerics':
     return None
-  if quantizer.calib_shared_axes != 'per_tensor':
+  if quantizer.calib_shared_axes != 'per_tensor' or _delayed(quantizer):
     return None
   kw = _calibration_kwargs(quantizer)
   if getattr(quantizer.numerics, 'noise_fn', None):
@@ -1110,7 +1165,7 @@ def _pair_spec(quantizer):
   """The per-tensor fp8 or int8 / bf16 spec of `quantizer`, or None if it is anything else."""
   if type(quantizer.numerics).__name__ not in ('Fp8Numerics', 'IntSymmetric'):
     return None
-  if quantizer.calib_shared_axes != 'per_tensor':
+  if quantizer.calib_shared_axes != 'per_tensor' or _delayed(quantizer):
     return None
   if getattr(quantizer.numerics, 'noise_fn', None) or getattr(
       quantizer.numerics, 'stochastic_rounding', False):

@@ -370,6 +370,46 @@ int aqtb200_set_gemm_impl(int impl);
 int aqtb200_set_gemm_sm_budget(int max_sms);
 
 /*
+ * Delayed scaling (flax/delayed_scaling_calibration.py:28-124, per-tensor): the
+ * scale of a step comes from the maxima of earlier steps, so quantization does
+ * not wait for a reduction over its own operand.
+ *   aqtb200_delayed_scaling_scale: get_bound() + get_scale_and_bias_and_sparsity():
+ *     new_bound = max(history) when that is > 0 and finite, else bound[0]
+ *     (compute_bound, :107-111); bound[0] = new_bound when update_bound (TRAIN /
+ *     CALIBRATE modes, :93-95); scale_out[0] = cast(new_bound / quant_bound),
+ *     rounded to a power of two first when spec->po2_scale. f32 arithmetic, as
+ *     the reference's f32 state arrays give.
+ *   aqtb200_delayed_scaling_push: compute_history (:113-118):
+ *     history = roll(history, -1), then history[0] = amax[0] (the operand's
+ *     max |x|, e.g. from aqtb200_absmax_raw or a producer's amax_out).
+ * history: f32[len], 1 <= len <= 4096; bound, amax: f32[1]. Call _scale before
+ * _push within a step (the new bound reads the old history).
+ */
+int aqtb200_delayed_scaling_scale(const float* history, int64_t len, float* bound,
+                                  int32_t update_bound, const aqtb200_quant_spec* spec,
+                                  void* scale_out, void* stream);
+int aqtb200_delayed_scaling_push(float* history, int64_t len, const float* amax, void* stream);
+/* out[i] = |round_T(amax[i] * round_T(prescale[0]))|: the maximum of a tensor
+ * once ONE prescale value has been folded into it, as the cotangent's is by
+ * _maybe_use_fwd_quant (aqt_dot_general.py:714-720); T = compute_dtype. */
+int aqtb200_prescale_amax(const float* amax, int64_t n, const void* prescale, int32_t prescale_dtype,
+                          int32_t compute_dtype, float* out, void* stream);
+
+/*
+ * aqtb200_jax_noise: the stochastic-rounding noise tensor, generated on the
+ * device. Replaces stochastic_rounding.JaxUniform (stochastic_rounding.py:
+ * 35-46: jax.random.uniform(key, shape) - 0.5; kind 0 with shift 0.5) and
+ * RandomCenteredUniform (:49-78: 16 random bits in an f32 mantissa, minus
+ * 1.5 - 2^-17; kind 1, shift ignored). (key0, key1) is the raw threefry key;
+ * `partitionable` picks jax's counter layout (jax_threefry_partitionable);
+ * out receives n floats in row-major order of the noise tensor's shape.
+ * jax's generator is restated from its published algorithm; it could not be
+ * compared with a jax installation.
+ */
+int aqtb200_jax_noise(uint32_t key0, uint32_t key1, int64_t n, int32_t kind,
+                      int32_t partitionable, float shift, float* out, void* stream);
+
+/*
  * aqtb200_mma_peak: measurement helper, no counterpart in the reference.
  * Launches one CTA per SM that issues `mmas_per_sm` (rounded up to a multiple
  * of 16) tcgen05 MMAs of 128 x 256 x 32 -- kind::i8 when is_int, else

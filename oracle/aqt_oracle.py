@@ -33,6 +33,7 @@ from __future__ import annotations
 import dataclasses
 import functools
 from typing import Any, Sequence
+import weakref
 
 import ml_dtypes
 import numpy as np
@@ -278,9 +279,52 @@ def _calibration_kwargs(quantizer):
   if isinstance(cal, functools.partial):
     kw = dict(cal.keywords)
     cal = cal.func
-  assert cal.__name__ == 'AbsMaxCalibration', (
-      f'oracle restates AbsMaxCalibration only, got {cal}')
+  assert cal.__name__ in ('AbsMaxCalibration', 'DelayedScalingCalibration'), (
+      f'oracle restates AbsMax and delayed-scaling calibration, got {cal}')
   return kw
+
+
+# Delayed scaling, flax/delayed_scaling_calibration.py:28-124. The oracle keeps
+# its OWN copy of every calibrator's state (amax_history f32[L], bound f32[1]),
+# keyed by the calibrator's state holder, so that it can be driven with the
+# same configuration object as the device path without sharing anything.
+_DELAYED_STATE = weakref.WeakKeyDictionary()
+
+
+def delayed_state(calibrator):
+  key = calibrator.stats
+  if key not in _DELAYED_STATE:
+    _DELAYED_STATE[key] = [
+        np.zeros(calibrator.amax_history_length, np.float32),
+        np.zeros(1, np.float32)]
+  return _DELAYED_STATE[key]
+
+
+def delayed_scaling_scale(calibrator, x: np.ndarray, numerics_, context,
+                          scale_dtype=None) -> np.ndarray:
+  """get_bound + get_scale_and_bias_and_sparsity (:57-105), one call."""
+  state = delayed_state(calibrator)
+  history, prev_bound = state
+  quant_mode = context.quant_mode.name if context is not None and getattr(
+      context, 'quant_mode', None) is not None else 'SERVE'
+  amax = np.max(history, axis=0)  # :82
+  # compute_bound (:107-111)
+  new_bound = np.where(amax > 0.0, amax, prev_bound)
+  new_bound = np.where(np.isfinite(amax), new_bound, prev_bound).astype(
+      np.float32)
+  # compute_history (:113-118)
+  update = np.max(np.abs(_f32(x))).astype(np.float32) if x.size else (
+      np.float32(0))
+  new_history = np.roll(history, -1)
+  new_history[0] = update
+  if quant_mode in ('TRAIN', 'CALIBRATE'):  # :93-95
+    state[0], state[1] = new_history, new_bound.reshape(1)
+  dtype = np_dtype(scale_dtype) or x.dtype
+  bound = new_bound.reshape((1,) * x.ndim)
+  scale = div(bound, quant_bound_of(numerics_, x.dtype))  # f32 (:103)
+  if calibrator.po2_scale:
+    scale = ceil_to_po2(scale)
+  return scale.astype(dtype)
 
 
 def quantizer_calibrate(quantizer, x: np.ndarray, calibration_axes) -> OQTensor:
@@ -293,6 +337,12 @@ def quantizer_calibrate(quantizer, x: np.ndarray, calibration_axes) -> OQTensor:
     shared = quantizer.calib_shared_axes or calibration_axes
   assert shared is not None
   kw = _calibration_kwargs(quantizer)
+  cal = getattr(quantizer, '_calibrator', None)
+  if type(cal).__name__ == 'DelayedScalingCalibration':
+    scale = delayed_scaling_scale(cal, x, quantizer.numerics,
+                                  quantizer.context,
+                                  kw.get('dtype', quantizer.scale_dtype))
+    return OQTensor(qvalue=None, scale=[scale], dequant_dtype=x.dtype)
   scale = absmax_scale(
       x, shared, quantizer.numerics,
       scale_dtype=kw.get('dtype', quantizer.scale_dtype),

@@ -176,6 +176,40 @@ class FakeLib:
     _strided(scale_out, spec.scale_dtype, [n], [1], True)[...] = scale.astype(S)
     return 0
 
+  def aqtb200_prescale_amax(self, amax, n, pre, pre_dtype, t_dtype, out,
+                            stream):
+    T = _NP[t_dtype]
+    a = np.array(_strided(amax, _lib.F32, [n], [1])).astype(T)
+    p = np.array(_strided(pre, pre_dtype, [1], [1])).astype(np.float32).astype(T)
+    _strided(out, _lib.F32, [n], [1], True)[...] = np.abs(
+        orc.mul(a, p)).astype(np.float32)
+    return 0
+
+  def aqtb200_delayed_scaling_scale(self, history, length, bound, update,
+                                    spec, scale_out, stream):
+    spec = _deref(spec, _lib.QuantSpec)
+    h = _strided(history, _lib.F32, [length], [1])
+    b = _strided(bound, _lib.F32, [1], [1], True)
+    amax = np.max(np.array(h))
+    nb = amax if amax > 0 else b[0]
+    nb = np.float32(nb if np.isfinite(amax) else b[0])
+    if update:
+      b[0] = nb
+    with np.errstate(divide='ignore'):
+      s = np.asarray(nb, np.float32) / np.float32(spec.quant_bound)
+      if spec.po2_scale:
+        s = orc.ceil_to_po2(np.asarray(s, np.float32))
+    _strided(scale_out, spec.scale_dtype, [1], [1], True)[...] = np.asarray(
+        s, np.float32).astype(_NP[spec.scale_dtype])
+    return 0
+
+  def aqtb200_delayed_scaling_push(self, history, length, amax, stream):
+    h = _strided(history, _lib.F32, [length], [1], True)
+    new = np.roll(np.array(h), -1)
+    new[0] = _strided(amax, _lib.F32, [1], [1])[0]
+    h[...] = new
+    return 0
+
   def aqtb200_requant_amax(self, amax, n, pre, pre_dtype, spec, scale, out,
                            stream):
     spec = _deref(spec, _lib.QuantSpec)
