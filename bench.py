@@ -481,9 +481,12 @@ def build_workload(name, args, torch, dev):
     w = rn((kk, n), kk ** -0.5, torch.bfloat16)
     cfg = adg.dot_general_make(lhs_bits=8, rhs_bits=4)
     cfg.fwd.dg_quantizer.rhs.numerics.dtype = utils.int8
-    conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
+    conv = aqt_flax.AqtDotGeneral(
+        cfg, rhs_quant_mode=utils.QuantMode.CONVERT,
+        rhs_freeze_mode=aqt_flax.FreezerMode.CALIBRATION_AND_VALUE,
+        use_legacy_freezer=False)
     conv(x, w, DIMS)
-    rhs_qt = conv.rhs_qtensor
+    rhs_qt = conv.variables['aqt']['qrhs']['frozen']
     del conv
 
     def step():

@@ -1,6 +1,7 @@
 """AqtDotGeneral / AqtEinsum wrappers and the autograd bridge (host logic)."""
 
 import numpy as np
+import pytest
 import torch
 
 from aqt_b200.v2 import aqt_dot_general as aqt
@@ -65,16 +66,67 @@ def test_convert_then_serve_is_bit_identical(monkeypatch):
   w = util.to_torch(util.rand_normal(rng, (32, 16), 0.2, np.float32))
   cfg = config.fully_quantized(use_stochastic_rounding=False)
   train = aqt_flax.AqtDotGeneral(cfg)(x, w, dims)
-  conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
-  conv(x, w, dims)
-  frozen = conv.rhs_qtensor
-  assert frozen is not None and frozen.qvalue.dtype == torch.int8
-  assert tuple(frozen.qvalue.shape) == (32, 16)
-  assert tuple(frozen.scale[0].shape) == (1, 16)
-  serve = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE)
-  serve.rhs_qtensor = frozen
-  got = serve(x, torch.zeros_like(w), dims)  # the float weights are unused
+  both = aqt_flax.FreezerMode.CALIBRATION_AND_VALUE
+  with pytest.raises(ValueError, match='Freezer mode NONE'):
+    aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)(
+        x, w, dims)
+  for legacy in (True, False):
+    conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT,
+                                  rhs_freeze_mode=both,
+                                  use_legacy_freezer=legacy)
+    conv(x, w, dims)
+    stored = conv.variables['aqt']['qrhs']
+    if legacy:  # aqt_flax.py:149-232: 'value' and 'scale' (= scale_t)
+      assert set(stored) == {'value', 'scale'}
+      assert stored['value'].dtype == torch.int8
+      assert tuple(stored['value'].shape) == (32, 16)
+      assert tuple(stored['scale'].shape) == (1, 16)  # output layout [M, N]
+    else:  # flax/freezer.py: one 'frozen' QTensor
+      frozen = stored['frozen']
+      assert frozen.qvalue.dtype == torch.int8
+      assert tuple(frozen.scale[0].shape) == (1, 16)
+    serve = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE,
+                                   rhs_freeze_mode=both,
+                                   use_legacy_freezer=legacy,
+                                   variables=conv.variables)
+    got = serve(x, torch.zeros_like(w), dims)  # the float weights are unused
+    np.testing.assert_array_equal(util.to_numpy(got), util.to_numpy(train))
+  # handing the frozen operand over directly, freezers bypassed
+  direct = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE,
+                                  rhs_apply_quant_mode=False,
+                                  rhs_qtensor=frozen)
+  got = direct(x, torch.zeros_like(w), dims)
   np.testing.assert_array_equal(util.to_numpy(got), util.to_numpy(train))
+
+
+def test_calibration_only_freezing_keeps_static_activation_scales(monkeypatch):
+  # FreezerMode.CALIBRATION stores the scale without the values: serving then
+  # quantizes new activations with the frozen (static) scale.
+  fake_lib.install(monkeypatch)
+  rng = np.random.default_rng(8)
+  dims = (((1,), (0,)), ((), ()))
+  x = util.to_torch(util.rand_normal(rng, (8, 32), 1.0, np.float32))
+  w = util.to_torch(util.rand_normal(rng, (32, 16), 0.2, np.float32))
+  cfg = config.fully_quantized(use_stochastic_rounding=False)
+  cfg.fwd.dg_quantizer.lhs.calib_shared_axes = 'per_tensor'
+  conv = aqt_flax.AqtDotGeneral(
+      cfg, lhs_quant_mode=utils.QuantMode.CONVERT,
+      lhs_freeze_mode=aqt_flax.FreezerMode.CALIBRATION,
+      use_legacy_freezer=False)
+  conv(x, w, dims)
+  frozen = conv.variables['aqt']['qlhs']['frozen']
+  assert frozen.qvalue is None and frozen.scale[0].numel() == 1
+  serve = aqt_flax.AqtDotGeneral(
+      cfg, lhs_quant_mode=utils.QuantMode.SERVE,
+      lhs_freeze_mode=aqt_flax.FreezerMode.CALIBRATION,
+      use_legacy_freezer=False, variables=conv.variables)
+  x2 = x * 0.5  # its own maximum would give another scale
+  got = serve(x2, w, dims)
+  lhs_qt = orc.OQTensor(qvalue=None, scale=[util.to_numpy(frozen.scale[0])],
+                        dequant_dtype=orc.float32)
+  want, _ = orc.dg_fwd(cfg, util.to_numpy(x2), util.to_numpy(w), dims,
+                       lhs_qt=lhs_qt)
+  np.testing.assert_array_equal(util.to_numpy(got), want)
 
 
 def test_aqt_einsum_convert_then_serve(monkeypatch):
@@ -87,14 +139,17 @@ def test_aqt_einsum_convert_then_serve(monkeypatch):
   cfg = config.fully_quantized(use_stochastic_rounding=False)
   for eqn in ('ab,bc->ac', 'ab,bc->ca'):
     train = aqt_flax.AqtEinsum(cfg)(eqn, x, w)
-    conv = aqt_flax.AqtEinsum(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
+    both = aqt_flax.FreezerMode.CALIBRATION_AND_VALUE
+    conv = aqt_flax.AqtEinsum(cfg, rhs_quant_mode=utils.QuantMode.CONVERT,
+                              rhs_freeze_mode=both)
     conv(eqn, x, w)
-    frozen = conv.rhs_qtensor
-    assert frozen is not None and frozen.qvalue.dtype == torch.int8
-    assert tuple(frozen.qvalue.shape) == (32, 16), eqn
-    assert conv.lhs_qtensor is None
-    serve = aqt_flax.AqtEinsum(cfg, rhs_quant_mode=utils.QuantMode.SERVE)
-    serve.rhs_qtensor = frozen
+    # "rhs" is the SECOND einsum argument whatever the operand order
+    stored = conv.variables['aqt']['qrhs']
+    assert stored['value'].dtype == torch.int8
+    assert tuple(stored['value'].shape) == (32, 16), eqn
+    assert 'qlhs' not in conv.variables['aqt']
+    serve = aqt_flax.AqtEinsum(cfg, rhs_quant_mode=utils.QuantMode.SERVE,
+                               rhs_freeze_mode=both, variables=conv.variables)
     for _ in range(2):
       got = serve(eqn, x, torch.zeros_like(w))
       np.testing.assert_array_equal(util.to_numpy(got), util.to_numpy(train))

@@ -469,19 +469,32 @@ def test_serving_int4_weights_in_int8_container(m):
   w = util.rand_normal(rng, (k, n), 1.0 / 32, orc.bfloat16)
   cfg = aqt.dot_general_make(lhs_bits=8, rhs_bits=4)
   cfg.fwd.dg_quantizer.rhs.numerics.dtype = utils.int8
-  conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
+  both = aqt_flax.FreezerMode.CALIBRATION_AND_VALUE
+  conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT,
+                                rhs_freeze_mode=both, use_legacy_freezer=False)
   train_out = conv(_cuda(x), _cuda(w), dims)
-  frozen = conv.rhs_qtensor
+  frozen = conv.variables['aqt']['qrhs']['frozen']
   _sync()
   want, res = orc.dg_fwd(cfg, x, w, dims)
   _exact(frozen.qvalue, res.rhs.qx.qvalue, 'frozen weights')
   assert int(frozen.qvalue.abs().max()) <= 7
   _exact(train_out, want, 'train-mode out')
-  serve = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE)
-  serve.rhs_qtensor = frozen
+  serve = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE,
+                                 rhs_freeze_mode=both, use_legacy_freezer=False,
+                                 variables=conv.variables)
   got = serve(_cuda(x), torch.zeros_like(_cuda(w)), dims)
   _sync()
   _exact(got, want, 'served out')
+  # the legacy two-variable layout ('value', 'scale' in the output's layout)
+  conv2 = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT,
+                                 rhs_freeze_mode=both)
+  conv2(_cuda(x), _cuda(w), dims)
+  serve2 = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE,
+                                  rhs_freeze_mode=both,
+                                  variables=conv2.variables)
+  got2 = serve2(_cuda(x), torch.zeros_like(_cuda(w)), dims)
+  _sync()
+  _exact(got2, want, 'served out (legacy freezer)')
 
 
 def test_piecewise_quantizer_api():

@@ -256,16 +256,19 @@ def serving_weights():
   cfg = aqt.dot_general_make(lhs_bits=8, rhs_bits=4)
   cfg.fwd.dg_quantizer.rhs.numerics.dtype = utils.int8
   x0 = util.rand_normal(rng, (16, kk), 1.0, orc.bfloat16)
-  conv = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.CONVERT)
+  conv = aqt_flax.AqtDotGeneral(
+      cfg, rhs_quant_mode=utils.QuantMode.CONVERT,
+      rhs_freeze_mode=aqt_flax.FreezerMode.CALIBRATION_AND_VALUE,
+      use_legacy_freezer=False)
   conv(_cuda(x0), _cuda(w), DIMS)
   _sync()
-  frozen = conv.rhs_qtensor
+  frozen = conv.variables['aqt']['qrhs']['frozen']
   want = _oracle_quant(cfg.fwd.dg_quantizer.rhs, w, [0])
-  return cfg, frozen, want, (kk, n)
+  return cfg, (frozen, conv.variables), want, (kk, n)
 
 
 def test_config4_frozen_weights_full_size(serving_weights):
-  _, frozen, want, _ = serving_weights
+  _, (frozen, _), want, _ = serving_weights
   _exact(frozen.scale[0], want.scale[0], 'weight scales')
   _exact(frozen.qvalue, want.qvalue, 'frozen int4-in-int8 weights')
   assert int(frozen.qvalue.abs().max()) <= 7
@@ -275,11 +278,13 @@ def test_config4_frozen_weights_full_size(serving_weights):
 def test_config4_serving_full_size(serving_weights, m):
   """K = 8192, N = 28672; all of N for M = 16 and 256, a 512-column band of
   the result for M = 4096 (the whole GEMM still runs on the device)."""
-  cfg, frozen, want_w, (kk, n) = serving_weights
+  cfg, (_, variables), want_w, (kk, n) = serving_weights
   rng = np.random.default_rng(m)
   x = util.rand_normal(rng, (m, kk), 1.0, orc.bfloat16)
-  serve = aqt_flax.AqtDotGeneral(cfg, rhs_quant_mode=utils.QuantMode.SERVE)
-  serve.rhs_qtensor = frozen
+  serve = aqt_flax.AqtDotGeneral(
+      cfg, rhs_quant_mode=utils.QuantMode.SERVE,
+      rhs_freeze_mode=aqt_flax.FreezerMode.CALIBRATION_AND_VALUE,
+      use_legacy_freezer=False, variables=variables)
   dummy_w = torch.empty((kk, n), dtype=torch.bfloat16, device=DEV)
   got = serve(_cuda(x), dummy_w, DIMS)
   _sync()
