@@ -74,6 +74,16 @@ class DgRawDesc(C.Structure):
   ]
 
 
+class DualDesc(C.Structure):
+  _fields_ = [
+      ('x', View), ('spec_t', QuantSpec), ('spec_s', QuantSpec),
+      ('prescale_t', View), ('prescale_s', View),
+      ('noise_t', View), ('noise_s', View),
+      ('q_t', C.c_void_p), ('scale_t', C.c_void_p),
+      ('q_s', C.c_void_p), ('scale_s', C.c_void_p),
+  ]
+
+
 # name -> (restype, argtypes); every symbol include/aqt_b200.h declares.
 SYMBOLS = {
     'aqtb200_quantize': (C.c_int, [
@@ -98,6 +108,10 @@ SYMBOLS = {
         C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
         C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
         C.c_int32, C.c_void_p, C.c_void_p]),
+    'aqtb200_quantize_dual_workspace_bytes': (C.c_size_t, [
+        C.POINTER(DualDesc)]),
+    'aqtb200_quantize_dual': (C.c_int, [
+        C.POINTER(DualDesc), C.c_void_p, C.c_size_t, C.c_void_p]),
     'aqtb200_requant_amax': (C.c_int, [
         C.c_void_p, C.c_int64, C.c_void_p, C.c_int32, C.POINTER(QuantSpec),
         C.c_void_p, C.c_void_p, C.c_void_p]),

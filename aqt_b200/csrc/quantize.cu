@@ -1558,6 +1558,245 @@ __global__ void dequant_kernel(DeqParams D, int64_t total) {
   }
 }
 
+// ===========================================================================
+// One read of the cotangent for BOTH gradient dots when the scales are per row
+// (per token / per channel), the forward scales folded into it vary along
+// the contraction and stochastic-rounding noise is added: the batched,
+// per-channel counterpart of quant_pair_kernel.
+//
+// The backward pass quantizes the cotangent g twice (aqt_dot_general.py:
+// 1206-1217): for dlhs along its last index, for drhs along the one before.
+// With x = g viewed as [b][c][r] (r contiguous):
+//   output S [b][c][r]  (x's orientation; contraction index r)
+//       v = round(x * pre_s[b][r]);  scale_s[b][c] = max_r |v| / bound
+//   output T [b][r][c]  (transposed; contraction index c)
+//       v = round(x * pre_t[b][c]);  scale_t[b][r] = max_c |v| / bound
+// absmax_dual_kernel takes both families of maxima in one pass over x;
+// quant_dual_kernel writes both int8 layouts in one more pass, each with its
+// own noise tensor. bf16 input, bf16 arithmetic (packed), int8 outputs.
+struct DualParams {
+  DView x;                 // bf16, sr == 1; rows % 8 == 0
+  const void* pre_t;       // bf16 prescale of output T, indexed [b0][b1][c]; null = none
+  int64_t pt_b0, pt_b1, pt_c;
+  const void* pre_s;       // bf16 prescale of output S, indexed [b0][b1][r]; null = none
+  int64_t ps_b0, ps_b1, ps_r;
+  const float* noise_t;    // f32, x's layout [b][c][r]; null = none
+  const float* noise_s;
+  uint32_t* amax_t;        // [b][rows] f32 bits
+  uint32_t* amax_s;        // [b][cols]
+  const float* sinv_t;     // [b][rows] reciprocal scales (already rounded to bf16)
+  const float* sinv_s;     // [b][cols]
+  float clip_t, clip_s;
+  uint8_t* q_t;            // [b][rows][ld_t]
+  uint8_t* q_s;            // [b][cols][ld_s]
+  int64_t ld_t, ld_s;
+};
+
+__device__ __forceinline__ uint32_t ld_bf16_pair(const void* base, int64_t i0, int64_t i1) {
+  const unsigned short* p = (const unsigned short*)base;
+  return (uint32_t)__ldg(p + i0) | ((uint32_t)__ldg(p + i1) << 16);
+}
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 r = __hmul2(*(const __nv_bfloat162*)&a, *(const __nv_bfloat162*)&b);
+  return *(const uint32_t*)&r;
+}
+
+// Block = one strip: 128 rows (r) by ALL columns (c) of one batch element, walked
+// 128 columns at a time. Thread (tx, ty): rows r0 + 8 tx .. +7 (one 16-byte
+// vector), columns ty*4 + e (+64) of each 128-column tile. The maxima over c
+// (amax_t, per row) stay in registers for the whole strip and are written once;
+// the maxima over r (amax_s, per column) are folded over the 16 row groups of
+// the block with shuffles and merged across strips with one atomic per column.
+template <bool PRE_T, bool PRE_S>
+__global__ void __launch_bounds__(256)
+absmax_dual_kernel(DualParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_strips) {
+  __shared__ uint32_t srow[16][128];  // [ty][row in strip]: packed halves folded later
+  const DView& x = P.x;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int64_t u = blockIdx.x; u < total_strips; u += gridDim.x) {
+    const int64_t rt = u % row_tiles;
+    const int64_t b = u / row_tiles;
+    const int64_t i1 = b % x.b1, i0 = b / x.b1;
+    const int64_t r0 = rt * 128 + tx * 8;
+    const bool row_ok = r0 < x.rows;
+    const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + (row_ok ? r0 : 0)) * 2;
+    uint32_t ps[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+    if (PRE_S && row_ok) {
+      const int64_t pb = i0 * P.ps_b0 + i1 * P.ps_b1;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        ps[j] = ld_bf16_pair(P.pre_s, pb + (r0 + 2 * j) * P.ps_r, pb + (r0 + 2 * j + 1) * P.ps_r);
+    }
+    uint32_t run_t[4] = {0u, 0u, 0u, 0u};  // per row pair, max over every column of the strip
+    for (int64_t ct = 0; ct < col_tiles; ++ct) {
+      uint4 raw[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+          raw[i][e] = (row_ok && c < x.cols) ? ldg16(xp, c * x.sc * 2) : make_uint4(0u, 0u, 0u, 0u);
+        }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+          const uint32_t w[4] = {raw[i][e].x, raw[i][e].y, raw[i][e].z, raw[i][e].w};
+          uint32_t pt2 = 0x3f803f80u;
+          if (PRE_T && c < x.cols) {
+            const uint32_t v = __ldg((const unsigned short*)P.pre_t + i0 * P.pt_b0 + i1 * P.pt_b1 + c * P.pt_c);
+            pt2 = v | (v << 16);
+          }
+          uint32_t m2 = 0u;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint32_t vt = PRE_T ? hmul2_u32(w[j], pt2) : w[j];
+            run_t[j] = __vmaxu2(run_t[j], vt & 0x7fff7fffu);
+            const uint32_t vs = PRE_S ? hmul2_u32(w[j], ps[j]) : w[j];
+            m2 = __vmaxu2(m2, vs & 0x7fff7fffu);
+          }
+          // this thread's 8 rows of column c -> fold over the 16 row groups
+          uint32_t m = max(m2 & 0xffffu, m2 >> 16);
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+          if (tx == 0 && m != 0u && c < x.cols)
+            atomicMax(P.amax_s + b * x.cols + c, m << 16);
+        }
+      }
+    }
+    // rows: fold the 16 column groups (ty) through shared memory
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      srow[ty][tx * 8 + 2 * j] = run_t[j] & 0xffffu;
+      srow[ty][tx * 8 + 2 * j + 1] = run_t[j] >> 16;
+    }
+    __syncthreads();
+    if (tid < 128) {
+      uint32_t m = 0u;
+#pragma unroll
+      for (int k = 0; k < 16; ++k) m = max(m, srow[k][tid]);
+      const int64_t r = rt * 128 + tid;
+      if (r < x.rows) P.amax_t[b * x.rows + r] = m << 16;  // the strip owns these rows
+    }
+    __syncthreads();
+  }
+}
+
+// One tile (128 r x 128 c) per step, same thread layout as quant_pair_kernel.
+template <bool PRE_T, bool PRE_S, bool NOISE>
+__global__ void __launch_bounds__(256, 2)
+quant_dual_kernel(DualParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_units) {
+  constexpr int EPV = 8, TR = 16 * EPV;
+  __shared__ __align__(16) uint32_t tile[TR][32];
+  const DView& x = P.x;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int64_t u = blockIdx.x; u < total_units; u += gridDim.x) {
+    const int64_t rt = u % row_tiles;
+    int64_t t = u / row_tiles;
+    const int64_t ct = t % col_tiles;
+    const int64_t b = t / col_tiles;
+    const int64_t i1 = b % x.b1, i0 = b / x.b1;
+    const int64_t r0 = rt * TR + tx * EPV;
+    const bool row_ok = r0 < x.rows;  // rows % 8 == 0: a vector is all in or all out
+    const int64_t xoff = i0 * x.sb0 + i1 * x.sb1 + (row_ok ? r0 : 0);  // elements
+    const char* xp = (const char*)x.ptr + xoff * 2;
+    uint8_t* qs_base = P.q_s + (b * x.cols + ct * 128 + ty * 4) * P.ld_s + r0;
+    // per-row constants of this thread: prescale of S and reciprocal scale of T
+    uint32_t ps[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+    uint32_t it[4] = {0x3f803f80u, 0x3f803f80u, 0x3f803f80u, 0x3f803f80u};
+    if (row_ok) {
+      if (PRE_S) {
+        const int64_t pb = i0 * P.ps_b0 + i1 * P.ps_b1;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          ps[j] = ld_bf16_pair(P.pre_s, pb + (r0 + 2 * j) * P.ps_r, pb + (r0 + 2 * j + 1) * P.ps_r);
+      }
+      const float4 a = __ldg((const float4*)(P.sinv_t + b * x.rows + r0));
+      const float4 c4 = __ldg((const float4*)(P.sinv_t + b * x.rows + r0 + 4));
+      it[0] = pack_bf16x2(a.x, a.y); it[1] = pack_bf16x2(a.z, a.w);
+      it[2] = pack_bf16x2(c4.x, c4.y); it[3] = pack_bf16x2(c4.z, c4.w);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      uint4 raw[4];
+      uint4 nt[4][2], ns[4][2];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+        const bool in = row_ok && c < x.cols;
+        raw[e] = in ? ldg16(xp, c * x.sc * 2) : make_uint4(0u, 0u, 0u, 0u);
+        if (NOISE) {
+          const int64_t no = (xoff + c * x.sc) * 4;
+          nt[e][0] = in ? ldg16(P.noise_t, no) : make_uint4(0u, 0u, 0u, 0u);
+          nt[e][1] = in ? ldg16(P.noise_t, no + 16) : make_uint4(0u, 0u, 0u, 0u);
+          ns[e][0] = in ? ldg16(P.noise_s, no) : make_uint4(0u, 0u, 0u, 0u);
+          ns[e][1] = in ? ldg16(P.noise_s, no + 16) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
+      uint32_t q4[4][2];  // transposed output: [column e][row group g]
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+        const bool in = row_ok && c < x.cols;
+        uint32_t pt2 = 0x3f803f80u, is2 = 0x3f803f80u;
+        if (in) {
+          if (PRE_T) {
+            const uint32_t v = __ldg((const unsigned short*)P.pre_t + i0 * P.pt_b0 + i1 * P.pt_b1 + c * P.pt_c);
+            pt2 = v | (v << 16);
+          }
+          const float s = __ldg(P.sinv_s + b * x.cols + c);
+          is2 = pack_bf16x2(s, s);
+        }
+        const uint32_t w[4] = {raw[e].x, raw[e].y, raw[e].z, raw[e].w};
+        float fnt[8], fns[8];
+        if (NOISE) {
+          const uint32_t a[8] = {nt[e][0].x, nt[e][0].y, nt[e][0].z, nt[e][0].w,
+                                 nt[e][1].x, nt[e][1].y, nt[e][1].z, nt[e][1].w};
+          const uint32_t c8[8] = {ns[e][0].x, ns[e][0].y, ns[e][0].z, ns[e][0].w,
+                                  ns[e][1].x, ns[e][1].y, ns[e][1].z, ns[e][1].w};
+#pragma unroll
+          for (int k = 0; k < 8; ++k) { fnt[k] = __uint_as_float(a[k]); fns[k] = __uint_as_float(c8[k]); }
+        }
+        // output T: prescale by column, reciprocal scale by row
+        const uint32_t qt_lo = bf16x4_to_s8x4(w[0], w[1], pt2, pt2, PRE_T, it[0], it[1], fnt, NOISE, P.clip_t);
+        const uint32_t qt_hi = bf16x4_to_s8x4(w[2], w[3], pt2, pt2, PRE_T, it[2], it[3], fnt + 4, NOISE, P.clip_t);
+        // output S: prescale by row, reciprocal scale by column
+        const uint32_t qs_lo = bf16x4_to_s8x4(w[0], w[1], ps[0], ps[1], PRE_S, is2, is2, fns, NOISE, P.clip_s);
+        const uint32_t qs_hi = bf16x4_to_s8x4(w[2], w[3], ps[2], ps[3], PRE_S, is2, is2, fns + 4, NOISE, P.clip_s);
+        q4[e][0] = in ? qt_lo : 0u;
+        q4[e][1] = in ? qt_hi : 0u;
+        if (in) {
+          // same orientation: rows r0..r0+7 of column c are 8 contiguous bytes
+          *(uint2*)(qs_base + (int64_t)(i * 64 + e) * P.ld_s) = make_uint2(qs_lo, qs_hi);
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const uint32_t cols4[4] = {q4[0][g], q4[1][g], q4[2][g], q4[3][g]};
+        uint32_t rows4[4];
+        transpose4x4(cols4, rows4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          tile[tx * EPV + 4 * g + j][(i * 16 + ty + 4 * tx) & 31] = rows4[j];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int s2 = 0; s2 < TR / 32; ++s2) {
+      const int id = tid + 256 * s2;
+      const int row = id >> 3, seg = id & 7;
+      const int64_t gr = rt * TR + row;
+      const int64_t gc = ct * 128 + seg * 16;
+      if (gr < x.rows && gc < P.ld_t) {
+        const uint4 o = *(const uint4*)&tile[row][(seg * 4 + 4 * (row / EPV)) & 31];
+        *(uint4*)(P.q_t + (b * x.rows + gr) * P.ld_t + gc) = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 
@@ -2017,6 +2256,117 @@ int aqtb200_quantize_pair(const aqtb200_view* x,
   if (ints) AQT_PAIR(true); else AQT_PAIR(false);
 #undef AQT_PAIR
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+size_t aqtb200_quantize_dual_workspace_bytes(const aqtb200_dual_desc* d) {
+  if (d == nullptr) return 0;
+  const int64_t nb = d->x.b0 * d->x.b1;
+  return 2 * align256((size_t)std::max<int64_t>(1, nb * d->x.rows) * 4) +
+         2 * align256((size_t)std::max<int64_t>(1, nb * d->x.cols) * 4);
+}
+
+int aqtb200_quantize_dual(const aqtb200_dual_desc* d, void* workspace, size_t workspace_bytes,
+                          void* stream) {
+  AQT_REQUIRE(d != nullptr, AQTB200_EINVAL, "null descriptor");
+  const aqtb200_view& xv = d->x;
+  AQT_REQUIRE(xv.b0 >= 0 && xv.b1 >= 0 && xv.rows >= 0 && xv.cols >= 0, AQTB200_EINVAL,
+              "negative extent");
+  const int64_t nb = xv.b0 * xv.b1;
+  if (nb * xv.rows * xv.cols == 0) return 0;
+  AQT_REQUIRE(xv.ptr != nullptr && d->q_t != nullptr && d->q_s != nullptr &&
+                  d->scale_t != nullptr && d->scale_s != nullptr,
+              AQTB200_EINVAL, "null pointer");
+  for (const aqtb200_quant_spec* sp : {&d->spec_t, &d->spec_s})
+    AQT_REQUIRE(sp->kind == AQTB200_NUM_INT && sp->qdtype == AQTB200_S8 && !sp->per_tensor &&
+                    sp->compute_dtype == AQTB200_BF16 && sp->scale_dtype == AQTB200_BF16 &&
+                    sp->quant_bound > 0.f && sp->clip_bound > 0.f,
+                AQTB200_EUNSUPPORTED,
+                "aqtb200_quantize_dual: int8 numerics, per-row scales, bf16 compute and scale dtype");
+  DualParams P{};
+  P.x = to_dview(&xv);
+  AQT_REQUIRE(xv.dtype == AQTB200_BF16 && P.x.sr == 1 && xv.rows % 16 == 0 && xv.cols % 16 == 0 &&
+                  col_fast_ok(P.x, xv.rows, 8),
+              AQTB200_EUNSUPPORTED,
+              "aqtb200_quantize_dual: bf16 input with rows the contiguous index, both extents "
+              "multiples of 16, every stride a multiple of 16 bytes");
+  AQT_REQUIRE(aligned(d->q_t, 16) && aligned(d->q_s, 16), AQTB200_EINVAL, "outputs not 16-byte aligned");
+  if (d->prescale_t.ptr != nullptr) {
+    AQT_REQUIRE(d->prescale_t.dtype == AQTB200_BF16, AQTB200_EUNSUPPORTED, "prescales must be bf16");
+    P.pre_t = d->prescale_t.ptr; P.pt_b0 = d->prescale_t.b0_stride; P.pt_b1 = d->prescale_t.b1_stride;
+    P.pt_c = d->prescale_t.col_stride;
+  }
+  if (d->prescale_s.ptr != nullptr) {
+    AQT_REQUIRE(d->prescale_s.dtype == AQTB200_BF16, AQTB200_EUNSUPPORTED, "prescales must be bf16");
+    P.pre_s = d->prescale_s.ptr; P.ps_b0 = d->prescale_s.b0_stride; P.ps_b1 = d->prescale_s.b1_stride;
+    P.ps_r = d->prescale_s.row_stride;
+  }
+  const bool noise = d->noise_t.ptr != nullptr;
+  AQT_REQUIRE(noise == (d->noise_s.ptr != nullptr), AQTB200_EUNSUPPORTED,
+              "aqtb200_quantize_dual: noise for both outputs or for neither");
+  if (noise) {
+    for (const aqtb200_view* nv : {&d->noise_t, &d->noise_s})
+      AQT_REQUIRE(nv->dtype == AQTB200_F32 && nv->row_stride == 1 && nv->col_stride == xv.col_stride &&
+                      nv->b0_stride == xv.b0_stride && nv->b1_stride == xv.b1_stride &&
+                      aligned(nv->ptr, 16),
+                  AQTB200_EUNSUPPORTED, "aqtb200_quantize_dual: noise must be f32 in x's layout");
+    P.noise_t = (const float*)d->noise_t.ptr;
+    P.noise_s = (const float*)d->noise_s.ptr;
+  }
+  const size_t need = aqtb200_quantize_dual_workspace_bytes(d);
+  AQT_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned(workspace, 256),
+              AQTB200_EWORKSPACE, "workspace: need %zu bytes, 256-byte aligned (got %zu)", need,
+              workspace_bytes);
+  const int64_t n_t = nb * xv.rows, n_s = nb * xv.cols;
+  char* ws = (char*)workspace;
+  P.amax_t = (uint32_t*)ws; ws += align256((size_t)n_t * 4);
+  P.amax_s = (uint32_t*)ws; ws += align256((size_t)n_s * 4);
+  float* sinv_t = (float*)ws; ws += align256((size_t)n_t * 4);
+  float* sinv_s = (float*)ws;
+  P.sinv_t = sinv_t; P.sinv_s = sinv_s;
+  P.clip_t = d->spec_t.clip_bound; P.clip_s = d->spec_s.clip_bound;
+  P.q_t = (uint8_t*)d->q_t; P.q_s = (uint8_t*)d->q_s;
+  P.ld_t = xv.cols; P.ld_s = xv.rows;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int64_t rts = (xv.rows + 127) / 128, cts = (xv.cols + 127) / 128;
+
+  // 1. both families of maxima in one pass
+  AQT_CUDA_OK(cudaMemsetAsync(P.amax_s, 0, (size_t)n_s * 4, st));
+  {
+    const int grid = grid_for(nb * rts, 4);
+#define AQT_DUAL_ABSMAX(PT, PS) absmax_dual_kernel<PT, PS><<<grid, 256, 0, st>>>(P, rts, cts, nb * rts)
+    if (P.pre_t != nullptr) { if (P.pre_s != nullptr) AQT_DUAL_ABSMAX(true, true); else AQT_DUAL_ABSMAX(true, false); }
+    else { if (P.pre_s != nullptr) AQT_DUAL_ABSMAX(false, true); else AQT_DUAL_ABSMAX(false, false); }
+#undef AQT_DUAL_ABSMAX
+    AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  }
+  // 2. maxima -> scales and reciprocals
+  for (int k = 0; k < 2; ++k) {
+    const aqtb200_quant_spec& sp = k == 0 ? d->spec_t : d->spec_s;
+    FinalizeParams F{};
+    F.amax = k == 0 ? P.amax_t : P.amax_s;
+    F.scale_out = k == 0 ? d->scale_t : d->scale_s;
+    F.sinv = k == 0 ? sinv_t : sinv_s;
+    F.n = k == 0 ? n_t : n_s;
+    F.t_dtype = F.s_dtype = AQTB200_BF16;
+    F.quant_bound = sp.quant_bound; F.clipping_scale = sp.clipping_scale; F.po2 = sp.po2_scale;
+    finalize_scale_kernel<<<(int)((F.n + 255) / 256), 256, 0, st>>>(F);
+    AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  }
+  // 3. both int8 layouts in one pass
+  {
+    const int64_t units = nb * rts * cts;
+    const int grid = grid_for(units, 2);
+#define AQT_DUAL_QUANT(PT, PS)                                                                  \
+  do {                                                                                          \
+    if (noise) quant_dual_kernel<PT, PS, true><<<grid, 256, 0, st>>>(P, rts, cts, units);       \
+    else quant_dual_kernel<PT, PS, false><<<grid, 256, 0, st>>>(P, rts, cts, units);            \
+  } while (0)
+    if (P.pre_t != nullptr) { if (P.pre_s != nullptr) AQT_DUAL_QUANT(true, true); else AQT_DUAL_QUANT(true, false); }
+    else { if (P.pre_s != nullptr) AQT_DUAL_QUANT(false, true); else AQT_DUAL_QUANT(false, false); }
+#undef AQT_DUAL_QUANT
+    AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  }
   return 0;
 }
 

@@ -1344,6 +1344,127 @@ def cotangent_pair(cfg, res, g, reduce_max=None):
   return qt(q_s, s_dl), qt(q_t.t(), s_dr)
 
 
+def cotangent_dual(cfg, res, g, fwd_dimension_numbers):
+  """Both quantizations of the cotangent in two passes over it, for per-row
+  scales (aqtb200_quantize_dual): the batched / per-channel counterpart of
+  cotangent_pair, with the forward scales folded in and stochastic-rounding
+  noise. Applies when g is a contiguous bf16 tensor [..., t, s] whose LAST
+  axis is what dlhs contracts and whose second-to-last is what drhs
+  contracts, the leading axes being batch axes of both gradient dots (a plain
+  matmul, or an einsum like 'bthd,bshd->bhts'). Returns full QTensors (g for
+  dlhs, g for drhs) or None when the configuration is outside that."""
+  from aqt_b200.v2 import aqt_dot_general as adg
+  from aqt_b200.v2 import aqt_tensor
+  if not (isinstance(g, torch.Tensor) and g.dtype == torch.bfloat16 and
+          g.ndim >= 2 and g.is_contiguous() and _on_device(g) and
+          g.numel() > 0 and g.data_ptr() % 16 == 0):
+    return None
+  nd = g.ndim
+  t_ext, s_ext = g.shape[-2], g.shape[-1]
+  if t_ext % 16 or s_ext % 16:
+    return None
+  upd = adg._update_dimension_numbers_for_backward  # pylint: disable=protected-access
+  d_dims, _ = upd(fwd_dimension_numbers, False, nd, res.rhs.mt.x.ndim)
+  r_dims, _ = upd(fwd_dimension_numbers, True, nd, res.lhs.mt.x.ndim)
+  batch = list(range(nd - 2))
+  for (gca, _), (gba, _), want in ((d_dims[0], d_dims[1], nd - 1),
+                                   (r_dims[0], r_dims[1], nd - 2)):
+    if list(gca) != [want] or list(gba) != batch:
+      return None
+  specs, pres, noises = [], [], []
+  for raw, mt, dims_b in ((cfg.dlhs, res.rhs.mt, d_dims),
+                          (cfg.drhs, res.lhs.mt, r_dims)):
+    try:
+      q = _check_raw_supported(raw)
+    except NotImplementedError:
+      return None
+    qz = q.lhs
+    if type(qz.numerics).__name__ != 'IntSymmetric' or _delayed(qz):
+      return None
+    (gca, yra), (gba, yba) = dims_b
+    if qz.calib_shared_axes not in (None, list(gca), tuple(gca)):
+      return None
+    try:
+      spec = _make_spec(qz, _lib.BF16, True)
+    except NotImplementedError:
+      return None
+    if spec is None or spec.scale_dtype != _lib.BF16 or spec.qdtype != _lib.S8:
+      return None
+    specs.append(spec)
+    pre = None
+    if raw.rhs.use_fwd_quant:
+      sc = mt.qx.scale
+      if sc is None or len(sc) != 1 or sc[0].dtype != torch.bfloat16:
+        return None
+      pre = sc[0]
+      if pre.ndim < mt.x.ndim:
+        pre = pre.reshape(list(pre.shape) + [1] * (mt.x.ndim - pre.ndim))
+      # a forward scale never varies along the axes the backward dot keeps
+      kept = [a for a in range(pre.ndim) if a not in list(yra) + list(yba)]
+      if any(pre.shape[a] != 1 for a in kept):
+        return None
+      st = lambda a: 0 if pre.shape[a] == 1 else pre.stride(a)
+      pres.append((pre, [st(a) for a in yba], st(yra[0])))
+    else:
+      pres.append(None)
+    noise = _noise_for(qz, g.shape, g.device)
+    if noise is not None and (noise.stride() != g.stride() or
+                              noise.data_ptr() % 16):
+      return None
+    noises.append(noise)
+  if (noises[0] is None) != (noises[1] is None):
+    return None
+  # leading axes -> at most two batch dims on which g and both prescales agree
+  strides = [[g.stride(a) for a in batch]]
+  strides += [p[1] for p in pres if p is not None]
+  bdims = _merge([g.shape[a] for a in batch], strides, 2)
+  if bdims is None:
+    return None
+  while len(bdims) < 2:
+    bdims.insert(0, (1, [0] * len(strides)))
+  b_ext = [bdims[0][0], bdims[1][0]]
+  nb = b_ext[0] * b_ext[1]
+  desc = _lib.DualDesc()
+  desc.x = _view(g.data_ptr(), _lib.BF16, b_ext, s_ext, t_ext,
+                 [bdims[0][1][0], bdims[1][1][0]], 1, s_ext)
+  desc.spec_s, desc.spec_t = specs[0], specs[1]
+  col = 1
+  for which, p in (('prescale_s', pres[0]), ('prescale_t', pres[1])):
+    if p is None:
+      continue
+    bs = [bdims[0][1][col], bdims[1][1][col]]
+    col += 1
+    # prescale_s varies along x's rows (s), prescale_t along x's cols (t)
+    rs, cs = (p[2], 0) if which == 'prescale_s' else (0, p[2])
+    setattr(desc, which, _view(p[0].data_ptr(), _lib.BF16, b_ext, s_ext, t_ext,
+                               bs, rs, cs))
+  if noises[0] is not None:
+    for which, nz in (('noise_s', noises[0]), ('noise_t', noises[1])):
+      setattr(desc, which, _view(nz.data_ptr(), _lib.F32, b_ext, s_ext, t_ext,
+                                 [bdims[0][1][0], bdims[1][1][0]], 1, s_ext))
+  dev = g.device
+  q_s = _empty((nb, t_ext, s_ext), torch.int8, dev)
+  q_t = _empty((nb, s_ext, t_ext), torch.int8, dev)
+  sc_s = _empty(nb * t_ext, torch.bfloat16, dev)
+  sc_t = _empty(nb * s_ext, torch.bfloat16, dev)
+  desc.q_s, desc.q_t = q_s.data_ptr(), q_t.data_ptr()
+  desc.scale_s, desc.scale_t = sc_s.data_ptr(), sc_t.data_ptr()
+  lib = _lib.load()
+  ws_bytes = lib.aqtb200_quantize_dual_workspace_bytes(C.byref(desc))
+  ws = _empty(max(ws_bytes, 256), torch.uint8, dev)
+  rc = _call(lib.aqtb200_quantize_dual, C.byref(desc), ws.data_ptr(),
+             ws.numel(), _stream())
+  _lib.check(rc, 'aqtb200_quantize_dual')
+  lead = list(g.shape[:-2])
+  dd = utils.as_dtype(g.dtype)
+  qt = lambda qv, sc: aqt_tensor.QTensor(qvalue=qv, scale=[sc], scale_t=None,
+                                         bias=[], dequant_dtype=dd)
+  g_dlhs = qt(q_s.view(lead + [t_ext, s_ext]), sc_s.view(lead + [t_ext, 1]))
+  g_drhs = qt(q_t.view(lead + [s_ext, t_ext]).transpose(-1, -2),
+              sc_t.view(lead + [1, s_ext]))
+  return g_dlhs, g_drhs
+
+
 def quantize_with_scale(x, scale, numerics, noise=None):
   """Quantizer.calculate_qvalue with a given scale: returns qvalue."""
   shared = [a for a in range(x.ndim) if scale.shape[a] == 1 and x.shape[a] != 1]

@@ -540,6 +540,9 @@ def dg_core_vjp_bwd(fwd_dimension_numbers, res, g):
     try:
       shared = engine.cotangent_pair(cfg, dg_res, g)
       if shared is None:
+        shared = engine.cotangent_dual(cfg, dg_res, g,
+                                       fwd_dimension_numbers)
+      if shared is None:
         shared = engine.shared_cotangent_scales(cfg, dg_res, g)
     except NotImplementedError:
       shared = None

@@ -230,6 +230,44 @@ int aqtb200_requant_amax(const float* amax, int64_t n, const void* prescale,
                          int32_t prescale_dtype, const aqtb200_quant_spec* spec,
                          const void* scale, float* amax_q_out, void* stream);
 
+/*
+ * aqtb200_quantize_dual: the cotangent's TWO calibrations and quantizations
+ * (one per gradient dot, aqt_dot_general.py:1206-1217, each with the other
+ * operand's forward scale folded in first, :714-720, and each with its own
+ * stochastic-rounding noise, numerics/int_numerics.py:88-110) in two passes
+ * over it instead of four, for per-row ("per token" / "per channel") scales:
+ * the batched counterpart of aqtb200_quantize_pair.
+ *
+ * x is viewed as [b0][b1][cols][rows] with rows contiguous (row_stride 1).
+ *   output S [b][cols][rows], x's orientation, contraction index = rows:
+ *     v = round(x * prescale_s[b][row]); scale_s[b][col] = max_row |v| / bound;
+ *     q_s = int8(round_half_even(clip(round(v / scale_s) + noise_s)))
+ *   output T [b][rows][cols], transposed, contraction index = cols:
+ *     v = round(x * prescale_t[b][col]); scale_t[b][row] = max_col |v| / bound;
+ *     q_t likewise with noise_t.
+ * For the cotangent g[..., t, s] of an einsum: rows = s, cols = t; S feeds dlhs
+ * (contracts s), T feeds drhs (contracts t).
+ * Requirements: x bf16; both specs int8, per-row scales, bf16 compute and scale
+ * dtype; rows and cols multiples of 16; prescales bf16 (ptr NULL = none),
+ * prescale_t indexed through its b0/b1/col strides, prescale_s through its
+ * b0/b1/row strides; noise f32 in x's own layout, for both outputs or neither.
+ * Results are bit-identical to two aqtb200_quantize calls. Anything else: -2.
+ */
+typedef struct aqtb200_dual_desc {
+  aqtb200_view x;
+  aqtb200_quant_spec spec_t, spec_s;
+  aqtb200_view prescale_t, prescale_s;
+  aqtb200_view noise_t, noise_s;
+  void* q_t;      /* [b0][b1][rows][cols] int8 */
+  void* scale_t;  /* [b0][b1][rows] bf16 */
+  void* q_s;      /* [b0][b1][cols][rows] int8 */
+  void* scale_s;  /* [b0][b1][cols] bf16 */
+} aqtb200_dual_desc;
+
+size_t aqtb200_quantize_dual_workspace_bytes(const aqtb200_dual_desc* desc);
+int aqtb200_quantize_dual(const aqtb200_dual_desc* desc, void* workspace, size_t workspace_bytes,
+                          void* stream);
+
 int64_t aqtb200_round_up(int64_t v, int64_t multiple);
 
 /*

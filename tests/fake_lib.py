@@ -145,6 +145,40 @@ class FakeLib:
                           _deref(spec, _lib.QuantSpec), scale_in, q_out,
                           scale_out)
 
+  def aqtb200_quantize_dual_workspace_bytes(self, desc):
+    return 1024
+
+  def aqtb200_quantize_dual(self, desc, ws, ws_bytes, stream):
+    """Two plain quantizations of the same tensor, one per orientation."""
+    d = _deref(desc, _lib.DualDesc)
+    x = d.x
+    if x.row_stride != 1 or x.rows % 16 or x.cols % 16:
+      return self._fail(-2, 'aqtb200_quantize_dual: layout')
+
+    def view(v, transposed):
+      if not v.ptr:
+        return None
+      o = _lib.View()
+      o.ptr, o.dtype = v.ptr, v.dtype
+      o.b0, o.b1 = x.b0, x.b1
+      o.b0_stride, o.b1_stride = v.b0_stride, v.b1_stride
+      if transposed:  # rows stay rows, the contraction runs over x's cols
+        o.rows, o.cols = x.rows, x.cols
+        o.row_stride, o.col_stride = v.row_stride, v.col_stride
+      else:           # x's orientation: the contraction runs over x's rows
+        o.rows, o.cols = x.cols, x.rows
+        o.row_stride, o.col_stride = v.col_stride, v.row_stride
+      return o
+
+    rc = self._quantize(view(x, True), view(d.prescale_t, True),
+                        view(d.noise_t, True), d.spec_t, None, d.q_t,
+                        d.scale_t)
+    if rc:
+      return rc
+    return self._quantize(view(x, False), view(d.prescale_s, False),
+                          view(d.noise_s, False), d.spec_s, None, d.q_s,
+                          d.scale_s)
+
   def aqtb200_absmax_scale(self, x, pre, spec, scale_out, ws, ws_bytes,
                            stream):
     return self._quantize(_deref(x, _lib.View), _deref(pre, _lib.View), None,

@@ -229,3 +229,49 @@ def test_traced_step_replays_the_same_calls(monkeypatch, kind):
   _assert_same(dr, wr, 'drhs')
   with pytest.raises(AssertionError):
     traced(tl.clone(), tr, tg)
+
+
+@pytest.mark.parametrize('dims,ls,rs', [
+    ((((1,), (0,)), ((), ())), (32, 48), (48, 16)),
+    ((((3,), (3,)), ((0, 2), (0, 2))), (2, 16, 3, 32), (2, 32, 3, 32)),
+    ((((2,), (1,)), ((0,), (0,))), (3, 16, 32), (3, 32, 48)),
+])
+@pytest.mark.parametrize('use_fwd_quant', [True, False])
+@pytest.mark.parametrize('noise', [False, True])
+def test_cotangent_read_twice_for_both_gradient_dots(monkeypatch, dims, ls, rs,
+                                                     use_fwd_quant, noise):
+  """Per-row scales, bf16: aqtb200_quantize_dual calibrates and quantizes the
+  cotangent for dlhs and drhs together; same results as one dot at a time."""
+  from aqt_b200 import engine
+  from aqt_b200.v2 import stochastic_rounding as sr
+  fake = fake_lib.install(monkeypatch)
+  calls = []
+  real = fake.aqtb200_quantize_dual
+  fake.aqtb200_quantize_dual = lambda *a: calls.append(1) or real(*a)
+  rng = np.random.default_rng(2)
+  lhs = util.rand_normal(rng, ls, 1.0, orc.bfloat16)
+  rhs = util.rand_normal(rng, rs, 0.3, orc.bfloat16)
+  cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                               use_fwd_quant=use_fwd_quant,
+                               use_stochastic_rounding=noise)
+  if noise:
+    table = {}
+
+    def noise_fn(shape, key):
+      kk = (tuple(shape), int(key[0]), int(key[1]))
+      if kk not in table:
+        table[kk] = torch.from_numpy(
+            (rng.random(shape, np.float32) - 0.5).astype(np.float32))
+      return table[kk]
+
+    for raw in (cfg.dlhs, cfg.drhs):
+      raw.dg_quantizer.lhs.numerics.noise_fn = noise_fn
+      raw.dg_quantizer.rhs.numerics.noise_fn = noise_fn
+    cfg = config.set_context(cfg, key=sr.PRNGKey(1), train_step=None)
+  out_shape = orc.dg_fwd(cfg, lhs, rhs, dims)[0].shape
+  g = util.rand_normal(rng, out_shape, 1.0, orc.bfloat16)
+  (out, dl, dr), (wo, wl, wr, _) = _run_both(cfg, lhs, rhs, g, dims)
+  assert calls, 'the two-pass path did not run'
+  _assert_same(out, wo, 'out')
+  _assert_same(dl, wl, 'dlhs')
+  _assert_same(dr, wr, 'drhs')

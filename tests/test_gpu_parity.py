@@ -565,3 +565,50 @@ def test_full_size_checksum_8192(kind):
     bound = qa[rows].abs() @ qb.abs()
     assert ((acc.reshape(n, n)[rows].to(torch.float64) - exact).abs()
             <= 1e-5 * bound).all()
+
+
+@pytest.mark.parametrize('dims,ls,rs', [
+    ((((1,), (0,)), ((), ())), (272, 64), (64, 400)),
+    ((((3,), (3,)), ((0, 2), (0, 2))), (2, 144, 3, 32), (2, 304, 3, 32)),
+    ((((2,), (1,)), ((0,), (0,))), (3, 16, 32), (3, 32, 48)),
+])
+@pytest.mark.parametrize('use_fwd_quant', [True, False])
+@pytest.mark.parametrize('noise', [False, True])
+def test_cotangent_two_pass_quantization_bit_exact(monkeypatch, dims, ls, rs,
+                                                   use_fwd_quant, noise):
+  """aqtb200_quantize_dual (per-row scales, forward scales folded in, optional
+  noise; ragged 128 x 128 tiles) against the oracle's one-dot-at-a-time flow."""
+  calls = []
+  real = engine.cotangent_dual
+  monkeypatch.setattr(engine, 'cotangent_dual',
+                      lambda *a: calls.append(real(*a)) or calls[-1])
+  rng = np.random.default_rng(2)
+  lhs = util.rand_normal(rng, ls, 1.0, orc.bfloat16)
+  rhs = util.rand_normal(rng, rs, 0.3, orc.bfloat16)
+  cfg = config.fully_quantized(fwd_bits=8, bwd_bits=8,
+                               use_fwd_quant=use_fwd_quant,
+                               use_stochastic_rounding=noise)
+  if noise:
+    table = {}
+
+    def noise_fn(shape, key):
+      kk = (tuple(shape), int(key[0]), int(key[1]))
+      if kk not in table:
+        table[kk] = torch.from_numpy(
+            (rng.random(shape, np.float32) - 0.5).astype(np.float32)).to(DEV)
+      return table[kk]
+
+    for raw in (cfg.dlhs, cfg.drhs):
+      raw.dg_quantizer.lhs.numerics.noise_fn = noise_fn
+      raw.dg_quantizer.rhs.numerics.noise_fn = noise_fn
+    cfg = config.set_context(cfg, key=sr.PRNGKey(1), train_step=None)
+  wo, res = orc.dg_fwd(cfg, lhs, rhs, dims)
+  g = util.rand_normal(rng, wo.shape, 1.0, orc.bfloat16)
+  out, bp = cfg.vjp(_cuda(lhs), _cuda(rhs), dims)
+  dl, dr = bp(_cuda(g))
+  _sync()
+  assert calls and calls[0] is not None, 'the two-pass path did not run'
+  wl, wr = orc.dg_bwd(cfg, dims, res, g)
+  _exact(out, wo, 'out')
+  _exact(dl, wl, 'dlhs')
+  _exact(dr, wr, 'drhs')
