@@ -131,9 +131,18 @@ __device__ __forceinline__ void atomic_max_nonneg(uint32_t* cell, float v) {
   atomicMax(cell, __float_as_uint(v));
 }
 
+// Maximum of two NON-NEGATIVE floats through their bit patterns. Unlike fmaxf
+// it keeps a NaN (whose pattern, sign cleared, ranks above infinity), which is
+// what jnp.max(jnp.abs(x)) does: one NaN in the reduced range gives a NaN
+// maximum and so a NaN scale (calibration.py:149).
+__device__ __forceinline__ float amax_nn(float a, float b) {
+  return __uint_as_float(max(__float_as_uint(a), __float_as_uint(b)));
+}
+
+// warp-wide maximum of non-negative floats (NaN-keeping, see amax_nn)
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  for (int o = 16; o > 0; o >>= 1) v = amax_nn(v, __shfl_xor_sync(0xffffffffu, v, o));
   return v;
 }
 

@@ -128,7 +128,7 @@ absmax_row_kernel(QParams P, int64_t chunks_per_row, int64_t total_units) {
           for (int j = 0; j < 16; ++j) v[j] = apply_pre(v[j], p[j], P.t_dtype);
         }
 #pragma unroll
-        for (int j = 0; j < 16; ++j) m = fmaxf(m, fabsf(v[j]));
+        for (int j = 0; j < 16; ++j) m = amax_nn(m, fabsf(v[j]));
       }
     } else {
       for (int64_t c = c0 + lane; c < c1; c += 32) {
@@ -136,19 +136,19 @@ absmax_row_kernel(QParams P, int64_t chunks_per_row, int64_t total_units) {
         if (has_pre)
           v = apply_pre(v, load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc),
                         P.t_dtype);
-        m = fmaxf(m, fabsf(v));
+        m = amax_nn(m, fabsf(v));
       }
     }
     if (P.per_tensor) {
-      tmax = fmaxf(tmax, m);
+      tmax = amax_nn(tmax, m);
     } else {
       m = warp_max(m);
-      if (lane == 0 && m > 0.f) atomic_max_nonneg(P.amax + brow, m);
+      if (lane == 0 && m != 0.f) atomic_max_nonneg(P.amax + brow, m);
     }
   }
   if (P.per_tensor) {
     tmax = block_max(tmax, red);
-    if (threadIdx.x == 0 && tmax > 0.f) atomic_max_nonneg(P.amax, tmax);
+    if (threadIdx.x == 0 && tmax != 0.f) atomic_max_nonneg(P.amax, tmax);
   }
 }
 
@@ -192,18 +192,18 @@ absmax_col_kernel(QParams P, int64_t row_blocks, int64_t col_chunks,
 #pragma unroll
         for (int j = 0; j < V; ++j) {
           float w = has_pre ? apply_pre(v[j], p, P.t_dtype) : v[j];
-          m[j] = fmaxf(m[j], fabsf(w));
+          m[j] = amax_nn(m[j], fabsf(w));
         }
       }
     }
     if (P.per_tensor) {
 #pragma unroll
-      for (int j = 0; j < V; ++j) tmax = fmaxf(tmax, m[j]);
+      for (int j = 0; j < V; ++j) tmax = amax_nn(tmax, m[j]);
     } else if (r0 < x.rows) {
       const int64_t sbase = (i0 * x.b1 + i1) * x.rows;
 #pragma unroll
       for (int j = 0; j < V; ++j)
-        if (r0 + j < x.rows && m[j] > 0.f)
+        if (r0 + j < x.rows && m[j] != 0.f)
           atomic_max_nonneg(P.amax + sbase + r0 + j, m[j]);
     }
   }
@@ -215,7 +215,7 @@ absmax_col_kernel(QParams P, int64_t row_blocks, int64_t col_chunks,
     if (ty == 0) {
       v = tx < 8 ? red[tx] : 0.f;
       v = warp_max(v);
-      if (tx == 0 && v > 0.f) atomic_max_nonneg(P.amax, v);
+      if (tx == 0 && v != 0.f) atomic_max_nonneg(P.amax, v);
     }
   }
 }
@@ -288,7 +288,7 @@ __device__ __forceinline__ float packed_hmax(const uint4& run, int dt) {
   packed_to_floats<EPV>(run, dt, v);
   float m = 0.f;
 #pragma unroll
-  for (int i = 0; i < EPV; ++i) m = fmaxf(m, v[i]);
+  for (int i = 0; i < EPV; ++i) m = amax_nn(m, v[i]);
   return m;
 }
 
@@ -459,26 +459,26 @@ absmax_row_fast(QParams P, int64_t chunks_per_row, int64_t total_units, int chun
             unpack<EPV>(raw[k], x.dtype, v);
             loadN<EPV>(P.pre.ptr, P.pre.dtype, pbase + c0 + idx * EPV, p);
 #pragma unroll
-            for (int j = 0; j < EPV; ++j) fm = fmaxf(fm, fabsf(apply_pre(v[j], p[j], P.t_dtype)));
+            for (int j = 0; j < EPV; ++j) fm = amax_nn(fm, fabsf(apply_pre(v[j], p[j], P.t_dtype)));
           }
         } else {
           packed_absmax<EPV>(run, raw[k], x.dtype);
         }
       }
     }
-    float m = PRE == 2 ? fmaxf(fm, packed_hmax<EPV>(run, x.dtype)) : packed_hmax<EPV>(run, x.dtype);
+    float m = PRE == 2 ? amax_nn(fm, packed_hmax<EPV>(run, x.dtype)) : packed_hmax<EPV>(run, x.dtype);
     if constexpr (PRE == 1)
       m = apply_pre_abs(m, load1(P.pre.ptr, P.pre.dtype, pbase), P.t_dtype);
     if (P.per_tensor) {
-      tmax = fmaxf(tmax, m);
+      tmax = amax_nn(tmax, m);
     } else {
       m = warp_max(m);
-      if (lane == 0 && m > 0.f) atomic_max_nonneg(P.amax + brow, m);
+      if (lane == 0 && m != 0.f) atomic_max_nonneg(P.amax + brow, m);
     }
   }
   if (P.per_tensor) {
     tmax = block_max(tmax, red);
-    if (threadIdx.x == 0 && tmax > 0.f) atomic_max_nonneg(P.amax, tmax);
+    if (threadIdx.x == 0 && tmax != 0.f) atomic_max_nonneg(P.amax, tmax);
   }
 }
 
@@ -518,7 +518,7 @@ absmax_shortrow_fast(QParams P, int64_t nbrow, int nvec) {
       uint4 run = make_uint4(0u, 0u, 0u, 0u);
       packed_absmax<EPV>(run, raw[k], x.dtype);
       float m = packed_hmax<EPV>(run, x.dtype);
-      for (int o = nvec >> 1; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+      for (int o = nvec >> 1; o > 0; o >>= 1) m = amax_nn(m, __shfl_xor_sync(0xffffffffu, m, o));
       const bool ok = g0 + k < groups && brow[k] < nbrow;
       if constexpr (PRE == 1) {
         if (ok) {
@@ -529,7 +529,7 @@ absmax_shortrow_fast(QParams P, int64_t nbrow, int nvec) {
         }
       }
       if (P.per_tensor) {
-        if (ok) tmax = fmaxf(tmax, m);
+        if (ok) tmax = amax_nn(tmax, m);
       } else if (ok && vi == 0) {
         P.amax[brow[k]] = __float_as_uint(m);  // the whole row is in this group: no atomic needed
       }
@@ -537,7 +537,7 @@ absmax_shortrow_fast(QParams P, int64_t nbrow, int nvec) {
   }
   if (P.per_tensor) {
     tmax = block_max(tmax, red);
-    if (threadIdx.x == 0 && tmax > 0.f) atomic_max_nonneg(P.amax, tmax);
+    if (threadIdx.x == 0 && tmax != 0.f) atomic_max_nonneg(P.amax, tmax);
   }
 }
 
@@ -607,7 +607,7 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
               unpack<EPV>(raw[k], x.dtype, v);
               const float p = load1(P.pre.ptr, P.pre.dtype, pbase + ck * P.pre.sc);
 #pragma unroll
-              for (int j = 0; j < EPV; ++j) fm[j] = fmaxf(fm[j], fabsf(apply_pre(v[j], p, P.t_dtype)));
+              for (int j = 0; j < EPV; ++j) fm[j] = amax_nn(fm[j], fabsf(apply_pre(v[j], p, P.t_dtype)));
             }
           } else {
             packed_absmax<EPV>(run, raw[k], x.dtype);
@@ -620,7 +620,7 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
       float pm[EPV];
       packed_to_floats<EPV>(run, x.dtype, pm);  // the packed-bf16 path's maxima (zero otherwise)
 #pragma unroll
-      for (int j = 0; j < EPV; ++j) m[j] = fmaxf(fm[j], pm[j]);
+      for (int j = 0; j < EPV; ++j) m[j] = amax_nn(fm[j], pm[j]);
     } else {
       packed_to_floats<EPV>(run, x.dtype, m);
       if constexpr (PRE == 1) {
@@ -631,12 +631,12 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
     }
     if (P.per_tensor) {
 #pragma unroll
-      for (int j = 0; j < EPV; ++j) tmax = fmaxf(tmax, m[j]);
+      for (int j = 0; j < EPV; ++j) tmax = amax_nn(tmax, m[j]);
     } else if (r0 < x.rows) {
       const int64_t sbase = (i0 * x.b1 + i1) * x.rows;
 #pragma unroll
       for (int j = 0; j < EPV; ++j)
-        if (m[j] > 0.f) atomic_max_nonneg(P.amax + sbase + r0 + j, m[j]);
+        if (m[j] != 0.f) atomic_max_nonneg(P.amax + sbase + r0 + j, m[j]);
     }
   }
   if (P.per_tensor) {
@@ -646,7 +646,7 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
     if (ty == 0) {
       v = tx < 8 ? red[tx] : 0.f;
       v = warp_max(v);
-      if (tx == 0 && v > 0.f) atomic_max_nonneg(P.amax, v);
+      if (tx == 0 && v != 0.f) atomic_max_nonneg(P.amax, v);
     }
   }
 }

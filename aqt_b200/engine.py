@@ -119,6 +119,45 @@ def check_status():
           f'GEMM kernel gave up waiting on a barrier (role {code})')
 
 
+_status_host = {}
+
+
+def poll_status(device):
+  """Non-blocking look at the status word: every raw dot starts with one.
+
+  The word travels to pinned host memory by an asynchronous copy; a call
+  examines the copy the previous call started (if it has landed) and starts
+  the next one. A bounded wait that ran out therefore surfaces as an exception
+  one or two dots later, without a synchronisation anywhere -- instead of a
+  partially written result going unnoticed until someone calls
+  check_status(). Skipped while the stream is being captured into a graph
+  (replays are checked by the caller's own check_status())."""
+  if device.type != 'cuda' or torch.cuda.is_current_stream_capturing():
+    return
+  key = str(device)
+  slot = _status_host.get(key)
+  if slot is None:
+    slot = _status_host[key] = {
+        'host': torch.zeros(4, dtype=torch.int32).pin_memory(),
+        'event': None}
+  ev = slot['event']
+  if ev is not None:
+    if not ev.query():
+      return
+    code = int(slot['host'][0])
+    if code:
+      _status_buf(device).zero_()
+      slot['host'].zero_()
+      slot['event'] = None
+      raise _lib.AqtB200Error(
+          f'GEMM kernel gave up waiting on a barrier (role {code}); results '
+          'since the last check are incomplete')
+  slot['host'].copy_(_status_buf(device), non_blocking=True)
+  ev = torch.cuda.Event()
+  ev.record()
+  slot['event'] = ev
+
+
 def set_gemm_impl(name: str):
   """'tcgen05' (default), 'simt' (cross-check kernel), 'cta1', 'cta2', 'wide'."""
   code = {'tcgen05': 0, 'simt': 1, 'cta1': 2, 'cta2': 3, 'wide': 4}[name]
@@ -781,6 +820,8 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
   lib = _lib.load()
   ws_bytes = lib.aqtb200_dot_general_raw_workspace_bytes(C.byref(desc))
   ws = _empty(max(ws_bytes, 256), torch.uint8, dev)
+  if _tape is None:
+    poll_status(dev)
   status = _status_buf(dev)
   rc = _call(lib.aqtb200_dot_general_raw, C.byref(desc), ws.data_ptr(),
              ws.numel(), status.data_ptr(), _stream())

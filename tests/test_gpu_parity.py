@@ -612,3 +612,34 @@ def test_cotangent_two_pass_quantization_bit_exact(monkeypatch, dims, ls, rs,
   _exact(out, wo, 'out')
   _exact(dl, wl, 'dlhs')
   _exact(dr, wr, 'drhs')
+
+
+@pytest.mark.parametrize('bad', [float('nan'), float('inf')])
+@pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
+@pytest.mark.parametrize('per_tensor', [False, True])
+def test_nan_and_inf_reach_the_scale_whatever_the_kernel_variant(
+    bad, np_dtype, per_tensor):
+  """jnp.max(jnp.abs(x)) keeps a NaN; so must every absmax kernel: the
+  16-byte-vector ones (aligned view), the scalar ones (a view that starts one
+  element in), row-wise and column-wise."""
+  from aqt_b200.v2 import aqt_quantizer
+  rng = np.random.default_rng(12)
+  base = util.rand_normal(rng, (64, 130), 1.0, np_dtype)
+  base[5, 17] = bad
+  base[40, 3] = bad
+  for view in (lambda a: a[:, :128], lambda a: a[:, 1:129],
+               lambda a: a[:32, 2:66]):
+    for axes in ([1], [0]):
+      x = np.ascontiguousarray(view(base))
+      t = view(_cuda(base))  # strided, possibly misaligned view of the parent
+      qz = aqt_quantizer.quantizer_make(8)
+      if per_tensor:
+        qz.calib_shared_axes = 'per_tensor'
+      got = qz.calibrate(t, calibration_axes=axes)
+      _sync()
+      want = orc.quantizer_calibrate(qz, x, axes)
+      g = util.to_numpy(got.scale[0]).astype(np.float32)
+      w = want.scale[0].astype(np.float32)
+      assert g.shape == w.shape
+      assert np.array_equal(np.isnan(g), np.isnan(w)), (axes, g, w)
+      np.testing.assert_array_equal(g[~np.isnan(g)], w[~np.isnan(w)])
