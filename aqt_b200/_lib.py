@@ -107,7 +107,7 @@ SYMBOLS = {
         C.POINTER(View),
         C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
         C.POINTER(QuantSpec), C.c_void_p, C.c_void_p, C.c_int32, C.c_void_p,
-        C.c_int32, C.c_void_p, C.c_void_p]),
+        C.c_int32, C.c_void_p, C.c_void_p, C.c_void_p]),
     'aqtb200_quantize_dual_workspace_bytes': (C.c_size_t, [
         C.POINTER(DualDesc)]),
     'aqtb200_quantize_dual': (C.c_int, [

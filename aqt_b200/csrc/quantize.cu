@@ -970,6 +970,9 @@ struct PairParams {
   // amax != null: the scales are computed here from amax[0] and written out
   // (block 0), instead of being read
   const uint32_t* amax;
+  // optional: receives max |x| (f32 bits, atomic max; zeroed by the host), for
+  // callers whose scales do not come from this step's maximum (delayed scaling)
+  uint32_t* amax_out;
   float qb_t, qb_s, cs_t, cs_s;  // quant_bound / clipping_scale per output
   int po2_t, po2_s;
   uint8_t* q_t;            // [b][rows][ld_t]
@@ -1074,6 +1077,7 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
   const __nv_fp8_interpretation_t kt = P.qdtype_t == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
   const __nv_fp8_interpretation_t ks = P.qdtype_s == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
   constexpr bool int_t = IS_INT, int_s = IS_INT;
+  uint32_t run_max = 0u;  // packed bf16 magnitudes, when amax_out is wanted
   for (int64_t uf = blockIdx.x; uf < total_units; uf += gridDim.x) {
     const int64_t u = total_units - 1 - uf;  // back to front: the calibration pass's tail is still in L2
     // Neighbouring blocks take neighbouring tiles along the CONTIGUOUS index of
@@ -1105,6 +1109,10 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
         const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
         const bool in = row_ok && c < x.cols;
         const uint32_t rw[4] = {raw[i][e].x, raw[i][e].y, raw[i][e].z, raw[i][e].w};
+        if (P.amax_out != nullptr) {  // out-of-range vectors were loaded as zeros
+#pragma unroll
+          for (int j = 0; j < 4; ++j) run_max = __vmaxu2(run_max, rw[j] & 0x7fff7fffu);
+        }
         uint32_t qt[4], qs[4];  // two bytes each (rows 2j, 2j+1)
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -1152,6 +1160,12 @@ quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
       }
     }
     __syncthreads();
+  }
+  if (P.amax_out != nullptr) {
+    uint32_t m = max(run_max & 0xffffu, run_max >> 16) << 16;  // f32 bits of the bf16 magnitude
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((tid & 31) == 0 && m != 0u) atomicMax(P.amax_out, m);
   }
 }
 
@@ -2200,7 +2214,7 @@ int aqtb200_quantize_pair(const aqtb200_view* x,
                           const void* prescale_t, int32_t prescale_t_dtype, void* q_t,
                           const aqtb200_quant_spec* spec_s, void* scale_s,
                           const void* prescale_s, int32_t prescale_s_dtype, void* q_s,
-                          int32_t chain, const float* amax, void* stream) {
+                          int32_t chain, const float* amax, float* amax_out, void* stream) {
   AQT_REQUIRE(x != nullptr && spec_t != nullptr && spec_s != nullptr && scale_t != nullptr &&
                   scale_s != nullptr && q_t != nullptr && q_s != nullptr,
               AQTB200_EINVAL, "null argument");
@@ -2234,6 +2248,7 @@ int aqtb200_quantize_pair(const aqtb200_view* x,
   P.qdtype_t = spec_t->qdtype; P.qdtype_s = spec_s->qdtype;
   P.clip_t = spec_t->clip_bound; P.clip_s = spec_s->clip_bound;
   P.amax = (const uint32_t*)amax;
+  P.amax_out = (uint32_t*)amax_out;
   P.qb_t = spec_t->quant_bound; P.qb_s = spec_s->quant_bound;
   P.cs_t = spec_t->clipping_scale; P.cs_s = spec_s->clipping_scale;
   P.po2_t = spec_t->po2_scale; P.po2_s = spec_s->po2_scale;
@@ -2247,6 +2262,7 @@ int aqtb200_quantize_pair(const aqtb200_view* x,
               "aqtb200_quantize_pair: both outputs int8 or both fp8");
   const int grid = grid_for(units, 4);
   cudaStream_t st = (cudaStream_t)stream;
+  if (amax_out != nullptr) AQT_CUDA_OK(cudaMemsetAsync(amax_out, 0, 4, st));
 #define AQT_PAIR(I)                                                                   \
   do {                                                                                \
     if (chain == 0) quant_pair_kernel<I, 0><<<grid, 256, 0, st>>>(P, rts, cts, units);      \

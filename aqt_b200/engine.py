@@ -1203,10 +1203,11 @@ _BWD_COPY = '_aqt_b200_bwd_copy'  # attribute of the forward qvalue tensor
 
 
 def _pair_spec(quantizer):
-  """The per-tensor fp8 or int8 / bf16 spec of `quantizer`, or None if it is anything else."""
+  """The per-tensor fp8 or int8 / bf16 spec of `quantizer`, or None if it is
+  anything else. Delayed scaling counts as per-tensor whatever the axes."""
   if type(quantizer.numerics).__name__ not in ('Fp8Numerics', 'IntSymmetric'):
     return None
-  if quantizer.calib_shared_axes != 'per_tensor' or _delayed(quantizer):
+  if quantizer.calib_shared_axes != 'per_tensor' and not _delayed(quantizer):
     return None
   if getattr(quantizer.numerics, 'noise_fn', None) or getattr(
       quantizer.numerics, 'stochastic_rounding', False):
@@ -1243,12 +1244,26 @@ def _scale_of_amax(amax, spec, prescale=None):
   return out
 
 
+def _requant_amax(amax, spec, scale, prescale=None):
+  """|value of Q(amax)| under (spec, scale[, prescale]): the maximum of the
+  quantized values of a tensor whose maximum is amax (aqtb200_requant_amax)."""
+  out = _empty(1, torch.float32, amax.device)
+  pre_ptr, pre_code = (None, 0) if prescale is None else (
+      prescale.data_ptr(), _code(prescale.dtype))
+  rc = _call(_lib.load().aqtb200_requant_amax, amax.data_ptr(), 1, pre_ptr,
+             pre_code, C.byref(spec), scale.data_ptr(), out.data_ptr(),
+             _stream())
+  _lib.check(rc, 'aqtb200_requant_amax')
+  return out
+
+
 def _quantize_pair(x, spec_t, scale_t, pre_t, spec_s, scale_s, pre_s, chain,
-                   amax=None):
+                   amax=None, amax_out=None):
   """x: [C, R] row-major bf16. Returns (q_t [R][C], q_s [C][R]) buffers.
 
   With `amax` (the raw maximum of x) the kernel computes both scales itself
-  and writes them into scale_t / scale_s; otherwise it reads them.
+  and writes them into scale_t / scale_s; otherwise it reads them. `amax_out`
+  (one f32) receives max |x| from the same read.
   """
   c, r = x.shape
   view = _view(x.data_ptr(), _lib.BF16, [1, 1], r, c, [0, 0], 1, r)
@@ -1261,7 +1276,7 @@ def _quantize_pair(x, spec_t, scale_t, pre_t, spec_s, scale_s, pre_s, chain,
       scale_t.data_ptr(), pt, ptc,
       q_t.data_ptr(), C.byref(spec_s), scale_s.data_ptr(), ps, psc,
       q_s.data_ptr(), chain, None if amax is None else amax.data_ptr(),
-      _stream())
+      None if amax_out is None else amax_out.data_ptr(), _stream())
   _lib.check(rc, 'aqtb200_quantize_pair')
   return q_t, q_s
 
@@ -1299,6 +1314,14 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers,
     return None
   f_lhs, f_rhs, b_lhs, b_rhs = specs
   dd = utils.as_dtype(lhs.dtype)
+  quantizers = (cfg.fwd.dg_quantizer.lhs, cfg.fwd.dg_quantizer.rhs,
+                cfg.drhs.dg_quantizer.rhs, cfg.dlhs.dg_quantizer.rhs)
+  n_delayed = sum(_delayed(q) is not None for q in quantizers)
+  if n_delayed not in (0, 4):
+    return None  # mixed calibrations: one quantization per dot
+  if n_delayed:
+    return _prequantize_delayed(quantizers, specs, lhs, rhs, dd,
+                                reduce_max_lhs)
 
   def new_scales(x):
     mk = lambda: _empty(1, torch.bfloat16, x.device)
@@ -1338,6 +1361,60 @@ def prequantize_for_training(cfg, lhs, rhs, dimension_numbers,
   return lhs_qt, rhs_qt
 
 
+def _sync_reduce(reduce_max, t):
+  """Applies a cross-rank maximum that may be handed over as (tensor, wait)."""
+  if reduce_max is None:
+    return t
+  r = reduce_max(t)
+  if isinstance(r, tuple):
+    r[1]()
+    return r[0]
+  return r
+
+
+def _prequantize_delayed(quantizers, specs, lhs, rhs, dd, reduce_max_lhs):
+  """prequantize_for_training under delayed scaling: every scale comes from
+  its quantizer's history, so each operand is read ONCE in all -- the paired
+  quantization also takes max |x| for the histories (of the forward quantizer
+  directly, of the chained backward quantizer through |Q(max)|)."""
+  from aqt_b200.v2 import aqt_tensor
+  q_fl, q_fr, q_bl, q_br = quantizers
+  f_lhs, f_rhs, b_lhs, b_rhs = specs
+
+  def qt(qvalue, scale):
+    return aqt_tensor.QTensor(qvalue=qvalue, scale=[scale.view(1, 1)],
+                              scale_t=None, bias=[], dequant_dtype=dd)
+
+  def one(x, q_first, sp_first, q_second, sp_second, chain, reduce_max):
+    cal1, cal2 = _delayed(q_first), _delayed(q_second)
+    s1 = cal1.next_scale(x.device, q_first.numerics, x.dtype, q_first.context)
+    s2 = cal2.next_scale(x.device, q_second.numerics, x.dtype,
+                         q_second.context)
+    amax = _empty(1, torch.float32, x.device)
+    if chain == 1:  # x -> q_t (first) -> q_s (second)
+      q_t, q_s = _quantize_pair(x, sp_first, s1, None, sp_second, s2, None,
+                                chain=1, amax_out=amax)
+    else:           # x -> q_s (first) -> q_t (second)
+      q_t, q_s = _quantize_pair(x, sp_second, s2, None, sp_first, s1, None,
+                                chain=2, amax_out=amax)
+    amax = _sync_reduce(reduce_max, amax)
+    if cal1.updates_state(q_first.context):
+      cal1.push_amax(amax)
+    if cal2.updates_state(q_second.context):
+      cal2.push_amax(_requant_amax(amax, sp_first, s1))
+    return q_t, q_s, s1, s2
+
+  # rhs [K, N]: the transposed copy, [N][K], is the forward one
+  q_t, q_s, s1, s2 = one(rhs, q_fr, f_rhs, q_br, b_rhs, 1, None)
+  rhs_qt = qt(q_t.t(), s1)
+  setattr(rhs_qt.qvalue, _BWD_COPY, qt(q_s, s2))
+  # lhs [M, K]: its own orientation is the forward copy
+  q_t, q_s, s1, s2 = one(lhs, q_fl, f_lhs, q_bl, b_lhs, 2, reduce_max_lhs)
+  lhs_qt = qt(q_s, s1)
+  setattr(lhs_qt.qvalue, _BWD_COPY, qt(q_t.t(), s2))
+  return lhs_qt, rhs_qt
+
+
 def bwd_copy(qt):
   """The backward-pass copy made by prequantize_for_training, if any.
 
@@ -1370,15 +1447,34 @@ def cotangent_pair(cfg, res, g, reduce_max=None):
       pres.append(mt.qx.scale[0])
     else:
       pres.append(None)
-  amax = absmax_raw(g)
-  if reduce_max is not None:
-    amax = reduce_max(amax)
-  mk = lambda: _empty(1, torch.bfloat16, g.device)
-  s_dl, s_dr = mk(), mk()
+  q_dl, q_dr = cfg.dlhs.dg_quantizer.lhs, cfg.drhs.dg_quantizer.lhs
+  n_delayed = sum(_delayed(q) is not None for q in (q_dl, q_dr))
+  if n_delayed == 1:
+    return None
   # g [M, N]: own orientation (N contiguous) feeds dlhs, the transposed copy
   # [N][M] feeds drhs.
-  q_t, q_s = _quantize_pair(g, sp_dr, s_dr, pres[1], sp_dl, s_dl, pres[0],
-                            chain=0, amax=amax)
+  if n_delayed:
+    # scales from the histories; max |g| for them from the same read
+    s_dl = _delayed(q_dl).next_scale(g.device, q_dl.numerics, g.dtype,
+                                     q_dl.context)
+    s_dr = _delayed(q_dr).next_scale(g.device, q_dr.numerics, g.dtype,
+                                     q_dr.context)
+    amax = _empty(1, torch.float32, g.device)
+    q_t, q_s = _quantize_pair(g, sp_dr, s_dr, pres[1], sp_dl, s_dl, pres[0],
+                              chain=0, amax_out=amax)
+    amax = _sync_reduce(reduce_max, amax)
+    for q, pre in ((q_dl, pres[0]), (q_dr, pres[1])):
+      if _delayed(q).updates_state(q.context):
+        _delayed(q).push_amax(amax if pre is None else
+                              prescale_amax(amax, pre, _lib.BF16))
+  else:
+    amax = absmax_raw(g)
+    if reduce_max is not None:
+      amax = reduce_max(amax)
+    mk = lambda: _empty(1, torch.bfloat16, g.device)
+    s_dl, s_dr = mk(), mk()
+    q_t, q_s = _quantize_pair(g, sp_dr, s_dr, pres[1], sp_dl, s_dl, pres[0],
+                              chain=0, amax=amax)
   dd = utils.as_dtype(g.dtype)
   qt = lambda qv, sc: aqt_tensor.QTensor(qvalue=qv, scale=[sc.view(1, 1)],
                                          scale_t=None, bias=[], dequant_dtype=dd)

@@ -80,39 +80,58 @@ class DelayedScalingCalibration(calibration.Calibration):
     self.stats  # pylint: disable=pointless-statement
 
   # -- the calibration ---------------------------------------------------------
-  def device_scale(self, x, numerics_, context=None, amax_fn=None,
-                   compute_dtype=None):
-    """One step of the scheme for operand x: returns the one-element scale
-    (dtype `dtype` or x's) and, in TRAIN / CALIBRATE modes, updates bound and
-    amax_history. `amax_fn`: optional callable returning a one-element f32
-    device tensor with max |x| (e.g. taken from whoever produced x); otherwise
-    it is reduced here. `compute_dtype`: the float dtype x counts as when it
-    is a stored int8 / fp8 tensor."""
+  @staticmethod
+  def updates_state(context) -> bool:
+    """TRAIN / CALIBRATE write the state back; SERVE, or no context, do not
+    (reference :77-79, 93-95)."""
+    quant_mode = context.quant_mode if context else utils.QuantMode.SERVE
+    return quant_mode in (utils.QuantMode.TRAIN, utils.QuantMode.CALIBRATE)
+
+  def next_scale(self, device, numerics_, compute_dtype, context=None):
+    """First half of a step: the one-element scale from the history (dtype
+    `dtype` or compute_dtype); updates `bound` in TRAIN / CALIBRATE modes."""
+    from aqt_b200 import _lib
+    from aqt_b200 import engine
+    self.setup(device)
+    spec = engine._spec_for(  # pylint: disable=protected-access
+        numerics_, engine._code(compute_dtype),  # pylint: disable=protected-access
+        self.dtype, True, None, self.po2_scale)
+    scale = engine._empty(  # pylint: disable=protected-access
+        1, engine._CODE_TORCH[spec.scale_dtype], device)  # pylint: disable=protected-access
+    rc = engine._call(  # pylint: disable=protected-access
+        _lib.load().aqtb200_delayed_scaling_scale,
+        self.amax_history.data_ptr(), self.amax_history_length,
+        self.bound.data_ptr(), 1 if self.updates_state(context) else 0,
+        C.byref(spec), scale.data_ptr(), engine._stream())  # pylint: disable=protected-access
+    _lib.check(rc, 'aqtb200_delayed_scaling_scale')
+    return scale
+
+  def push_amax(self, amax):
+    """Second half: max |x| (one-element f32 device tensor) enters the history."""
     import torch
     from aqt_b200 import _lib
     from aqt_b200 import engine
-    self.setup(x.device)
-    quant_mode = context.quant_mode if context else utils.QuantMode.SERVE
-    update = quant_mode in (utils.QuantMode.TRAIN, utils.QuantMode.CALIBRATE)
-    spec = engine._spec_for(  # pylint: disable=protected-access
-        numerics_,
-        engine._code(compute_dtype if compute_dtype is not None else x.dtype),  # pylint: disable=protected-access
-        self.dtype, True, None, self.po2_scale)
-    scale = engine._empty(  # pylint: disable=protected-access
-        1, engine._CODE_TORCH[spec.scale_dtype], x.device)  # pylint: disable=protected-access
-    lib = _lib.load()
+    assert amax.dtype == torch.float32 and amax.numel() == 1
     rc = engine._call(  # pylint: disable=protected-access
-        lib.aqtb200_delayed_scaling_scale, self.amax_history.data_ptr(),
-        self.amax_history_length, self.bound.data_ptr(), 1 if update else 0,
-        C.byref(spec), scale.data_ptr(), engine._stream())  # pylint: disable=protected-access
-    _lib.check(rc, 'aqtb200_delayed_scaling_scale')
-    if update:
-      amax = amax_fn() if amax_fn is not None else engine.absmax_raw(x)
-      assert amax.dtype == torch.float32 and amax.numel() == 1
-      rc = engine._call(  # pylint: disable=protected-access
-          lib.aqtb200_delayed_scaling_push, self.amax_history.data_ptr(),
-          self.amax_history_length, amax.data_ptr(), engine._stream())  # pylint: disable=protected-access
-      _lib.check(rc, 'aqtb200_delayed_scaling_push')
+        _lib.load().aqtb200_delayed_scaling_push, self.amax_history.data_ptr(),
+        self.amax_history_length, amax.data_ptr(), engine._stream())  # pylint: disable=protected-access
+    _lib.check(rc, 'aqtb200_delayed_scaling_push')
+
+  def device_scale(self, x, numerics_, context=None, amax_fn=None,
+                   compute_dtype=None):
+    """One step of the scheme for operand x: returns the one-element scale
+    and, in TRAIN / CALIBRATE modes, updates bound and amax_history.
+    `amax_fn`: optional callable returning a one-element f32 device tensor
+    with max |x| (e.g. taken from whoever produced x); otherwise it is reduced
+    here. `compute_dtype`: the float dtype x counts as when it is a stored
+    int8 / fp8 tensor."""
+    from aqt_b200 import engine
+    scale = self.next_scale(
+        x.device, numerics_,
+        compute_dtype if compute_dtype is not None else x.dtype, context)
+    if self.updates_state(context):
+      self.push_amax(amax_fn() if amax_fn is not None else
+                     engine.absmax_raw(x))
     return scale
 
   def get_bound(self, x, shared_axes, context=None):

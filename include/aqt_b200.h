@@ -210,6 +210,11 @@ int aqtb200_scale_from_amax(const float* amax, int64_t n, const void* prescale,
  * chain = 1: q_s quantizes the values of q_t (x -> q_t -> q_s: q_t is the
  *            forward copy, q_s the backward re-quantization of it);
  * chain = 2: q_t quantizes the values of q_s.
+ * amax_out, when non-NULL, receives max |x| (one f32, set by this call): with
+ * scales that do not depend on this step's maximum (delayed scaling,
+ * flax/delayed_scaling_calibration.py) the operand is then read ONCE in all --
+ * quantized with the history's scales while its maximum for the next steps'
+ * history is taken from the same read.
  * Results are bit-identical to two aqtb200_quantize calls. Other dtypes,
  * per-channel scales or noise: -2 (AQTB200_EUNSUPPORTED); call
  * aqtb200_quantize twice.
@@ -225,7 +230,7 @@ int aqtb200_quantize_pair(const aqtb200_view* x,
                           const void* prescale_t, int32_t prescale_t_dtype, void* q_t,
                           const aqtb200_quant_spec* spec_s, void* scale_s,
                           const void* prescale_s, int32_t prescale_s_dtype, void* q_s,
-                          int32_t chain, const float* amax, void* stream);
+                          int32_t chain, const float* amax, float* amax_out, void* stream);
 int aqtb200_requant_amax(const float* amax, int64_t n, const void* prescale,
                          int32_t prescale_dtype, const aqtb200_quant_spec* spec,
                          const void* scale, float* amax_q_out, void* stream);

@@ -266,9 +266,12 @@ class FakeLib:
 
   def aqtb200_quantize_pair(self, x, spec_t, scale_t, pre_t, pre_t_dtype, q_t,
                             spec_s, scale_s, pre_s, pre_s_dtype, q_s, chain,
-                            amax, stream):
+                            amax, amax_out, stream):
     self.calls.append(('quantize_pair', chain))
     x = _deref(x, _lib.View)
+    if amax_out:
+      _strided(amax_out, _lib.F32, [1], [1], True)[0] = np.abs(
+          _view_array(x).astype(np.float32)).max(initial=0)
     spec_t = _deref(spec_t, _lib.QuantSpec)
     spec_s = _deref(spec_s, _lib.QuantSpec)
     if amax:

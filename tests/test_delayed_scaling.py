@@ -75,7 +75,7 @@ def _check_state(cfg):
 def test_training_steps_match_oracle_on_the_stand_in(monkeypatch, kind,
                                                      np_dtype, po2):
   from tests import fake_lib
-  fake_lib.install(monkeypatch)
+  fake = fake_lib.install(monkeypatch)
   cfg = _delayed_cfg(kind, po2=po2)
   for step, got, want in _run_steps(cfg, 'cpu', np_dtype, 5):
     for a, b, what in zip(got, want, ('out', 'dlhs', 'drhs')):
@@ -86,6 +86,10 @@ def test_training_steps_match_oracle_on_the_stand_in(monkeypatch, kind,
             util.to_numpy(a).astype(np.float32), b.astype(np.float32),
             rtol=2e-2, atol=1e-3, err_msg=f'{what} step {step}')
     _check_state(cfg)
+  # bf16: every operand is read once (paired quantization that also takes the
+  # maximum for the histories); f32: one quantization per dot
+  paired = any(c[0] == 'quantize_pair' for c in fake.calls)
+  assert paired == (np_dtype == orc.bfloat16)
 
 
 def test_state_survives_deep_copies_and_serve_mode_freezes_it(monkeypatch):
