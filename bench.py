@@ -56,7 +56,7 @@ def parse_args():
   p.add_argument('--sustained-seconds', type=float, default=2.0,
                  help='length of the second, long timed region (0 = skip)')
   p.add_argument('--workload', default='c2',
-                 choices=['c1', 'c2', 'c3', 'c4', 'int8', 'stack'],
+                 choices=['c1', 'c2', 'c3', 'c4', 'int8', 'c2_delayed', 'stack'],
                  help='c2 is the headline workload (with the others as '
                  '`extras` in its line); naming another one times that alone')
   p.add_argument('--m', type=int, default=16,
@@ -431,20 +431,32 @@ def build_workload(name, args, torch, dev):
     return (step, 3 * 2 * 1024 * 4096 * 4096, 201e6,
             'config 1: int8 [1024,4096]x[4096,4096] f32 in/out, per-channel '
             'absmax, RNE, fwd+dlhs+drhs', 'hbm')
-  if name == 'int8':
+  if name in ('int8', 'c2_delayed'):
     n = args.size
     lhs = rn((n, n), 1.0, torch.bfloat16)
     rhs = rn((n, n), n ** -0.5, torch.bfloat16)
     g = rn((n, n), 1.0, torch.bfloat16)
-    cfg = make_cfg('int8')
+    if name == 'int8':
+      cfg = make_cfg('int8')
+      what = (f'int8 dot_general {n}^3 fwd+dlhs+drhs, bf16 in/out, per-tensor '
+              'absmax scales (config 2 in int8)')
+    else:
+      import functools
+      from aqt_b200.v2.flax import delayed_scaling_calibration as dsc
+      cfg = make_cfg('fp8')
+      for raw in (cfg.fwd, cfg.dlhs, cfg.drhs):
+        for qz in (raw.dg_quantizer.lhs, raw.dg_quantizer.rhs):
+          qz.calibration = functools.partial(dsc.DelayedScalingCalibration)
+      cfg = config.set_context(cfg, key=None, train_step=None)
+      what = (f'fp8 dot_general {n}^3 fwd+dlhs+drhs, bf16 in/out, per-tensor '
+              'DELAYED scaling (history of 1024 maxima): config 2 without an '
+              'absmax pass on the critical path')
 
     def step():
       out, bp = cfg.vjp(lhs, rhs, DIMS)
       return out, bp(g)
 
-    return (step, 3 * 2 * n ** 3, 6 * 2 * n * n,
-            f'int8 dot_general {n}^3 fwd+dlhs+drhs, bf16 in/out, per-tensor '
-            'absmax scales (config 2 in int8)', 'tensor')
+    return (step, 3 * 2 * n ** 3, 6 * 2 * n * n, what, 'tensor')
   if name == 'c3':
     b, t, h, d = 8, 2048, 32, 128
     q = rn((b, t, h, d), 1.0, torch.bfloat16)
@@ -720,8 +732,8 @@ def run_ours(args, lines):
   if world == 1 and not args.no_extras and args.size == 8192:
     del outs
     extras = {}
-    todo = [('int8', None), ('c1', None), ('c3', None), ('c4', 16), ('c4', 256),
-            ('c4', 4096)]
+    todo = [('int8', None), ('c2_delayed', None), ('c1', None), ('c3', None),
+            ('c4', 16), ('c4', 256), ('c4', 4096)]
     if args.kind == 'int8':
       todo = todo[1:]
     for name, m in todo:
