@@ -126,6 +126,24 @@ SYMBOLS = {
         C.POINTER(DgRawDesc), C.c_void_p]),
     'aqtb200_dequantize': (C.c_int, [
         C.POINTER(View), C.POINTER(View), C.c_int32, C.c_void_p, C.c_void_p]),
+    'aqtb200_set_device': (C.c_int, [C.c_int]),
+    'aqtb200_dev_alloc': (C.c_int, [C.POINTER(C.c_void_p), C.c_size_t]),
+    'aqtb200_dev_free': (C.c_int, [C.c_void_p]),
+    'aqtb200_dev_memset': (C.c_int, [C.c_void_p, C.c_int, C.c_size_t,
+                                     C.c_void_p]),
+    'aqtb200_h2d': (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    'aqtb200_d2h': (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
+    'aqtb200_sync': (C.c_int, [C.c_void_p]),
+    'aqtb200_comm_unique_id': (C.c_int, [C.c_void_p]),
+    'aqtb200_comm_init': (C.c_int, [C.c_int, C.c_int, C.c_void_p,
+                                    C.POINTER(C.c_void_p)]),
+    'aqtb200_comm_destroy': (C.c_int, [C.c_void_p]),
+    'aqtb200_allreduce': (C.c_int, [C.c_void_p, C.c_void_p, C.c_int64,
+                                    C.c_int32, C.c_int32, C.c_void_p]),
+    'aqtb200_reduce_scatter_sum': (C.c_int, [
+        C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
+    'aqtb200_all_gather': (C.c_int, [
+        C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     'aqtb200_version': (C.c_int, []),
     'aqtb200_last_error': (C.c_char_p, []),
     'aqtb200_device_sm_count': (C.c_int, [C.POINTER(C.c_int)]),

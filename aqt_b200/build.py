@@ -13,7 +13,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 LIB = os.path.join(HERE, 'libaqt_b200.so')
-SOURCES = ['quantize.cu', 'gemm.cu', 'noise.cu', 'api.cu']
+SOURCES = ['quantize.cu', 'gemm.cu', 'noise.cu', 'runtime.cu', 'api.cu']
 HEADERS = [os.path.join(CSRC, 'common.cuh'),
            os.path.join(HERE, '..', 'include', 'aqt_b200.h')]
 NVCC_FLAGS = [
@@ -51,7 +51,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
           '-c', src_path, '-o', obj]
       subprocess.run(cmd, check=True)
   if force or _stale(LIB, objs):
-    subprocess.run([nvcc, '-shared', '-o', LIB] + objs + ['-lcudart'],
+    subprocess.run([nvcc, '-shared', '-o', LIB] + objs + ['-lcudart', '-ldl'],
                    check=True)
   return LIB
 

@@ -451,6 +451,12 @@ class DeferredDequant:
   def __init__(self, desc, acc, out, keep):
     self._desc, self.acc, self._out, self._keep = desc, acc, out, keep
 
+  @property
+  def acc_mn(self):
+    """The accumulators as [batch, lhs rows, rhs rows], whichever operand the
+    GEMM put on its tile rows."""
+    return self.acc.transpose(1, 2) if self._desc.swap_ab else self.acc
+
   def finish(self):
     desc = _copy_struct(self._desc)
     desc.out = self._out.data_ptr()

@@ -391,6 +391,46 @@ int aqtb200_dot_general_raw_dequant(const aqtb200_dg_raw_desc* desc,
 int aqtb200_dequantize(const aqtb200_view* q, const aqtb200_view* scale,
                        int32_t dequant_dtype, void* out, void* stream);
 
+/*
+ * Device memory and copies for hosts that bring no allocator of their own (a
+ * ctypes harness, a test written in C). No counterpart in the reference: XLA
+ * owns all buffers there. The copies are asynchronous on `stream`;
+ * aqtb200_sync waits for it. Compute entry points never call these.
+ */
+int aqtb200_set_device(int device);
+int aqtb200_dev_alloc(void** out, size_t bytes);
+int aqtb200_dev_free(void* ptr);
+int aqtb200_dev_memset(void* ptr, int value, size_t bytes, void* stream);
+int aqtb200_h2d(void* dst, const void* src, size_t bytes, void* stream);
+int aqtb200_d2h(void* dst, const void* src, size_t bytes, void* stream);
+int aqtb200_sync(void* stream);
+
+/*
+ * Collectives of the row-sharded path (one process per GPU; the rows of lhs
+ * and of the cotangent split over the ranks). The reference has no collective
+ * on this path (flax/aqt_flax_calibration.py:161-164 refuses cross-replica
+ * statistics); these are what a sharded host needs to keep the result equal
+ * to one device's: a max-all-reduce of the absolute maxima behind per-tensor
+ * scales, and the sum of drhs's raw accumulators before the one dequantization
+ * (all-reduce, or reduce-scatter + all-gather of the finished bands).
+ * NCCL (libnccl.so.2) is opened on first use. Rank 0 makes a 128-byte id with
+ * aqtb200_comm_unique_id and hands it to every rank by whatever channel the
+ * host has; all ranks then call aqtb200_comm_init. dtype: AQTB200_F32, _S32 or
+ * _BF16; the calls are asynchronous on `stream`.
+ */
+int aqtb200_comm_unique_id(void* id128);
+int aqtb200_comm_init(int nranks, int rank, const void* id128, void** comm_out);
+int aqtb200_comm_destroy(void* comm);
+/* in place; op_max != 0: maximum, else sum */
+int aqtb200_allreduce(void* comm, void* buf, int64_t count, int32_t dtype, int32_t op_max,
+                      void* stream);
+/* send holds nranks * recv_count elements; rank r receives the sum of block r */
+int aqtb200_reduce_scatter_sum(void* comm, const void* send, void* recv, int64_t recv_count,
+                               int32_t dtype, void* stream);
+/* recv holds nranks * send_count elements (send may be recv + rank * send_count) */
+int aqtb200_all_gather(void* comm, const void* send, void* recv, int64_t send_count, int32_t dtype,
+                       void* stream);
+
 /* library / device queries */
 int aqtb200_version(void);
 const char* aqtb200_last_error(void);

@@ -355,8 +355,11 @@ def test_wide_kernel_raw_accumulators_and_band_dequantization(kind, shape):
   _sync()
   if kind == 'int8':
     assert torch.equal(acc, acc_simt.reshape(m, n))
-  else:  # the CUDA-core kernel sums in f64
-    bound = lhs.float().abs() @ rhs.float().abs()
+  else:  # the CUDA-core kernel sums in f64; bound: sum |a_k||b_k| of the
+    # quantized operands the accumulators are made of
+    res = engine.dg_raw(raw, lhs, rhs, None, None, dims)[1]
+    bound = (res.lhs.mt.qx.qvalue.float().abs() @
+             res.rhs.mt.qx.qvalue.float().abs())
     assert ((acc - acc_simt.reshape(m, n)).abs() <= 1e-5 * bound + 1e-30).all()
   assert torch.equal(whole, want)
   # bands: rows [0, 128) and [128, m) from copies of the accumulator rows
