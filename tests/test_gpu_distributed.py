@@ -33,8 +33,37 @@ dist.init_process_group('nccl', device_id=dev)
 # max(1 bf16 ulp, 1e-5 * sum |g||lhs|) (bench.sharded_parity_check).
 result = bench.sharded_parity_check(torch, dist, rank, world, dev)
 print(f'rank {rank}: {result}', flush=True)
+
+# the library's own collectives (NCCL opened by the library) against torch's
+import ctypes as C
+from aqt_b200 import _lib
+lib = _lib.load()
+ident = [bytes(128)]
+if rank == 0:
+  buf = C.create_string_buffer(128)
+  _lib.check(lib.aqtb200_comm_unique_id(buf), 'unique_id')
+  ident = [buf.raw]
+dist.broadcast_object_list(ident, src=0)
+comm = C.c_void_p()
+_lib.check(lib.aqtb200_comm_init(world, rank, ident[0], C.byref(comm)), 'comm_init')
+st = torch.cuda.current_stream().cuda_stream
+x = torch.arange(1024, device=dev, dtype=torch.float32) * (rank + 1)
+want = x.clone(); dist.all_reduce(want, op=dist.ReduceOp.MAX)
+_lib.check(lib.aqtb200_allreduce(comm, x.data_ptr(), x.numel(), _lib.F32, 1, st), 'allreduce')
+acc = (torch.arange(4096 * world, device=dev) %% 97).to(torch.int32) * (rank + 3)
+mine = torch.empty(4096, device=dev, dtype=torch.int32)
+_lib.check(lib.aqtb200_reduce_scatter_sum(comm, acc.data_ptr(), mine.data_ptr(), 4096, _lib.S32, st), 'rs')
+want_rs = acc.clone(); dist.all_reduce(want_rs)
+full = torch.zeros(4096 * world, device=dev, dtype=torch.bfloat16)
+full[rank * 4096:(rank + 1) * 4096] = rank + 1
+_lib.check(lib.aqtb200_all_gather(comm, full[rank * 4096:].data_ptr(), full.data_ptr(), 4096, _lib.BF16, st), 'ag')
+torch.cuda.synchronize()
+lib_ok = (torch.equal(x, want) and torch.equal(mine, want_rs[rank * 4096:(rank + 1) * 4096])
+          and all(bool((full[r * 4096:(r + 1) * 4096] == r + 1).all()) for r in range(world)))
+print(f'rank {rank}: library collectives {"ok" if lib_ok else "MISMATCH"}', flush=True)
+_lib.check(lib.aqtb200_comm_destroy(comm), 'comm_destroy')
 dist.destroy_process_group()
-sys.exit(0 if all(v == 'ok' for v in result.values()) else 1)
+sys.exit(0 if lib_ok and all(v == 'ok' for v in result.values()) else 1)
 '''
 
 
