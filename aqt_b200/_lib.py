@@ -52,6 +52,7 @@ class GemmDesc(C.Structure):
       ('out_b0_stride', C.c_int64), ('out_b1_stride', C.c_int64),
       ('out_m_stride', C.c_int64), ('out_n_stride', C.c_int64),
       ('acc_out', C.c_void_p), ('amax_out', C.c_void_p),
+      ('workspace', C.c_void_p), ('workspace_bytes', C.c_size_t),
   ]
 
 
@@ -118,6 +119,7 @@ SYMBOLS = {
     'aqtb200_round_up': (C.c_int64, [C.c_int64, C.c_int64]),
     'aqtb200_gemm_dequant': (C.c_int, [
         C.POINTER(GemmDesc), C.c_void_p, C.c_void_p]),
+    'aqtb200_gemm_workspace_bytes': (C.c_size_t, [C.POINTER(GemmDesc)]),
     'aqtb200_dot_general_raw_workspace_bytes': (C.c_size_t, [
         C.POINTER(DgRawDesc)]),
     'aqtb200_dot_general_raw': (C.c_int, [

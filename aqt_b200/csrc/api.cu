@@ -24,6 +24,7 @@ void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int sm_count();
 int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st);
+size_t gemm_workspace_bytes(const aqtb200_gemm_desc* d);
 int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st);
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
@@ -136,10 +137,20 @@ int aqtb200_device_sm_count(int* out) {
   return 0;
 }
 
+// extents and kernel choice are all gemm_workspace_bytes looks at
+static size_t raw_gemm_scratch(const aqtb200_dg_raw_desc* d) {
+  aqtb200_gemm_desc g{};
+  g.b0 = d->lhs.b0; g.b1 = d->lhs.b1; g.k = d->lhs.cols;
+  g.m = d->swap_ab ? d->rhs.rows : d->lhs.rows;
+  g.n = d->swap_ab ? d->lhs.rows : d->rhs.rows;
+  return gemm_workspace_bytes(&g);
+}
+
 size_t aqtb200_dot_general_raw_workspace_bytes(const aqtb200_dg_raw_desc* d) {
   if (d == nullptr) return 0;
   return align256(aqtb200_quantize_workspace_bytes(&d->lhs, &d->lhs_spec)) +
-         align256(aqtb200_quantize_workspace_bytes(&d->rhs, &d->rhs_spec));
+         align256(aqtb200_quantize_workspace_bytes(&d->rhs, &d->rhs_spec)) +
+         align256(raw_gemm_scratch(d));
 }
 
 int aqtb200_dot_general_raw(const aqtb200_dg_raw_desc* d, void* workspace, size_t workspace_bytes,
@@ -175,6 +186,12 @@ int aqtb200_dot_general_raw(const aqtb200_dg_raw_desc* d, void* workspace, size_
 
   aqtb200_gemm_desc g{};
   fill_gemm_desc(d, L, R, &g);
+  const size_t rhs_ws = align256(aqtb200_quantize_workspace_bytes(&d->rhs, &d->rhs_spec));
+  const size_t gemm_ws = raw_gemm_scratch(d);
+  if (gemm_ws > 0 && workspace_bytes >= lhs_ws + rhs_ws + gemm_ws) {
+    g.workspace = (char*)workspace + lhs_ws + rhs_ws;
+    g.workspace_bytes = gemm_ws;
+  }
   return gemm_dequant(&g, status, st);
 }
 

@@ -57,6 +57,15 @@ struct GemmParams {
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
   int64_t n_tiles3, total_tiles3;  // 512-column tiles of the wide CTA-pair kernel
   int stages1, b_stage;  // single-CTA kernel: ring depth and bytes of one B tile
+  // single-CTA kernel, skinny problems: every tile's contraction is cut into
+  // split_k parts that different CTAs take (units = tiles x parts), so that
+  // the units fill the SMs evenly; the part that finishes a tile last sums
+  // the partial accumulators of all of them and dequantizes.
+  int split_k;
+  int64_t kb_per_part;
+  uint32_t* partials;    // [tile][part][128 rows][n_mma] raw accumulators
+  int32_t* tile_counter;  // [tile][4 row quarters], zeroed before the launch
+  int n_mma;
   int stage_ok;  // output rows can be written as aligned 16-byte pieces
   int tma_store;  // a tensor map of the bf16 output exists: staged rows leave through the TMA unit
   int32_t* status;
@@ -565,6 +574,85 @@ __device__ __forceinline__ void epilogue_slice(const GemmParams& P, const CUtens
   epilogue_tile<IS_INT, EPI>(P, taddr, lane, i0, i1, row, ncol0, stage, sc, amax);
 }
 
+// Epilogue of one (tile, k-part) unit of a split contraction (single-CTA
+// kernel, at most 64 columns, so only the warps of the first column half have
+// work). Each warp owns 32 rows of the tile. It parks its raw accumulators in
+// global scratch and takes a ticket from a counter per (tile, 32-row quarter);
+// the warp that draws the last ticket adds up all parts of its quarter -- in
+// part order, so the f32 sum does not depend on who came last -- and runs the
+// dequantizing chain. Nothing waits on another CTA: whoever is last does the
+// work. The counters are zeroed by the host before every launch.
+template <bool IS_INT>
+__device__ __forceinline__ void epilogue_split(const GemmParams& P, uint32_t taddr, int lane,
+                                               int quarter, int64_t tile, int64_t part,
+                                               int64_t i0, int64_t i1, int64_t row, float sa,
+                                               uint32_t& amax) {
+  const int nm = P.n_mma;  // 16 ... 64, a multiple of 16
+  const int row_in_tile = quarter * 32 + lane;
+  uint32_t* mine = P.partials + ((tile * P.split_k + part) * BM + row_in_tile) * nm;
+  for (int c = 0; c < nm; c += 16) {
+    uint32_t acc[16];
+    tc_ld16(taddr + (uint32_t)c, acc);
+    tc_wait_ld();
+#pragma unroll
+    for (int v = 0; v < 4; ++v)
+      __stcg((uint4*)(mine + c) + v,
+             make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]));
+  }
+  __threadfence();
+  __syncwarp();
+  int prev = 0;
+  if (lane == 0) {
+    prev = atomicAdd(P.tile_counter + tile * 4 + quarter, 1);
+    __threadfence();
+  }
+  prev = __shfl_sync(0xffffffffu, prev, 0);
+  if (prev != P.split_k - 1 || row >= P.m) return;
+  const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
+  const uint32_t* base = P.partials + (tile * P.split_k * BM + row_in_tile) * nm;
+  for (int c = 0; c < nm && c < P.n; c += 4) {
+    uint4 sum = make_uint4(0u, 0u, 0u, 0u);
+    for (int p = 0; p < P.split_k; ++p) {
+      const uint4 v = __ldcg((const uint4*)(base + (int64_t)p * BM * nm + c));
+      if (IS_INT) {
+        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
+      } else {
+        sum.x = __float_as_uint(__fadd_rn(__uint_as_float(sum.x), __uint_as_float(v.x)));
+        sum.y = __float_as_uint(__fadd_rn(__uint_as_float(sum.y), __uint_as_float(v.y)));
+        sum.z = __float_as_uint(__fadd_rn(__uint_as_float(sum.z), __uint_as_float(v.z)));
+        sum.w = __float_as_uint(__fadd_rn(__uint_as_float(sum.w), __uint_as_float(v.w)));
+      }
+    }
+    const uint32_t raw[4] = {sum.x, sum.y, sum.z, sum.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int64_t col = c + j;
+      if (col >= P.n) break;
+      if (P.acc_out != nullptr)
+        ((uint32_t*)P.acc_out)[((i0 * P.b1 + i1) * P.m + row) * P.n + col] = raw[j];
+      if (P.out == nullptr) continue;
+      float r = IS_INT ? __int2float_rn((int)raw[j]) : __uint_as_float(raw[j]);
+      int cur = P.d_dtype;
+      r = round_to(r, cur);
+      const float sb = has_b ? load1(P.b_scale, P.b_scale_dtype,
+                                     i0 * P.sb_b0 + i1 * P.sb_b1 + col * P.sb_n)
+                             : 1.f;
+      if (P.b_scale_first) {
+        if (has_b) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+        if (has_a) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+      } else {
+        if (has_a) r = scale_mul(r, sa, cur, P.a_scale_dtype);
+        if (has_b) r = scale_mul(r, sb, cur, P.b_scale_dtype);
+      }
+      r = round_to(round_to(r, P.d_dtype), P.out_dtype);
+      if (P.amax_out != nullptr) amax_f32(amax, r);
+      const int64_t oi = i0 * P.o_b0 + i1 * P.o_b1 + row * P.o_m + col * P.o_n;
+      if (P.out_dtype == AQTB200_BF16) ((__nv_bfloat16*)P.out)[oi] = __float2bfloat16_rn(r);
+      else ((float*)P.out)[oi] = r;
+    }
+  }
+}
+
 template <bool IS_INT, int EPI>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -619,10 +707,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int64_t t = blockIdx.x; t < P.total_tiles && !fail; t += gridDim.x) {
+      for (int64_t u = blockIdx.x; u < P.total_tiles * P.split_k && !fail; u += gridDim.x) {
+        const int64_t t = u / P.split_k, part = u % P.split_k;
         int64_t i0, i1, mt, nt;
         decode_tile(P, t, i0, i1, mt, nt);
-        for (int64_t kb = 0; kb < P.num_kb; ++kb) {
+        const int64_t kb0 = part * P.kb_per_part;
+        const int64_t kb1 = min(P.num_kb, kb0 + P.kb_per_part);
+        for (int64_t kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
           mbar_expect_tx(&full_bar[stage], A_STAGE + P.b_stage);
           tma_load_4d(smem_a + stage * A_STAGE, &tmA, &full_bar[stage], (int)(kb * BK),
@@ -641,11 +732,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t phase = 0;
       int buf = 0;
       uint32_t aphase = 0;
-      for (int64_t t = blockIdx.x; t < P.total_tiles && !fail; t += gridDim.x) {
+      for (int64_t u = blockIdx.x; u < P.total_tiles * P.split_k && !fail; u += gridDim.x) {
+        const int64_t part = u % P.split_k;
+        const int64_t kb0 = part * P.kb_per_part;
+        const int64_t kb1 = min(P.num_kb, kb0 + P.kb_per_part);
         if (!mbar_wait(&tempty_bar[buf], aphase ^ 1, abortp)) { fail = 2; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
-        for (int64_t kb = 0; kb < P.num_kb; ++kb) {
+        for (int64_t kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full_bar[stage], phase, abortp)) { fail = 2; break; }
           tc_fence_after();
           const uint64_t ad = make_smem_desc(smem_u32(smem_a + stage * A_STAGE));
@@ -654,7 +748,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
           for (int k = 0; k < BK / 32; ++k) {
             // advance 32 bytes of k inside the swizzle row: +2 in 16-byte units
             tc_mma<IS_INT>(d_tmem, ad + (uint64_t)(2 * k), bd + (uint64_t)(2 * k), P.idesc,
-                           (kb > 0 || k > 0) ? 1u : 0u);
+                           (kb > kb0 || k > 0) ? 1u : 0u);
           }
           tc_commit(&empty_bar[stage]);
           if (++stage == P.stages1) { stage = 0; phase ^= 1; }
@@ -673,7 +767,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int buf = 0;
     uint32_t aphase = 0;
     uint32_t amax = 0;
-    for (int64_t t = blockIdx.x; t < P.total_tiles; t += gridDim.x) {
+    for (int64_t u = blockIdx.x; u < P.total_tiles * P.split_k; u += gridDim.x) {
+      const int64_t t = u / P.split_k;
       int64_t i0, i1, mt, nt;
       decode_tile(P, t, i0, i1, mt, nt);
       const int64_t row = mt * BM + quarter * 32 + lane;
@@ -683,9 +778,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
       tc_fence_after();
-      epilogue_slice<IS_INT, EPI>(
-          P, &tmO, tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128), lane,
-          i0, i1, row, nt * BN + half * 128, epi_stage[warp - 2], sc, amax);
+      const uint32_t taddr =
+          tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128);
+      if (P.split_k > 1) {
+        if (half == 0)
+          epilogue_split<IS_INT>(P, taddr, lane, quarter, t, u % P.split_k, i0, i1, row, sc.sa,
+                                 amax);
+      } else {
+        epilogue_slice<IS_INT, EPI>(P, &tmO, taddr, lane, i0, i1, row, nt * BN + half * 128,
+                                    epi_stage[warp - 2], sc, amax);
+      }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty_bar[buf]);
@@ -922,12 +1024,26 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
     int buf = 0;
     uint32_t aphase = 0;
     uint32_t amax = 0;
-    for (int64_t t = cluster_id; t < P.total_tiles2; t += num_clusters) {
-      int64_t i0, i1, mt, nt;
-      decode_tile2(P, t, i0, i1, mt, nt);
-      const int64_t row = mt * BM2 + rank * 128 + quarter * 32 + lane;
-      EpiScales sc;
+    // The scales of a tile are requested one tile ahead: with a short
+    // contraction the accumulator of the next tile is ready as soon as this
+    // one is drained, and a scale fetch issued only then (a round trip to L2,
+    // per-column scales being a strided gather) would sit on every tile's
+    // critical path.
+    int64_t i0 = 0, i1 = 0, mt = 0, nt = 0, row = 0;
+    EpiScales sc;
+    if (cluster_id < P.total_tiles2) {
+      decode_tile2(P, cluster_id, i0, i1, mt, nt);
+      row = mt * BM2 + rank * 128 + quarter * 32 + lane;
       load_epi_scales<EPI>(P, lane, i0, i1, row, nt * BN + half * 128, sc);
+    }
+    for (int64_t t = cluster_id; t < P.total_tiles2; t += num_clusters) {
+      int64_t j0 = 0, j1 = 0, mt2 = 0, nt2 = 0, row2 = 0;
+      EpiScales sc2;
+      if (t + num_clusters < P.total_tiles2) {
+        decode_tile2(P, t + num_clusters, j0, j1, mt2, nt2);
+        row2 = mt2 * BM2 + rank * 128 + quarter * 32 + lane;
+        load_epi_scales<EPI>(P, lane, j0, j1, row2, nt2 * BN + half * 128, sc2);
+      }
       int ok = mbar_wait(&tfull_bar[buf], aphase, abortp) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) { fail = 3; break; }
@@ -940,6 +1056,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
       buf ^= 1;
       if (buf == 0) aphase ^= 1;
+      i0 = j0; i1 = j1; mt = mt2; nt = nt2; row = row2;
+      sc = sc2;
     }
     if (P.amax_out != nullptr) amax_publish(P.amax_out, amax, lane);
     if (lane == 0) tma_store_wait_read();  // shared memory outlives its last store
@@ -1744,6 +1862,9 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   const int64_t n_mma = d->n < BN ? std::max<int64_t>(16, (d->n + 15) / 16 * 16) : BN;
   P.idesc = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(n_mma >> 3) << 17) |
             ((uint32_t)(BM >> 4) << 24);
+  P.n_mma = (int)n_mma;
+  P.split_k = 1;
+  P.kb_per_part = std::max<int64_t>(1, (d->k + BK - 1) / BK);
   P.b_stage = (int)(n_mma * BK);
   P.stages1 = (int)std::min<int64_t>(MAX_STAGES1, (int64_t)(GEMM_SMEM - 1024) / (A_STAGE + P.b_stage));
   P.idesc2 = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
@@ -1754,6 +1875,47 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   P.total_tiles3 = d->b0 * d->b1 * P.m_tiles2 * P.n_tiles3;
 
   return 0;
+}
+
+// Split of the contraction for skinny problems on the single-CTA kernel (few
+// columns, many row tiles -- decode-time serving): with T tiles on S SMs the
+// last wave is mostly empty unless T is a multiple of S; cutting every tile's
+// contraction into `parts` makes T * parts units that fill the SMs evenly.
+// Returns 1 when splitting does not pay.
+static int choose_split(int64_t tiles, int64_t num_kb, int64_t n_mma, int sms) {
+  if (n_mma > 64 || tiles <= 0 || num_kb < 16) return 1;
+  auto eff = [&](int64_t units) {
+    const int64_t waves = (units + sms - 1) / sms;
+    return (double)units / (double)(waves * sms);
+  };
+  int best = 1;
+  double best_eff = eff(tiles);
+  for (int s = 2; s <= 6; ++s) {
+    const int64_t per = (num_kb + s - 1) / s;
+    if (per < 8 || (int64_t)(s - 1) * per >= num_kb) continue;  // no short or empty parts
+    const double e = eff(tiles * s);
+    if (e > best_eff + 0.03) { best_eff = e; best = s; }
+  }
+  return best_eff > eff(tiles) + 0.08 ? best : 1;
+}
+
+static size_t split_workspace_bytes(int64_t tiles, int parts, int64_t n_mma) {
+  const size_t counters = ((size_t)tiles * 4 * sizeof(int32_t) + 255) & ~(size_t)255;
+  return counters + (size_t)tiles * parts * BM * n_mma * sizeof(uint32_t);
+}
+
+static bool single_cta_path(const aqtb200_gemm_desc* d) {
+  // mirrors the kernel choice in gemm_dequant for the automatic setting
+  return g_gemm_impl == 0 && !(d->m > 128 && d->n >= 128) && d->k > 0;
+}
+
+size_t gemm_workspace_bytes(const aqtb200_gemm_desc* d) {
+  if (d == nullptr || !single_cta_path(d) || d->b0 * d->b1 * d->m * d->n == 0) return 0;
+  const int64_t tiles = d->b0 * d->b1 * ((d->m + BM - 1) / BM) * ((d->n + BN - 1) / BN);
+  const int64_t n_mma = d->n < BN ? std::max<int64_t>(16, (d->n + 15) / 16 * 16) : BN;
+  const int64_t num_kb = std::max<int64_t>(1, (d->k + BK - 1) / BK);
+  const int parts = choose_split(tiles, num_kb, n_mma, sm_count());
+  return parts > 1 ? split_workspace_bytes(tiles, parts, n_mma) : 0;
 }
 
 int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
@@ -1815,9 +1977,21 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   rc = make_operand_map(&tmB, d->b, d->k, d->n, d->b1, d->b0, d->ldb, d->b_b1_stride,
                         d->b_b0_stride, pair ? 128 : P.b_stage / BK);
   if (rc) return rc;
+  if (!pair && single_cta_path(d) && d->workspace != nullptr) {
+    const int parts = choose_split(P.total_tiles, P.num_kb, P.n_mma, sm_count());
+    if (parts > 1 && d->workspace_bytes >= split_workspace_bytes(P.total_tiles, parts, P.n_mma) &&
+        ((uintptr_t)d->workspace & 255) == 0) {
+      P.split_k = parts;
+      P.kb_per_part = (P.num_kb + parts - 1) / parts;
+      const size_t counters = ((size_t)P.total_tiles * 4 * sizeof(int32_t) + 255) & ~(size_t)255;
+      P.tile_counter = (int32_t*)d->workspace;
+      P.partials = (uint32_t*)((char*)d->workspace + counters);
+      AQT_CUDA_OK(cudaMemsetAsync(P.tile_counter, 0, counters, st));
+    }
+  }
   const int64_t pair_tiles = wide ? P.total_tiles3 : P.total_tiles2;
   const int grid = pair ? 2 * std::max((int)std::min<int64_t>(pair_tiles, gemm_sms() / 2), 1)
-                        : (int)std::min<int64_t>(P.total_tiles, gemm_sms());
+                        : (int)std::min<int64_t>(P.total_tiles * P.split_k, gemm_sms());
   const size_t smem = wide ? GEMM3_SMEM : (pair ? GEMM2_SMEM : GEMM_SMEM);
   // the shared-memory opt-in is a per-device attribute of each kernel
   int dev = 0;
@@ -1890,6 +2064,10 @@ extern "C" {
 
 int aqtb200_gemm_dequant(const aqtb200_gemm_desc* desc, int32_t* status, void* stream) {
   return aqtb200::gemm_dequant(desc, status, (cudaStream_t)stream);
+}
+
+size_t aqtb200_gemm_workspace_bytes(const aqtb200_gemm_desc* desc) {
+  return aqtb200::gemm_workspace_bytes(desc);
 }
 
 int aqtb200_mma_peak(int32_t is_int, int64_t mmas_per_sm, int32_t* status, void* stream) {

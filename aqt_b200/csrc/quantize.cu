@@ -840,6 +840,22 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       uint32_t q4[4][EPV / 4];  // [column e][row group g]: bytes of rows 4g..4g+3
+      // The noise of the four columns of this pass is requested up front (EPV
+      // floats per column, as 16-byte vectors), so that its latency is paid
+      // once per pass and not once per group of four rows.
+      uint4 nzv[4][EPV / 4];
+      const bool nz_pre = has_noise && P.noise_vec;
+      if (nz_pre) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+          const bool in = row_ok && c < x.cols;
+#pragma unroll
+          for (int g = 0; g < EPV / 4; ++g)
+            nzv[e][g] = in ? ldg16(P.noise.ptr, (nbase + c * P.noise.sc + r0 + 4 * g) * 4)
+                           : make_uint4(0u, 0u, 0u, 0u);
+        }
+      }
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
@@ -867,8 +883,10 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
 #pragma unroll
           for (int g = 0; g < EPV / 4; ++g) {
             float nz[4] = {0.f, 0.f, 0.f, 0.f};
-            if (has_noise && in)
-              loadN<4>(P.noise.ptr, AQTB200_F32, nbase + c * P.noise.sc + r0 + 4 * g, nz);
+            if (has_noise && in) {
+              nz[0] = __uint_as_float(nzv[e][g].x); nz[1] = __uint_as_float(nzv[e][g].y);
+              nz[2] = __uint_as_float(nzv[e][g].z); nz[3] = __uint_as_float(nzv[e][g].w);
+            }
             const uint32_t q = bf16x4_to_s8x4(
                 rw[(2 * g) & 3], rw[(2 * g + 1) & 3], pre2, pre2, PRE != 0,
                 pack_bf16x2(sinv[(4 * g) % EPV], sinv[(4 * g + 1) % EPV]),
@@ -889,7 +907,8 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
               w4[j] = PRE ? apply_pre(v[4 * g + j], p, P.t_dtype) : v[4 * g + j];
             if (has_noise && in) {
               if (P.noise_vec) {
-                loadN<4>(P.noise.ptr, AQTB200_F32, nbase + c * P.noise.sc + r0 + 4 * g, nz);
+                nz[0] = __uint_as_float(nzv[e][g].x); nz[1] = __uint_as_float(nzv[e][g].y);
+                nz[2] = __uint_as_float(nzv[e][g].z); nz[3] = __uint_as_float(nzv[e][g].w);
               } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
@@ -1387,6 +1406,88 @@ quant_row_onepass(OnePassParams O, int64_t nbrow) {
   }
 }
 
+// Short rows (at most 32 sixteen-byte vectors, e.g. the 128-element rows of an
+// attention head): calibrate and quantize in one pass with several rows per
+// warp. Each lane holds one vector of its row; the row maximum is a segmented
+// butterfly over the row's lanes; the quantized vector goes straight back
+// out. One read and one launch where the three-step flow takes two reads and
+// three launches. `dense`: the batch strides are those of a dense
+// [b0][b1][rows] stack, so a row's offset is its flat index times the row stride.
+template <int EPV, int PRE>
+__global__ void __launch_bounds__(256)
+quant_shortrow_onepass(OnePassParams O, int64_t nbrow, int nvec, int dense) {
+  constexpr int ES = 16 / EPV;
+  constexpr int U = 4;
+  const QParams& P = O.q;
+  const DView& x = P.x;
+  const int lane = threadIdx.x & 31;
+  const int rows_per_warp = 32 / nvec;
+  const int sub = lane / nvec, vi = lane % nvec;
+  const int64_t warp_g = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int64_t nwarps = (int64_t)gridDim.x * (blockDim.x >> 5);
+  const int64_t groups = (nbrow + rows_per_warp - 1) / rows_per_warp;
+  const float nz[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int64_t g0 = warp_g * U; g0 < groups; g0 += nwarps * U) {
+    uint4 raw[U];
+    int64_t brow[U];
+    float pconst[U];
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      brow[k] = (g0 + k) * rows_per_warp + sub;
+      raw[k] = make_uint4(0u, 0u, 0u, 0u);
+      pconst[k] = 0.f;
+      if (g0 + k < groups && brow[k] < nbrow) {
+        int64_t off, poff = 0;
+        if (dense) {
+          off = brow[k] * x.sr;
+          if constexpr (PRE == 1) {
+            int64_t i0, i1, r;
+            decode_brow(x, brow[k], i0, i1, r);
+            poff = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+          }
+        } else {
+          int64_t i0, i1, r;
+          decode_brow(x, brow[k], i0, i1, r);
+          off = i0 * x.sb0 + i1 * x.sb1 + r * x.sr;
+          poff = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+        }
+        raw[k] = ldg16(x.ptr, off * ES + (int64_t)vi * 16);
+        if constexpr (PRE == 1) pconst[k] = load1(P.pre.ptr, P.pre.dtype, poff);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      uint4 run = make_uint4(0u, 0u, 0u, 0u);
+      packed_absmax<EPV>(run, raw[k], x.dtype);
+      float m = packed_hmax<EPV>(run, x.dtype);
+      for (int o = nvec >> 1; o > 0; o >>= 1) m = amax_nn(m, __shfl_xor_sync(0xffffffffu, m, o));
+      const bool ok = g0 + k < groups && brow[k] < nbrow;
+      if constexpr (PRE == 1) m = apply_pre_abs(m, pconst[k], P.t_dtype);
+      const float sc = scale_of_amax(m, P.t_dtype, P.s_dtype, O.quant_bound, O.clipping_scale, O.po2);
+      if (ok && vi == 0) {
+        if (P.s_dtype == AQTB200_BF16) ((__nv_bfloat16*)O.scale_out)[brow[k]] = __float2bfloat16_rn(sc);
+        else ((float*)O.scale_out)[brow[k]] = sc;
+      }
+      const float sinv = recip_of_scale(sc, P.s_dtype);
+      const float sinv4[4] = {sinv, sinv, sinv, sinv};
+      float v[EPV];
+      unpack<EPV>(raw[k], x.dtype, v);
+      if constexpr (PRE == 1) {
+#pragma unroll
+        for (int j = 0; j < EPV; ++j) v[j] = apply_pre(v[j], pconst[k], P.t_dtype);
+      }
+      uint32_t outw[EPV / 4];
+#pragma unroll
+      for (int g = 0; g < EPV / 4; ++g) outw[g] = quant4(v + 4 * g, sinv4, nz, false, P);
+      if (ok) {
+        uint8_t* qp = P.q + brow[k] * P.ldq + (int64_t)vi * EPV;
+        if constexpr (EPV == 8) *(uint2*)qp = make_uint2(outw[0], outw[1]);
+        else *(uint32_t*)qp = outw[0];
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // quantize, contraction contiguous: one thread per 16 output bytes.
 template <bool VEC>
@@ -1644,12 +1745,16 @@ absmax_dual_kernel(DualParams P, int64_t row_tiles, int64_t col_tiles, int64_t t
     uint32_t run_t[4] = {0u, 0u, 0u, 0u};  // per row pair, max over every column of the strip
     for (int64_t ct = 0; ct < col_tiles; ++ct) {
       uint4 raw[2][4];
+      uint32_t ptv[2][4];  // the columns' prescales, requested together with the data
 #pragma unroll
       for (int i = 0; i < 2; ++i)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
           raw[i][e] = (row_ok && c < x.cols) ? ldg16(xp, c * x.sc * 2) : make_uint4(0u, 0u, 0u, 0u);
+          ptv[i][e] = 0x3f80u;
+          if (PRE_T && c < x.cols)
+            ptv[i][e] = __ldg((const unsigned short*)P.pre_t + i0 * P.pt_b0 + i1 * P.pt_b1 + c * P.pt_c);
         }
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
@@ -1657,11 +1762,7 @@ absmax_dual_kernel(DualParams P, int64_t row_tiles, int64_t col_tiles, int64_t t
         for (int e = 0; e < 4; ++e) {
           const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
           const uint32_t w[4] = {raw[i][e].x, raw[i][e].y, raw[i][e].z, raw[i][e].w};
-          uint32_t pt2 = 0x3f803f80u;
-          if (PRE_T && c < x.cols) {
-            const uint32_t v = __ldg((const unsigned short*)P.pre_t + i0 * P.pt_b0 + i1 * P.pt_b1 + c * P.pt_c);
-            pt2 = v | (v << 16);
-          }
+          const uint32_t pt2 = ptv[i][e] | (ptv[i][e] << 16);
           uint32_t m2 = 0u;
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -1735,11 +1836,20 @@ quant_dual_kernel(DualParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
     for (int i = 0; i < 2; ++i) {
       uint4 raw[4];
       uint4 nt[4][2], ns[4][2];
+      uint32_t ptv[4];  // per column: prescale of T (bf16 bits) ...
+      float isv[4];     // ... and reciprocal scale of S
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
         const bool in = row_ok && c < x.cols;
         raw[e] = in ? ldg16(xp, c * x.sc * 2) : make_uint4(0u, 0u, 0u, 0u);
+        ptv[e] = 0x3f80u;
+        isv[e] = 1.f;
+        if (in) {
+          if (PRE_T)
+            ptv[e] = __ldg((const unsigned short*)P.pre_t + i0 * P.pt_b0 + i1 * P.pt_b1 + c * P.pt_c);
+          isv[e] = __ldg(P.sinv_s + b * x.cols + c);
+        }
         if (NOISE) {
           const int64_t no = (xoff + c * x.sc) * 4;
           nt[e][0] = in ? ldg16(P.noise_t, no) : make_uint4(0u, 0u, 0u, 0u);
@@ -1753,15 +1863,8 @@ quant_dual_kernel(DualParams P, int64_t row_tiles, int64_t col_tiles, int64_t to
       for (int e = 0; e < 4; ++e) {
         const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
         const bool in = row_ok && c < x.cols;
-        uint32_t pt2 = 0x3f803f80u, is2 = 0x3f803f80u;
-        if (in) {
-          if (PRE_T) {
-            const uint32_t v = __ldg((const unsigned short*)P.pre_t + i0 * P.pt_b0 + i1 * P.pt_b1 + c * P.pt_c);
-            pt2 = v | (v << 16);
-          }
-          const float s = __ldg(P.sinv_s + b * x.cols + c);
-          is2 = pack_bf16x2(s, s);
-        }
+        const uint32_t pt2 = ptv[e] | (ptv[e] << 16);
+        const uint32_t is2 = pack_bf16x2(isv[e], isv[e]);
         const uint32_t w[4] = {raw[e].x, raw[e].y, raw[e].z, raw[e].w};
         float fnt[8], fns[8];
         if (NOISE) {
@@ -1986,6 +2089,32 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
     }                                                                                    \
   } while (0)
 
+  // Per-row scales over short rows (several rows per warp): one kernel, one read.
+  {
+    const int64_t row_vecs = xv->cols / epv;
+    if (scale_in == nullptr && want_q && amax_only_out == nullptr && fast_row && epv != 16 &&
+        !P.per_tensor && P.noise.ptr == nullptr && pre_kind != 2 && xv->cols % 16 == 0 &&
+        xv->cols % epv == 0 && row_vecs >= 1 && row_vecs <= 32 && (row_vecs & (row_vecs - 1)) == 0 &&
+        nbrow > 0) {
+      OnePassParams O{};
+      O.q = P;
+      O.quant_bound = spec->quant_bound; O.clipping_scale = spec->clipping_scale;
+      O.po2 = spec->po2_scale; O.scale_out = scale_out;
+      const int dense = (xv->b1 <= 1 || P.x.sb1 == xv->rows * P.x.sr) &&
+                        (xv->b0 <= 1 || P.x.sb0 == xv->b1 * xv->rows * P.x.sr);
+      const int64_t groups = (nbrow + (32 / row_vecs) - 1) / (32 / row_vecs);
+      const int grid = grid_for((groups + 31) / 32, 8);
+      if (epv == 4) {
+        if (pre_kind == 0) quant_shortrow_onepass<4, 0><<<grid, 256, 0, st>>>(O, nbrow, (int)row_vecs, dense);
+        else quant_shortrow_onepass<4, 1><<<grid, 256, 0, st>>>(O, nbrow, (int)row_vecs, dense);
+      } else {
+        if (pre_kind == 0) quant_shortrow_onepass<8, 0><<<grid, 256, 0, st>>>(O, nbrow, (int)row_vecs, dense);
+        else quant_shortrow_onepass<8, 1><<<grid, 256, 0, st>>>(O, nbrow, (int)row_vecs, dense);
+      }
+      AQT_CUDA_OK(cudaGetLastError()); count_launch();
+      return 0;
+    }
+  }
   // Per-row scales over rows that fit in a block: one kernel, one read.
   {
     const int nv = epv == 16 ? 1 : 16 / epv;     // input vectors per 16 outputs

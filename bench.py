@@ -459,6 +459,8 @@ def build_workload(name, args, torch, dev):
     return (step, 3 * 2 * n ** 3, 6 * 2 * n * n, what, 'tensor')
   if name == 'c3':
     b, t, h, d = 8, 2048, 32, 128
+    if os.environ.get('AQT_C3_BH'):  # a slice of the batch, for profiling
+      b, h = (int(v) for v in os.environ['AQT_C3_BH'].split(','))
     q = rn((b, t, h, d), 1.0, torch.bfloat16)
     k = rn((b, t, h, d), 1.0, torch.bfloat16)
     g = rn((b, h, t, t), 1.0, torch.bfloat16)
@@ -482,8 +484,8 @@ def build_workload(name, args, torch, dev):
       out, bp = cfg.vjp(q, k, dims)
       return out, bp(g)
 
-    return (step, 3 * 2 * b * h * t * t * d, 5.1e9,
-            "config 3: int8 einsum 'bthd,bshd->bhts' B8 H32 T=S=2048 D128, "
+    return (step, 3 * 2 * b * h * t * t * d, 5.1e9 * (b * h) / 256.0,
+            f"config 3: int8 einsum 'bthd,bshd->bhts' B{b} H{h} T=S=2048 D128, "
             'bf16, per-token scales, fwd + both gradients, stochastic '
             'rounding from 4 given f32 noise tensors (2 x 4.29 GB + 2 x 0.27 GB '
             'read on top of the minimum bytes)', 'hbm')

@@ -320,6 +320,14 @@ typedef struct aqtb200_gemm_desc {
      calibrator (flax/delayed_scaling_calibration.py:119-124) -- then needs no
      pass of its own over it. NULL = not wanted. */
   float* amax_out;
+  /* optional scratch, 256-byte aligned, aqtb200_gemm_workspace_bytes() bytes:
+     with it a skinny problem (at most 64 columns against many row tiles, the
+     decode-time serving GEMM) has its contraction split into parts that fill
+     the SMs evenly, the part that finishes a tile last summing the others'
+     accumulators and dequantizing. Without it (NULL) every tile is one unit of
+     work. Results are identical for int8; fp8 sums its parts in part order. */
+  void* workspace;
+  size_t workspace_bytes;
 } aqtb200_gemm_desc;
 
 /* status: device int32[4], zeroed by the caller before first use; a kernel
@@ -327,6 +335,9 @@ typedef struct aqtb200_gemm_desc {
  * May be NULL. */
 int aqtb200_gemm_dequant(const aqtb200_gemm_desc* desc, int32_t* status,
                          void* stream);
+/* scratch that lets aqtb200_gemm_dequant split the contraction (0 when the
+ * problem would not be split) */
+size_t aqtb200_gemm_workspace_bytes(const aqtb200_gemm_desc* desc);
 
 /*
  * aqtb200_dot_general_raw: one whole DotGeneralRaw.__call__

@@ -240,7 +240,11 @@ def test_every_tensor_core_kernel_agrees_with_cuda_core_kernel(impl, shape,
 
 
 @pytest.mark.parametrize('shape', [(16, 512, 1024), (1, 256, 4096),
-                                   (64, 1040, 520), (40, 144, 2048)])
+                                   (64, 1040, 520), (40, 144, 2048),
+                                   # long contractions: split into parts that
+                                   # other CTAs take, summed by the last one
+                                   (16, 4096, 2048), (33, 8192, 1000),
+                                   (64, 2048, 4736)])
 @pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
 def test_skinny_lhs_uses_narrow_mmas_and_agrees(shape, np_dtype):
   """A few rows against many: the planner puts the many on the tile's row side
@@ -263,6 +267,29 @@ def test_skinny_lhs_uses_narrow_mmas_and_agrees(shape, np_dtype):
   want, _ = orc.dg_raw(raw, util.to_numpy(lhs), util.to_numpy(rhs), None, None,
                        dims)
   _exact(a[0], want, 'out vs oracle')
+
+
+def test_skinny_fp8_with_split_contraction():
+  """fp8 through the split contraction: parts are added in part order."""
+  m, k, n = 16, 8192, 2048
+  rng = np.random.default_rng(21)
+  dims = (((1,), (0,)), ((), ()))
+  lhs = util.rand_normal(rng, (m, k), 1.0, orc.bfloat16)
+  rhs = util.rand_normal(rng, (k, n), 0.02, orc.bfloat16)
+  raw = aqt.dot_general_raw_make('e4m3', 'e4m3')
+  got, res, acc = engine.dg_raw(raw, _cuda(lhs), _cuda(rhs), None, None, dims,
+                                want_acc=True)
+  _sync()
+  want, wres = orc.dg_raw(raw, lhs, rhs, None, None, dims)
+  _exact(res.lhs.mt.qx.qvalue, wres.lhs.qx.qvalue, 'q_lhs')
+  f = lambda a: np.abs(np.asarray(a).astype(np.float32).astype(np.float64))
+  mag = f(wres.lhs.qx.qvalue) @ f(wres.rhs.qx.qvalue)
+  exact = (np.asarray(wres.lhs.qx.qvalue).astype(np.float64) @
+           np.asarray(wres.rhs.qx.qvalue).astype(np.float64))
+  a = util.to_numpy(acc.reshape(m, n)).astype(np.float64)
+  assert (np.abs(a - exact) <= 1e-5 * mag + 1e-30).all()
+  _fp8_close(got, want, mag * f(wres.lhs.qx.scale[0]) * f(wres.rhs.qx.scale[0])
+             , 'out')
 
 
 @pytest.mark.parametrize('k', [16, 32, 64, 128])
