@@ -147,6 +147,7 @@ SYMBOLS = {
     'aqtb200_all_gather': (C.c_int, [
         C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int32, C.c_void_p]),
     'aqtb200_version': (C.c_int, []),
+    'aqtb200_has_xla_ffi': (C.c_int, []),
     'aqtb200_last_error': (C.c_char_p, []),
     'aqtb200_device_sm_count': (C.c_int, [C.POINTER(C.c_int)]),
     'aqtb200_kernel_launch_count': (C.c_int64, []),

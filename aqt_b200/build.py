@@ -13,7 +13,8 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, 'csrc')
 LIB = os.path.join(HERE, 'libaqt_b200.so')
-SOURCES = ['quantize.cu', 'gemm.cu', 'noise.cu', 'runtime.cu', 'api.cu']
+SOURCES = ['quantize.cu', 'gemm.cu', 'noise.cu', 'runtime.cu', 'api.cu',
+           'xla_ffi.cc']
 HEADERS = [os.path.join(CSRC, 'common.cuh'),
            os.path.join(HERE, '..', 'include', 'aqt_b200.h')]
 NVCC_FLAGS = [
@@ -27,6 +28,16 @@ def _nvcc():
   if not os.path.exists(exe):
     raise RuntimeError('nvcc not found; the sm_100a kernels cannot be built')
   return exe
+
+
+def _ffi_include():
+  """-I for jaxlib's XLA FFI header when jax is installed (csrc/xla_ffi.cc is
+  empty without it)."""
+  try:
+    import jax.ffi  # pylint: disable=import-outside-toplevel
+    return ['-I', jax.ffi.include_dir()]
+  except Exception:  # pylint: disable=broad-except
+    return []
 
 
 def _stale(target, deps):
@@ -44,11 +55,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
   objs = []
   for src in SOURCES:
     src_path = os.path.join(CSRC, src)
-    obj = os.path.join(build_dir, src.replace('.cu', '.o'))
+    obj = os.path.join(build_dir, os.path.splitext(src)[0] + '.o')
     objs.append(obj)
     if force or _stale(obj, [src_path] + HEADERS):
-      cmd = [nvcc] + NVCC_FLAGS + (['-Xptxas', '-v'] if verbose else []) + [
-          '-c', src_path, '-o', obj]
+      cmd = [nvcc] + NVCC_FLAGS + _ffi_include() + (
+          ['-Xptxas', '-v'] if verbose else []) + ['-c', src_path, '-o', obj]
       subprocess.run(cmd, check=True)
   if force or _stale(LIB, objs):
     subprocess.run([nvcc, '-shared', '-o', LIB] + objs + ['-lcudart', '-ldl'],

@@ -607,36 +607,63 @@ __device__ __forceinline__ void epilogue_split(const GemmParams& P, uint32_t tad
     __threadfence();
   }
   prev = __shfl_sync(0xffffffffu, prev, 0);
-  if (prev != P.split_k - 1 || row >= P.m) return;
+  if (prev != P.split_k - 1) return;
+  // Last to arrive: every part of these 32 rows is in global memory. All loads
+  // of a 16-column chunk (up to MAX_SPLIT parts x 4 vectors) and the columns'
+  // scales are requested together: the fix-up runs once per tile quarter and
+  // would otherwise pay one L2 round trip per vector.
+  constexpr int MAX_SPLIT = 6;
   const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
+  const bool row_ok = row < P.m;
   const uint32_t* base = P.partials + (tile * P.split_k * BM + row_in_tile) * nm;
-  for (int c = 0; c < nm && c < P.n; c += 4) {
-    uint4 sum = make_uint4(0u, 0u, 0u, 0u);
-    for (int p = 0; p < P.split_k; ++p) {
-      const uint4 v = __ldcg((const uint4*)(base + (int64_t)p * BM * nm + c));
-      if (IS_INT) {
-        sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
-      } else {
-        sum.x = __float_as_uint(__fadd_rn(__uint_as_float(sum.x), __uint_as_float(v.x)));
-        sum.y = __float_as_uint(__fadd_rn(__uint_as_float(sum.y), __uint_as_float(v.y)));
-        sum.z = __float_as_uint(__fadd_rn(__uint_as_float(sum.z), __uint_as_float(v.z)));
-        sum.w = __float_as_uint(__fadd_rn(__uint_as_float(sum.w), __uint_as_float(v.w)));
-      }
-    }
-    const uint32_t raw[4] = {sum.x, sum.y, sum.z, sum.w};
+  // lane l holds the scales of columns l and l + 32
+  float sb_lane[2] = {1.f, 1.f};
+  if (has_b) {
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const int64_t col = c + j;
-      if (col >= P.n) break;
+    for (int h = 0; h < 2; ++h) {
+      const int64_t col = lane + 32 * h;
+      if (col < P.n && col < nm)
+        sb_lane[h] = load1(P.b_scale, P.b_scale_dtype, i0 * P.sb_b0 + i1 * P.sb_b1 + col * P.sb_n);
+    }
+  }
+  for (int c0 = 0; c0 < nm && c0 < P.n; c0 += 16) {
+    uint4 v[MAX_SPLIT][4];
+#pragma unroll
+    for (int p = 0; p < MAX_SPLIT; ++p)
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        v[p][q] = p < P.split_k ? __ldcg((const uint4*)(base + (int64_t)p * BM * nm + c0) + q)
+                                : make_uint4(0u, 0u, 0u, 0u);
+    uint32_t raw[16];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      uint4 sum = v[0][q];
+#pragma unroll
+      for (int p = 1; p < MAX_SPLIT; ++p) {
+        if (IS_INT) {
+          sum.x += v[p][q].x; sum.y += v[p][q].y; sum.z += v[p][q].z; sum.w += v[p][q].w;
+        } else if (p < P.split_k) {  // adding +0.0 could turn a -0.0 sum into +0.0
+          sum.x = __float_as_uint(__fadd_rn(__uint_as_float(sum.x), __uint_as_float(v[p][q].x)));
+          sum.y = __float_as_uint(__fadd_rn(__uint_as_float(sum.y), __uint_as_float(v[p][q].y)));
+          sum.z = __float_as_uint(__fadd_rn(__uint_as_float(sum.z), __uint_as_float(v[p][q].z)));
+          sum.w = __float_as_uint(__fadd_rn(__uint_as_float(sum.w), __uint_as_float(v[p][q].w)));
+        }
+      }
+      raw[4 * q] = sum.x; raw[4 * q + 1] = sum.y; raw[4 * q + 2] = sum.z; raw[4 * q + 3] = sum.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      const int64_t col = c0 + j;
+      // every lane takes part in the shuffle; the rest is per lane
+      const float sb = __shfl_sync(0xffffffffu, (c0 + j) < 32 ? sb_lane[0] : sb_lane[1],
+                                   (c0 + j) & 31);
+      if (col >= P.n || !row_ok) continue;
       if (P.acc_out != nullptr)
         ((uint32_t*)P.acc_out)[((i0 * P.b1 + i1) * P.m + row) * P.n + col] = raw[j];
       if (P.out == nullptr) continue;
       float r = IS_INT ? __int2float_rn((int)raw[j]) : __uint_as_float(raw[j]);
       int cur = P.d_dtype;
       r = round_to(r, cur);
-      const float sb = has_b ? load1(P.b_scale, P.b_scale_dtype,
-                                     i0 * P.sb_b0 + i1 * P.sb_b1 + col * P.sb_n)
-                             : 1.f;
       if (P.b_scale_first) {
         if (has_b) r = scale_mul(r, sb, cur, P.b_scale_dtype);
         if (has_a) r = scale_mul(r, sa, cur, P.a_scale_dtype);

@@ -35,6 +35,7 @@ struct QParams {
   int fast_bf16;  // bf16 in, bf16 scale, fp8 out, no noise: packed bf16 arithmetic
   int pre_bf16;   // bf16 input, bf16 prescale, bf16 compute dtype: x * pre as packed bf16 multiplies
   int int_bf16;   // bf16 in, bf16 scale and prescale, int8 out (with or without noise): packed bf16 arithmetic
+  int s8_bf16;    // int8 in (a stored QTensor counted as bf16), bf16 scale and prescale, int8 out: the same arithmetic
   uint32_t* amax;
   float* sinv;
   uint8_t* q;
@@ -394,6 +395,12 @@ __device__ __forceinline__ uint32_t bf16x4_to_s8x4(uint32_t w0, uint32_t w1, uin
            << (16 * h);
   }
   return out;
+}
+
+// four int8 values of one word -> two packed bf16 pairs (exact)
+__device__ __forceinline__ void s8x4_to_bf16x2x2(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  lo = pack_bf16x2((float)(signed char)(w & 0xffu), (float)(signed char)((w >> 8) & 0xffu));
+  hi = pack_bf16x2((float)(signed char)((w >> 16) & 0xffu), (float)(signed char)(w >> 24));
 }
 
 constexpr int kFastRowChunk = 8192;  // most elements of one (row, chunk) work unit
@@ -889,6 +896,28 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
             }
             const uint32_t q = bf16x4_to_s8x4(
                 rw[(2 * g) & 3], rw[(2 * g + 1) & 3], pre2, pre2, PRE != 0,
+                pack_bf16x2(sinv[(4 * g) % EPV], sinv[(4 * g + 1) % EPV]),
+                pack_bf16x2(sinv[(4 * g + 2) % EPV], sinv[(4 * g + 3) % EPV]), nz, has_noise,
+                P.clip_bound);
+            q4[e][g] = in ? q : 0u;
+          }
+        } else if (EPV == 16 && P.s8_bf16 && (!has_noise || P.noise_vec)) {
+          // a stored int8 operand re-quantized (the backward pass, use_fwd_quant):
+          // widen to bf16 exactly, then the packed bf16 arithmetic of the bf16 path
+          float p = pconst;
+          if constexpr (PRE == 2) p = in ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
+          const uint32_t pre2 = pack_bf16x2(p, p);
+#pragma unroll
+          for (int g = 0; g < EPV / 4; ++g) {
+            float nz[4] = {0.f, 0.f, 0.f, 0.f};
+            if (has_noise && in) {
+              nz[0] = __uint_as_float(nzv[e][g].x); nz[1] = __uint_as_float(nzv[e][g].y);
+              nz[2] = __uint_as_float(nzv[e][g].z); nz[3] = __uint_as_float(nzv[e][g].w);
+            }
+            uint32_t w0, w1;
+            s8x4_to_bf16x2x2(rw[g & 3], w0, w1);
+            const uint32_t q = bf16x4_to_s8x4(
+                w0, w1, pre2, pre2, PRE != 0,
                 pack_bf16x2(sinv[(4 * g) % EPV], sinv[(4 * g + 1) % EPV]),
                 pack_bf16x2(sinv[(4 * g + 2) % EPV], sinv[(4 * g + 3) % EPV]), nz, has_noise,
                 P.clip_bound);
@@ -1470,15 +1499,33 @@ quant_shortrow_onepass(OnePassParams O, int64_t nbrow, int nvec, int dense) {
       }
       const float sinv = recip_of_scale(sc, P.s_dtype);
       const float sinv4[4] = {sinv, sinv, sinv, sinv};
-      float v[EPV];
-      unpack<EPV>(raw[k], x.dtype, v);
-      if constexpr (PRE == 1) {
-#pragma unroll
-        for (int j = 0; j < EPV; ++j) v[j] = apply_pre(v[j], pconst[k], P.t_dtype);
-      }
       uint32_t outw[EPV / 4];
+      if (EPV == 8 && (P.int_bf16 || P.fast_bf16)) {
+        // all-bf16: packed multiplies, one rounding each (see bf16x2_to_fp8x2)
+        const uint32_t s2 = pack_bf16x2(sinv, sinv), p2 = pack_bf16x2(pconst[k], pconst[k]);
+        const uint32_t w[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+        if (P.int_bf16) {
 #pragma unroll
-      for (int g = 0; g < EPV / 4; ++g) outw[g] = quant4(v + 4 * g, sinv4, nz, false, P);
+          for (int g = 0; g < EPV / 4; ++g)
+            outw[g] = bf16x4_to_s8x4(w[(2 * g) & 3], w[(2 * g + 1) & 3], p2, p2, PRE == 1, s2, s2,
+                                     nz, false, P.clip_bound);
+        } else {
+          const __nv_fp8_interpretation_t f8k = P.qdtype == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
+#pragma unroll
+          for (int g = 0; g < EPV / 4; ++g)
+            outw[g] = bf16x2_to_fp8x2(w[(2 * g) & 3], p2, PRE == 1, s2, f8k) |
+                      (bf16x2_to_fp8x2(w[(2 * g + 1) & 3], p2, PRE == 1, s2, f8k) << 16);
+        }
+      } else {
+        float v[EPV];
+        unpack<EPV>(raw[k], x.dtype, v);
+        if constexpr (PRE == 1) {
+#pragma unroll
+          for (int j = 0; j < EPV; ++j) v[j] = apply_pre(v[j], pconst[k], P.t_dtype);
+        }
+#pragma unroll
+        for (int g = 0; g < EPV / 4; ++g) outw[g] = quant4(v + 4 * g, sinv4, nz, false, P);
+      }
       if (ok) {
         uint8_t* qp = P.q + brow[k] * P.ldq + (int64_t)vi * EPV;
         if constexpr (EPV == 8) *(uint2*)qp = make_uint2(outw[0], outw[1]);
@@ -2067,6 +2114,8 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
                P.t_dtype == AQTB200_BF16;
   P.int_bf16 = P.x.dtype == AQTB200_BF16 && P.t_dtype == AQTB200_BF16 && P.s_dtype == AQTB200_BF16 &&
                P.kind == AQTB200_NUM_INT && (P.pre.ptr == nullptr || P.pre.dtype == AQTB200_BF16);
+  P.s8_bf16 = P.x.dtype == AQTB200_S8 && P.t_dtype == AQTB200_BF16 && P.s_dtype == AQTB200_BF16 &&
+              P.kind == AQTB200_NUM_INT && (P.pre.ptr == nullptr || P.pre.dtype == AQTB200_BF16);
   // prescale class: 0 none, 1 constant along the contraction index, 2 varying
   const int pre_kind = P.pre.ptr == nullptr ? 0 : (P.pre.sc == 0 || xv->cols <= 1 ? 1 : 2);
   const bool fast_row = row_mode && row_vec_ok(P.x, xv->cols);

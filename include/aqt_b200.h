@@ -444,6 +444,9 @@ int aqtb200_all_gather(void* comm, const void* send, void* recv, int64_t send_co
 
 /* library / device queries */
 int aqtb200_version(void);
+/* 1 when the library was built with jaxlib's xla/ffi/api/ffi.h available and so
+ * also exports the XLA FFI handler AqtB200DgRaw (csrc/xla_ffi.cc), else 0. */
+int aqtb200_has_xla_ffi(void);
 const char* aqtb200_last_error(void);
 int aqtb200_device_sm_count(int* out);
 /* number of kernels this library has launched in this process (all threads);

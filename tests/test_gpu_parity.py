@@ -312,6 +312,27 @@ def test_short_contraction_rows(k, np_dtype):
   _exact(got, want, 'out')
 
 
+@pytest.mark.parametrize('k', [16, 64, 256])
+@pytest.mark.parametrize('bits', [8, 4, 'e4m3', 'e5m2'])
+def test_short_rows_quantized_in_one_pass(k, bits):
+  """bf16 rows of at most 32 vectors, contraction axis last: calibrated and
+  quantized by one kernel in packed bf16 arithmetic; values and scales bit for
+  bit for every numerics."""
+  rng = np.random.default_rng(k + 7)
+  dims = (((3,), (3,)), ((0, 2), (0, 2)))
+  lhs = util.rand_normal(rng, (2, 150, 3, k), 1.0, orc.bfloat16)
+  rhs = util.rand_normal(rng, (2, 90, 3, k), 3.0, orc.bfloat16)
+  lhs[0, 7, 1, :] = 0
+  raw = aqt.dot_general_raw_make(bits, bits)
+  _, res = engine.dg_raw(raw, _cuda(lhs), _cuda(rhs), None, None, dims)
+  _sync()
+  _, wres = orc.dg_raw(raw, lhs, rhs, None, None, dims)
+  for side in ('lhs', 'rhs'):
+    g, w = getattr(res, side).mt.qx, getattr(wres, side).qx
+    _exact(g.scale[0], w.scale[0], 's_' + side)
+    _exact(g.qvalue, w.qvalue, 'q_' + side)
+
+
 def test_wide_kernel_batched_and_transposed_output():
   """The 256 x 512 kernel under batch dims and the drhs output transpose."""
   rng = np.random.default_rng(11)
