@@ -57,13 +57,16 @@ struct GemmParams {
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
   int64_t n_tiles3, total_tiles3;  // 512-column tiles of the wide CTA-pair kernel
   int stages1, b_stage;  // single-CTA kernel: ring depth and bytes of one B tile
-  // single-CTA kernel, skinny problems: every tile's contraction is cut into
-  // split_k parts that different CTAs take (units = tiles x parts), so that
-  // the units fill the SMs evenly; the part that finishes a tile last sums
-  // the partial accumulators of all of them and dequantizes.
-  int split_k;
-  int64_t kb_per_part;
-  uint32_t* partials;    // [tile][part][128 rows][n_mma] raw accumulators
+  int stages3;  // wide kernel: ring depth, 2 (short contractions: the freed stages hold a second
+                // set of staging rows for the epilogue) or STAGES3
+  // single-CTA kernel, skinny problems: the k-slabs of all tiles form one
+  // sequence that is cut into equal shares, one per CTA, so every SM streams
+  // the same number of bytes whatever the tile count. A tile whose slabs fall
+  // into several shares is computed in parts; the part that finishes last
+  // sums the partial accumulators of all of them and dequantizes.
+  int stream_k;          // 0: whole tiles, round robin
+  int max_parts;         // most parts any tile is cut into (slots per tile in `partials`)
+  uint32_t* partials;    // [tile][max_parts][128 rows][n_mma] raw accumulators
   int32_t* tile_counter;  // [tile][4 row quarters], zeroed before the launch
   int n_mma;
   int stage_ok;  // output rows can be written as aligned 16-byte pieces
@@ -139,6 +142,10 @@ __device__ __forceinline__ void tma_store_4d(const CUtensorMap* tm, const void* 
 // store this thread has issued (the global writes may still be in flight).
 __device__ __forceinline__ void tma_store_wait_read() {
   asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+// The same, but the newest store may still be reading (two staging buffers in turn).
+__device__ __forceinline__ void tma_store_wait_read_but_one() {
+  asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
 }
 
 __device__ __forceinline__ void tc_fence_before() {
@@ -574,6 +581,41 @@ __device__ __forceinline__ void epilogue_slice(const GemmParams& P, const CUtens
   epilogue_tile<IS_INT, EPI>(P, taddr, lane, i0, i1, row, ncol0, stage, sc, amax);
 }
 
+// The work of one CTA of the single-CTA kernel, as a list of segments: k-slabs
+// [kb0, kb1) of one tile. Without stream_k: whole tiles, round robin. With it:
+// this CTA's share of the sequence of all k-slabs; the tiles it shares with a
+// neighbour come first (their fix-up then overlaps with the whole tiles that
+// follow), and `part` of `parts` numbers the CTAs of a tile in slab order.
+struct Segment {
+  int64_t tile, kb0, kb1;
+  int part, parts;
+};
+__device__ __forceinline__ bool cta_segment(const GemmParams& P, int64_t idx, Segment& sg) {
+  if (!P.stream_k) {
+    sg.tile = blockIdx.x + idx * gridDim.x;
+    sg.kb0 = 0;
+    sg.kb1 = P.num_kb;
+    sg.part = 0;
+    sg.parts = 1;
+    return sg.tile < P.total_tiles;
+  }
+  const int64_t G = gridDim.x, total = P.total_tiles * P.num_kb;
+  const int64_t beg = ((int64_t)blockIdx.x * total) / G, end = (((int64_t)blockIdx.x + 1) * total) / G;
+  if (beg >= end) return false;
+  const int64_t t_first = beg / P.num_kb, t_last = (end - 1) / P.num_kb;
+  if (idx > t_last - t_first) return false;
+  sg.tile = idx == 0 ? t_first : (idx == 1 ? t_last : t_first + idx - 1);
+  const int64_t T0 = sg.tile * P.num_kb;
+  sg.kb0 = max(beg, T0) - T0;
+  sg.kb1 = min(end, T0 + P.num_kb) - T0;
+  // the largest g whose share starts at or before slab X is ((X + 1) G - 1) / total
+  const int64_t g_first = ((T0 + 1) * G - 1) / total;
+  const int64_t g_last = ((T0 + P.num_kb) * G - 1) / total;
+  sg.part = (int)((int64_t)blockIdx.x - g_first);
+  sg.parts = (int)(g_last - g_first + 1);
+  return true;
+}
+
 // Epilogue of one (tile, k-part) unit of a split contraction (single-CTA
 // kernel, at most 64 columns, so only the warps of the first column half have
 // work). Each warp owns 32 rows of the tile. It parks its raw accumulators in
@@ -584,12 +626,12 @@ __device__ __forceinline__ void epilogue_slice(const GemmParams& P, const CUtens
 // work. The counters are zeroed by the host before every launch.
 template <bool IS_INT>
 __device__ __forceinline__ void epilogue_split(const GemmParams& P, uint32_t taddr, int lane,
-                                               int quarter, int64_t tile, int64_t part,
+                                               int quarter, int64_t tile, int part, int parts,
                                                int64_t i0, int64_t i1, int64_t row, float sa,
                                                uint32_t& amax) {
   const int nm = P.n_mma;  // 16 ... 64, a multiple of 16
   const int row_in_tile = quarter * 32 + lane;
-  uint32_t* mine = P.partials + ((tile * P.split_k + part) * BM + row_in_tile) * nm;
+  uint32_t* mine = P.partials + ((tile * P.max_parts + part) * BM + row_in_tile) * nm;
   for (int c = 0; c < nm; c += 16) {
     uint32_t acc[16];
     tc_ld16(taddr + (uint32_t)c, acc);
@@ -599,23 +641,25 @@ __device__ __forceinline__ void epilogue_split(const GemmParams& P, uint32_t tad
       __stcg((uint4*)(mine + c) + v,
              make_uint4(acc[4 * v], acc[4 * v + 1], acc[4 * v + 2], acc[4 * v + 3]));
   }
-  __threadfence();
+  // the lanes' stores happen before the warp barrier, the barrier before lane
+  // 0's fence and ticket: whoever draws the last ticket (and fences) sees them
   __syncwarp();
   int prev = 0;
   if (lane == 0) {
-    prev = atomicAdd(P.tile_counter + tile * 4 + quarter, 1);
     __threadfence();
+    prev = atomicAdd(P.tile_counter + tile * 4 + quarter, 1);
   }
   prev = __shfl_sync(0xffffffffu, prev, 0);
-  if (prev != P.split_k - 1) return;
+  if (prev != parts - 1) return;
+  __threadfence();
   // Last to arrive: every part of these 32 rows is in global memory. All loads
   // of a 16-column chunk (up to MAX_SPLIT parts x 4 vectors) and the columns'
   // scales are requested together: the fix-up runs once per tile quarter and
   // would otherwise pay one L2 round trip per vector.
-  constexpr int MAX_SPLIT = 6;
+  constexpr int MAX_SPLIT = 6;  // == MAX_PARTS on the host side
   const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
   const bool row_ok = row < P.m;
-  const uint32_t* base = P.partials + (tile * P.split_k * BM + row_in_tile) * nm;
+  const uint32_t* base = P.partials + (tile * P.max_parts * BM + row_in_tile) * nm;
   // lane l holds the scales of columns l and l + 32
   float sb_lane[2] = {1.f, 1.f};
   if (has_b) {
@@ -632,7 +676,7 @@ __device__ __forceinline__ void epilogue_split(const GemmParams& P, uint32_t tad
     for (int p = 0; p < MAX_SPLIT; ++p)
 #pragma unroll
       for (int q = 0; q < 4; ++q)
-        v[p][q] = p < P.split_k ? __ldcg((const uint4*)(base + (int64_t)p * BM * nm + c0) + q)
+        v[p][q] = p < parts ? __ldcg((const uint4*)(base + (int64_t)p * BM * nm + c0) + q)
                                 : make_uint4(0u, 0u, 0u, 0u);
     uint32_t raw[16];
 #pragma unroll
@@ -642,7 +686,7 @@ __device__ __forceinline__ void epilogue_split(const GemmParams& P, uint32_t tad
       for (int p = 1; p < MAX_SPLIT; ++p) {
         if (IS_INT) {
           sum.x += v[p][q].x; sum.y += v[p][q].y; sum.z += v[p][q].z; sum.w += v[p][q].w;
-        } else if (p < P.split_k) {  // adding +0.0 could turn a -0.0 sum into +0.0
+        } else if (p < parts) {  // adding +0.0 could turn a -0.0 sum into +0.0
           sum.x = __float_as_uint(__fadd_rn(__uint_as_float(sum.x), __uint_as_float(v[p][q].x)));
           sum.y = __float_as_uint(__fadd_rn(__uint_as_float(sum.y), __uint_as_float(v[p][q].y)));
           sum.z = __float_as_uint(__fadd_rn(__uint_as_float(sum.z), __uint_as_float(v[p][q].z)));
@@ -734,13 +778,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
-      for (int64_t u = blockIdx.x; u < P.total_tiles * P.split_k && !fail; u += gridDim.x) {
-        const int64_t t = u / P.split_k, part = u % P.split_k;
+      Segment sg;
+      for (int64_t idx = 0; !fail && cta_segment(P, idx, sg); ++idx) {
         int64_t i0, i1, mt, nt;
-        decode_tile(P, t, i0, i1, mt, nt);
-        const int64_t kb0 = part * P.kb_per_part;
-        const int64_t kb1 = min(P.num_kb, kb0 + P.kb_per_part);
-        for (int64_t kb = kb0; kb < kb1; ++kb) {
+        decode_tile(P, sg.tile, i0, i1, mt, nt);
+        for (int64_t kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
           mbar_expect_tx(&full_bar[stage], A_STAGE + P.b_stage);
           tma_load_4d(smem_a + stage * A_STAGE, &tmA, &full_bar[stage], (int)(kb * BK),
@@ -759,10 +801,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t phase = 0;
       int buf = 0;
       uint32_t aphase = 0;
-      for (int64_t u = blockIdx.x; u < P.total_tiles * P.split_k && !fail; u += gridDim.x) {
-        const int64_t part = u % P.split_k;
-        const int64_t kb0 = part * P.kb_per_part;
-        const int64_t kb1 = min(P.num_kb, kb0 + P.kb_per_part);
+      Segment sg;
+      for (int64_t idx = 0; !fail && cta_segment(P, idx, sg); ++idx) {
+        const int64_t kb0 = sg.kb0, kb1 = sg.kb1;
         if (!mbar_wait(&tempty_bar[buf], aphase ^ 1, abortp)) { fail = 2; break; }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(buf * BN);
@@ -794,8 +835,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     int buf = 0;
     uint32_t aphase = 0;
     uint32_t amax = 0;
-    for (int64_t u = blockIdx.x; u < P.total_tiles * P.split_k; u += gridDim.x) {
-      const int64_t t = u / P.split_k;
+    Segment sg;
+    for (int64_t idx = 0; cta_segment(P, idx, sg); ++idx) {
+      const int64_t t = sg.tile;
       int64_t i0, i1, mt, nt;
       decode_tile(P, t, i0, i1, mt, nt);
       const int64_t row = mt * BM + quarter * 32 + lane;
@@ -807,10 +849,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       tc_fence_after();
       const uint32_t taddr =
           tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + half * 128);
-      if (P.split_k > 1) {
+      if (sg.parts > 1) {
         if (half == 0)
-          epilogue_split<IS_INT>(P, taddr, lane, quarter, t, u % P.split_k, i0, i1, row, sc.sa,
-                                 amax);
+          epilogue_split<IS_INT>(P, taddr, lane, quarter, t, sg.part, sg.parts, i0, i1, row,
+                                 sc.sa, amax);
       } else {
         epilogue_slice<IS_INT, EPI>(P, &tmO, taddr, lane, i0, i1, row, nt * BN + half * 128,
                                     epi_stage[warp - 2], sc, amax);
@@ -1177,6 +1219,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
   const bool leader = rank == 0;
   const int64_t cluster_id = blockIdx.x >> 1;
   const int64_t num_clusters = gridDim.x >> 1;
+  const int nst = P.stages3;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES3; ++s) {
@@ -1229,7 +1272,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
           if (two)
             tma_load_4d_pair(sa + A_STAGE + B_HALF, &tmB, lbar, (int)(kb * BK),
                              (int)(nt * BNW + 256 + rank * 128), (int)i1, (int)i0);
-          if (++stage == STAGES3) { stage = 0; phase ^= 1; }
+          if (++stage == nst) { stage = 0; phase ^= 1; }
         }
       }
       if (fail) {
@@ -1255,9 +1298,9 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
         // accumulator finishes -- and its drain starts -- while the second is
         // still being fed. The shared-memory stages of such a group are
         // released after its second pass.
-        const int head = (int)min((int64_t)STAGES3, P.num_kb);
+        const int head = (int)min((int64_t)nst, P.num_kb);
         const int64_t rest = P.num_kb - head;
-        const int tail = (int)min((int64_t)STAGES3, rest);
+        const int tail = (int)min((int64_t)nst, rest);
         const int64_t middle = rest - tail;
         int stage_of[STAGES3];
         // -- one staggered group of `cnt` k-slabs; first == the tile's first slabs
@@ -1276,7 +1319,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
                   tc_mma_pair<IS_INT>(tmem_base, ad + (uint64_t)(2 * k), bd0 + (uint64_t)(2 * k),
                                       P.idesc2, (!first || q > 0 || k > 0) ? 1u : 0u);
                 stage_of[q] = stage;
-                if (++stage == STAGES3) { stage = 0; phase ^= 1; }
+                if (++stage == nst) { stage = 0; phase ^= 1; }
               }
             }
           }
@@ -1323,7 +1366,7 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
                                   bd1 + (uint64_t)(2 * k), P.idesc2, 1u);
           }
           tc_commit_pair(&empty_bar[stage]);
-          if (++stage == STAGES3) { stage = 0; phase ^= 1; }
+          if (++stage == nst) { stage = 0; phase ^= 1; }
         }
         if (fail) break;
         if (tail > 0) {
@@ -1353,8 +1396,15 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
     const int slice = (warp - 2) >> 2;
     const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
     const bool vary_b = has_b && P.sb_n != 0;
-    uint8_t* stage_rows = epi_stage[warp - 2];
+    // Staging rows: one set per warp, or two used in turn when the ring is
+    // short (the second set lives in the unused stages): the conversion of the
+    // next 32 columns then does not wait for the TMA unit to pick up the last.
+    const bool two_sets = !RAW && nst < STAGES3;
+    uint8_t* const set0 = epi_stage[warp - 2];
+    uint8_t* const set1 = two_sets ? smem + 2 * W_STAGE + (warp - 2) * (32 * kWidePitch) : set0;
+    uint8_t* stage_rows = set0;
     uint8_t* srow = stage_rows + lane * kWidePitch;
+    uint32_t set = 0;
     const int swz = (lane >> 1) & 3;
     uint32_t aphase = 0;
     uint32_t amax = 0;
@@ -1403,8 +1453,13 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
         const int a = g >> 1;
         const int64_t colg = col_s + a * 256 + (g & 1) * 32;
         if constexpr (!RAW) {
-          // the staging rows are free once the previous store has read them
-          if (lane == 0) tma_store_wait_read();
+          // the staging rows are free once the store that last used them has read them
+          stage_rows = set ? set1 : set0;
+          srow = stage_rows + lane * kWidePitch;
+          if (lane == 0) {
+            if (two_sets) tma_store_wait_read_but_one();
+            else tma_store_wait_read();
+          }
           __syncwarp();
         }
         uint32_t sb_g = 0;
@@ -1470,8 +1525,12 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
         if constexpr (!RAW) {
           asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
           __syncwarp();
-          if (lane == 0 && row0 < P.m && colg < P.n)
+          const bool stores = row0 < P.m && colg < P.n;  // the same for the whole warp
+          if (lane == 0 && stores)
             tma_store_4d(&tmO, stage_rows, (int)colg, (int)row0, (int)i1, (int)i0);
+          // the sets alternate with the stores actually issued: the set written
+          // next is then the one of the store before the newest
+          if (two_sets && stores) set ^= 1u;
         }
         if (g & 1) {
           // this accumulator's columns have all been read (the read in flight,
@@ -1890,8 +1949,8 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   P.idesc = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(n_mma >> 3) << 17) |
             ((uint32_t)(BM >> 4) << 24);
   P.n_mma = (int)n_mma;
-  P.split_k = 1;
-  P.kb_per_part = std::max<int64_t>(1, (d->k + BK - 1) / BK);
+  P.stream_k = 0;
+  P.max_parts = 1;
   P.b_stage = (int)(n_mma * BK);
   P.stages1 = (int)std::min<int64_t>(MAX_STAGES1, (int64_t)(GEMM_SMEM - 1024) / (A_STAGE + P.b_stage));
   P.idesc2 = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
@@ -1904,26 +1963,27 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   return 0;
 }
 
-// Split of the contraction for skinny problems on the single-CTA kernel (few
-// columns, many row tiles -- decode-time serving): with T tiles on S SMs the
-// last wave is mostly empty unless T is a multiple of S; cutting every tile's
-// contraction into `parts` makes T * parts units that fill the SMs evenly.
-// Returns 1 when splitting does not pay.
-static int choose_split(int64_t tiles, int64_t num_kb, int64_t n_mma, int sms) {
-  if (n_mma > 64 || tiles <= 0 || num_kb < 16) return 1;
-  auto eff = [&](int64_t units) {
-    const int64_t waves = (units + sms - 1) / sms;
-    return (double)units / (double)(waves * sms);
-  };
-  int best = 1;
-  double best_eff = eff(tiles);
-  for (int s = 2; s <= 6; ++s) {
-    const int64_t per = (num_kb + s - 1) / s;
-    if (per < 8 || (int64_t)(s - 1) * per >= num_kb) continue;  // no short or empty parts
-    const double e = eff(tiles * s);
-    if (e > best_eff + 0.03) { best_eff = e; best = s; }
-  }
-  return best_eff > eff(tiles) + 0.08 ? best : 1;
+// Skinny problems on the single-CTA kernel (few columns, many row tiles --
+// decode-time serving): with T tiles on S SMs the last wave is mostly empty
+// unless T is a multiple of S. Cutting the sequence of all k-slabs into one
+// equal share per CTA keeps every SM busy to the end; tiles that straddle a
+// share boundary are computed in parts. Returns the number of CTAs and the most
+// parts a tile can have, or parts 1 when whole tiles already fill the waves.
+constexpr int MAX_PARTS = 6;  // slots the fix-up can sum (see epilogue_split)
+struct StreamPlan {
+  int grid, parts;
+};
+static StreamPlan plan_stream(int64_t tiles, int64_t num_kb, int64_t n_mma, int sms) {
+  StreamPlan none = {0, 1};
+  if (n_mma > 64 || tiles <= 0 || num_kb < 16 || sms <= 0) return none;
+  const int64_t waves = (tiles + sms - 1) / sms;
+  if ((double)tiles / (double)(waves * sms) > 0.92) return none;
+  const int64_t grid = std::min<int64_t>(sms, tiles * 4);
+  const int64_t share = tiles * num_kb / grid;  // >= num_kb / 4
+  const int64_t parts = (num_kb + share - 1) / share + 1;
+  if (parts > MAX_PARTS) return none;
+  StreamPlan p = {(int)grid, (int)parts};
+  return p;
 }
 
 static size_t split_workspace_bytes(int64_t tiles, int parts, int64_t n_mma) {
@@ -1941,8 +2001,9 @@ size_t gemm_workspace_bytes(const aqtb200_gemm_desc* d) {
   const int64_t tiles = d->b0 * d->b1 * ((d->m + BM - 1) / BM) * ((d->n + BN - 1) / BN);
   const int64_t n_mma = d->n < BN ? std::max<int64_t>(16, (d->n + 15) / 16 * 16) : BN;
   const int64_t num_kb = std::max<int64_t>(1, (d->k + BK - 1) / BK);
-  const int parts = choose_split(tiles, num_kb, n_mma, sm_count());
-  return parts > 1 ? split_workspace_bytes(tiles, parts, n_mma) : 0;
+  // the most any SM count up to the device's can need (fewer CTAs: fewer parts)
+  const StreamPlan plan = plan_stream(tiles, num_kb, n_mma, sm_count());
+  return plan.parts > 1 ? split_workspace_bytes(tiles, MAX_PARTS, n_mma) : 0;
 }
 
 int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
@@ -1961,8 +2022,15 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   // CTA pairs pay off once a 256-row tile is mostly full; skinny problems keep
   // the single-CTA 128-row tiles. Long contractions take the 256 x 512 pair
   // tile. g_gemm_impl 2 / 3 / 4 force one kernel.
+  // Very short contractions with a large output are bound by the drain of the
+  // accumulators alone: the wide kernel's sixteen epilogue warps with two sets
+  // of staging rows drain fastest.
+  const int64_t wide_tiles = d->b0 * d->b1 * ((d->m + BM2 - 1) / BM2) * ((d->n + BNW - 1) / BNW);
+  const bool drain_bound = P.num_kb <= 2 && wide_tiles >= 2 * (int64_t)sm_count();
   bool wide = g_gemm_impl == 4 ? true
-              : (g_gemm_impl == 0 && d->m > 128 && d->n > 256 && P.num_kb >= WIDE_MIN_KB);
+              : (g_gemm_impl == 0 && d->m > 128 && d->n > 256 &&
+                 (P.num_kb >= WIDE_MIN_KB || drain_bound));
+  P.stages3 = P.num_kb <= 2 ? 2 : STAGES3;
   const bool sa_bf = d->a_scale == nullptr || d->a_scale_dtype == AQTB200_BF16;
   const bool sb_bf = d->b_scale == nullptr || d->b_scale_dtype == AQTB200_BF16;
   const bool sa_f = d->a_scale == nullptr || d->a_scale_dtype == AQTB200_F32;
@@ -2004,12 +2072,15 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   rc = make_operand_map(&tmB, d->b, d->k, d->n, d->b1, d->b0, d->ldb, d->b_b1_stride,
                         d->b_b0_stride, pair ? 128 : P.b_stage / BK);
   if (rc) return rc;
+  int stream_grid = 0;
   if (!pair && single_cta_path(d) && d->workspace != nullptr) {
-    const int parts = choose_split(P.total_tiles, P.num_kb, P.n_mma, sm_count());
-    if (parts > 1 && d->workspace_bytes >= split_workspace_bytes(P.total_tiles, parts, P.n_mma) &&
+    const StreamPlan plan = plan_stream(P.total_tiles, P.num_kb, P.n_mma, gemm_sms());
+    if (plan.parts > 1 &&
+        d->workspace_bytes >= split_workspace_bytes(P.total_tiles, plan.parts, P.n_mma) &&
         ((uintptr_t)d->workspace & 255) == 0) {
-      P.split_k = parts;
-      P.kb_per_part = (P.num_kb + parts - 1) / parts;
+      P.stream_k = 1;
+      P.max_parts = plan.parts;
+      stream_grid = plan.grid;
       const size_t counters = ((size_t)P.total_tiles * 4 * sizeof(int32_t) + 255) & ~(size_t)255;
       P.tile_counter = (int32_t*)d->workspace;
       P.partials = (uint32_t*)((char*)d->workspace + counters);
@@ -2018,7 +2089,8 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   }
   const int64_t pair_tiles = wide ? P.total_tiles3 : P.total_tiles2;
   const int grid = pair ? 2 * std::max((int)std::min<int64_t>(pair_tiles, gemm_sms() / 2), 1)
-                        : (int)std::min<int64_t>(P.total_tiles * P.split_k, gemm_sms());
+                        : (stream_grid ? stream_grid
+                                       : (int)std::min<int64_t>(P.total_tiles, gemm_sms()));
   const size_t smem = wide ? GEMM3_SMEM : (pair ? GEMM2_SMEM : GEMM_SMEM);
   // the shared-memory opt-in is a per-device attribute of each kernel
   int dev = 0;

@@ -349,7 +349,7 @@ def sharded_parity_check(torch, dist, rank, world, dev, m_local=2048, k=1024,
   """Runs a small row-sharded step and, on every rank, the same problem
   unsharded; returns a dict of 'ok' / 'MISMATCH' per case. int8: bit for bit.
   fp8: out and dlhs bit for bit (rows are independent given the agreed
-  scales), drhs within max(1 bf16 ulp, 1e-5 * sum |g||lhs|) because the
+  scales), drhs within max(6 bf16 ulps, 1e-5 * sum |g||lhs|) because the
   ranks' f32 partial sums are added in another order than one device's."""
   from aqt_b200 import distributed as aqt_dist
   from aqt_b200 import engine
@@ -384,19 +384,31 @@ def sharded_parity_check(torch, dist, rank, world, dev, m_local=2048, k=1024,
       wl, wr = wbp(g)
       torch.cuda.synchronize()
       engine.check_status()
-      same = torch.equal(out, wo[sl]) and torch.equal(dl, wl[sl])
+      bad = []
+      if not torch.equal(out, wo[sl]):
+        bad.append('out')
+      if not torch.equal(dl, wl[sl]):
+        bad.append('dlhs')
       if kind == 'int8':
-        same = same and torch.equal(dr, wr)
+        if not torch.equal(dr, wr):
+          bad.append('drhs')
       else:
+        # The f32 accumulators differ by rounding noise; each of the three
+        # bf16 roundings of the dequantizing chain (cast, x scale, x scale)
+        # can then land one step apart and the steps add up: 2 bf16 ulps
+        # per rounding bound the end-to-end difference.
         want = wr.double()
         ulp = 2.0 ** (torch.floor(torch.log2(want.abs().clamp_min(1e-38))) - 7)
         bound = 2.0 * (lhs.float().abs().t() @ g.float().abs()).double()
-        tol = torch.maximum(ulp, 1e-5 * bound)
-        same = same and bool(((dr.double() - want).abs() <= tol).all())
-      flag = torch.tensor([1 if same else 0], device=dev)
+        tol = torch.maximum(6.0 * ulp, 1e-5 * bound)
+        diff = (dr.double() - want).abs()
+        if not bool((diff <= tol).all()):
+          bad.append('drhs(max %.1f ulp)' % float((diff / ulp).max().item()))
+      flag = torch.tensor([0 if bad else 1], device=dev)
       dist.all_reduce(flag, op=dist.ReduceOp.MIN)
       result[f'{kind}_{"per_tensor" if per_tensor else "per_channel"}'] = (
-          'ok' if int(flag.item()) else 'MISMATCH')
+          'ok' if int(flag.item()) else 'MISMATCH' + (
+              ': ' + ', '.join(bad) if bad else ' (on another rank)'))
   return result
 
 

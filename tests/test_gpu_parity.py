@@ -241,10 +241,13 @@ def test_every_tensor_core_kernel_agrees_with_cuda_core_kernel(impl, shape,
 
 @pytest.mark.parametrize('shape', [(16, 512, 1024), (1, 256, 4096),
                                    (64, 1040, 520), (40, 144, 2048),
-                                   # long contractions: split into parts that
-                                   # other CTAs take, summed by the last one
+                                   # long contractions: tiles that straddle
+                                   # the CTAs' equal shares of the k-slabs are
+                                   # computed in 2 to 5 parts, summed by the
+                                   # part that finishes last
                                    (16, 4096, 2048), (33, 8192, 1000),
-                                   (64, 2048, 4736)])
+                                   (64, 2048, 4736), (16, 2048, 28672),
+                                   (48, 8192, 3584)])
 @pytest.mark.parametrize('np_dtype', [np.float32, orc.bfloat16])
 def test_skinny_lhs_uses_narrow_mmas_and_agrees(shape, np_dtype):
   """A few rows against many: the planner puts the many on the tile's row side
