@@ -86,6 +86,16 @@ class DualDesc(C.Structure):
 
 
 # name -> (restype, argtypes); every symbol include/aqt_b200.h declares.
+MAX_RANKS = 8
+
+
+class ExchangeDesc(C.Structure):
+  """aqtb200_exchange_desc."""
+  _fields_ = [('world', C.c_int32), ('rank', C.c_int32),
+              ('acc', C.c_void_p * MAX_RANKS), ('out', C.c_void_p * MAX_RANKS),
+              ('max_sms', C.c_int32)]
+
+
 SYMBOLS = {
     'aqtb200_quantize': (C.c_int, [
         C.POINTER(View), C.POINTER(View), C.POINTER(View),
@@ -126,6 +136,8 @@ SYMBOLS = {
         C.POINTER(DgRawDesc), C.c_void_p, C.c_size_t, C.c_void_p, C.c_void_p]),
     'aqtb200_dot_general_raw_dequant': (C.c_int, [
         C.POINTER(DgRawDesc), C.c_void_p]),
+    'aqtb200_dot_general_raw_exchange': (C.c_int, [
+        C.POINTER(DgRawDesc), C.POINTER(ExchangeDesc), C.c_void_p]),
     'aqtb200_dequantize': (C.c_int, [
         C.POINTER(View), C.POINTER(View), C.c_int32, C.c_void_p, C.c_void_p]),
     'aqtb200_set_device': (C.c_int, [C.c_int]),
@@ -136,6 +148,9 @@ SYMBOLS = {
     'aqtb200_h2d': (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     'aqtb200_d2h': (C.c_int, [C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p]),
     'aqtb200_sync': (C.c_int, [C.c_void_p]),
+    'aqtb200_ipc_export': (C.c_int, [C.c_void_p, C.c_void_p]),
+    'aqtb200_ipc_open': (C.c_int, [C.c_void_p, C.POINTER(C.c_void_p)]),
+    'aqtb200_ipc_close': (C.c_int, [C.c_void_p]),
     'aqtb200_comm_unique_id': (C.c_int, [C.c_void_p]),
     'aqtb200_comm_init': (C.c_int, [C.c_int, C.c_int, C.c_void_p,
                                     C.POINTER(C.c_void_p)]),

@@ -26,6 +26,7 @@ int sm_count();
 int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st);
 size_t gemm_workspace_bytes(const aqtb200_gemm_desc* d);
 int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st);
+int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x, cudaStream_t st);
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -207,6 +208,20 @@ int aqtb200_dot_general_raw_dequant(const aqtb200_dg_raw_desc* d, void* stream) 
   aqtb200_gemm_desc g{};
   fill_gemm_desc(d, L, R, &g);
   return dequant_acc(&g, d->acc_out, (cudaStream_t)stream);
+}
+
+int aqtb200_dot_general_raw_exchange(const aqtb200_dg_raw_desc* d, const aqtb200_exchange_desc* x,
+                                     void* stream) {
+  AQT_REQUIRE(d != nullptr && x != nullptr, AQTB200_EINVAL, "null descriptor");
+  Side L{}, R{};
+  side_after_quantize(d->lhs, d->lhs_spec, d->lhs_scale_in, d->lhs_is_quantized, d->lhs_q,
+                      d->lhs_scale, &L);
+  side_after_quantize(d->rhs, d->rhs_spec, d->rhs_scale_in, d->rhs_is_quantized, d->rhs_q,
+                      d->rhs_scale, &R);
+  aqtb200_gemm_desc g{};
+  fill_gemm_desc(d, L, R, &g);
+  g.out = x->out[x->rank >= 0 && x->rank < AQTB200_MAX_RANKS ? x->rank : 0];
+  return exchange_dequant(&g, x, (cudaStream_t)stream);
 }
 
 }  // extern "C"

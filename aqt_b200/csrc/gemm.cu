@@ -57,6 +57,7 @@ struct GemmParams {
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
   int64_t n_tiles3, total_tiles3;  // 512-column tiles of the wide CTA-pair kernel
   int stages1, b_stage;  // single-CTA kernel: ring depth and bytes of one B tile
+  int issue_batch;       // single-CTA kernel: k-slabs the producer requests back to back
   int stages3;  // wide kernel: ring depth, 2 (short contractions: the freed stages hold a second
                 // set of staging rows for the epilogue) or STAGES3
   // single-CTA kernel, skinny problems: the k-slabs of all tiles form one
@@ -783,6 +784,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         int64_t i0, i1, mt, nt;
         decode_tile(P, sg.tile, i0, i1, mt, nt);
         for (int64_t kb = sg.kb0; kb < sg.kb1; ++kb) {
+          if (P.issue_batch > 1 && (kb - sg.kb0) % P.issue_batch == 0) {
+            // Skinny problems stream the A operand from DRAM in 128-byte row
+            // pieces. Requesting several consecutive k-slabs back to back puts
+            // neighbouring pieces of every row in flight together (512
+            // contiguous bytes per row instead of 128 every stage time).
+            const int nb = (int)min((int64_t)P.issue_batch, sg.kb1 - kb);
+            int ls = stage + nb - 1;
+            uint32_t lp = phase;
+            if (ls >= P.stages1) { ls -= P.stages1; lp ^= 1; }
+            if (!mbar_wait(&empty_bar[ls], lp ^ 1, abortp)) { fail = 1; break; }
+          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
           mbar_expect_tx(&full_bar[stage], A_STAGE + P.b_stage);
           tma_load_4d(smem_a + stage * A_STAGE, &tmA, &full_bar[stage], (int)(kb * BK),
@@ -1801,6 +1813,78 @@ __global__ void __launch_bounds__(256) dequant_acc_kernel(GemmParams P, const ui
   if (P.amax_out != nullptr) amax_publish(P.amax_out, amax, threadIdx.x & 31);
 }
 
+
+// ---------------------------------------------------------------------------
+// Sum of one band of raw accumulators over the ranks of a row-sharded dot,
+// dequantized once and written to every rank: the reduce-scatter, the
+// dequantizing epilogue and the all-gather of the finished band in ONE kernel
+// over peer memory. X.acc[r] is rank r's copy of the band ([m][n] 4-byte
+// accumulators; the other ranks' through their peer mappings), X.out[r] rank
+// r's copy of the band's place in the output. Every thread keeps eight 16-byte
+// loads in flight (UU units x WORLD ranks), sums them in rank order -- so the
+// f32 sum does not depend on which rank computes the band -- and stores the
+// result WORLD times. Needs n % 4 == 0, an unbatched dot and unit column
+// stride of the output.
+struct ExchangeArgs {
+  const uint32_t* acc[AQTB200_MAX_RANKS];
+  void* out[AQTB200_MAX_RANKS];
+  int world;
+};
+
+template <int WORLD>
+__global__ void __launch_bounds__(256, 4) exchange_dequant_kernel(GemmParams P, ExchangeArgs X) {
+  constexpr int UU = 8 / WORLD;
+  const int64_t nq = P.n / 4;
+  const int64_t total = P.m * nq;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
+  for (int64_t i0u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0u < total;
+       i0u += nthreads * UU) {
+    uint4 v[UU][WORLD];
+#pragma unroll
+    for (int k = 0; k < UU; ++k) {
+      const int64_t i = i0u + k * nthreads;
+#pragma unroll
+      for (int r = 0; r < WORLD; ++r)
+        v[k][r] = i < total ? __ldcg((const uint4*)X.acc[r] + i) : make_uint4(0u, 0u, 0u, 0u);
+    }
+#pragma unroll
+    for (int k = 0; k < UU; ++k) {
+      const int64_t i = i0u + k * nthreads;
+      if (i >= total) continue;
+      uint32_t raw[4] = {v[k][0].x, v[k][0].y, v[k][0].z, v[k][0].w};
+#pragma unroll
+      for (int r = 1; r < WORLD; ++r) {
+        const uint32_t w[4] = {v[k][r].x, v[k][r].y, v[k][r].z, v[k][r].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          raw[j] = P.is_int ? raw[j] + w[j]
+                            : __float_as_uint(__fadd_rn(__uint_as_float(raw[j]), __uint_as_float(w[j])));
+      }
+      const int64_t col = (i % nq) * 4, row = i / nq;
+      const float sa = P.a_scale ? load1(P.a_scale, P.a_scale_dtype, row * P.sa_m) : 1.f;
+      float res[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float sb = P.b_scale ? load1(P.b_scale, P.b_scale_dtype, (col + j) * P.sb_n) : 1.f;
+        res[j] = dequant_one(P, raw[j], sa, sb);
+      }
+      const int64_t oi = row * P.o_m + col;
+      if (es == 2) {
+        const __nv_bfloat162 p0 = __floats2bfloat162_rn(res[0], res[1]);
+        const __nv_bfloat162 p1 = __floats2bfloat162_rn(res[2], res[3]);
+        const uint2 o = make_uint2(*(const uint32_t*)&p0, *(const uint32_t*)&p1);
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) *(uint2*)((__nv_bfloat16*)X.out[r] + oi) = o;
+      } else {
+        const float4 o = make_float4(res[0], res[1], res[2], res[3]);
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r) *(float4*)((float*)X.out[r] + oi) = o;
+      }
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // host side
 
@@ -1953,6 +2037,7 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   P.max_parts = 1;
   P.b_stage = (int)(n_mma * BK);
   P.stages1 = (int)std::min<int64_t>(MAX_STAGES1, (int64_t)(GEMM_SMEM - 1024) / (A_STAGE + P.b_stage));
+  P.issue_batch = (n_mma <= 64 && P.stages1 >= 8) ? 4 : 1;
   P.idesc2 = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
              ((uint32_t)(256 >> 4) << 24);
   P.m_tiles2 = (d->m + 255) / 256;
@@ -2153,6 +2238,41 @@ int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st) {
     dequant_acc_kernel<true><<<grid, 256, 0, st>>>(P, (const uint32_t*)acc);
   else
     dequant_acc_kernel<false><<<grid, 256, 0, st>>>(P, (const uint32_t*)acc);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x, cudaStream_t st) {
+  GemmParams P;
+  bool empty = false;
+  int rc0 = fill_params(d, nullptr, P, &empty);
+  if (rc0 || empty) return rc0;
+  AQT_REQUIRE(x != nullptr, AQTB200_EINVAL, "null exchange descriptor");
+  AQT_REQUIRE(x->world == 2 || x->world == 4 || x->world == 8, AQTB200_EUNSUPPORTED,
+              "the fused exchange handles 2, 4 or 8 ranks");
+  AQT_REQUIRE(x->rank >= 0 && x->rank < x->world, AQTB200_EINVAL, "rank out of range");
+  AQT_REQUIRE(d->b0 * d->b1 == 1 && d->n % 4 == 0 && P.o_n == 1, AQTB200_EUNSUPPORTED,
+              "the fused exchange needs an unbatched dot, n % 4 == 0 and unit output column stride");
+  AQT_REQUIRE(d->amax_out == nullptr, AQTB200_EUNSUPPORTED, "no amax_out in the fused exchange");
+  const int es = d->out_dtype == AQTB200_BF16 ? 2 : 4;
+  AQT_REQUIRE((P.o_m * es) % (4 * es) == 0, AQTB200_EUNSUPPORTED, "output rows must keep 4-element alignment");
+  ExchangeArgs X{};
+  X.world = x->world;
+  for (int r = 0; r < x->world; ++r) {
+    AQT_REQUIRE(x->acc[r] != nullptr && x->out[r] != nullptr, AQTB200_EINVAL, "null band pointer");
+    AQT_REQUIRE(((uintptr_t)x->acc[r] & 15) == 0 && ((uintptr_t)x->out[r] & (4 * es - 1)) == 0,
+                AQTB200_EINVAL, "band pointers must be 16-byte (accumulators) / 4-element (output) aligned");
+    X.acc[r] = (const uint32_t*)x->acc[r];
+    X.out[r] = x->out[r];
+  }
+  const int64_t total = d->m * d->n / 4;
+  const int per_block = 256 * (8 / x->world);
+  int64_t grid = (total + per_block - 1) / per_block;
+  const int64_t cap = (int64_t)(x->max_sms > 0 ? x->max_sms : sm_count()) * 4;
+  grid = std::max<int64_t>(1, std::min(grid, cap));
+  if (x->world == 2) exchange_dequant_kernel<2><<<(int)grid, 256, 0, st>>>(P, X);
+  else if (x->world == 4) exchange_dequant_kernel<4><<<(int)grid, 256, 0, st>>>(P, X);
+  else exchange_dequant_kernel<8><<<(int)grid, 256, 0, st>>>(P, X);
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   return 0;
 }

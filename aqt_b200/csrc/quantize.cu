@@ -828,15 +828,6 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
     const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + (row_ok ? r0 : 0)) * ES;
     const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
     const int64_t nbase = i0 * P.noise.sb0 + i1 * P.noise.sb1;
-    uint4 raw[2][4];
-#pragma unroll
-    for (int i = 0; i < 2; ++i)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
-        raw[i][e] = (row_ok && c < x.cols) ? ldg16(xp, c * x.sc * ES)
-                                           : make_uint4(0u, 0u, 0u, 0u);
-      }
     float sinv[EPV];
 #pragma unroll
     for (int j = 0; j < EPV; ++j)
@@ -844,8 +835,17 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
     float pconst = 0.f;
     if constexpr (PRE == 1) pconst = load1(P.pre.ptr, P.pre.dtype, pbase);
     const __nv_fp8_interpretation_t f8k = P.qdtype == AQTB200_E4M3 ? __NV_E4M3 : __NV_E5M2;
-#pragma unroll
+    // One-byte inputs (16 rows per vector) keep the two passes as a loop: the
+    // unrolled body of both does not fit the instruction cache, and the eight
+    // warps of a block then wait for instructions instead of data.
+#pragma unroll(EPV == 16 ? 1 : 2)
     for (int i = 0; i < 2; ++i) {
+      uint4 raw[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+        raw[e] = (row_ok && c < x.cols) ? ldg16(xp, c * x.sc * ES) : make_uint4(0u, 0u, 0u, 0u);
+      }
       uint32_t q4[4][EPV / 4];  // [column e][row group g]: bytes of rows 4g..4g+3
       // The noise of the four columns of this pass is requested up front (EPV
       // floats per column, as 16-byte vectors), so that its latency is paid
@@ -867,7 +867,7 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
       for (int e = 0; e < 4; ++e) {
         const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
         const bool in = row_ok && c < x.cols;
-        const uint32_t rw[4] = {raw[i][e].x, raw[i][e].y, raw[i][e].z, raw[i][e].w};
+        const uint32_t rw[4] = {raw[e].x, raw[e].y, raw[e].z, raw[e].w};
         if (EPV == 16 && P.use_lut) {
 #pragma unroll
           for (int g = 0; g < EPV / 4; ++g) q4[e][g] = in ? lut4(rw[g & 3], lut) : 0u;
@@ -901,31 +901,9 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
                 P.clip_bound);
             q4[e][g] = in ? q : 0u;
           }
-        } else if (EPV == 16 && P.s8_bf16 && (!has_noise || P.noise_vec)) {
-          // a stored int8 operand re-quantized (the backward pass, use_fwd_quant):
-          // widen to bf16 exactly, then the packed bf16 arithmetic of the bf16 path
-          float p = pconst;
-          if constexpr (PRE == 2) p = in ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
-          const uint32_t pre2 = pack_bf16x2(p, p);
-#pragma unroll
-          for (int g = 0; g < EPV / 4; ++g) {
-            float nz[4] = {0.f, 0.f, 0.f, 0.f};
-            if (has_noise && in) {
-              nz[0] = __uint_as_float(nzv[e][g].x); nz[1] = __uint_as_float(nzv[e][g].y);
-              nz[2] = __uint_as_float(nzv[e][g].z); nz[3] = __uint_as_float(nzv[e][g].w);
-            }
-            uint32_t w0, w1;
-            s8x4_to_bf16x2x2(rw[g & 3], w0, w1);
-            const uint32_t q = bf16x4_to_s8x4(
-                w0, w1, pre2, pre2, PRE != 0,
-                pack_bf16x2(sinv[(4 * g) % EPV], sinv[(4 * g + 1) % EPV]),
-                pack_bf16x2(sinv[(4 * g + 2) % EPV], sinv[(4 * g + 3) % EPV]), nz, has_noise,
-                P.clip_bound);
-            q4[e][g] = in ? q : 0u;
-          }
         } else {
           float v[EPV];
-          unpack<EPV>(raw[i][e], x.dtype, v);
+          unpack<EPV>(raw[e], x.dtype, v);
           float p = pconst;
           if constexpr (PRE == 2) p = in ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
 #pragma unroll
@@ -946,6 +924,114 @@ quant_col_fast(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_un
               }
             }
             q4[e][g] = in ? quant4(w4, sinv + 4 * g, nz, has_noise, P) : 0u;
+          }
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < EPV / 4; ++g) {
+        const uint32_t cols4[4] = {q4[0][g], q4[1][g], q4[2][g], q4[3][g]};
+        uint32_t rows4[4];
+        transpose4x4(cols4, rows4);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          tile[tx * EPV + 4 * g + j][(i * 16 + ty + 4 * tx) & 31] = rows4[j];
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int s = 0; s < TR / 32; ++s) {
+      const int id = tid + 256 * s;
+      const int row = id >> 3, seg = id & 7;
+      const int64_t gr = rt * TR + row;
+      const int64_t gc = ct * 128 + seg * 16;
+      if (gr < x.rows && gc < P.ldq) {
+        const uint4 o = *(const uint4*)&tile[row][(seg * 4 + 4 * (row / EPV)) & 31];
+        *(uint4*)(P.q + (sbase + gr) * P.ldq + gc) = o;
+      }
+    }
+    __syncthreads();
+  }
+}
+
+// quant_col_fast for one case only: a stored int8 operand re-quantized to int8
+// in bf16 arithmetic (the backward pass under use_fwd_quant), with or without a
+// vectorisable f32 noise tensor. Same tile and thread layout (256 kept rows x
+// 128 contraction indices, thread = 16 rows of 8 columns); compiled without
+// the general kernel's other branches it fits two blocks per SM, and the noise
+// of two columns at a time (32 registers) is requested ahead of their use.
+template <int PRE, bool NOISE>
+__global__ void __launch_bounds__(256, 2)
+quant_col_s8_kernel(QParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_units) {
+  constexpr int EPV = 16, TR = 16 * EPV;
+  __shared__ __align__(16) uint32_t tile[TR][32];
+  const DView& x = P.x;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  for (int64_t uf = blockIdx.x; uf < total_units; uf += gridDim.x) {
+    const int64_t u = total_units - 1 - uf;
+    const int64_t ct = u % col_tiles;
+    int64_t t = u / col_tiles;
+    const int64_t rt = t % row_tiles;
+    const int64_t b = t / row_tiles;
+    const int64_t i1 = b % x.b1, i0 = b / x.b1;
+    const int64_t sbase = (i0 * x.b1 + i1) * x.rows;
+    const int64_t r0 = rt * TR + tx * EPV;
+    const bool row_ok = r0 < x.rows;
+    const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + (row_ok ? r0 : 0));
+    const int64_t pbase = i0 * P.pre.sb0 + i1 * P.pre.sb1;
+    const int64_t nbase = i0 * P.noise.sb0 + i1 * P.noise.sb1;
+    uint32_t sinv2[EPV / 2];  // reciprocal scales of the thread's rows, as bf16 pairs
+#pragma unroll
+    for (int j = 0; j < EPV / 2; ++j) {
+      const float a = P.per_tensor ? P.sinv[0] : (row_ok ? P.sinv[sbase + r0 + 2 * j] : 1.f);
+      const float c = P.per_tensor ? P.sinv[0] : (row_ok ? P.sinv[sbase + r0 + 2 * j + 1] : 1.f);
+      sinv2[j] = pack_bf16x2(a, c);
+    }
+    float pconst = 0.f;
+    if constexpr (PRE == 1) pconst = load1(P.pre.ptr, P.pre.dtype, pbase);
+#pragma unroll 1
+    for (int i = 0; i < 2; ++i) {
+      uint4 raw[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+        raw[e] = (row_ok && c < x.cols) ? ldg16(xp, c * x.sc) : make_uint4(0u, 0u, 0u, 0u);
+      }
+      uint32_t q4[4][EPV / 4];
+#pragma unroll
+      for (int eh = 0; eh < 2; ++eh) {
+        uint4 nzv[2][EPV / 4];
+        if constexpr (NOISE) {
+#pragma unroll
+          for (int e2 = 0; e2 < 2; ++e2) {
+            const int64_t c = ct * 128 + i * 64 + ty * 4 + eh * 2 + e2;
+            const bool in = row_ok && c < x.cols;
+#pragma unroll
+            for (int g = 0; g < EPV / 4; ++g)
+              nzv[e2][g] = in ? ldg16(P.noise.ptr, (nbase + c * P.noise.sc + r0 + 4 * g) * 4)
+                              : make_uint4(0u, 0u, 0u, 0u);
+          }
+        }
+#pragma unroll
+        for (int e2 = 0; e2 < 2; ++e2) {
+          const int e = eh * 2 + e2;
+          const int64_t c = ct * 128 + i * 64 + ty * 4 + e;
+          const bool in = row_ok && c < x.cols;
+          const uint32_t rw[4] = {raw[e].x, raw[e].y, raw[e].z, raw[e].w};
+          float p = pconst;
+          if constexpr (PRE == 2) p = in ? load1(P.pre.ptr, P.pre.dtype, pbase + c * P.pre.sc) : 0.f;
+          const uint32_t pre2 = pack_bf16x2(p, p);
+#pragma unroll
+          for (int g = 0; g < EPV / 4; ++g) {
+            float nz[4] = {0.f, 0.f, 0.f, 0.f};
+            if constexpr (NOISE) {
+              nz[0] = __uint_as_float(nzv[e2][g].x); nz[1] = __uint_as_float(nzv[e2][g].y);
+              nz[2] = __uint_as_float(nzv[e2][g].z); nz[3] = __uint_as_float(nzv[e2][g].w);
+            }
+            uint32_t w0, w1;
+            s8x4_to_bf16x2x2(rw[g], w0, w1);
+            const uint32_t q = bf16x4_to_s8x4(w0, w1, pre2, pre2, PRE != 0, sinv2[2 * g],
+                                              sinv2[2 * g + 1], nz, NOISE, P.clip_bound);
+            q4[e][g] = in ? q : 0u;
           }
         }
       }
@@ -2269,7 +2355,19 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
     int64_t cts = (P.ldq + 127) / 128;
     int64_t units = xv->b0 * xv->b1 * rts * cts;
     int grid = grid_for(units, 4);
-    AQT_DISPATCH_EPV_PRE(quant_col_fast, grid, 256, P, rts, cts, units);
+    if (epv == 16 && P.s8_bf16 && !P.use_lut && (P.noise.ptr == nullptr || P.noise_vec)) {
+      if (P.noise.ptr != nullptr) {
+        if (pre_kind == 0) quant_col_s8_kernel<0, true><<<grid, 256, 0, st>>>(P, rts, cts, units);
+        else if (pre_kind == 1) quant_col_s8_kernel<1, true><<<grid, 256, 0, st>>>(P, rts, cts, units);
+        else quant_col_s8_kernel<2, true><<<grid, 256, 0, st>>>(P, rts, cts, units);
+      } else {
+        if (pre_kind == 0) quant_col_s8_kernel<0, false><<<grid, 256, 0, st>>>(P, rts, cts, units);
+        else if (pre_kind == 1) quant_col_s8_kernel<1, false><<<grid, 256, 0, st>>>(P, rts, cts, units);
+        else quant_col_s8_kernel<2, false><<<grid, 256, 0, st>>>(P, rts, cts, units);
+      }
+    } else {
+      AQT_DISPATCH_EPV_PRE(quant_col_fast, grid, 256, P, rts, cts, units);
+    }
   } else {
     int64_t rts = (xv->rows + 63) / 64;
     int64_t cts = (P.ldq + 127) / 128;

@@ -115,6 +115,27 @@ int aqtb200_set_device(int device) {
   return 0;
 }
 
+// ---- peer memory -----------------------------------------------------------
+int aqtb200_ipc_export(const void* ptr, void* handle64) {
+  AQT_REQUIRE(ptr != nullptr && handle64 != nullptr, AQTB200_EINVAL, "null argument");
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle is documented as 64 bytes");
+  cudaIpcMemHandle_t h;
+  AQT_CUDA_OK(cudaIpcGetMemHandle(&h, const_cast<void*>(ptr)));
+  memcpy(handle64, &h, sizeof(h));
+  return 0;
+}
+int aqtb200_ipc_open(const void* handle64, void** out) {
+  AQT_REQUIRE(handle64 != nullptr && out != nullptr, AQTB200_EINVAL, "null argument");
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64, sizeof(h));
+  AQT_CUDA_OK(cudaIpcOpenMemHandle(out, h, cudaIpcMemLazyEnablePeerAccess));
+  return 0;
+}
+int aqtb200_ipc_close(void* ptr) {
+  AQT_CUDA_OK(cudaIpcCloseMemHandle(ptr));
+  return 0;
+}
+
 // ---- collectives ---------------------------------------------------------
 int aqtb200_comm_unique_id(void* id128) {
   AQT_REQUIRE(id128 != nullptr, AQTB200_EINVAL, "null argument");

@@ -21,6 +21,16 @@ concatenated lhs -- bit for bit for int8, to f32 summation order for fp8:
     the exchange of one slice runs under the next slice's GEMM and under
     dlhs. Otherwise the accumulators are all-reduced and dequantized whole.
 
+On GPUs of one node the three steps of that exchange are ONE kernel over peer
+memory (aqtb200_dot_general_raw_exchange): the accumulators and the result
+live in a device allocation whose handle every rank opens; after a small
+collective that tells a slice's GEMM has finished everywhere, each rank reads
+its band of the slice from every rank's accumulators, adds them in rank
+order, dequantizes once and writes the band into every rank's result. The
+kernel runs on a second stream beside the next slice's GEMM and beside dlhs.
+Where peer mappings cannot be made (host tensors, other world sizes than 2, 4
+or 8, no peer access) the NCCL calls above are used instead.
+
 Only a 2-D contraction lhs[M,K] . rhs[K,N] is handled; that is the projection
 layer the reference's data-parallel users shard. The reference itself has no
 collective on this path (cross-replica statistics raise NotImplementedError,
@@ -32,11 +42,13 @@ sharded step can be recorded and replayed by engine.TracedStep.
 
 from __future__ import annotations
 
+import ctypes as C
 import functools
 
 import torch
 import torch.distributed as dist
 
+from aqt_b200 import _lib
 from aqt_b200 import engine
 from aqt_b200.v2 import aqt_dot_general as adg
 from aqt_b200.v2 import aqt_tensor
@@ -66,13 +78,92 @@ class _StreamCtx:
       self._ctx.__exit__(*exc)
 
 
+class _DeviceMemory:
+  """Zero-copy torch view of a device allocation made outside torch."""
+
+  def __init__(self, ptr, nbytes):
+    self.__cuda_array_interface__ = {
+        'shape': (nbytes,), 'typestr': '|u1', 'data': (ptr, False),
+        'version': 2, 'strides': None}
+
+
+class PeerBuffers:
+  """The accumulators [K][N] (4-byte) and the result [K][N] of a sharded drhs
+  in one device allocation per rank that every other rank of the group has
+  mapped. acc / out are this rank's torch views; acc_base[r] / out_base[r]
+  the addresses of rank r's copies as seen from this rank."""
+
+  def __init__(self, group, device, k, n, acc_dtype, out_dtype):
+    lib = _lib.load()
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    acc_bytes = (k * n * 4 + 255) // 256 * 256
+    out_bytes = k * n * torch.empty((), dtype=out_dtype).element_size()
+    self._own = C.c_void_p()
+    self._opened = []
+    self._lib = lib
+    ok = 1
+    handle = C.create_string_buffer(64)
+    try:
+      _lib.check(lib.aqtb200_dev_alloc(C.byref(self._own), acc_bytes + out_bytes),
+                 'dev_alloc')
+      _lib.check(lib.aqtb200_ipc_export(self._own, handle), 'ipc_export')
+    except Exception:  # pylint: disable=broad-except
+      ok = 0
+    gathered = [None] * world
+    dist.all_gather_object(gathered, (ok, handle.raw), group=group)
+    bases = [None] * world
+    if all(g[0] for g in gathered):
+      try:
+        for r, (_, raw) in enumerate(gathered):
+          if r == rank:
+            bases[r] = self._own.value
+            continue
+          ptr = C.c_void_p()
+          _lib.check(lib.aqtb200_ipc_open(C.create_string_buffer(raw, 64),
+                                          C.byref(ptr)), 'ipc_open')
+          self._opened.append(ptr)
+          bases[r] = ptr.value
+      except Exception:  # pylint: disable=broad-except
+        ok = 0
+    else:
+      ok = 0
+    flag = torch.tensor([ok], device=device, dtype=torch.int32)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+    self.ok = bool(int(flag.item()))
+    if not self.ok:
+      self.close()
+      return
+    self.acc_base = bases
+    self.out_base = [b + acc_bytes for b in bases]
+    mem = torch.as_tensor(_DeviceMemory(self._own.value, acc_bytes + out_bytes),
+                          device=device)
+    self._mem = mem
+    self.acc = mem[:k * n * 4].view(acc_dtype).view(k, n)
+    self.out = mem[acc_bytes:acc_bytes + out_bytes].view(out_dtype).view(k, n)
+
+  def close(self):
+    for ptr in self._opened:
+      self._lib.aqtb200_ipc_close(ptr)
+    self._opened = []
+    if self._own:
+      self._lib.aqtb200_dev_free(self._own)
+      self._own = C.c_void_p()
+
+
 class ShardedDotGeneral:
   """cfg.vjp for row-sharded operands (see module docstring)."""
 
   def __init__(self, cfg: adg.DotGeneral, group=None, overlap_sms: int = 32,
-               drhs_slices: int = 2, slice_multiple: int = 256):
+               drhs_slices: int = 2, slice_multiple: int = 256,
+               exchange: str = 'auto'):
     self.cfg = cfg
     self.group = group
+    # 'auto': the fused kernel over peer memory where it can be set up, else
+    # NCCL reduce-scatter + all-gather; 'nccl': always the latter.
+    assert exchange in ('auto', 'nccl')
+    self.exchange = exchange
+    self._peer = {}
+    self.exchange_used = None  # 'p2p' or 'nccl' once a sliced drhs has run
     # SMs left to the collective's kernel while a GEMM runs beside it.
     self.overlap_sms = overlap_sms
     # drhs is computed in this many row slices so that the exchange of one
@@ -295,6 +386,12 @@ class ShardedDotGeneral:
     rank = dist.get_rank(self.group)
     rows = k // s
     band = rows // world
+    peer = self._peer_buffers(g, k, n, x_qt)
+    if peer is not None:
+      self.exchange_used = 'p2p'
+      return self._drhs_fused(g, res, g_qt, x_qt, r_dims, r_perm, internal,
+                              peer, rows, band, rank)
+    self.exchange_used = 'nccl'
     drhs = engine._empty((k, n), g.dtype, g.device)  # pylint: disable=protected-access
     side = self._side_stream(g.device)
     mt = res.lhs.mt
@@ -352,3 +449,86 @@ class ShardedDotGeneral:
       del keep[:]
 
     return drhs, join
+
+  # -- the exchange as one kernel over peer memory ---------------------------
+  def _peer_buffers(self, g, k, n, x_qt):
+    """PeerBuffers for a [k][n] drhs, or None where the NCCL path applies."""
+    world = self._world()
+    if (self.exchange != 'auto' or g.device.type != 'cuda' or
+        world not in (2, 4, 8) or n % 4):
+      return None
+    ints = x_qt.qvalue.dtype == torch.int8
+    key = (k, n, g.dtype, ints, str(g.device))
+    if key not in self._peer:
+      try:
+        pb = PeerBuffers(self.group, g.device, k, n,
+                         torch.int32 if ints else torch.float32, g.dtype)
+      except Exception:  # pylint: disable=broad-except
+        # every rank must take the same path: agree on the failure
+        flag = torch.tensor([0], device=g.device, dtype=torch.int32)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+        pb = None
+      self._peer[key] = pb if (pb is not None and pb.ok) else None
+      self._flag = torch.zeros(1, device=g.device, dtype=torch.int32)
+    return self._peer[key]
+
+  def _barrier_on(self, stream):
+    """Orders everything queued on `stream` after what every rank had queued
+    on its own when it got here (a one-element all-reduce)."""
+    flag = self._flag
+
+    def op():
+      with _StreamCtx(stream):
+        dist.all_reduce(flag, group=self.group)
+
+    engine.tape_op(op)
+
+  def _drhs_fused(self, g, res, g_qt, x_qt, r_dims, r_perm, internal, peer,
+                  rows, band, rank):
+    """drhs in row slices: GEMM into the shared accumulators on the compute
+    stream; on the second stream a barrier and the kernel that sums this
+    rank's band of the slice over all ranks, dequantizes it and writes it to
+    every rank. Returns (drhs, join); drhs is the shared result buffer, valid
+    until this op's next backward pass."""
+    cfg = self.cfg
+    s = self.drhs_slices
+    n = g.shape[1]
+    side = self._side_stream(g.device)
+    main = torch.cuda.current_stream(g.device)
+    mt = res.lhs.mt
+    budget = self.overlap_sms
+    try:
+      for i in range(s):
+        sl = slice(i * rows, (i + 1) * rows)
+        mt_i = adg.MultiTensor(
+            x=mt.x[:, sl], qx=mt.qx.replace(qvalue=mt.qx.qvalue[:, sl]))
+        x_i = x_qt.replace(qvalue=x_qt.qvalue[:, sl])
+        if i == 1 and budget:
+          engine.set_gemm_sm_budget(max(engine.sm_count() - budget, 2))
+        d, _ = engine.dg_raw(cfg.drhs, g, mt_i, g_qt, x_i, r_dims,
+                             out_transpose_axes=r_perm, defer_dequant=True,
+                             internal_qt=internal, out=peer.out[sl],
+                             acc_buf=peer.acc[sl])
+        assert d.acc.data_ptr() == peer.acc[sl].data_ptr()
+        acc_row, out_row = d.band_stride_bytes()
+        assert acc_row == 4 * n and out_row == n * peer.out.element_size(), (
+            'drhs accumulators are expected as [rows of drhs][columns]')
+        first = i * rows + rank * band
+        engine.tape_op(lambda: side.wait_stream(main))
+        self._barrier_on(side)
+        with _StreamCtx(side):
+          d.exchange_rows(
+              rank * band, band, rank,
+              [b + first * acc_row for b in peer.acc_base],
+              [b + first * out_row for b in peer.out_base],
+              max_sms=budget if budget else 0)
+    finally:
+      if budget:
+        engine.set_gemm_sm_budget(0)
+
+    def join():
+      # every rank's bands have landed here once every rank's kernels are done
+      self._barrier_on(side)
+      engine.tape_op(lambda: main.wait_stream(side))
+
+    return peer.out, join

@@ -491,10 +491,49 @@ class DeferredDequant:
     return self._out
 
 
+  def exchange_rows(self, start: int, count: int, rank: int, acc_ptrs,
+                    out_ptrs, max_sms: int = 0):
+    """The fused exchange for accumulator rows [start, start + count): sums
+    the band over the ranks (acc_ptrs[r]: address of rank r's band, peer
+    mappings for the others), dequantizes once and writes it to every rank
+    (out_ptrs[r]: address of the band's place in rank r's output)."""
+    desc = _copy_struct(self._desc)
+    assert desc.lhs.b0 * desc.lhs.b1 == 1, 'exchange_rows: unbatched dots only'
+    swap = bool(desc.swap_ab)
+    side = desc.rhs if swap else desc.lhs
+    spec = desc.rhs_spec if swap else desc.lhs_spec
+    assert 0 <= start and start + count <= side.rows
+    side.rows = count
+    if not spec.per_tensor:
+      off = start * (2 if spec.scale_dtype == _lib.BF16 else 4)
+      for name in (('rhs_scale', 'rhs_scale_in') if swap else
+                   ('lhs_scale', 'lhs_scale_in')):
+        ptr = getattr(desc, name)
+        if ptr:
+          setattr(desc, name, ptr + off)
+    x = _lib.ExchangeDesc()
+    x.world, x.rank, x.max_sms = len(acc_ptrs), rank, max_sms
+    for r, (a, o) in enumerate(zip(acc_ptrs, out_ptrs)):
+      x.acc[r], x.out[r] = a, o
+    desc.out = out_ptrs[rank]
+    desc.acc_out = acc_ptrs[rank]
+    rc = _call(_lib.load().aqtb200_dot_general_raw_exchange, C.byref(desc),
+               C.byref(x), _stream())
+    _lib.check(rc, 'aqtb200_dot_general_raw_exchange')
+
+  def band_stride_bytes(self):
+    """(accumulator bytes, output bytes) between consecutive accumulator rows."""
+    desc = self._desc
+    swap = bool(desc.swap_ab)
+    n = desc.lhs.rows if swap else desc.rhs.rows
+    stride = desc.out_n_stride if swap else desc.out_m_stride
+    return 4 * n, stride * self._out.element_size()
+
+
 def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
            out_transpose_axes=None, want_acc=False, defer_dequant=False,
            internal_qt=False, out=None, amax_out=None, _regrouped=False,
-           _noise=None):
+           _noise=None, acc_buf=None):
   """DotGeneralRaw.__call__ on the device (aqt_dot_general.py:757-840).
 
   Returns (out, DotGeneralRes[, acc]). `out` is laid out as
@@ -506,6 +545,8 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
   tensor) of the transposed result's shape and the result dtype.
   amax_out: optional one-element f32 device tensor, zeroed by the caller, that
   receives max |out| from the GEMM epilogue (atomic max).
+  acc_buf: optional preallocated contiguous int32 / f32 tensor the raw
+  accumulators are written to (e.g. memory other ranks can read).
   """
   from aqt_b200.v2 import aqt_dot_general as adg
   from aqt_b200.v2 import aqt_tensor
@@ -810,7 +851,13 @@ def dg_raw(raw, lhs, rhs, lhs_qt, rhs_qt, dimension_numbers,
     want_acc = True
   if want_acc:
     acc_shape = (nB, N, M) if swap else (nB, M, N)
-    acc = _empty(acc_shape, torch.int32 if ints[0] else torch.float32, dev)
+    acc_dtype = torch.int32 if ints[0] else torch.float32
+    if acc_buf is not None:
+      assert (acc_buf.is_contiguous() and acc_buf.dtype == acc_dtype and
+              acc_buf.numel() == nB * M * N), 'acc_buf: wrong size or dtype'
+      acc = acc_buf.view(acc_shape)
+    else:
+      acc = _empty(acc_shape, acc_dtype, dev)
     desc.acc_out = acc.data_ptr()
     acc_storage = acc
     if swap:
@@ -1721,7 +1768,8 @@ class TracedStep:
     assert _tape is None, 'a step is already being traced'
     self._inputs = inputs
     self._stream = _stream()
-    want = _flat_tensors(fn(*inputs)) if verify else None
+    # copies: a step may hand out buffers it owns and overwrites on every run
+    want = [t.clone() for t in _flat_tensors(fn(*inputs))] if verify else None
     _tape = tape = _Tape()
     try:
       self.outputs = fn(*inputs)

@@ -70,6 +70,10 @@ def parse_args():
                  help='tile shape of the tensor-core kernel (default: automatic)')
   p.add_argument('--drhs-slices', type=int, default=2)
   p.add_argument('--overlap-sms', type=int, default=32)
+  p.add_argument('--exchange', default='auto', choices=['auto', 'nccl'],
+                 help='drhs exchange at several GPUs: auto = one kernel over '
+                 'peer memory where it can be set up, nccl = reduce-scatter + '
+                 'dequantize + all-gather')
   return p.parse_args()
 
 
@@ -345,7 +349,7 @@ def capture_graph(torch, step, barrier=None):
 
 
 def sharded_parity_check(torch, dist, rank, world, dev, m_local=2048, k=1024,
-                         n=1024, traced=True):
+                         n=1024, traced=True, exchange='auto'):
   """Runs a small row-sharded step and, on every rank, the same problem
   unsharded; returns a dict of 'ok' / 'MISMATCH' per case. int8: bit for bit.
   fp8: out and dlhs bit for bit (rows are independent given the agreed
@@ -370,7 +374,7 @@ def sharded_parity_check(torch, dist, rank, world, dev, m_local=2048, k=1024,
       g = torch.randn(m, n, device=dev, generator=gen).to(torch.bfloat16)
       sl = slice(rank * m_local, (rank + 1) * m_local)
       a, c = lhs[sl].contiguous(), g[sl].contiguous()
-      op = aqt_dist.ShardedDotGeneral(cfg)
+      op = aqt_dist.ShardedDotGeneral(cfg, exchange=exchange)
 
       def step(a_, b_, c_, op=op):
         out, bp = op.vjp(a_, b_, DIMS)
@@ -409,6 +413,7 @@ def sharded_parity_check(torch, dist, rank, world, dev, m_local=2048, k=1024,
       result[f'{kind}_{"per_tensor" if per_tensor else "per_channel"}'] = (
           'ok' if int(flag.item()) else 'MISMATCH' + (
               ': ' + ', '.join(bad) if bad else ' (on another rank)'))
+      result.setdefault('exchange', op.exchange_used)
   return result
 
 
@@ -597,7 +602,8 @@ def run_ours(args, lines):
   if world > 1:
     from aqt_b200 import distributed as aqt_dist
     op = aqt_dist.ShardedDotGeneral(cfg, drhs_slices=args.drhs_slices,
-                                    overlap_sms=args.overlap_sms)
+                                    overlap_sms=args.overlap_sms,
+                                    exchange=args.exchange)
 
   def eager_step(a, b, c):
     if op is not None:
@@ -689,7 +695,8 @@ def run_ours(args, lines):
   parity = None
   if world > 1:
     try:
-      parity = sharded_parity_check(torch, dist, rank, world, dev)
+      parity = sharded_parity_check(torch, dist, rank, world, dev,
+                                    exchange=args.exchange)
     except Exception as e:  # pylint: disable=broad-except
       parity = {'error': f'{type(e).__name__}: {e}'}
 

@@ -396,6 +396,32 @@ int aqtb200_dot_general_raw(const aqtb200_dg_raw_desc* desc, void* workspace,
 int aqtb200_dot_general_raw_dequant(const aqtb200_dg_raw_desc* desc,
                                     void* stream);
 
+/* The sum across ranks, the dequantization and the distribution of the result
+ * in one kernel over peer memory (one process per GPU on NVLink). With the
+ * SAME descriptor, narrowed to a band of accumulator rows as for
+ * aqtb200_dot_general_raw_dequant: acc[r] is rank r's accumulator band
+ * ([rows][N], 4-byte, 16-byte aligned; the other ranks' through mappings made
+ * with aqtb200_ipc_open), out[r] the band's place in rank r's output. The
+ * calling rank reads every acc[r], adds them in rank order (so the f32 total
+ * does not depend on who computes a band), dequantizes once and writes the
+ * band to every out[r]. desc->out and desc->acc_out are ignored. The caller
+ * orders this call after every rank's contraction of the band (a barrier or a
+ * small collective on the same stream) and orders its readers of `out` after
+ * every rank's call. world: 2, 4 or 8. max_sms > 0 caps the SMs the kernel
+ * occupies (it runs beside a GEMM whose own cap is aqtb200_set_gemm_sm_budget).
+ * Replaces: nothing in the reference (which has no collective on this path);
+ * it is what ncclReduceScatter + dequantize + ncclAllGather would do. */
+#define AQTB200_MAX_RANKS 8
+typedef struct aqtb200_exchange_desc {
+  int32_t world, rank;
+  const void* acc[AQTB200_MAX_RANKS];
+  void* out[AQTB200_MAX_RANKS];
+  int32_t max_sms;
+} aqtb200_exchange_desc;
+int aqtb200_dot_general_raw_exchange(const aqtb200_dg_raw_desc* desc,
+                                     const aqtb200_exchange_desc* exchange,
+                                     void* stream);
+
 /* Elementwise helpers for the piecewise API (QTensor.quant / QTensor.dequant
  * used outside the fused path, aqt_tensor.py:125-200):
  *   dequantize: out = cast_D(q) * scale   (one scale, broadcast by strides) */
@@ -415,6 +441,13 @@ int aqtb200_dev_memset(void* ptr, int value, size_t bytes, void* stream);
 int aqtb200_h2d(void* dst, const void* src, size_t bytes, void* stream);
 int aqtb200_d2h(void* dst, const void* src, size_t bytes, void* stream);
 int aqtb200_sync(void* stream);
+/* Peer memory for the fused exchange: a 64-byte handle of a device allocation
+ * (ptr: its base address, e.g. from aqtb200_dev_alloc) that another process on
+ * the same node opens as a pointer valid on ITS current device (peer access is
+ * enabled on first use). Close every opened pointer before the owner frees. */
+int aqtb200_ipc_export(const void* ptr, void* handle64);
+int aqtb200_ipc_open(const void* handle64, void** out);
+int aqtb200_ipc_close(void* ptr);
 
 /*
  * Collectives of the row-sharded path (one process per GPU; the rows of lhs

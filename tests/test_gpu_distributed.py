@@ -30,9 +30,15 @@ torch.cuda.set_device(int(os.environ['LOCAL_RANK']))
 dev = torch.device('cuda', int(os.environ['LOCAL_RANK']))
 dist.init_process_group('nccl', device_id=dev)
 # int8: bit for bit. fp8: out and dlhs bit for bit, drhs within
-# max(1 bf16 ulp, 1e-5 * sum |g||lhs|) (bench.sharded_parity_check).
+# max(6 bf16 ulps, 1e-5 * sum |g||lhs|) (bench.sharded_parity_check). Once with
+# the exchange as one kernel over peer memory, once with the NCCL calls.
 result = bench.sharded_parity_check(torch, dist, rank, world, dev)
 print(f'rank {rank}: {result}', flush=True)
+assert result.pop('exchange') == 'p2p', 'the fused exchange was not used'
+nccl = bench.sharded_parity_check(torch, dist, rank, world, dev, exchange='nccl')
+print(f'rank {rank}: {nccl}', flush=True)
+assert nccl.pop('exchange') == 'nccl'
+result.update({k + '/nccl': v for k, v in nccl.items()})
 
 # the library's own collectives (NCCL opened by the library) against torch's
 import ctypes as C
