@@ -137,7 +137,7 @@ SYMBOLS = {
     'aqtb200_dot_general_raw_dequant': (C.c_int, [
         C.POINTER(DgRawDesc), C.c_void_p]),
     'aqtb200_dot_general_raw_exchange': (C.c_int, [
-        C.POINTER(DgRawDesc), C.POINTER(ExchangeDesc), C.c_void_p]),
+        C.POINTER(DgRawDesc), C.POINTER(ExchangeDesc), C.c_void_p, C.c_void_p]),
     'aqtb200_dequantize': (C.c_int, [
         C.POINTER(View), C.POINTER(View), C.c_int32, C.c_void_p, C.c_void_p]),
     'aqtb200_set_device': (C.c_int, [C.c_int]),

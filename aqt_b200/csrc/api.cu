@@ -26,7 +26,8 @@ int sm_count();
 int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st);
 size_t gemm_workspace_bytes(const aqtb200_gemm_desc* d);
 int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st);
-int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x, cudaStream_t st);
+int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x, int32_t* status,
+                     cudaStream_t st);
 
 static size_t align256(size_t v) { return (v + 255) & ~(size_t)255; }
 
@@ -211,7 +212,7 @@ int aqtb200_dot_general_raw_dequant(const aqtb200_dg_raw_desc* d, void* stream) 
 }
 
 int aqtb200_dot_general_raw_exchange(const aqtb200_dg_raw_desc* d, const aqtb200_exchange_desc* x,
-                                     void* stream) {
+                                     int32_t* status, void* stream) {
   AQT_REQUIRE(d != nullptr && x != nullptr, AQTB200_EINVAL, "null descriptor");
   Side L{}, R{};
   side_after_quantize(d->lhs, d->lhs_spec, d->lhs_scale_in, d->lhs_is_quantized, d->lhs_q,
@@ -221,7 +222,7 @@ int aqtb200_dot_general_raw_exchange(const aqtb200_dg_raw_desc* d, const aqtb200
   aqtb200_gemm_desc g{};
   fill_gemm_desc(d, L, R, &g);
   g.out = x->out[x->rank >= 0 && x->rank < AQTB200_MAX_RANKS ? x->rank : 0];
-  return exchange_dequant(&g, x, (cudaStream_t)stream);
+  return exchange_dequant(&g, x, status, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -57,7 +57,6 @@ struct GemmParams {
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
   int64_t n_tiles3, total_tiles3;  // 512-column tiles of the wide CTA-pair kernel
   int stages1, b_stage;  // single-CTA kernel: ring depth and bytes of one B tile
-  int issue_batch;       // single-CTA kernel: k-slabs the producer requests back to back
   int stages3;  // wide kernel: ring depth, 2 (short contractions: the freed stages hold a second
                 // set of staging rows for the epilogue) or STAGES3
   // single-CTA kernel, skinny problems: the k-slabs of all tiles form one
@@ -784,17 +783,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
         int64_t i0, i1, mt, nt;
         decode_tile(P, sg.tile, i0, i1, mt, nt);
         for (int64_t kb = sg.kb0; kb < sg.kb1; ++kb) {
-          if (P.issue_batch > 1 && (kb - sg.kb0) % P.issue_batch == 0) {
-            // Skinny problems stream the A operand from DRAM in 128-byte row
-            // pieces. Requesting several consecutive k-slabs back to back puts
-            // neighbouring pieces of every row in flight together (512
-            // contiguous bytes per row instead of 128 every stage time).
-            const int nb = (int)min((int64_t)P.issue_batch, sg.kb1 - kb);
-            int ls = stage + nb - 1;
-            uint32_t lp = phase;
-            if (ls >= P.stages1) { ls -= P.stages1; lp ^= 1; }
-            if (!mbar_wait(&empty_bar[ls], lp ^ 1, abortp)) { fail = 1; break; }
-          }
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
           mbar_expect_tx(&full_bar[stage], A_STAGE + P.b_stage);
           tma_load_4d(smem_a + stage * A_STAGE, &tmA, &full_bar[stage], (int)(kb * BK),
@@ -2037,7 +2025,6 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   P.max_parts = 1;
   P.b_stage = (int)(n_mma * BK);
   P.stages1 = (int)std::min<int64_t>(MAX_STAGES1, (int64_t)(GEMM_SMEM - 1024) / (A_STAGE + P.b_stage));
-  P.issue_batch = (n_mma <= 64 && P.stages1 >= 8) ? 4 : 1;
   P.idesc2 = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
              ((uint32_t)(256 >> 4) << 24);
   P.m_tiles2 = (d->m + 255) / 256;
@@ -2048,12 +2035,15 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   return 0;
 }
 
-// Skinny problems on the single-CTA kernel (few columns, many row tiles --
-// decode-time serving): with T tiles on S SMs the last wave is mostly empty
-// unless T is a multiple of S. Cutting the sequence of all k-slabs into one
-// equal share per CTA keeps every SM busy to the end; tiles that straddle a
-// share boundary are computed in parts. Returns the number of CTAs and the most
-// parts a tile can have, or parts 1 when whole tiles already fill the waves.
+// Skinny problems on the single-CTA kernel with fewer tiles than half the SMs:
+// whole tiles would leave most SMs idle while a few stream the long
+// contraction. Cutting the sequence of all k-slabs into equal shares, one per
+// CTA and up to four CTAs per tile, puts more SMs (and more bytes in flight)
+// on the problem; tiles that straddle a share boundary are computed in parts.
+// With at least half the SMs busy the stream from DRAM is already the bound
+// (measured: equal shares then gain nothing, and the partial tiles cost), so
+// whole tiles are kept. Returns the number of CTAs and the most parts a tile
+// can have, or parts 1 for whole tiles.
 constexpr int MAX_PARTS = 6;  // slots the fix-up can sum (see epilogue_split)
 struct StreamPlan {
   int grid, parts;
@@ -2061,8 +2051,7 @@ struct StreamPlan {
 static StreamPlan plan_stream(int64_t tiles, int64_t num_kb, int64_t n_mma, int sms) {
   StreamPlan none = {0, 1};
   if (n_mma > 64 || tiles <= 0 || num_kb < 16 || sms <= 0) return none;
-  const int64_t waves = (tiles + sms - 1) / sms;
-  if ((double)tiles / (double)(waves * sms) > 0.92) return none;
+  if (tiles * 2 > sms) return none;
   const int64_t grid = std::min<int64_t>(sms, tiles * 4);
   const int64_t share = tiles * num_kb / grid;  // >= num_kb / 4
   const int64_t parts = (num_kb + share - 1) / share + 1;
@@ -2242,7 +2231,130 @@ int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st) {
   return 0;
 }
 
-int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x, cudaStream_t st) {
+// The same exchange with the accumulators pulled through the TMA unit: one
+// thread per CTA requests 32 KB stages (one chunk of every rank's band, the
+// peers' chunks straight from their memory) with bulk copies into a six-deep
+// ring, so 192 KB per SM are in flight whatever the register budget -- what a
+// read over NVLink, microseconds away, needs to run at link speed on a few
+// SMs. Eight warps add the chunks in rank order, dequantize and store the
+// result to every rank. Waits are bounded; a wait that runs out sets *status.
+constexpr int EX_STAGE_BYTES = 32 * 1024;
+constexpr int EX_STAGES = 6;
+constexpr int EX_CONSUMERS = 8;
+constexpr int EX_THREADS = 32 * (1 + EX_CONSUMERS);
+constexpr size_t EX_SMEM = (size_t)EX_STAGES * EX_STAGE_BYTES + 128;
+
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+
+template <int WORLD>
+__global__ void __launch_bounds__(EX_THREADS, 1)
+exchange_tma_kernel(GemmParams P, ExchangeArgs X, int32_t* status) {
+  constexpr int CHUNK = EX_STAGE_BYTES / WORLD;  // bytes of one rank's share of a stage
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  __shared__ __align__(8) uint64_t full_bar[EX_STAGES];
+  __shared__ __align__(8) uint64_t empty_bar[EX_STAGES];
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t total_bytes = P.m * P.n * 4;
+  const int64_t chunks = (total_bytes + CHUNK - 1) / CHUNK;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < EX_STAGES; ++s) {
+      mbar_init(&full_bar[s], 1);
+      mbar_init(&empty_bar[s], EX_CONSUMERS);
+    }
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncthreads();
+  volatile int* abortp = &abort_flag;
+  int stage = 0;
+  uint32_t phase = 0;
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int64_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) {
+          *abortp = 1;
+          if (status) atomicCAS(status, 0, 4);
+          break;
+        }
+        const uint32_t bytes = (uint32_t)min((int64_t)CHUNK, total_bytes - c * CHUNK);
+        mbar_expect_tx(&full_bar[stage], WORLD * bytes);
+#pragma unroll
+        for (int r = 0; r < WORLD; ++r)
+          bulk_load(smem + stage * EX_STAGE_BYTES + r * CHUNK, (const char*)X.acc[r] + c * CHUNK,
+                    bytes, &full_bar[stage]);
+        if (++stage == EX_STAGES) { stage = 0; phase ^= 1; }
+      }
+    }
+  } else {
+    const int tid = threadIdx.x - 32;
+    const int es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
+    for (int64_t c = blockIdx.x; c < chunks; c += gridDim.x) {
+      int ok = mbar_wait(&full_bar[stage], phase, abortp) ? 1 : 0;
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) {
+        if (lane == 0) { *abortp = 1; if (status) atomicCAS(status, 0, 5); }
+        break;
+      }
+      const int units = (int)(min((int64_t)CHUNK, total_bytes - c * CHUNK) >> 4);
+      const uint8_t* sp = smem + stage * EX_STAGE_BYTES;
+      for (int u = tid; u < units; u += 32 * EX_CONSUMERS) {
+        const uint4 v0 = *(const uint4*)(sp + u * 16);
+        uint32_t raw[4] = {v0.x, v0.y, v0.z, v0.w};
+#pragma unroll
+        for (int r = 1; r < WORLD; ++r) {
+          const uint4 vr = *(const uint4*)(sp + r * CHUNK + u * 16);
+          const uint32_t w[4] = {vr.x, vr.y, vr.z, vr.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            raw[j] = P.is_int ? raw[j] + w[j]
+                              : __float_as_uint(__fadd_rn(__uint_as_float(raw[j]), __uint_as_float(w[j])));
+        }
+        const int64_t e = (c * CHUNK >> 2) + (int64_t)u * 4;  // first of four elements of one row
+        const int64_t row = e / P.n, col = e - row * P.n;
+        const float sa = P.a_scale ? load1(P.a_scale, P.a_scale_dtype, row * P.sa_m) : 1.f;
+        float res[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float sb = P.b_scale ? load1(P.b_scale, P.b_scale_dtype, (col + j) * P.sb_n) : 1.f;
+          res[j] = dequant_one(P, raw[j], sa, sb);
+        }
+        const int64_t oi = row * P.o_m + col;
+        if (es == 2) {
+          const __nv_bfloat162 p0 = __floats2bfloat162_rn(res[0], res[1]);
+          const __nv_bfloat162 p1 = __floats2bfloat162_rn(res[2], res[3]);
+          const uint2 o = make_uint2(*(const uint32_t*)&p0, *(const uint32_t*)&p1);
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r) *(uint2*)((__nv_bfloat16*)X.out[r] + oi) = o;
+        } else {
+          const float4 o = make_float4(res[0], res[1], res[2], res[3]);
+#pragma unroll
+          for (int r = 0; r < WORLD; ++r) *(float4*)((float*)X.out[r] + oi) = o;
+        }
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      if (++stage == EX_STAGES) { stage = 0; phase ^= 1; }
+    }
+  }
+  __syncthreads();
+  if (*abortp) {
+    // copies still in flight must land before the shared memory is released
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000LL) { }
+  }
+}
+
+int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x, int32_t* status,
+                     cudaStream_t st) {
   GemmParams P;
   bool empty = false;
   int rc0 = fill_params(d, nullptr, P, &empty);
@@ -2265,14 +2377,26 @@ int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x,
     X.acc[r] = (const uint32_t*)x->acc[r];
     X.out[r] = x->out[r];
   }
-  const int64_t total = d->m * d->n / 4;
-  const int per_block = 256 * (8 / x->world);
-  int64_t grid = (total + per_block - 1) / per_block;
-  const int64_t cap = (int64_t)(x->max_sms > 0 ? x->max_sms : sm_count()) * 4;
-  grid = std::max<int64_t>(1, std::min(grid, cap));
-  if (x->world == 2) exchange_dequant_kernel<2><<<(int)grid, 256, 0, st>>>(P, X);
-  else if (x->world == 4) exchange_dequant_kernel<4><<<(int)grid, 256, 0, st>>>(P, X);
-  else exchange_dequant_kernel<8><<<(int)grid, 256, 0, st>>>(P, X);
+  const int64_t chunks = (d->m * d->n * 4 + EX_STAGE_BYTES / x->world - 1) / (EX_STAGE_BYTES / x->world);
+  const int64_t cap = x->max_sms > 0 ? x->max_sms : sm_count();
+  const int grid = (int)std::max<int64_t>(1, std::min(chunks, cap));
+  int dev = 0;
+  AQT_CUDA_OK(cudaGetDevice(&dev));
+  dev &= 63;
+#define AQT_LAUNCH_EXCHANGE(W)                                                                  \
+  do {                                                                                          \
+    static bool attr_done[64] = {false};                                                        \
+    if (!attr_done[dev]) {                                                                      \
+      AQT_CUDA_OK(cudaFuncSetAttribute(exchange_tma_kernel<W>,                                  \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EX_SMEM)); \
+      attr_done[dev] = true;                                                                    \
+    }                                                                                           \
+    exchange_tma_kernel<W><<<grid, EX_THREADS, EX_SMEM, st>>>(P, X, status);                    \
+  } while (0)
+  if (x->world == 2) AQT_LAUNCH_EXCHANGE(2);
+  else if (x->world == 4) AQT_LAUNCH_EXCHANGE(4);
+  else AQT_LAUNCH_EXCHANGE(8);
+#undef AQT_LAUNCH_EXCHANGE
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   return 0;
 }

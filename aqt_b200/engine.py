@@ -517,8 +517,9 @@ class DeferredDequant:
       x.acc[r], x.out[r] = a, o
     desc.out = out_ptrs[rank]
     desc.acc_out = acc_ptrs[rank]
+    status = _status_buf(self._out.device)
     rc = _call(_lib.load().aqtb200_dot_general_raw_exchange, C.byref(desc),
-               C.byref(x), _stream())
+               C.byref(x), status.data_ptr(), _stream())
     _lib.check(rc, 'aqtb200_dot_general_raw_exchange')
 
   def band_stride_bytes(self):

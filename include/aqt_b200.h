@@ -409,6 +409,9 @@ int aqtb200_dot_general_raw_dequant(const aqtb200_dg_raw_desc* desc,
  * small collective on the same stream) and orders its readers of `out` after
  * every rank's call. world: 2, 4 or 8. max_sms > 0 caps the SMs the kernel
  * occupies (it runs beside a GEMM whose own cap is aqtb200_set_gemm_sm_budget).
+ * The accumulators travel through the TMA unit (bulk copies, 192 KB in flight
+ * per SM); status as for aqtb200_dot_general_raw (4 / 5: a bounded wait of the
+ * exchange ran out).
  * Replaces: nothing in the reference (which has no collective on this path);
  * it is what ncclReduceScatter + dequantize + ncclAllGather would do. */
 #define AQTB200_MAX_RANKS 8
@@ -420,7 +423,7 @@ typedef struct aqtb200_exchange_desc {
 } aqtb200_exchange_desc;
 int aqtb200_dot_general_raw_exchange(const aqtb200_dg_raw_desc* desc,
                                      const aqtb200_exchange_desc* exchange,
-                                     void* stream);
+                                     int32_t* status, void* stream);
 
 /* Elementwise helpers for the piecewise API (QTensor.quant / QTensor.dequant
  * used outside the fused path, aqt_tensor.py:125-200):
