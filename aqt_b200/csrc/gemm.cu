@@ -2240,7 +2240,7 @@ int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st) {
 // result to every rank. Waits are bounded; a wait that runs out sets *status.
 constexpr int EX_STAGE_BYTES = 32 * 1024;
 constexpr int EX_STAGES = 6;
-constexpr int EX_CONSUMERS = 8;
+constexpr int EX_CONSUMERS = 16;
 constexpr int EX_THREADS = 32 * (1 + EX_CONSUMERS);
 constexpr size_t EX_SMEM = (size_t)EX_STAGES * EX_STAGE_BYTES + 128;
 
@@ -2252,7 +2252,11 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
       : "memory");
 }
 
-template <int WORLD>
+// FAST: the all-bf16 chain (bf16 dequantization, output and scales) in packed
+// arithmetic, as in the GEMM's own bf16 epilogue; otherwise the general chain.
+// The band has fewer than 2^32 elements (checked by the host), so positions
+// are 32-bit.
+template <int WORLD, bool FAST>
 __global__ void __launch_bounds__(EX_THREADS, 1)
 exchange_tma_kernel(GemmParams P, ExchangeArgs X, int32_t* status) {
   constexpr int CHUNK = EX_STAGE_BYTES / WORLD;  // bytes of one rank's share of a stage
@@ -2297,6 +2301,11 @@ exchange_tma_kernel(GemmParams P, ExchangeArgs X, int32_t* status) {
   } else {
     const int tid = threadIdx.x - 32;
     const int es = P.out_dtype == AQTB200_BF16 ? 2 : 4;
+    const uint32_t n32 = (uint32_t)P.n;
+    const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
+    const bool sa_const = !has_a || P.sa_m == 0, sb_const = !has_b || P.sb_n == 0;
+    const float sa0 = has_a ? load1(P.a_scale, P.a_scale_dtype, 0) : 1.f;
+    const float sb0 = has_b ? load1(P.b_scale, P.b_scale_dtype, 0) : 1.f;
     for (int64_t c = blockIdx.x; c < chunks; c += gridDim.x) {
       int ok = mbar_wait(&full_bar[stage], phase, abortp) ? 1 : 0;
       ok = __all_sync(0xffffffffu, ok);
@@ -2306,6 +2315,8 @@ exchange_tma_kernel(GemmParams P, ExchangeArgs X, int32_t* status) {
       }
       const int units = (int)(min((int64_t)CHUNK, total_bytes - c * CHUNK) >> 4);
       const uint8_t* sp = smem + stage * EX_STAGE_BYTES;
+      const uint32_t e0 = (uint32_t)c * (uint32_t)(CHUNK >> 2);
+#pragma unroll 2
       for (int u = tid; u < units; u += 32 * EX_CONSUMERS) {
         const uint4 v0 = *(const uint4*)(sp + u * 16);
         uint32_t raw[4] = {v0.x, v0.y, v0.z, v0.w};
@@ -2318,26 +2329,61 @@ exchange_tma_kernel(GemmParams P, ExchangeArgs X, int32_t* status) {
             raw[j] = P.is_int ? raw[j] + w[j]
                               : __float_as_uint(__fadd_rn(__uint_as_float(raw[j]), __uint_as_float(w[j])));
         }
-        const int64_t e = (c * CHUNK >> 2) + (int64_t)u * 4;  // first of four elements of one row
-        const int64_t row = e / P.n, col = e - row * P.n;
-        const float sa = P.a_scale ? load1(P.a_scale, P.a_scale_dtype, row * P.sa_m) : 1.f;
-        float res[4];
+        const uint32_t e = e0 + (uint32_t)u * 4u;  // first of four elements of one row
+        const uint32_t row = e / n32, col = e - row * n32;
+        const float sa = sa_const ? sa0 : load1(P.a_scale, P.a_scale_dtype, (int64_t)row * P.sa_m);
+        const int64_t oi = (int64_t)row * P.o_m + col;
+        if constexpr (FAST) {
+          const __nv_bfloat162 sa2 = __float2bfloat162_rn(sa);
+          __nv_bfloat162 sb2[2];
+          if (sb_const) {
+            sb2[0] = sb2[1] = __float2bfloat162_rn(sb0);
+          } else if (P.sb_n == 1) {
+            const uint2 w2 = __ldg((const uint2*)((const __nv_bfloat16*)P.b_scale + col));
+            sb2[0] = *(const __nv_bfloat162*)&w2.x;
+            sb2[1] = *(const __nv_bfloat162*)&w2.y;
+          } else {
+            const __nv_bfloat16* bs = (const __nv_bfloat16*)P.b_scale;
+            sb2[0] = __halves2bfloat162(bs[(int64_t)col * P.sb_n], bs[(int64_t)(col + 1) * P.sb_n]);
+            sb2[1] = __halves2bfloat162(bs[(int64_t)(col + 2) * P.sb_n], bs[(int64_t)(col + 3) * P.sb_n]);
+          }
+          uint32_t o[2];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float sb = P.b_scale ? load1(P.b_scale, P.b_scale_dtype, (col + j) * P.sb_n) : 1.f;
-          res[j] = dequant_one(P, raw[j], sa, sb);
-        }
-        const int64_t oi = row * P.o_m + col;
-        if (es == 2) {
-          const __nv_bfloat162 p0 = __floats2bfloat162_rn(res[0], res[1]);
-          const __nv_bfloat162 p1 = __floats2bfloat162_rn(res[2], res[3]);
-          const uint2 o = make_uint2(*(const uint32_t*)&p0, *(const uint32_t*)&p1);
+          for (int h = 0; h < 2; ++h) {
+            const float f0 = P.is_int ? __int2float_rn((int)raw[2 * h]) : __uint_as_float(raw[2 * h]);
+            const float f1 = P.is_int ? __int2float_rn((int)raw[2 * h + 1]) : __uint_as_float(raw[2 * h + 1]);
+            __nv_bfloat162 v = __floats2bfloat162_rn(f0, f1);
+            if (P.b_scale_first) {
+              if (has_b) v = __hmul2(v, sb2[h]);
+              if (has_a) v = __hmul2(v, sa2);
+            } else {
+              if (has_a) v = __hmul2(v, sa2);
+              if (has_b) v = __hmul2(v, sb2[h]);
+            }
+            o[h] = *(const uint32_t*)&v;
+          }
 #pragma unroll
-          for (int r = 0; r < WORLD; ++r) *(uint2*)((__nv_bfloat16*)X.out[r] + oi) = o;
+          for (int r = 0; r < WORLD; ++r)
+            *(uint2*)((__nv_bfloat16*)X.out[r] + oi) = make_uint2(o[0], o[1]);
         } else {
-          const float4 o = make_float4(res[0], res[1], res[2], res[3]);
+          float res[4];
 #pragma unroll
-          for (int r = 0; r < WORLD; ++r) *(float4*)((float*)X.out[r] + oi) = o;
+          for (int j = 0; j < 4; ++j) {
+            const float sb = sb_const ? sb0
+                                      : load1(P.b_scale, P.b_scale_dtype, (int64_t)(col + j) * P.sb_n);
+            res[j] = dequant_one(P, raw[j], sa, sb);
+          }
+          if (es == 2) {
+            const __nv_bfloat162 p0 = __floats2bfloat162_rn(res[0], res[1]);
+            const __nv_bfloat162 p1 = __floats2bfloat162_rn(res[2], res[3]);
+            const uint2 o = make_uint2(*(const uint32_t*)&p0, *(const uint32_t*)&p1);
+#pragma unroll
+            for (int r = 0; r < WORLD; ++r) *(uint2*)((__nv_bfloat16*)X.out[r] + oi) = o;
+          } else {
+            const float4 o = make_float4(res[0], res[1], res[2], res[3]);
+#pragma unroll
+            for (int r = 0; r < WORLD; ++r) *(float4*)((float*)X.out[r] + oi) = o;
+          }
         }
       }
       __syncwarp();
@@ -2366,6 +2412,8 @@ int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x,
   AQT_REQUIRE(d->b0 * d->b1 == 1 && d->n % 4 == 0 && P.o_n == 1, AQTB200_EUNSUPPORTED,
               "the fused exchange needs an unbatched dot, n % 4 == 0 and unit output column stride");
   AQT_REQUIRE(d->amax_out == nullptr, AQTB200_EUNSUPPORTED, "no amax_out in the fused exchange");
+  AQT_REQUIRE(d->m * d->n < ((int64_t)1 << 32), AQTB200_EUNSUPPORTED,
+              "a band of the fused exchange holds fewer than 2^32 elements");
   const int es = d->out_dtype == AQTB200_BF16 ? 2 : 4;
   AQT_REQUIRE((P.o_m * es) % (4 * es) == 0, AQTB200_EUNSUPPORTED, "output rows must keep 4-element alignment");
   ExchangeArgs X{};
@@ -2383,19 +2431,23 @@ int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x,
   int dev = 0;
   AQT_CUDA_OK(cudaGetDevice(&dev));
   dev &= 63;
-#define AQT_LAUNCH_EXCHANGE(W)                                                                  \
+#define AQT_LAUNCH_EXCHANGE(W, F)                                                               \
   do {                                                                                          \
     static bool attr_done[64] = {false};                                                        \
     if (!attr_done[dev]) {                                                                      \
-      AQT_CUDA_OK(cudaFuncSetAttribute(exchange_tma_kernel<W>,                                  \
+      AQT_CUDA_OK(cudaFuncSetAttribute(exchange_tma_kernel<W, F>,                               \
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EX_SMEM)); \
       attr_done[dev] = true;                                                                    \
     }                                                                                           \
-    exchange_tma_kernel<W><<<grid, EX_THREADS, EX_SMEM, st>>>(P, X, status);                    \
+    exchange_tma_kernel<W, F><<<grid, EX_THREADS, EX_SMEM, st>>>(P, X, status);                 \
   } while (0)
-  if (x->world == 2) AQT_LAUNCH_EXCHANGE(2);
-  else if (x->world == 4) AQT_LAUNCH_EXCHANGE(4);
-  else AQT_LAUNCH_EXCHANGE(8);
+  const bool sa_bf = d->a_scale == nullptr || d->a_scale_dtype == AQTB200_BF16;
+  const bool sb_bf = d->b_scale == nullptr || d->b_scale_dtype == AQTB200_BF16;
+  const bool fast = d->dequant_dtype == AQTB200_BF16 && d->out_dtype == AQTB200_BF16 && sa_bf && sb_bf &&
+                    (d->b_scale == nullptr || P.sb_n != 1 || ((uintptr_t)d->b_scale & 7) == 0);
+  if (x->world == 2) { if (fast) AQT_LAUNCH_EXCHANGE(2, true); else AQT_LAUNCH_EXCHANGE(2, false); }
+  else if (x->world == 4) { if (fast) AQT_LAUNCH_EXCHANGE(4, true); else AQT_LAUNCH_EXCHANGE(4, false); }
+  else { if (fast) AQT_LAUNCH_EXCHANGE(8, true); else AQT_LAUNCH_EXCHANGE(8, false); }
 #undef AQT_LAUNCH_EXCHANGE
   AQT_CUDA_OK(cudaGetLastError()); count_launch();
   return 0;
