@@ -153,7 +153,7 @@ class PeerBuffers:
 class ShardedDotGeneral:
   """cfg.vjp for row-sharded operands (see module docstring)."""
 
-  def __init__(self, cfg: adg.DotGeneral, group=None, overlap_sms: int = 32,
+  def __init__(self, cfg: adg.DotGeneral, group=None, overlap_sms: int = 16,
                drhs_slices: int = 2, slice_multiple: int = 256,
                exchange: str = 'auto'):
     self.cfg = cfg
@@ -164,7 +164,8 @@ class ShardedDotGeneral:
     self.exchange = exchange
     self._peer = {}
     self.exchange_used = None  # 'p2p' or 'nccl' once a sliced drhs has run
-    # SMs left to the collective's kernel while a GEMM runs beside it.
+    # SMs left to the exchange while a GEMM runs beside it (measured at two
+    # ranks, 8192^3: 12 -> 1.55 ms per step, 16 -> 1.46, 24 -> 1.50, 32 -> 1.50).
     self.overlap_sms = overlap_sms
     # drhs is computed in this many row slices so that the exchange of one
     # slice's accumulators runs under the next slice's GEMM.

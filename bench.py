@@ -69,7 +69,7 @@ def parse_args():
                  choices=['tcgen05', 'cta1', 'cta2', 'wide'],
                  help='tile shape of the tensor-core kernel (default: automatic)')
   p.add_argument('--drhs-slices', type=int, default=2)
-  p.add_argument('--overlap-sms', type=int, default=32)
+  p.add_argument('--overlap-sms', type=int, default=16)
   p.add_argument('--exchange', default='auto', choices=['auto', 'nccl'],
                  help='drhs exchange at several GPUs: auto = one kernel over '
                  'peer memory where it can be set up, nccl = reduce-scatter + '
