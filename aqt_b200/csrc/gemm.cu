@@ -1794,6 +1794,364 @@ struct ExchangeArgs {
   int world;
 };
 
+
+// ---------------------------------------------------------------------------
+// host side
+
+static int g_gemm_impl = 0;
+static int g_sm_budget = 0;
+static int gemm_sms() {
+  int n = sm_count();
+  return (g_sm_budget > 0 && g_sm_budget < n) ? g_sm_budget : n;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault,
+                                         &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)p;
+  }
+  return fn;
+}
+
+// 4-D map over a 1-byte tensor [b0][b1][rows][k] with k contiguous.
+static int make_operand_map(CUtensorMap* tm, const void* ptr, int64_t k, int64_t rows, int64_t b1,
+                            int64_t b0, int64_t ld, int64_t s_b1, int64_t s_b0, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  AQT_REQUIRE(enc != nullptr, AQTB200_EDRIVER, "cuTensorMapEncodeTiled entry point not found");
+  AQT_REQUIRE(((uintptr_t)ptr & 15) == 0, AQTB200_EINVAL, "operand not 16-byte aligned");
+  if (b1 <= 1 || s_b1 == 0) s_b1 = ld * rows;
+  if (b0 <= 1 || s_b0 == 0) s_b0 = s_b1 * std::max<int64_t>(b1, 1);
+  AQT_REQUIRE(ld % 16 == 0 && s_b1 % 16 == 0 && s_b0 % 16 == 0, AQTB200_EINVAL,
+              "operand strides must be multiples of 16 bytes (ld=%lld)", (long long)ld);
+  cuuint64_t dims[4] = {(cuuint64_t)k, (cuuint64_t)rows, (cuuint64_t)std::max<int64_t>(b1, 1),
+                        (cuuint64_t)std::max<int64_t>(b0, 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)ld, (cuuint64_t)s_b1, (cuuint64_t)s_b0};
+  cuuint32_t box[4] = {(cuuint32_t)BK, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(ptr), dims, strides,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  AQT_REQUIRE(r == CUDA_SUCCESS, AQTB200_EDRIVER, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+// 4-D map over a bf16 output [b0][b1][m][n] with n contiguous: boxes of 32 rows
+// by 64 columns in the 128-byte swizzle (or 32 columns in the 64-byte swizzle),
+// the layouts the epilogues stage their rows in.
+static bool make_output_map(CUtensorMap* tm, void* ptr, int64_t n, int64_t m, int64_t b1,
+                            int64_t b0, int64_t s_m, int64_t s_b1, int64_t s_b0, int box_cols) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return false;
+  if (b1 <= 1 || s_b1 == 0) s_b1 = s_m * m;
+  if (b0 <= 1 || s_b0 == 0) s_b0 = s_b1 * std::max<int64_t>(b1, 1);
+  if (((uintptr_t)ptr & 15) || s_m % 8 || s_b1 % 8 || s_b0 % 8 || s_m <= 0 || s_b1 <= 0 || s_b0 <= 0)
+    return false;
+  cuuint64_t dims[4] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)std::max<int64_t>(b1, 1),
+                        (cuuint64_t)std::max<int64_t>(b0, 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)s_m * 2, (cuuint64_t)s_b1 * 2, (cuuint64_t)s_b0 * 2};
+  cuuint32_t box[4] = {(cuuint32_t)box_cols, 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ptr, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+// 4-D map over the contiguous 32-bit accumulator tensor [b0][b1][m][n]: boxes
+// of 32 rows by 16 columns (64 bytes) in the 64-byte swizzle.
+static bool make_acc_map(CUtensorMap* tm, void* ptr, int64_t n, int64_t m, int64_t b1, int64_t b0) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr || ((uintptr_t)ptr & 15) || n % 4 != 0) return false;
+  b1 = std::max<int64_t>(b1, 1);
+  b0 = std::max<int64_t>(b0, 1);
+  cuuint64_t dims[4] = {(cuuint64_t)n, (cuuint64_t)m, (cuuint64_t)b1, (cuuint64_t)b0};
+  cuuint64_t strides[3] = {(cuuint64_t)n * 4, (cuuint64_t)n * m * 4, (cuuint64_t)n * m * b1 * 4};
+  cuuint32_t box[4] = {16, 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(tm, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, ptr, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static bool is_fp8(int dt) { return dt == AQTB200_E4M3 || dt == AQTB200_E5M2; }
+
+static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& P, bool* empty) {
+  AQT_REQUIRE(d != nullptr, AQTB200_EINVAL, "null gemm descriptor");
+  AQT_REQUIRE(d->b0 >= 0 && d->b1 >= 0 && d->m >= 0 && d->n >= 0 && d->k >= 0, AQTB200_EINVAL,
+              "negative extent");
+  const bool ints = d->a_dtype == AQTB200_S8 && d->b_dtype == AQTB200_S8;
+  const bool fps = is_fp8(d->a_dtype) && is_fp8(d->b_dtype);
+  AQT_REQUIRE(ints || fps, AQTB200_EUNSUPPORTED,
+              "operand dtypes %d x %d: need int8 x int8 or fp8 x fp8", d->a_dtype, d->b_dtype);
+  AQT_REQUIRE(d->dequant_dtype == AQTB200_F32 || d->dequant_dtype == AQTB200_BF16, AQTB200_EINVAL,
+              "dequant dtype must be f32 or bf16");
+  AQT_REQUIRE(d->out_dtype == AQTB200_F32 || d->out_dtype == AQTB200_BF16, AQTB200_EINVAL,
+              "out dtype must be f32 or bf16");
+  *empty = d->b0 * d->b1 * d->m * d->n == 0;
+  if (*empty) return 0;
+  AQT_REQUIRE(d->out != nullptr || d->acc_out != nullptr, AQTB200_EINVAL, "null output");
+  AQT_REQUIRE(d->k == 0 || (d->a != nullptr && d->b != nullptr), AQTB200_EINVAL, "null operand");
+  AQT_REQUIRE(d->k < (int64_t)1 << 31 && d->m < (int64_t)1 << 31 && d->n < (int64_t)1 << 31,
+              AQTB200_EUNSUPPORTED, "extent too large for a tensor map");
+
+  P = GemmParams{};
+  P.b0 = d->b0; P.b1 = d->b1; P.m = d->m; P.n = d->n; P.k = d->k;
+  P.a_scale = d->a_scale; P.sa_b0 = d->a_scale_b0_stride; P.sa_b1 = d->a_scale_b1_stride;
+  P.sa_m = d->a_scale_m_stride;
+  P.b_scale = d->b_scale; P.sb_b0 = d->b_scale_b0_stride; P.sb_b1 = d->b_scale_b1_stride;
+  P.sb_n = d->b_scale_n_stride;
+  P.a_scale_dtype = d->a_scale_dtype; P.b_scale_dtype = d->b_scale_dtype;
+  P.b_scale_first = d->b_scale_first; P.d_dtype = d->dequant_dtype; P.out_dtype = d->out_dtype;
+  P.is_int = ints ? 1 : 0;
+  P.out = d->out; P.o_b0 = d->out_b0_stride; P.o_b1 = d->out_b1_stride;
+  P.o_m = d->out_m_stride; P.o_n = d->out_n_stride;
+  P.acc_out = d->acc_out;
+  P.amax_out = (uint32_t*)d->amax_out;
+  P.stage_ok = d->out != nullptr && d->out_dtype == AQTB200_BF16 && d->out_n_stride == 1 &&
+               (((uintptr_t)d->out) & 15) == 0 && d->out_m_stride % 8 == 0 &&
+               d->out_b0_stride % 8 == 0 && d->out_b1_stride % 8 == 0;
+  P.m_tiles = (d->m + BM - 1) / BM;
+  P.n_tiles = (d->n + BN - 1) / BN;
+  P.total_tiles = d->b0 * d->b1 * P.m_tiles * P.n_tiles;
+  P.num_kb = std::max<int64_t>(1, (d->k + BK - 1) / BK);
+  P.status = status;
+  P.a = (const uint8_t*)d->a; P.b = (const uint8_t*)d->b;
+  P.a_b0 = d->a_b0_stride; P.a_b1 = d->a_b1_stride; P.lda = d->lda;
+  P.b_b0 = d->b_b0_stride; P.b_b1 = d->b_b1_stride; P.ldb = d->ldb;
+  P.a_dtype = d->a_dtype; P.b_dtype = d->b_dtype;
+  const uint32_t cfmt = ints ? 2u : 1u;
+  const uint32_t afmt = ints ? 1u : (d->a_dtype == AQTB200_E5M2 ? 1u : 0u);
+  const uint32_t bfmt = ints ? 1u : (d->b_dtype == AQTB200_E5M2 ? 1u : 0u);
+  // A problem at most one tile wide lets the single-CTA kernel issue MMAs only
+  // as wide as the columns that exist (a multiple of 16): the tensor pipe's
+  // time scales with N, which is what makes a skinny GEMM -- a few tokens
+  // against many weight rows, with the weights on the row side -- stream its
+  // big operand at memory speed instead of multiplying zero columns.
+  const int64_t n_mma = d->n < BN ? std::max<int64_t>(16, (d->n + 15) / 16 * 16) : BN;
+  P.idesc = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(n_mma >> 3) << 17) |
+            ((uint32_t)(BM >> 4) << 24);
+  P.n_mma = (int)n_mma;
+  P.stream_k = 0;
+  P.max_parts = 1;
+  P.b_stage = (int)(n_mma * BK);
+  P.stages1 = (int)std::min<int64_t>(MAX_STAGES1, (int64_t)(GEMM_SMEM - 1024) / (A_STAGE + P.b_stage));
+  P.idesc2 = (cfmt << 4) | (afmt << 7) | (bfmt << 10) | ((uint32_t)(BN >> 3) << 17) |
+             ((uint32_t)(256 >> 4) << 24);
+  P.m_tiles2 = (d->m + 255) / 256;
+  P.total_tiles2 = d->b0 * d->b1 * P.m_tiles2 * P.n_tiles;
+  P.n_tiles3 = (d->n + 511) / 512;
+  P.total_tiles3 = d->b0 * d->b1 * P.m_tiles2 * P.n_tiles3;
+
+  return 0;
+}
+
+// Skinny problems on the single-CTA kernel with fewer tiles than half the SMs:
+// whole tiles would leave most SMs idle while a few stream the long
+// contraction. Cutting the sequence of all k-slabs into equal shares, one per
+// CTA and up to four CTAs per tile, puts more SMs (and more bytes in flight)
+// on the problem; tiles that straddle a share boundary are computed in parts.
+// With at least half the SMs busy the stream from DRAM is already the bound
+// (measured: equal shares then gain nothing, and the partial tiles cost), so
+// whole tiles are kept. Returns the number of CTAs and the most parts a tile
+// can have, or parts 1 for whole tiles.
+constexpr int MAX_PARTS = 6;  // slots the fix-up can sum (see epilogue_split)
+struct StreamPlan {
+  int grid, parts;
+};
+static StreamPlan plan_stream(int64_t tiles, int64_t num_kb, int64_t n_mma, int sms) {
+  StreamPlan none = {0, 1};
+  if (n_mma > 64 || tiles <= 0 || num_kb < 16 || sms <= 0) return none;
+  if (tiles * 2 > sms) return none;
+  const int64_t grid = std::min<int64_t>(sms, tiles * 4);
+  const int64_t share = tiles * num_kb / grid;  // >= num_kb / 4
+  const int64_t parts = (num_kb + share - 1) / share + 1;
+  if (parts > MAX_PARTS) return none;
+  StreamPlan p = {(int)grid, (int)parts};
+  return p;
+}
+
+static size_t split_workspace_bytes(int64_t tiles, int parts, int64_t n_mma) {
+  const size_t counters = ((size_t)tiles * 4 * sizeof(int32_t) + 255) & ~(size_t)255;
+  return counters + (size_t)tiles * parts * BM * n_mma * sizeof(uint32_t);
+}
+
+static bool single_cta_path(const aqtb200_gemm_desc* d) {
+  // mirrors the kernel choice in gemm_dequant for the automatic setting
+  return g_gemm_impl == 0 && !(d->m > 128 && d->n >= 128) && d->k > 0;
+}
+
+size_t gemm_workspace_bytes(const aqtb200_gemm_desc* d) {
+  if (d == nullptr || !single_cta_path(d) || d->b0 * d->b1 * d->m * d->n == 0) return 0;
+  const int64_t tiles = d->b0 * d->b1 * ((d->m + BM - 1) / BM) * ((d->n + BN - 1) / BN);
+  const int64_t n_mma = d->n < BN ? std::max<int64_t>(16, (d->n + 15) / 16 * 16) : BN;
+  const int64_t num_kb = std::max<int64_t>(1, (d->k + BK - 1) / BK);
+  // the most any SM count up to the device's can need (fewer CTAs: fewer parts)
+  const StreamPlan plan = plan_stream(tiles, num_kb, n_mma, sm_count());
+  return plan.parts > 1 ? split_workspace_bytes(tiles, MAX_PARTS, n_mma) : 0;
+}
+
+int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
+  GemmParams P;
+  bool empty = false;
+  int rc0 = fill_params(d, status, P, &empty);
+  if (rc0 || empty) return rc0;
+  if (g_gemm_impl == 1 || d->k == 0) {
+    int64_t total = d->b0 * d->b1 * d->m * d->n;
+    int grid = (int)std::min<int64_t>((total + 255) / 256, (int64_t)sm_count() * 16);
+    gemm_simt_kernel<<<grid, 256, 0, st>>>(P);
+    AQT_CUDA_OK(cudaGetLastError()); count_launch();
+    return 0;
+  }
+
+  // CTA pairs pay off once a 256-row tile is mostly full; skinny problems keep
+  // the single-CTA 128-row tiles. Long contractions take the 256 x 512 pair
+  // tile. g_gemm_impl 2 / 3 / 4 force one kernel.
+  // Very short contractions with a large output are bound by the drain of the
+  // accumulators alone: the wide kernel's sixteen epilogue warps drain fastest
+  // (measured on the attention-score einsum, K = 128: 0.70 ms against 0.96 ms).
+  const int64_t wide_tiles = d->b0 * d->b1 * ((d->m + BM2 - 1) / BM2) * ((d->n + BNW - 1) / BNW);
+  const bool drain_bound = P.num_kb <= 2 && wide_tiles >= 2 * (int64_t)sm_count();
+  bool wide = g_gemm_impl == 4 ? true
+              : (g_gemm_impl == 0 && d->m > 128 && d->n > 256 &&
+                 (P.num_kb >= WIDE_MIN_KB || drain_bound));
+  const bool sa_bf = d->a_scale == nullptr || d->a_scale_dtype == AQTB200_BF16;
+  const bool sb_bf = d->b_scale == nullptr || d->b_scale_dtype == AQTB200_BF16;
+  const bool sa_f = d->a_scale == nullptr || d->a_scale_dtype == AQTB200_F32;
+  const bool sb_f = d->b_scale == nullptr || d->b_scale_dtype == AQTB200_F32;
+  int epi = 0;
+  if (d->dequant_dtype == AQTB200_BF16 && d->out_dtype == AQTB200_BF16 && sa_bf && sb_bf) epi = 1;
+  if (d->dequant_dtype == AQTB200_F32 && d->out_dtype == AQTB200_F32 && sa_f && sb_f) epi = 2;
+  // Outputs that qualify for the staged bf16 epilogue leave through the TMA
+  // unit when a tensor map can describe them; otherwise the same staged rows
+  // are stored by the warps. The 256 x 512 kernel has only that epilogue and
+  // one that writes the raw accumulators alone (no dequantized output); for
+  // anything else (no map, other dtypes, both outputs wanted) the 256 x 256
+  // kernel runs instead, whatever was asked for.
+  CUtensorMap tmO;
+  memset(&tmO, 0, sizeof(tmO));
+  P.tma_store = 0;
+  const bool can_map = epi == 1 && P.stage_ok;
+  bool wide_raw = false;
+  if (wide) {
+    if (d->out == nullptr && d->acc_out != nullptr) {
+      wide_raw = wide = make_acc_map(&tmO, d->acc_out, d->n, d->m, d->b1, d->b0);
+    } else {
+      wide = can_map && d->acc_out == nullptr &&
+             make_output_map(&tmO, d->out, d->n, d->m, d->b1, d->b0, d->out_m_stride,
+                             d->out_b1_stride, d->out_b0_stride, 32);
+    }
+    P.tma_store = wide ? 1 : 0;
+  }
+  if (!wide && can_map)
+    P.tma_store = make_output_map(&tmO, d->out, d->n, d->m, d->b1, d->b0, d->out_m_stride,
+                                  d->out_b1_stride, d->out_b0_stride, 64) ? 1 : 0;
+  // fewer than 128 columns: the single-CTA kernel with narrow MMAs (see fill_params)
+  const bool pair = wide || (g_gemm_impl == 3 ? true
+                                              : (g_gemm_impl == 2 ? false : d->m > 128 && d->n >= 128));
+  CUtensorMap tmA, tmB;
+  int rc = make_operand_map(&tmA, d->a, d->k, d->m, d->b1, d->b0, d->lda, d->a_b1_stride,
+                            d->a_b0_stride, BM);
+  if (rc) return rc;
+  rc = make_operand_map(&tmB, d->b, d->k, d->n, d->b1, d->b0, d->ldb, d->b_b1_stride,
+                        d->b_b0_stride, pair ? 128 : P.b_stage / BK);
+  if (rc) return rc;
+  int stream_grid = 0;
+  if (!pair && single_cta_path(d) && d->workspace != nullptr) {
+    const StreamPlan plan = plan_stream(P.total_tiles, P.num_kb, P.n_mma, gemm_sms());
+    if (plan.parts > 1 &&
+        d->workspace_bytes >= split_workspace_bytes(P.total_tiles, plan.parts, P.n_mma) &&
+        ((uintptr_t)d->workspace & 255) == 0) {
+      P.stream_k = 1;
+      P.max_parts = plan.parts;
+      stream_grid = plan.grid;
+      const size_t counters = ((size_t)P.total_tiles * 4 * sizeof(int32_t) + 255) & ~(size_t)255;
+      P.tile_counter = (int32_t*)d->workspace;
+      P.partials = (uint32_t*)((char*)d->workspace + counters);
+      AQT_CUDA_OK(cudaMemsetAsync(P.tile_counter, 0, counters, st));
+    }
+  }
+  const int64_t pair_tiles = wide ? P.total_tiles3 : P.total_tiles2;
+  const int grid = pair ? 2 * std::max((int)std::min<int64_t>(pair_tiles, gemm_sms() / 2), 1)
+                        : (stream_grid ? stream_grid
+                                       : (int)std::min<int64_t>(P.total_tiles, gemm_sms()));
+  const size_t smem = wide ? GEMM3_SMEM : (pair ? GEMM2_SMEM : GEMM_SMEM);
+  // the shared-memory opt-in is a per-device attribute of each kernel
+  int dev = 0;
+  AQT_CUDA_OK(cudaGetDevice(&dev));
+  dev = dev & 63;
+#define AQT_LAUNCH_GEMM(KERNEL, I, E)                                                         \
+  do {                                                                                        \
+    static bool attr_done[64] = {false};                                                      \
+    if (!attr_done[dev]) {                                                                    \
+      AQT_CUDA_OK(cudaFuncSetAttribute(KERNEL<I, E>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                       (int)smem));                                           \
+      attr_done[dev] = true;                                                                  \
+    }                                                                                         \
+    KERNEL<I, E><<<grid, GEMM_THREADS, smem, st>>>(tmA, tmB, tmO, P);                              \
+  } while (0)
+#define AQT_LAUNCH_GEMM_E(KERNEL, I)                    \
+  do {                                                  \
+    if (epi == 1) AQT_LAUNCH_GEMM(KERNEL, I, 1);        \
+    else if (epi == 2) AQT_LAUNCH_GEMM(KERNEL, I, 2);   \
+    else AQT_LAUNCH_GEMM(KERNEL, I, 0);                 \
+  } while (0)
+  if (wide) {
+#define AQT_LAUNCH_WIDE(I, R)                                                                  \
+  do {                                                                                         \
+    static bool attr_done[64] = {false};                                                       \
+    if (!attr_done[dev]) {                                                                     \
+      AQT_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_wide_kernel<I, R>,                         \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+      attr_done[dev] = true;                                                                   \
+    }                                                                                          \
+    gemm_tcgen05_wide_kernel<I, R><<<grid, WIDE_THREADS, smem, st>>>(tmA, tmB, tmO, P);        \
+  } while (0)
+    if (P.is_int) { if (wide_raw) AQT_LAUNCH_WIDE(true, true); else AQT_LAUNCH_WIDE(true, false); }
+    else { if (wide_raw) AQT_LAUNCH_WIDE(false, true); else AQT_LAUNCH_WIDE(false, false); }
+#undef AQT_LAUNCH_WIDE
+  } else if (pair) {
+    if (P.is_int) AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, true);
+    else AQT_LAUNCH_GEMM_E(gemm_tcgen05_pair_kernel, false);
+  } else {
+    if (P.is_int) AQT_LAUNCH_GEMM_E(gemm_tcgen05_kernel, true);
+    else AQT_LAUNCH_GEMM_E(gemm_tcgen05_kernel, false);
+  }
+#undef AQT_LAUNCH_GEMM_E
+#undef AQT_LAUNCH_GEMM
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
+int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st) {
+  GemmParams P;
+  bool empty = false;
+  int rc0 = fill_params(d, nullptr, P, &empty);
+  if (rc0 || empty) return rc0;
+  AQT_REQUIRE(acc != nullptr && d->out != nullptr, AQTB200_EINVAL, "null accumulator or output");
+  const int64_t total = d->b0 * d->b1 * d->m * d->n;
+  const bool vec = d->n % 4 == 0 && (((uintptr_t)acc) & 15) == 0;
+  int grid = (int)std::min<int64_t>((total / (vec ? 4 : 1) + 511) / 512, (int64_t)sm_count() * 8);
+  grid = std::max(grid, 1);
+  if (vec)
+    dequant_acc_kernel<true><<<grid, 256, 0, st>>>(P, (const uint32_t*)acc);
+  else
+    dequant_acc_kernel<false><<<grid, 256, 0, st>>>(P, (const uint32_t*)acc);
+  AQT_CUDA_OK(cudaGetLastError()); count_launch();
+  return 0;
+}
+
 // The accumulators are pulled through the TMA unit: one
 // thread per CTA requests 32 KB stages (one chunk of every rank's band, the
 // peers' chunks straight from their memory) with bulk copies into a six-deep
