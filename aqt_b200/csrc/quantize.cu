@@ -1905,9 +1905,9 @@ absmax_dual_kernel(DualParams P, int64_t row_tiles, int64_t col_tiles, int64_t t
             m2 = __vmaxu2(m2, vs & 0x7fff7fffu);
           }
           // this thread's 8 rows of column c -> fold over the 16 row groups
+          // (the half warp that shares ty) with one warp-reduce instruction
           uint32_t m = max(m2 & 0xffffu, m2 >> 16);
-#pragma unroll
-          for (int o = 8; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
+          m = __reduce_max_sync((threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu, m);
           if (tx == 0 && m != 0u && c < x.cols)
             atomicMax(P.amax_s + b * x.cols + c, m << 16);
         }

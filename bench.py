@@ -70,6 +70,9 @@ def parse_args():
                  help='tile shape of the tensor-core kernel (default: automatic)')
   p.add_argument('--drhs-slices', type=int, default=2)
   p.add_argument('--overlap-sms', type=int, default=16)
+  p.add_argument('--timeline', default='',
+                 help='after the measurements, write the device timeline of '
+                 'three more steps of rank 0 to this file (torch.profiler)')
   p.add_argument('--exchange', default='auto', choices=['auto', 'nccl'],
                  help='drhs exchange at several GPUs: auto = one kernel over '
                  'peer memory where it can be set up, nccl = reduce-scatter + '
@@ -324,6 +327,32 @@ def timed_region(torch, step, steps, device_index, barrier=None):
   sampler.mark_end()
   clocks = sampler.stop()
   return e0.elapsed_time(e1) / steps, clocks, host_ms
+
+
+def write_timeline(torch, step, path, steps=3):
+  """Diagnosis, outside every timed region: `steps` more calls of step() under
+  torch.profiler (CUPTI activity records, no replay of kernels) and the device
+  activities of this rank as text, one line per kernel / copy / collective:
+  start [us from the first], duration [us], stream, name."""
+  from torch.profiler import ProfilerActivity, profile
+  torch.cuda.synchronize()
+  with profile(activities=[ProfilerActivity.CUDA]) as prof:
+    for _ in range(steps):
+      step()
+    torch.cuda.synchronize()
+  import tempfile
+  with tempfile.NamedTemporaryFile(suffix='.json') as f:
+    prof.export_chrome_trace(f.name)
+    events = json.load(open(f.name)).get('traceEvents', [])
+  rows = [(e['ts'], e.get('dur', 0), e.get('args', {}).get('stream', ''),
+           e.get('name', '')) for e in events
+          if e.get('ph') == 'X' and e.get('cat') in (
+              'kernel', 'gpu_memcpy', 'gpu_memset')]
+  rows.sort()
+  t0 = rows[0][0] if rows else 0
+  with open(path, 'w') as f:
+    for ts, dur, stream, name in rows:
+      f.write('%10.1f %9.1f  s%-3s %s\n' % (ts - t0, dur, stream, name[:120]))
 
 
 def capture_graph(torch, step, barrier=None):
@@ -690,6 +719,11 @@ def run_ours(args, lines):
         'step_frac': sval / world / (2.0 * peaks['bf16_sustained']),
         'step_frac_of': '2 x bf16_tflops_sustained, ' + peaks['src']}
     engine.check_status()
+
+  if args.timeline:
+    path = args.timeline if rank == 0 else os.devnull
+    write_timeline(torch, step, path)
+    barrier()
 
   # ---- sharded against unsharded results, outside any timed region
   parity = None
