@@ -70,10 +70,7 @@ struct GemmParams {
   int stage_ok;  // output rows can be written as aligned 16-byte pieces
   int tma_store;  // a tensor map of the bf16 output exists: staged rows leave through the TMA unit
   int32_t* status;
-  // single-CTA kernel: the A operand is much larger than the L2 and is read
-  // once, so its rows are prefetched into the L2 a kilobyte at a time
-  int a_prefetch;
-  // SIMT reference kernel and the prefetch above:
+  // SIMT reference kernel only:
   const uint8_t* a; const uint8_t* b;
   int64_t a_b0, a_b1, lda, b_b0, b_b1, ldb;
   int a_dtype, b_dtype;
@@ -772,52 +769,25 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
-    // Lane 0 issues the tile loads. With a_prefetch the whole warp also asks
-    // the L2 for the A rows ahead of them: a tile load touches 128 bytes of
-    // each of 128 rows a row pitch apart, which DRAM serves as scattered
-    // 128-byte reads; one prefetch per row and kilobyte (eight k-slabs ahead)
-    // makes DRAM read whole kilobytes and leaves the tile loads to hit the L2.
-    int stage = 0;
-    uint32_t phase = 0;
-    Segment sg;
-    constexpr int PF_SLABS = 8;  // k-slabs per prefetch: 1 KB of a row
-    for (int64_t idx = 0; !fail && cta_segment(P, idx, sg); ++idx) {
-      int64_t i0, i1, mt, nt;
-      decode_tile(P, sg.tile, i0, i1, mt, nt);
-      for (int64_t kb = sg.kb0; kb < sg.kb1; ++kb) {
-        if (P.a_prefetch && (kb - sg.kb0) % PF_SLABS == 0) {
-          // slabs [kb + PF_SLABS, kb + 2 PF_SLABS), and at a segment's start also the first ones
-          for (int pass = (kb == sg.kb0 ? 0 : 1); pass < 2; ++pass) {
-            const int64_t k0 = (kb + pass * PF_SLABS) * BK;
-            const int64_t len = min((int64_t)PF_SLABS * BK, min(sg.kb1 * BK, P.lda) - k0) & ~(int64_t)15;
-            if (len <= 0) continue;
-            const uint8_t* base = P.a + i0 * P.a_b0 + i1 * P.a_b1 + k0;
-#pragma unroll
-            for (int r = 0; r < BM / 32; ++r) {
-              const int64_t row = mt * BM + r * 32 + lane;
-              if (row < P.m)
-                asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + row * P.lda),
-                             "r"((uint32_t)len)
-                             : "memory");
-            }
-          }
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      Segment sg;
+      for (int64_t idx = 0; !fail && cta_segment(P, idx, sg); ++idx) {
+        int64_t i0, i1, mt, nt;
+        decode_tile(P, sg.tile, i0, i1, mt, nt);
+        for (int64_t kb = sg.kb0; kb < sg.kb1; ++kb) {
+          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
+          mbar_expect_tx(&full_bar[stage], A_STAGE + P.b_stage);
+          tma_load_4d(smem_a + stage * A_STAGE, &tmA, &full_bar[stage], (int)(kb * BK),
+                      (int)(mt * BM), (int)i1, (int)i0);
+          tma_load_4d(smem_b + stage * P.b_stage, &tmB, &full_bar[stage], (int)(kb * BK),
+                      (int)(nt * BN), (int)i1, (int)i0);
+          if (++stage == P.stages1) { stage = 0; phase ^= 1; }
         }
-        if (lane == 0) {
-          if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; }
-          if (!fail) {
-            mbar_expect_tx(&full_bar[stage], A_STAGE + P.b_stage);
-            tma_load_4d(smem_a + stage * A_STAGE, &tmA, &full_bar[stage], (int)(kb * BK),
-                        (int)(mt * BM), (int)i1, (int)i0);
-            tma_load_4d(smem_b + stage * P.b_stage, &tmB, &full_bar[stage], (int)(kb * BK),
-                        (int)(nt * BN), (int)i1, (int)i0);
-          }
-        }
-        fail = __shfl_sync(0xffffffffu, fail, 0);
-        if (fail) break;
-        if (++stage == P.stages1) { stage = 0; phase ^= 1; }
       }
+      if (fail) { *abortp = 1; if (P.status) atomicCAS(P.status, 0, 1); }
     }
-    if (fail && lane == 0) { *abortp = 1; if (P.status) atomicCAS(P.status, 0, 1); }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
@@ -1958,10 +1928,6 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
   P.num_kb = std::max<int64_t>(1, (d->k + BK - 1) / BK);
   P.status = status;
   P.a = (const uint8_t*)d->a; P.b = (const uint8_t*)d->b;
-  // A read once from DRAM (more than half the L2's worth of it, rows 16-byte aligned)
-  P.a_prefetch = (d->b0 * d->b1 * d->m * d->k >= ((int64_t)64 << 20) && d->lda % 16 == 0 &&
-                  ((uintptr_t)d->a & 15) == 0 && d->a_b0_stride % 16 == 0 && d->a_b1_stride % 16 == 0)
-                     ? 1 : 0;
   P.a_b0 = d->a_b0_stride; P.a_b1 = d->a_b1_stride; P.lda = d->lda;
   P.b_b0 = d->b_b0_stride; P.b_b1 = d->b_b1_stride; P.ldb = d->ldb;
   P.a_dtype = d->a_dtype; P.b_dtype = d->b_dtype;
@@ -2014,6 +1980,18 @@ static StreamPlan plan_stream(int64_t tiles, int64_t num_kb, int64_t n_mma, int 
   if (parts > MAX_PARTS) return none;
   StreamPlan p = {(int)grid, (int)parts};
   return p;
+}
+
+// Whole tiles, round robin over a persistent grid: with w = ceil(tiles / SMs)
+// waves no CTA can finish before w tiles' time, so the grid is cut to
+// ceil(tiles / w) CTAs, the fewest that still need only w. Measured on the
+// serving shape (224 tiles streaming 235 MB of weights): 112 CTAs with two
+// tiles each are faster than 148 of which 76 take two -- fewer concurrent
+// streams get more out of DRAM while the critical path stays two tiles.
+static int balanced_grid(int64_t tiles, int sms) {
+  if (tiles <= sms) return (int)std::max<int64_t>(tiles, 1);
+  const int64_t waves = (tiles + sms - 1) / sms;
+  return (int)((tiles + waves - 1) / waves);
 }
 
 static size_t split_workspace_bytes(int64_t tiles, int parts, int64_t n_mma) {
@@ -2118,8 +2096,7 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
   }
   const int64_t pair_tiles = wide ? P.total_tiles3 : P.total_tiles2;
   const int grid = pair ? 2 * std::max((int)std::min<int64_t>(pair_tiles, gemm_sms() / 2), 1)
-                        : (stream_grid ? stream_grid
-                                       : (int)std::min<int64_t>(P.total_tiles, gemm_sms()));
+                        : (stream_grid ? stream_grid : balanced_grid(P.total_tiles, gemm_sms()));
   const size_t smem = wide ? GEMM3_SMEM : (pair ? GEMM2_SMEM : GEMM_SMEM);
   // the shared-memory opt-in is a per-device attribute of each kernel
   int dev = 0;
