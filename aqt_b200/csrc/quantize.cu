@@ -559,8 +559,14 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
   constexpr int ES = 16 / EPV;
   constexpr int U = 4;
   __shared__ float red[32];
+  // per kept row of the block: the eight row groups (ty) fold here first, so
+  // that one atomic per row and unit reaches global memory instead of eight
+  __shared__ uint32_t smax[32 * EPV];
   const DView& x = P.x;
   const int tx = threadIdx.x, ty = threadIdx.y;
+  const int tid = ty * 32 + tx;
+  for (int i = tid; i < 32 * EPV; i += 256) smax[i] = 0u;
+  __syncthreads();
   float tmax = 0.f;
   for (int64_t u = blockIdx.x; u < total_units; u += gridDim.x) {
     const int64_t cc = u % col_chunks;
@@ -639,11 +645,24 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
     if (P.per_tensor) {
 #pragma unroll
       for (int j = 0; j < EPV; ++j) tmax = amax_nn(tmax, m[j]);
-    } else if (r0 < x.rows) {
-      const int64_t sbase = (i0 * x.b1 + i1) * x.rows;
+    } else {
+      // the maxima are non-negative (or NaN, which as bits is larger than
+      // every number): unsigned order is their order
+      if (r0 < x.rows) {
 #pragma unroll
-      for (int j = 0; j < EPV; ++j)
-        if (m[j] != 0.f) atomic_max_nonneg(P.amax + sbase + r0 + j, m[j]);
+        for (int j = 0; j < EPV; ++j)
+          if (m[j] != 0.f) atomicMax(&smax[tx * EPV + j], __float_as_uint(m[j]));
+      }
+      __syncthreads();
+      const int64_t sbase = (i0 * x.b1 + i1) * x.rows + rb * 32 * EPV;
+      for (int i = tid; i < 32 * EPV; i += 256) {
+        const uint32_t v = smax[i];
+        if (v != 0u) {
+          if (rb * 32 * EPV + i < x.rows) atomic_max_nonneg(P.amax + sbase + i, __uint_as_float(v));
+          smax[i] = 0u;
+        }
+      }
+      __syncthreads();
     }
   }
   if (P.per_tensor) {
@@ -1164,7 +1183,7 @@ __device__ __forceinline__ uint32_t q8x2_to_bf16x2(uint32_t q2, bool is_int,
 // IS_INT: both outputs int8 (else both fp8); CHAIN as PairParams::chain. Compile-
 // time, because the kernel is bound by issue slots, not by memory.
 template <bool IS_INT, int CHAIN>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 quant_pair_kernel(PairParams P, int64_t row_tiles, int64_t col_tiles, int64_t total_units) {
   constexpr int EPV = 8, TR = 16 * EPV;
   __shared__ __align__(16) uint32_t tile[TR][32];
@@ -1570,20 +1589,58 @@ quant_shortrow_onepass(OnePassParams O, int64_t nbrow, int nvec, int dense) {
         if constexpr (PRE == 1) pconst[k] = load1(P.pre.ptr, P.pre.dtype, poff);
       }
     }
+    // The maxima of the U x rows_per_warp rows of this pass, then ONE scale
+    // computation per row (two divisions, the costly part of this kernel) on
+    // as many lanes as there are rows instead of one per row group and pass,
+    // then the scales back to the lanes of their rows.
+    float mk[U];
 #pragma unroll
     for (int k = 0; k < U; ++k) {
       uint4 run = make_uint4(0u, 0u, 0u, 0u);
       packed_absmax<EPV>(run, raw[k], x.dtype);
       float m = packed_hmax<EPV>(run, x.dtype);
       for (int o = nvec >> 1; o > 0; o >>= 1) m = amax_nn(m, __shfl_xor_sync(0xffffffffu, m, o));
-      const bool ok = g0 + k < groups && brow[k] < nbrow;
       if constexpr (PRE == 1) m = apply_pre_abs(m, pconst[k], P.t_dtype);
-      const float sc = scale_of_amax(m, P.t_dtype, P.s_dtype, O.quant_bound, O.clipping_scale, O.po2);
-      if (ok && vi == 0) {
-        if (P.s_dtype == AQTB200_BF16) ((__nv_bfloat16*)O.scale_out)[brow[k]] = __float2bfloat16_rn(sc);
-        else ((float*)O.scale_out)[brow[k]] = sc;
+      mk[k] = m;
+    }
+    float sck[U], sinvk[U];
+    if (U * rows_per_warp <= 32) {
+      // lane L < U * rows_per_warp takes row (k, sub) = (L / rows_per_warp, L % rows_per_warp)
+      float mine = 0.f;
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const float t = __shfl_sync(0xffffffffu, mk[k], (lane % rows_per_warp) * nvec);
+        if (lane / rows_per_warp == k) mine = t;
       }
-      const float sinv = recip_of_scale(sc, P.s_dtype);
+      const float sc1 = scale_of_amax(mine, P.t_dtype, P.s_dtype, O.quant_bound, O.clipping_scale, O.po2);
+      const float sinv1 = recip_of_scale(sc1, P.s_dtype);
+      const int64_t my_row = (g0 + lane / rows_per_warp) * rows_per_warp + lane % rows_per_warp;
+      if (lane < U * rows_per_warp && g0 + lane / rows_per_warp < groups && my_row < nbrow) {
+        if (P.s_dtype == AQTB200_BF16) ((__nv_bfloat16*)O.scale_out)[my_row] = __float2bfloat16_rn(sc1);
+        else ((float*)O.scale_out)[my_row] = sc1;
+      }
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        sck[k] = __shfl_sync(0xffffffffu, sc1, k * rows_per_warp + sub);
+        sinvk[k] = __shfl_sync(0xffffffffu, sinv1, k * rows_per_warp + sub);
+      }
+    } else {
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        sck[k] = scale_of_amax(mk[k], P.t_dtype, P.s_dtype, O.quant_bound, O.clipping_scale, O.po2);
+        sinvk[k] = recip_of_scale(sck[k], P.s_dtype);
+        if (g0 + k < groups && brow[k] < nbrow && vi == 0) {
+          if (P.s_dtype == AQTB200_BF16)
+            ((__nv_bfloat16*)O.scale_out)[brow[k]] = __float2bfloat16_rn(sck[k]);
+          else
+            ((float*)O.scale_out)[brow[k]] = sck[k];
+        }
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < U; ++k) {
+      const bool ok = g0 + k < groups && brow[k] < nbrow;
+      const float sinv = sinvk[k];
       const float sinv4[4] = {sinv, sinv, sinv, sinv};
       uint32_t outw[EPV / 4];
       if (EPV == 8 && (P.int_bf16 || P.fast_bf16)) {
@@ -1905,9 +1962,9 @@ absmax_dual_kernel(DualParams P, int64_t row_tiles, int64_t col_tiles, int64_t t
             m2 = __vmaxu2(m2, vs & 0x7fff7fffu);
           }
           // this thread's 8 rows of column c -> fold over the 16 row groups
-          // (the half warp that shares ty) with one warp-reduce instruction
           uint32_t m = max(m2 & 0xffffu, m2 >> 16);
-          m = __reduce_max_sync((threadIdx.x & 16) ? 0xffff0000u : 0x0000ffffu, m);
+#pragma unroll
+          for (int o = 8; o > 0; o >>= 1) m = max(m, __shfl_xor_sync(0xffffffffu, m, o));
           if (tx == 0 && m != 0u && c < x.cols)
             atomicMax(P.amax_s + b * x.cols + c, m << 16);
         }

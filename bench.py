@@ -931,7 +931,7 @@ def gemm_roofline(args, cfg, lhs, rhs, torch, engine, peaks):
   # DRAM bytes (read + write) of one launch of this kernel at this shape come
   # from an ncu capture of the same kernel (profiles/), not from this run:
   # nothing here is timed under a profiler.
-  traffic = 446.0e6 if (m, n, k) == (8192, 8192, 8192) else None
+  traffic = 456.5e6 if (m, n, k) == (8192, 8192, 8192) else None
   return {'bound': 'tensor',
           'kernel': 'gemm_tcgen05_wide_kernel (forward GEMM, 256x512 CTA-pair tiles)',
           'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s',
