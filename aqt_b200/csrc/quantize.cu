@@ -2207,6 +2207,32 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
                bool want_q, float* amax_only_out = nullptr) {
   int rc = validate(xv, prev, noisev, spec, want_q);
   if (rc) return rc;
+  // Kept index contiguous and the inner batch index contiguous right above it
+  // (e.g. the d of a [b, t, h, d] operand contracted over t, batched over b and
+  // h): the batch index is folded into the kept index. Scales, maxima and the
+  // quantized copy are laid out [b0][b1][rows] either way; the column kernels
+  // then read 512-byte-wide strips instead of rows of `rows` elements (128
+  // bytes for the attention operands, a quarter of every warp).
+  aqtb200_view x_merged, n_merged;
+  const bool no_pre = prev == nullptr || prev->ptr == nullptr;
+  const bool has_noise_view = noisev != nullptr && noisev->ptr != nullptr;
+  if (xv->b1 > 1 && xv->row_stride == 1 && xv->col_stride != 1 && xv->b1_stride == xv->rows &&
+      no_pre &&
+      (!has_noise_view || (noisev->row_stride == 1 && noisev->b1_stride == noisev->rows &&
+                           noisev->rows == xv->rows && noisev->b1 == xv->b1))) {
+    x_merged = *xv;
+    x_merged.rows = xv->rows * xv->b1;
+    x_merged.b1 = 1;
+    x_merged.b1_stride = 0;
+    xv = &x_merged;
+    if (has_noise_view) {
+      n_merged = *noisev;
+      n_merged.rows = noisev->rows * noisev->b1;
+      n_merged.b1 = 1;
+      n_merged.b1_stride = 0;
+      noisev = &n_merged;
+    }
+  }
   const int64_t ns = n_scales(xv, spec);
   const int64_t nbrow = xv->b0 * xv->b1 * xv->rows;
   const int64_t total = nbrow * xv->cols;

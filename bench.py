@@ -285,7 +285,7 @@ while True:
     except Exception:  # pylint: disable=broad-except
       self.proc.kill()
       rest = ''
-    clocks, bits = [], 0
+    clocks, bits, every = [], 0, []
     for line in rest.splitlines():
       parts = line.split()
       if len(parts) != 3:
@@ -294,11 +294,22 @@ while True:
         t, c, r = float(parts[0]), int(parts[1]), int(parts[2])
       except ValueError:
         continue
+      every.append((t, c, r))
       # only samples taken while the timed region was running count
       if self.t0 is not None and not self.t0 <= t <= self.t1:
         continue
       clocks.append(c)
       bits |= r
+    if not clocks and every and self.t0 is not None:
+      # A region of a few milliseconds can fall between two polls: take the
+      # polls on either side of it (the GPU is under the same load there: the
+      # warm-up before, the next region after).
+      before = [e for e in every if e[0] < self.t0][-1:]
+      after = [e for e in every if e[0] > self.t1][:1]
+      for t, c, r in before + after:
+        if min(abs(t - self.t0), abs(t - self.t1)) < 0.05:
+          clocks.append(c)
+          bits |= r
     clocks.sort()
     reasons = sorted(k for k, m in self.MASKS.items() if bits & m)
     return {'sm_mhz': clocks[len(clocks) // 2] if clocks else None,
