@@ -555,7 +555,8 @@ constexpr int kFastColChunk = 256;
 
 template <int EPV, int PRE>
 __global__ void __launch_bounds__(256)
-absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total_units) {
+absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total_units,
+                int row_lanes) {
   constexpr int ES = 16 / EPV;
   constexpr int U = 4;
   __shared__ float red[32];
@@ -563,8 +564,13 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
   // that one atomic per row and unit reaches global memory instead of eight
   __shared__ uint32_t smax[32 * EPV];
   const DView& x = P.x;
-  const int tx = threadIdx.x, ty = threadIdx.y;
-  const int tid = ty * 32 + tx;
+  // A warp's 32 lanes cover row_lanes vectors of kept rows times 32 / row_lanes
+  // consecutive contraction indices: with fewer than 32 vectors of rows (the
+  // 128-element d of an attention operand) the lanes left over take further
+  // contraction indices instead of idling.
+  const int tx = threadIdx.x % row_lanes, txc = threadIdx.x / row_lanes, ty = threadIdx.y;
+  const int col_lanes = 32 / row_lanes;
+  const int tid = ty * 32 + threadIdx.x;
   for (int i = tid; i < 32 * EPV; i += 256) smax[i] = 0u;
   __syncthreads();
   float tmax = 0.f;
@@ -574,7 +580,7 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
     const int64_t rb = t % row_blocks;
     const int64_t b = t / row_blocks;
     const int64_t i1 = b % x.b1, i0 = b / x.b1;
-    const int64_t r0 = (rb * 32 + tx) * EPV;
+    const int64_t r0 = (rb * row_lanes + tx) * EPV;
     const int64_t cbeg = cc * kFastColChunk;
     const int64_t cend = min(x.cols, cbeg + (int64_t)kFastColChunk);
     const char* xp = (const char*)x.ptr + (i0 * x.sb0 + i1 * x.sb1 + r0) * ES;
@@ -584,18 +590,19 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
 #pragma unroll
     for (int j = 0; j < (PRE == 2 ? EPV : 1); ++j) fm[j] = 0.f;
     if (r0 < x.rows) {
-      for (int64_t c = cbeg + ty; c < cend; c += 8 * U) {
+      const int64_t cstep = 8 * col_lanes;
+      for (int64_t c = cbeg + ty * col_lanes + txc; c < cend; c += cstep * U) {
         uint4 raw[U];
 #pragma unroll
         for (int k = 0; k < U; ++k) {
-          const int64_t ck = c + 8 * k;
+          const int64_t ck = c + cstep * k;
           raw[k] = ck < cend ? ldg16(xp, ck * x.sc * ES) : make_uint4(0u, 0u, 0u, 0u);
         }
 #pragma unroll
         for (int k = 0; k < U; ++k) {
           if constexpr (PRE == 2 && EPV == 8) {
             if (P.pre_bf16) {
-              const int64_t ck = c + 8 * k;
+              const int64_t ck = c + cstep * k;
               if (ck < cend) {
                 const float p = load1(P.pre.ptr, P.pre.dtype, pbase + ck * P.pre.sc);
                 const uint32_t p2 = pack_bf16x2(p, p);
@@ -614,7 +621,7 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
             }
           }
           if constexpr (PRE == 2) {
-            const int64_t ck = c + 8 * k;
+            const int64_t ck = c + cstep * k;
             if (ck < cend) {
               float v[EPV];
               unpack<EPV>(raw[k], x.dtype, v);
@@ -654,11 +661,11 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
           if (m[j] != 0.f) atomicMax(&smax[tx * EPV + j], __float_as_uint(m[j]));
       }
       __syncthreads();
-      const int64_t sbase = (i0 * x.b1 + i1) * x.rows + rb * 32 * EPV;
-      for (int i = tid; i < 32 * EPV; i += 256) {
+      const int64_t sbase = (i0 * x.b1 + i1) * x.rows + rb * row_lanes * EPV;
+      for (int i = tid; i < row_lanes * EPV; i += 256) {
         const uint32_t v = smax[i];
         if (v != 0u) {
-          if (rb * 32 * EPV + i < x.rows) atomic_max_nonneg(P.amax + sbase + i, __uint_as_float(v));
+          if (rb * row_lanes * EPV + i < x.rows) atomic_max_nonneg(P.amax + sbase + i, __uint_as_float(v));
           smax[i] = 0u;
         }
       }
@@ -666,13 +673,14 @@ absmax_col_fast(QParams P, int64_t row_blocks, int64_t col_chunks, int64_t total
     }
   }
   if (P.per_tensor) {
+    const int lane = threadIdx.x;
     float v = warp_max(tmax);
-    if (tx == 0) red[ty] = v;
+    if (lane == 0) red[ty] = v;
     __syncthreads();
     if (ty == 0) {
-      v = tx < 8 ? red[tx] : 0.f;
+      v = lane < 8 ? red[lane] : 0.f;
       v = warp_max(v);
-      if (tx == 0 && v != 0.f) atomic_max_nonneg(P.amax, v);
+      if (lane == 0 && v != 0.f) atomic_max_nonneg(P.amax, v);
     }
   }
 }
@@ -2391,12 +2399,16 @@ static int run(const aqtb200_view* xv, const aqtb200_view* prev,
         int grid = grid_for((units + 7) / 8, 8);
         absmax_row_kernel<false><<<grid, 256, 0, st>>>(P, chunks, units);
       } else if (fast_col) {
-        int64_t rbs = (xv->rows + 32 * epv - 1) / (32 * epv);
+        // lanes of a warp along the kept rows: all 32, or the power of two that
+        // covers the rows when there are fewer than 32 vectors of them
+        int row_lanes = 32;
+        while (row_lanes > 1 && (int64_t)(row_lanes / 2) * epv >= xv->rows) row_lanes /= 2;
+        int64_t rbs = (xv->rows + row_lanes * epv - 1) / (row_lanes * epv);
         int64_t ccs = (xv->cols + kFastColChunk - 1) / kFastColChunk;
         int64_t units = xv->b0 * xv->b1 * rbs * ccs;
         int grid = grid_for(units, 8);
         dim3 block(32, 8);
-        AQT_DISPATCH_EPV_PRE(absmax_col_fast, grid, block, P, rbs, ccs, units);
+        AQT_DISPATCH_EPV_PRE(absmax_col_fast, grid, block, P, rbs, ccs, units, row_lanes);
       } else {
         bool vec = col_vec_ok(P.x, xv->rows);
         int64_t rows_per_block = 32 * (vec ? 4 : 1);
