@@ -57,6 +57,10 @@ struct GemmParams {
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
   int64_t n_tiles3, total_tiles3;  // 512-column tiles of the wide CTA-pair kernel
   int stages1, b_stage;  // single-CTA kernel: ring depth and bytes of one B tile
+  // wide kernel, how the epilogue gets each scale: 0 = one value for the whole
+  // launch, read once; 1 = contiguous bf16 per row / column, staged in shared
+  // memory by the producer warp a tile ahead; 2 = read by the epilogue warps
+  int sa_mode, sb_mode;
   // single-CTA kernel, skinny problems: the k-slabs of all tiles form one
   // sequence that is cut into equal shares, one per CTA, so every SM streams
   // the same number of bytes whatever the tile count. A tile whose slabs fall
@@ -124,6 +128,16 @@ __device__ __forceinline__ void tma_load_4d(void* dst, const CUtensorMap* tm, ui
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes"
       " [%0], [%1, {%3, %4, %5, %6}], [%2];" ::"r"(smem_u32(dst)),
       "l"(tm), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+
+// Untiled bulk copy global -> shared memory (16-byte aligned, a multiple of 16
+// bytes), completing on an mbarrier; no multicast.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
       : "memory");
 }
 
@@ -1160,7 +1174,14 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmA,
 // the drain itself is exposed. Chosen for long contractions (see gemm_dequant).
 constexpr int STAGES3 = 4;
 constexpr int W_STAGE = A_STAGE + 2 * B_HALF;  // 48 KB per CTA per stage
-constexpr size_t GEMM3_SMEM = (size_t)STAGES3 * W_STAGE + 1024;
+constexpr int WIDE_EPI_WARPS = 16;  // four per TMEM lane quarter: the drain is exposed, so it is spread wide
+constexpr int kWidePitch = 64;      // bytes per staged row: 32 bf16 columns, 64-byte swizzle
+// dynamic shared memory of the wide kernel: the operand ring, the epilogue
+// warps' staging rows (2 KB each), the staged scales of one tile (128 row
+// scales + 512 column scales, bf16), and the slack of the 1024-byte alignment
+constexpr int W_EPI_BYTES = WIDE_EPI_WARPS * 32 * kWidePitch;
+constexpr int W_SCALE_BYTES = (128 + 512) * 2;
+constexpr size_t GEMM3_SMEM = (size_t)STAGES3 * W_STAGE + W_EPI_BYTES + W_SCALE_BYTES + 1024;
 constexpr int BNW = 512;
 // Shortest contraction (in 128-byte k-slabs) for which the exposed drain of the
 // wide tile costs less than the slower mainloop of the double-buffered one.
@@ -1181,9 +1202,7 @@ __device__ __forceinline__ void decode_tile3(const GemmParams& P, int64_t t, int
   nt = in / gm;
 }
 
-constexpr int WIDE_EPI_WARPS = 16;  // four per TMEM lane quarter: the drain is exposed, so it is spread wide
 constexpr int WIDE_THREADS = 32 * (2 + WIDE_EPI_WARPS);
-constexpr int kWidePitch = 64;  // bytes per staged row: 32 bf16 columns, 64-byte swizzle
 
 // Only the all-bf16 epilogue with a TMA-describable output runs here (the host
 // falls back to the 256 x 256 kernel otherwise), which keeps the register need
@@ -1204,9 +1223,13 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
   __shared__ __align__(8) uint64_t empty_bar[STAGES3];  // one per CTA
   __shared__ __align__(8) uint64_t tfull_bar[2];        // per accumulator; one per CTA
   __shared__ __align__(8) uint64_t tempty_bar[2];       // per accumulator; even CTA only
+  __shared__ __align__(8) uint64_t sfull_bar;            // staged scales of a tile; one per CTA
+  __shared__ __align__(8) uint64_t sempty_bar;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ __align__(1024) uint8_t epi_stage[WIDE_EPI_WARPS][32 * kWidePitch];
+  uint8_t* const epi_base = smem + STAGES3 * W_STAGE;   // [WIDE_EPI_WARPS][32 rows][64 bytes]
+  uint16_t* const sc_rows = (uint16_t*)(epi_base + W_EPI_BYTES);  // bf16 scales of this CTA's 128 tile rows
+  uint16_t* const sc_cols = sc_rows + 128;                         // bf16 scales of the tile's 512 columns
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -1223,6 +1246,8 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
     mbar_init(&tfull_bar[1], 1);
     mbar_init(&tempty_bar[0], 2 * WIDE_EPI_WARPS);
     mbar_init(&tempty_bar[1], 2 * WIDE_EPI_WARPS);
+    mbar_init(&sfull_bar, 1);
+    mbar_init(&sempty_bar, WIDE_EPI_WARPS);
     abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -1248,10 +1273,34 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
+      const bool stage_scales = !RAW && (P.sa_mode == 1 || P.sb_mode == 1);
+      uint32_t sphase = 0;
       for (int64_t t = cluster_id; t < P.total_tiles3 && !fail; t += num_clusters) {
         int64_t i0, i1, mt, nt;
         decode_tile3(P, t, i0, i1, mt, nt);
         const bool two = nt * BNW + 256 < P.n;  // the second accumulator has columns
+        if (stage_scales) {
+          // The epilogue's scales travel like the operands: bulk copies into
+          // shared memory, so the sixteen epilogue warps issue no global load
+          // (measured on the K = 128 score einsum: per-tile loads from those
+          // warps, even requested a tile ahead, cost 0.2 ms of 0.66 ms). One
+          // slot is enough: every warp moves its scales to registers at the top
+          // of a tile and hands the slot back, long before the next tile.
+          if (!mbar_wait(&sempty_bar, sphase ^ 1, abortp)) { fail = 1; break; }
+          const int64_t row0 = mt * BM2 + rank * 128, col0 = nt * BNW;
+          const uint32_t bytes_a =
+              P.sa_mode == 1 ? (uint32_t)(2 * max((int64_t)0, min((int64_t)128, P.m - row0))) : 0u;
+          const uint32_t bytes_b =
+              P.sb_mode == 1 ? (uint32_t)(2 * max((int64_t)0, min((int64_t)BNW, P.n - col0))) : 0u;
+          mbar_expect_tx(&sfull_bar, bytes_a + bytes_b);
+          if (bytes_a)
+            bulk_load(sc_rows, (const uint16_t*)P.a_scale + i0 * P.sa_b0 + i1 * P.sa_b1 + row0,
+                      bytes_a, &sfull_bar);
+          if (bytes_b)
+            bulk_load(sc_cols, (const uint16_t*)P.b_scale + i0 * P.sb_b0 + i1 * P.sb_b1 + col0,
+                      bytes_b, &sfull_bar);
+          sphase ^= 1;
+        }
         for (int64_t kb = 0; kb < P.num_kb; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
           const uint32_t lbar = map_to_cta(smem_u32(&full_bar[stage]), 0);
@@ -1389,11 +1438,26 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
     const int slice = (warp - 2) >> 2;
     const bool has_a = P.a_scale != nullptr, has_b = P.b_scale != nullptr;
     const bool vary_b = has_b && P.sb_n != 0;
-    uint8_t* stage_rows = epi_stage[warp - 2];
+    uint8_t* stage_rows = epi_base + (warp - 2) * (32 * kWidePitch);
     uint8_t* srow = stage_rows + lane * kWidePitch;
     const int swz = (lane >> 1) & 3;
     uint32_t aphase = 0;
     uint32_t amax = 0;
+    // Scales of a tile: one per row, one pair per two columns. A scale that is
+    // one value for the whole launch is read here, once; contiguous bf16
+    // scales are taken from the ring the producer warp fills (see there);
+    // anything else is read by this warp at the top of the tile.
+    float sa_const = 1.f;
+    uint32_t sb_const = 0x3f803f80u;  // (1.0, 1.0)
+    if constexpr (!RAW) {
+      if (has_a && P.sa_mode == 0) sa_const = load1(P.a_scale, P.a_scale_dtype, 0);
+      if (has_b && P.sb_mode == 0) {
+        const uint32_t v = __ldg((const unsigned short*)P.b_scale);
+        sb_const = v | (v << 16);
+      }
+    }
+    const bool staged = !RAW && (P.sa_mode == 1 || P.sb_mode == 1);
+    uint32_t sphase = 0;
     for (int64_t t = cluster_id; t < P.total_tiles3; t += num_clusters) {
       int64_t i0, i1, mt, nt;
       decode_tile3(P, t, i0, i1, mt, nt);
@@ -1401,28 +1465,41 @@ gemm_tcgen05_wide_kernel(const __grid_constant__ CUtensorMap tmA,
       const int64_t row = mt * BM2 + rank * 128 + quarter * 32 + lane;
       const int64_t row0 = row - lane;
       const int64_t col_s = nt * BNW + slice * 64;  // this warp's first column in accumulator 0
-      // scales do not depend on the accumulator: fetch them before waiting for it
-      float sa = 1.f;
-      uint32_t sbw[4];  // [accumulator * 2 + 32-column group]: lanes 0..15 hold column pairs
+      float sa = sa_const;
+      // [accumulator * 2 + 32-column group]: lanes 0..15 hold column pairs
+      uint32_t sbw[4] = {sb_const, sb_const, sb_const, sb_const};
       if constexpr (!RAW) {
-        if (has_a && row < P.m)
-          sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
+        if (staged) {
+          int oks = mbar_wait(&sfull_bar, sphase, abortp) ? 1 : 0;
+          oks = __all_sync(0xffffffffu, oks);
+          if (!oks) { fail = 3; break; }
+          if (P.sa_mode == 1)
+            sa = __bfloat162float(__ushort_as_bfloat16(sc_rows[quarter * 32 + lane]));
+          if (P.sb_mode == 1 && lane < 16) {
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint32_t w = 0x3f803f80u;  // (1.0, 1.0)
-          if (has_b) {
-            const unsigned short* sp = (const unsigned short*)P.b_scale + i0 * P.sb_b0 + i1 * P.sb_b1;
+            for (int q = 0; q < 4; ++q)
+              sbw[q] = *(const uint32_t*)&sc_cols[slice * 64 + (q >> 1) * 256 + (q & 1) * 32 + 2 * lane];
+          }
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&sempty_bar);
+          sphase ^= 1;
+        }
+        if (has_a && P.sa_mode == 2 && row < P.m)
+          sa = load1(P.a_scale, P.a_scale_dtype, i0 * P.sa_b0 + i1 * P.sa_b1 + row * P.sa_m);
+        if (has_b && P.sb_mode == 2) {
+          const unsigned short* sp = (const unsigned short*)P.b_scale + i0 * P.sb_b0 + i1 * P.sb_b1;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
             if (P.sb_n == 0) {
               const uint32_t v = __ldg(sp);
-              w = v | (v << 16);
+              sbw[q] = v | (v << 16);
             } else if (lane < 16) {
               const int64_t cc = col_s + (q >> 1) * 256 + (q & 1) * 32 + 2 * lane;
               const uint32_t lo = cc < P.n ? __ldg(sp + cc * P.sb_n) : 0x3f80u;
               const uint32_t hi = cc + 1 < P.n ? __ldg(sp + (cc + 1) * P.sb_n) : 0x3f80u;
-              w = lo | (hi << 16);
+              sbw[q] = lo | (hi << 16);
             }
           }
-          sbw[q] = w;
         }
       }
       const __nv_bfloat162 sa2 = __float2bfloat162_rn(sa);
@@ -2066,6 +2143,19 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
     }
     P.tma_store = wide ? 1 : 0;
   }
+  {
+    // how the wide kernel's epilogue gets its scales (see GemmParams)
+    auto mode = [&](const void* ptr, int dtype, int64_t s0, int64_t s1, int64_t sx, int64_t extent) {
+      if (ptr == nullptr) return 0;
+      if (s0 == 0 && s1 == 0 && sx == 0) return 0;
+      if (dtype == AQTB200_BF16 && sx == 1 && ((uintptr_t)ptr & 15) == 0 && s0 % 8 == 0 &&
+          s1 % 8 == 0 && extent % 8 == 0)
+        return 1;
+      return 2;
+    };
+    P.sa_mode = mode(d->a_scale, d->a_scale_dtype, P.sa_b0, P.sa_b1, P.sa_m, d->m);
+    P.sb_mode = mode(d->b_scale, d->b_scale_dtype, P.sb_b0, P.sb_b1, P.sb_n, d->n);
+  }
   if (!wide && can_map)
     P.tma_store = make_output_map(&tmO, d->out, d->n, d->m, d->b1, d->b0, d->out_m_stride,
                                   d->out_b1_stride, d->out_b0_stride, 64) ? 1 : 0;
@@ -2176,14 +2266,6 @@ constexpr int EX_STAGES = 6;
 constexpr int EX_CONSUMERS = 16;
 constexpr int EX_THREADS = 32 * (1 + EX_CONSUMERS);
 constexpr size_t EX_SMEM = (size_t)EX_STAGES * EX_STAGE_BYTES + 128;
-
-__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-          smem_u32(dst)),
-      "l"(src), "r"(bytes), "r"(smem_u32(bar))
-      : "memory");
-}
 
 // FAST: the all-bf16 chain (bf16 dequantization, output and scales) in packed
 // arithmetic, as in the GEMM's own bf16 epilogue; otherwise the general chain.
