@@ -23,7 +23,7 @@ static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int sm_count();
-int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st);
+int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st, bool a_ready);
 size_t gemm_workspace_bytes(const aqtb200_gemm_desc* d);
 int dequant_acc(const aqtb200_gemm_desc* d, const void* acc, cudaStream_t st);
 int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x, int32_t* status,
@@ -194,7 +194,11 @@ int aqtb200_dot_general_raw(const aqtb200_dg_raw_desc* d, void* workspace, size_
     g.workspace = (char*)workspace + lhs_ws + rhs_ws;
     g.workspace_bytes = gemm_ws;
   }
-  return gemm_dequant(&g, status, st);
+  // the GEMM may start under the kernel that quantizes its B operand when its A
+  // operand (the rows side after the swap) came in already quantized
+  const bool a_given = d->swap_ab ? d->rhs_is_quantized != 0 : d->lhs_is_quantized != 0;
+  const bool b_made_here = d->swap_ab ? d->lhs_is_quantized == 0 : d->rhs_is_quantized == 0;
+  return gemm_dequant(&g, status, st, a_given && b_made_here);
 }
 
 int aqtb200_dot_general_raw_dequant(const aqtb200_dg_raw_desc* d, void* stream) {

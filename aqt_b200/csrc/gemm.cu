@@ -57,6 +57,11 @@ struct GemmParams {
   int64_t m_tiles2, total_tiles2;  // 256-row tiles of the CTA-pair kernel
   int64_t n_tiles3, total_tiles3;  // 512-column tiles of the wide CTA-pair kernel
   int stages1, b_stage;  // single-CTA kernel: ring depth and bytes of one B tile
+  // single-CTA kernel launched as a programmatic dependent of the kernel before
+  // it on the stream (the one that quantizes the B operand): the A operand was
+  // complete earlier, so its first stages are requested before the wait for
+  // that kernel
+  int pdl;
   // wide kernel, how the epilogue gets each scale: 0 = one value for the whole
   // launch, read once; 1 = contiguous bf16 per row / column, staged in shared
   // memory by the producer warp a tile ahead; 2 = read by the epilogue warps
@@ -787,10 +792,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
       int stage = 0;
       uint32_t phase = 0;
       Segment sg;
+      bool primed = !P.pdl;
       for (int64_t idx = 0; !fail && cta_segment(P, idx, sg); ++idx) {
         int64_t i0, i1, mt, nt;
         decode_tile(P, sg.tile, i0, i1, mt, nt);
-        for (int64_t kb = sg.kb0; kb < sg.kb1; ++kb) {
+        int64_t kb_first = sg.kb0;
+        if (!primed) {
+          // First segment of a dependent launch: the ring is empty, so the A
+          // tiles of its first stages go out at once; the B tiles follow when
+          // the kernel that produces B has completed.
+          primed = true;
+          const int n = (int)min((int64_t)P.stages1, sg.kb1 - sg.kb0);
+          for (int j = 0; j < n; ++j) {
+            mbar_expect_tx(&full_bar[j], A_STAGE + P.b_stage);
+            tma_load_4d(smem_a + j * A_STAGE, &tmA, &full_bar[j], (int)((sg.kb0 + j) * BK),
+                        (int)(mt * BM), (int)i1, (int)i0);
+          }
+          asm volatile("griddepcontrol.wait;" ::: "memory");
+          for (int j = 0; j < n; ++j)
+            tma_load_4d(smem_b + j * P.b_stage, &tmB, &full_bar[j], (int)((sg.kb0 + j) * BK),
+                        (int)(nt * BN), (int)i1, (int)i0);
+          kb_first = sg.kb0 + n;
+          stage = n;
+          if (stage == P.stages1) { stage = 0; phase ^= 1; }
+        }
+        for (int64_t kb = kb_first; kb < sg.kb1; ++kb) {
           if (!mbar_wait(&empty_bar[stage], phase ^ 1, abortp)) { fail = 1; break; }
           mbar_expect_tx(&full_bar[stage], A_STAGE + P.b_stage);
           tma_load_4d(smem_a + stage * A_STAGE, &tmA, &full_bar[stage], (int)(kb * BK),
@@ -838,6 +864,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else {
     // ---------------- epilogue ----------------
+    // (a dependent launch reads scales the kernel before it wrote)
+    if (P.pdl) asm volatile("griddepcontrol.wait;" ::: "memory");
     const int quarter = warp & 3;          // TMEM lanes this warp may read
     const int half = (warp - 2) >> 2;      // which 128 columns of the tile it drains
     int buf = 0;
@@ -2021,6 +2049,7 @@ static int fill_params(const aqtb200_gemm_desc* d, int32_t* status, GemmParams& 
             ((uint32_t)(BM >> 4) << 24);
   P.n_mma = (int)n_mma;
   P.stream_k = 0;
+  P.pdl = 0;
   P.max_parts = 1;
   P.b_stage = (int)(n_mma * BK);
   P.stages1 = (int)std::min<int64_t>(MAX_STAGES1, (int64_t)(GEMM_SMEM - 1024) / (A_STAGE + P.b_stage));
@@ -2091,7 +2120,7 @@ size_t gemm_workspace_bytes(const aqtb200_gemm_desc* d) {
   return plan.parts > 1 ? split_workspace_bytes(tiles, MAX_PARTS, n_mma) : 0;
 }
 
-int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
+int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st, bool a_ready) {
   GemmParams P;
   bool empty = false;
   int rc0 = fill_params(d, status, P, &empty);
@@ -2184,6 +2213,9 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
       AQT_CUDA_OK(cudaMemsetAsync(P.tile_counter, 0, counters, st));
     }
   }
+  // dependent launch: single-CTA kernel, whole tiles (no memset node between the
+  // producing kernel and this one), A complete before that kernel
+  P.pdl = (!pair && a_ready && !P.stream_k && g_gemm_impl != 1) ? 1 : 0;
   const int64_t pair_tiles = wide ? P.total_tiles3 : P.total_tiles2;
   const int grid = pair ? 2 * std::max((int)std::min<int64_t>(pair_tiles, gemm_sms() / 2), 1)
                         : (stream_grid ? stream_grid : balanced_grid(P.total_tiles, gemm_sms()));
@@ -2200,7 +2232,21 @@ int gemm_dequant(const aqtb200_gemm_desc* d, int32_t* status, cudaStream_t st) {
                                        (int)smem));                                           \
       attr_done[dev] = true;                                                                  \
     }                                                                                         \
-    KERNEL<I, E><<<grid, GEMM_THREADS, smem, st>>>(tmA, tmB, tmO, P);                              \
+    if (P.pdl) {                                                                              \
+      cudaLaunchConfig_t cfg = {};                                                            \
+      cfg.gridDim = dim3(grid);                                                               \
+      cfg.blockDim = dim3(GEMM_THREADS);                                                      \
+      cfg.dynamicSmemBytes = smem;                                                            \
+      cfg.stream = st;                                                                        \
+      cudaLaunchAttribute attr[1];                                                            \
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;                        \
+      attr[0].val.programmaticStreamSerializationAllowed = 1;                                 \
+      cfg.attrs = attr;                                                                       \
+      cfg.numAttrs = 1;                                                                       \
+      AQT_CUDA_OK(cudaLaunchKernelEx(&cfg, KERNEL<I, E>, tmA, tmB, tmO, P));                  \
+    } else {                                                                                  \
+      KERNEL<I, E><<<grid, GEMM_THREADS, smem, st>>>(tmA, tmB, tmO, P);                       \
+    }                                                                                         \
   } while (0)
 #define AQT_LAUNCH_GEMM_E(KERNEL, I)                    \
   do {                                                  \
@@ -2473,7 +2519,7 @@ int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x,
 extern "C" {
 
 int aqtb200_gemm_dequant(const aqtb200_gemm_desc* desc, int32_t* status, void* stream) {
-  return aqtb200::gemm_dequant(desc, status, (cudaStream_t)stream);
+  return aqtb200::gemm_dequant(desc, status, (cudaStream_t)stream, false);
 }
 
 size_t aqtb200_gemm_workspace_bytes(const aqtb200_gemm_desc* desc) {

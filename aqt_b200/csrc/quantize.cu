@@ -1486,6 +1486,10 @@ struct OnePassParams {
 template <int EPV, int PRE>
 __global__ void __launch_bounds__(256)
 quant_row_onepass(OnePassParams O, int64_t nbrow) {
+  // A GEMM launched as a programmatic dependent of this kernel may start its
+  // prologue and the loads of its other operand now; it waits for this
+  // kernel's completion before it touches what is written here.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   constexpr int ES = 16 / EPV;
   constexpr int NV = 16 / EPV;   // input vectors per 16 outputs
   constexpr int UMAX = 4 / NV > 0 ? 4 / NV : 1;  // 16-output units per thread
