@@ -127,6 +127,18 @@ class PeerBuffers:
         ok = 0
     else:
       ok = 0
+    if ok:
+      try:
+        # this rank's views of its own allocation (zero-copy)
+        mem = torch.as_tensor(
+            _DeviceMemory(self._own.value, acc_bytes + out_bytes), device=device)
+        self._mem = mem
+        self.acc = mem[:k * n * 4].view(acc_dtype).view(k, n)
+        self.out = mem[acc_bytes:acc_bytes + out_bytes].view(out_dtype).view(k, n)
+        assert self.acc.data_ptr() == self._own.value
+      except Exception:  # pylint: disable=broad-except
+        ok = 0
+    # every rank takes the same path: all of them made it, or none uses it
     flag = torch.tensor([ok], device=device, dtype=torch.int32)
     dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
     self.ok = bool(int(flag.item()))
@@ -135,11 +147,6 @@ class PeerBuffers:
       return
     self.acc_base = bases
     self.out_base = [b + acc_bytes for b in bases]
-    mem = torch.as_tensor(_DeviceMemory(self._own.value, acc_bytes + out_bytes),
-                          device=device)
-    self._mem = mem
-    self.acc = mem[:k * n * 4].view(acc_dtype).view(k, n)
-    self.out = mem[acc_bytes:acc_bytes + out_bytes].view(out_dtype).view(k, n)
 
   def close(self):
     for ptr in self._opened:
