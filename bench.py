@@ -285,8 +285,14 @@ while True:
     except Exception:  # pylint: disable=broad-except
       self.proc.kill()
       rest = ''
+    return self.summarize(rest.splitlines(), self.t0, self.t1, self.mx)
+
+  @classmethod
+  def summarize(cls, lines, t0, t1, mx):
+    """Median / minimum SM clock and the clock event reasons of the polls
+    ("time clock reasons" per line) that fall between t0 and t1."""
     clocks, bits, every = [], 0, []
-    for line in rest.splitlines():
+    for line in lines:
       parts = line.split()
       if len(parts) != 3:
         continue
@@ -296,25 +302,25 @@ while True:
         continue
       every.append((t, c, r))
       # only samples taken while the timed region was running count
-      if self.t0 is not None and not self.t0 <= t <= self.t1:
+      if t0 is not None and not t0 <= t <= t1:
         continue
       clocks.append(c)
       bits |= r
-    if not clocks and every and self.t0 is not None:
+    if not clocks and every and t0 is not None:
       # A region of a few milliseconds can fall between two polls: take the
       # polls on either side of it (the GPU is under the same load there: the
       # warm-up before, the next region after).
-      before = [e for e in every if e[0] < self.t0][-1:]
-      after = [e for e in every if e[0] > self.t1][:1]
+      before = [e for e in every if e[0] < t0][-1:]
+      after = [e for e in every if e[0] > t1][:1]
       for t, c, r in before + after:
-        if min(abs(t - self.t0), abs(t - self.t1)) < 0.05:
+        if min(abs(t - t0), abs(t - t1)) < 0.05:
           clocks.append(c)
           bits |= r
     clocks.sort()
-    reasons = sorted(k for k, m in self.MASKS.items() if bits & m)
+    reasons = sorted(k for k, m in cls.MASKS.items() if bits & m)
     return {'sm_mhz': clocks[len(clocks) // 2] if clocks else None,
             'sm_min_mhz': clocks[0] if clocks else None,
-            'sm_max_mhz': self.mx, 'reasons': reasons,
+            'sm_max_mhz': mx, 'reasons': reasons,
             'samples': len(clocks)}
 
 

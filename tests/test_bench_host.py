@@ -41,3 +41,20 @@ def test_other_ranks_of_the_reference_arm_exit_quietly():
       capture_output=True, text=True, timeout=600, cwd=ROOT, env=env)
   assert out.returncode == 0, out.stderr[-2000:]
   assert out.stdout.strip() == ''
+
+
+def test_clock_poll_summary():
+  sys.path.insert(0, ROOT)
+  import bench
+  s = bench.ClockSampler.summarize
+  # polls inside the region only; reasons are OR-ed (0x4 = sw_power_cap, 0x8 = hw_slowdown)
+  r = s(['1.0 1900 0', '1.01 1800 4', '1.02 1700 4', '2.0 1000 8'], 1.005, 1.025,
+        1965)
+  assert r == {'sm_mhz': 1800, 'sm_min_mhz': 1700, 'sm_max_mhz': 1965,
+               'reasons': ['sw_power_cap'], 'samples': 2}
+  # a region that falls between two polls takes its neighbours (within 50 ms)
+  r = s(['1.0 1900 0', '1.04 1800 8'], 1.01, 1.03, 1965)
+  assert r['samples'] == 2 and r['reasons'] == ['hw_slowdown']
+  # ... but not polls from another time
+  r = s(['0.5 1900 0', '2.0 1800 8'], 1.01, 1.03, 1965)
+  assert r['samples'] == 0 and r['sm_mhz'] is None
