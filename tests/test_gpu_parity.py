@@ -336,6 +336,64 @@ def test_short_rows_quantized_in_one_pass(k, bits):
     _exact(g.qvalue, w.qvalue, 'q_' + side)
 
 
+@pytest.mark.parametrize('world,np_dtype', [(2, orc.bfloat16), (4, orc.bfloat16),
+                                            (8, orc.bfloat16), (4, np.float32)])
+@pytest.mark.parametrize('bits', [8, 'e4m3'])
+@pytest.mark.parametrize('per_tensor', [True, False])
+def test_fused_exchange_kernel_on_one_device(world, np_dtype, bits, per_tensor):
+  """aqtb200_dot_general_raw_exchange with every "rank's" accumulators and
+  result on this one GPU (the kernel does not care whose memory a pointer
+  names): the bands are added in rank order, dequantized once and written to
+  every result, bit for bit what the band dequantization gives on the sum."""
+  rng = np.random.default_rng(world)
+  dims = (((1,), (0,)), ((), ()))
+  m, k, n = 384, 256, 520
+  lhs = _cuda(util.rand_normal(rng, (m, k), 1.0, np_dtype))
+  rhs = _cuda(util.rand_normal(rng, (k, n), 0.1, np_dtype))
+  raw = aqt.dot_general_raw_make(bits, bits)
+  if per_tensor:
+    raw.dg_quantizer.lhs.calib_shared_axes = 'per_tensor'
+    raw.dg_quantizer.rhs.calib_shared_axes = 'per_tensor'
+  # f32 operands take the kernel's general arithmetic (f32 chain and results),
+  # bf16 operands the packed bf16 one
+  d, _ = engine.dg_raw(raw, lhs, rhs, None, None, dims, defer_dequant=True)
+  _sync()
+  acc0 = d.acc
+  rows = acc0.shape[1]
+  if acc0.dtype == torch.int32:
+    accs = [(acc0 * (r + 1) - 7 * r).contiguous() for r in range(world)]
+    total = accs[0].clone()
+    for a in accs[1:]:
+      total += a
+  else:
+    accs = [(acc0 * (0.5 + 0.37 * r)).contiguous() for r in range(world)]
+    total = accs[0].clone()
+    for a in accs[1:]:  # rank order, one f32 rounding per addition
+      total = total + a
+  want = d.finish_rows(0, rows, total.reshape(rows, -1)).clone()
+  outs = [torch.full_like(want, float('nan')) for _ in range(world)]
+  d.exchange_rows(0, rows, world - 1, [a.data_ptr() for a in accs],
+                  [o.data_ptr() for o in outs], max_sms=8)
+  _sync()
+  engine.check_status()
+  bits_of = torch.int16 if want.dtype == torch.bfloat16 else torch.int32
+  for r, o in enumerate(outs):
+    assert torch.equal(o.view(bits_of), want.view(bits_of)), 'copy %d differs' % r
+  # a band in the middle, the rest untouched
+  outs = [torch.zeros_like(want) for _ in range(world)]
+  start, count = 128, 64
+  acc_row, out_row = d.band_stride_bytes()
+  d.exchange_rows(start, count, 0,
+                  [a.data_ptr() + start * acc_row for a in accs],
+                  [o.data_ptr() + start * out_row for o in outs])
+  _sync()
+  full = want if want.shape[0] == rows else want.t()
+  for o in outs:
+    ob = o if o.shape[0] == rows else o.t()
+    assert torch.equal(ob[start:start + count], full[start:start + count])
+    assert not ob[:start].any() and not ob[start + count:].any()
+
+
 def test_wide_kernel_batched_and_transposed_output():
   """The 256 x 512 kernel under batch dims and the drhs output transpose."""
   rng = np.random.default_rng(11)
