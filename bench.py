@@ -56,7 +56,8 @@ def parse_args():
   p.add_argument('--sustained-seconds', type=float, default=2.0,
                  help='length of the second, long timed region (0 = skip)')
   p.add_argument('--workload', default='c2',
-                 choices=['c1', 'c2', 'c3', 'c4', 'int8', 'c2_delayed', 'stack'],
+                 choices=['c1', 'c2', 'c3', 'c4', 'int8', 'c2_delayed', 'stack',
+                          'exchange'],
                  help='c2 is the headline workload (with the others as '
                  '`extras` in its line); naming another one times that alone')
   p.add_argument('--m', type=int, default=16,
@@ -70,6 +71,8 @@ def parse_args():
                  help='tile shape of the tensor-core kernel (default: automatic)')
   p.add_argument('--drhs-slices', type=int, default=2)
   p.add_argument('--overlap-sms', type=int, default=16)
+  p.add_argument('--ranks', type=int, default=2, choices=[2, 4, 8],
+                 help='ranks emulated by --workload exchange')
   p.add_argument('--timeline', default='',
                  help='after the measurements, write the device timeline of '
                  'three more steps of rank 0 to this file (torch.profiler)')
@@ -577,6 +580,37 @@ def build_workload(name, args, torch, dev):
             f'config 4: serving GEMM M={m} K=8192 N=28672, int8 activations '
             'per token x int4-in-int8 frozen weights per channel, bf16 out',
             'hbm' if m <= 256 else 'tensor')
+  if name == 'exchange':
+    # The fused exchange kernel alone, on ONE device: every "rank's" band of
+    # accumulators and its copy of the result are buffers of this GPU (the
+    # kernel does not care whose memory a pointer names), so what is timed is
+    # the kernel's own rate -- bulk copies, sum, dequantization, stores --
+    # against HBM instead of NVLink. Band of the 2-slice 8192^3 step:
+    # 4096 / ranks rows x 8192 columns.
+    from aqt_b200 import engine
+    world = args.ranks
+    rows, n = 4096 // world, 8192
+    raw = make_cfg(args.kind).drhs
+    lhs = rn((rows, 128), 1.0, torch.bfloat16)
+    rhs = rn((128, n), 0.1, torch.bfloat16)
+    d, _ = engine.dg_raw(raw, lhs, rhs, None, None, DIMS, defer_dequant=True)
+    accs = [d.acc.clone() for _ in range(world)]
+    outs = [torch.empty((rows, n), device=dev, dtype=torch.bfloat16)
+            for _ in range(world)]
+    acc_ptrs = [a.data_ptr() for a in accs]
+    out_ptrs = [o.data_ptr() for o in outs]
+
+    def step(keep=(accs, outs, lhs, rhs)):
+      # (the default argument keeps the buffers alive: the kernel is given
+      # their addresses, not the tensors)
+      d.exchange_rows(0, rows, 0, acc_ptrs, out_ptrs, max_sms=args.overlap_sms)
+      return keep[1]
+
+    moved = world * rows * n * (4 + 2)
+    return (step, world * rows * n, moved,
+            f'fused exchange kernel on one device: {world} ranks, band of {rows} '
+            f'x {n} accumulators ({args.kind}), {args.overlap_sms} SMs '
+            '(0 = all), bytes = ranks x band x (4 read + 2 written)', 'hbm')
   raise ValueError(name)
 
 
