@@ -1897,6 +1897,9 @@ struct ExchangeArgs {
   const uint32_t* acc[AQTB200_MAX_RANKS];
   void* out[AQTB200_MAX_RANKS];
   int world;
+  // division of an element position (< 2^31) by the column count as a multiply
+  // and a shift: q = umulhi(e, div_mul) >> div_shr (div_mul == 0: n == 1)
+  uint32_t div_mul, div_shr;
 };
 
 
@@ -2391,7 +2394,8 @@ exchange_tma_kernel(GemmParams P, ExchangeArgs X, int32_t* status) {
                               : __float_as_uint(__fadd_rn(__uint_as_float(raw[j]), __uint_as_float(w[j])));
         }
         const uint32_t e = e0 + (uint32_t)u * 4u;  // first of four elements of one row
-        const uint32_t row = e / n32, col = e - row * n32;
+        const uint32_t row = X.div_mul ? (__umulhi(e, X.div_mul) >> X.div_shr) : e;
+        const uint32_t col = e - row * n32;
         const float sa = sa_const ? sa0 : load1(P.a_scale, P.a_scale_dtype, (int64_t)row * P.sa_m);
         const int64_t oi = (int64_t)row * P.o_m + col;
         if constexpr (FAST) {
@@ -2473,12 +2477,22 @@ int exchange_dequant(const aqtb200_gemm_desc* d, const aqtb200_exchange_desc* x,
   AQT_REQUIRE(d->b0 * d->b1 == 1 && d->n % 4 == 0 && P.o_n == 1, AQTB200_EUNSUPPORTED,
               "the fused exchange needs an unbatched dot, n % 4 == 0 and unit output column stride");
   AQT_REQUIRE(d->amax_out == nullptr, AQTB200_EUNSUPPORTED, "no amax_out in the fused exchange");
-  AQT_REQUIRE(d->m * d->n < ((int64_t)1 << 32), AQTB200_EUNSUPPORTED,
-              "a band of the fused exchange holds fewer than 2^32 elements");
+  AQT_REQUIRE(d->m * d->n < ((int64_t)1 << 31), AQTB200_EUNSUPPORTED,
+              "a band of the fused exchange holds fewer than 2^31 elements");
   const int es = d->out_dtype == AQTB200_BF16 ? 2 : 4;
   AQT_REQUIRE((P.o_m * es) % (4 * es) == 0, AQTB200_EUNSUPPORTED, "output rows must keep 4-element alignment");
   ExchangeArgs X{};
   X.world = x->world;
+  // exact for numerators below 2^31: mul = ceil(2^(31 + ceil(log2 n)) / n), shr = ceil(log2 n) - 1
+  X.div_mul = 0;
+  X.div_shr = 0;
+  if (d->n > 1) {
+    int lg = 0;
+    while (((int64_t)1 << lg) < d->n) ++lg;
+    const int p2 = 31 + lg;
+    X.div_mul = (uint32_t)((((uint64_t)1 << p2) + (uint64_t)d->n - 1) / (uint64_t)d->n);
+    X.div_shr = (uint32_t)(p2 - 32);
+  }
   for (int r = 0; r < x->world; ++r) {
     AQT_REQUIRE(x->acc[r] != nullptr && x->out[r] != nullptr, AQTB200_EINVAL, "null band pointer");
     AQT_REQUIRE(((uintptr_t)x->acc[r] & 15) == 0 && ((uintptr_t)x->out[r] & (4 * es - 1)) == 0,
